@@ -1,0 +1,383 @@
+// Warp-specialised tcgen05 GEMM pipeline for sm_100a.
+//
+//   D[M,N] = epilogue( A[M,K] · B[N,K]^T )      A, B: bf16 or fp16;  accumulate fp32 in TMEM
+//
+// This replaces the reference's scalar one-thread-per-output GEMM task
+// (maco/csrc/maco_worker.cuh:36-57) and the torch.mm call its live runtime makes
+// (maco/task_graph/runtime.py:188-209).
+//
+// One CTA = 6 warps:
+//   warp 0      TMA producer   cp.async.bulk.tensor tiles -> 128B-swizzled smem ring
+//   warp 1      MMA issuer     one lane issues tcgen05.mma (128 x BN x 16) into a TMEM accumulator
+//   warps 2..5  epilogue       tcgen05.ld the accumulator (one TMEM lane quarter per warp),
+//                              apply the fused epilogue, store to global (local or peer memory)
+// The accumulator is double buffered in TMEM (2 x BN columns) so the epilogue of tile i runs
+// under the main loop of tile i+1. All hand-offs are mbarriers; every wait is bounded and a
+// wait that runs out sets a CTA-wide abort word, after which all roles drain and the CTA frees
+// its TMEM and returns.
+//
+// Operands may be K-major (row-major [rows, K]) or MN-major (row-major [K, rows]); the latter is
+// what the backward GEMMs need (wgrad = dY^T · X contracts over the token dimension).
+#pragma once
+#include <cuda.h>
+#include "maco_atoms.cuh"
+#include "maco_types.h"
+
+namespace maco {
+
+constexpr int kBM = 128;       // tile rows  (UMMA M)
+constexpr int kBK = 64;        // k-block: 64 x 2 B = one 128-byte swizzle row
+constexpr int kUmmaK = 16;     // K per tcgen05.mma for 16-bit inputs
+constexpr int kGemmThreads = 192;
+
+template <int BN, int STAGES>
+struct GemmSmemLayout {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kRingBytes = STAGES * kStageBytes;
+  // after the ring: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem slot, abort word
+  static constexpr int kCtrlBytes = 256;
+  static constexpr int kTotalBytes = kRingBytes + kCtrlBytes + 1024;   // +1024: manual alignment slack
+  static_assert(2 * STAGES * 8 + 4 * 8 + 16 <= kCtrlBytes, "control block too small");
+};
+
+struct GemmCtrl {
+  uint64_t* full;        // [STAGES]  TMA -> MMA
+  uint64_t* empty;       // [STAGES]  MMA -> TMA
+  uint64_t* tmem_full;   // [2]       MMA -> epilogue
+  uint64_t* tmem_empty;  // [2]       epilogue -> MMA
+  uint32_t* tmem_slot;
+  volatile uint32_t* abort_word;
+};
+
+template <int BN, int STAGES>
+MACO_DEVICE GemmCtrl gemm_ctrl(uint8_t* smem_base) {
+  using L = GemmSmemLayout<BN, STAGES>;
+  GemmCtrl c;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_base + L::kRingBytes);
+  c.full = bars;
+  c.empty = bars + STAGES;
+  c.tmem_full = bars + 2 * STAGES;
+  c.tmem_empty = bars + 2 * STAGES + 2;
+  c.tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  c.abort_word = reinterpret_cast<volatile uint32_t*>(c.tmem_slot + 1);
+  return c;
+}
+
+// Raster order: groups of 8 tile-rows sweep all tile-columns, so CTAs that run together
+// share A row-blocks and B column-blocks in L2.
+MACO_DEVICE void gemm_tile_coords(int tile, int m_tiles, int n_tiles, int& m_blk, int& n_blk) {
+  const int G = 8;
+  int per_group = G * n_tiles;
+  int g = tile / per_group;
+  int first_m = g * G;
+  int gsize = min(G, m_tiles - first_m);
+  int r = tile - g * per_group;
+  m_blk = first_m + r % gsize;
+  n_blk = r / gsize;
+}
+
+// ---- producer ------------------------------------------------------------------------------
+// Loads one (128 x 64) A block and one (BN x 64) B block per k-step. K-major operands take one
+// box; MN-major operands take one 64-wide box per 64 rows (each box is a 64x64 swizzle panel).
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+MACO_DEVICE bool gemm_produce_tile(uint8_t* smem, const GemmCtrl& c, const CUtensorMap* tmA,
+                                   const CUtensorMap* tmB, int m0, int n0, int k0, int k_blocks,
+                                   uint32_t& it, uint64_t budget_ns) {
+  using L = GemmSmemLayout<BN, STAGES>;
+  for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+    if (!mbar_wait(&c.empty[s], ph ^ 1, budget_ns, c.abort_word)) return false;
+    uint8_t* sa = smem + s * L::kStageBytes;
+    uint8_t* sb = sa + L::kABytes;
+    mbar_arrive_expect_tx(&c.full[s], L::kStageBytes);
+    const int k = k0 + kb * kBK;
+    if constexpr (!A_MN) {
+      tma_load_2d(sa, tmA, &c.full[s], k, m0);
+    } else {
+#pragma unroll
+      for (int j = 0; j < kBM / 64; ++j) tma_load_2d(sa + j * 8192, tmA, &c.full[s], m0 + j * 64, k);
+    }
+    if constexpr (!B_MN) {
+      tma_load_2d(sb, tmB, &c.full[s], k, n0);
+    } else {
+#pragma unroll
+      for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, tmB, &c.full[s], n0 + j * 64, k);
+    }
+  }
+  return true;
+}
+
+// After an abort: give loads that are still in flight a bounded time to land before the CTA
+// leaves (their destination is this CTA's shared memory).
+template <int STAGES>
+MACO_DEVICE void gemm_drain_loads(const GemmCtrl& c, uint32_t issued) {
+  uint32_t first = issued > STAGES ? issued - STAGES : 0;
+  for (uint32_t i = first; i < issued; ++i) {
+    uint64_t t0 = globaltimer_ns();
+    while (!mbar_try_wait(&c.full[i % STAGES], (i / STAGES) & 1)) {
+      if (globaltimer_ns() - t0 > 2000000ull) break;
+    }
+  }
+}
+
+// ---- MMA issuer ----------------------------------------------------------------------------
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+MACO_DEVICE bool gemm_mma_tile(uint8_t* smem, const GemmCtrl& c, uint32_t tmem_base, uint32_t idesc,
+                               int k_blocks, uint32_t& it, uint32_t tile_seq, uint64_t budget_ns) {
+  using L = GemmSmemLayout<BN, STAGES>;
+  const uint32_t acc = tile_seq & 1, acc_ph = (tile_seq >> 1) & 1;
+  if (!mbar_wait(&c.tmem_empty[acc], acc_ph ^ 1, budget_ns, c.abort_word)) return false;
+  tc_fence_after();
+  const uint32_t d_tmem = tmem_base + acc * BN;
+  for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+    if (!mbar_wait(&c.full[s], ph, budget_ns, c.abort_word)) return false;
+    tc_fence_after();
+    const uint32_t a_base = smem_u32(smem + s * L::kStageBytes);
+    const uint32_t b_base = a_base + L::kABytes;
+#pragma unroll
+    for (int k = 0; k < kBK / kUmmaK; ++k) {
+      // K-major: 8-row groups are 1024 B apart (SBO); a K step of 16 elements is 32 B inside
+      // the swizzled row. MN-major: 64-row panels are 8192 B apart (LBO), 8-k groups 1024 B
+      // apart (SBO); a K step of 16 is two groups = 2048 B.
+      const uint64_t adesc = A_MN ? make_smem_desc(a_base + k * 2048, 8192, 1024, 2)
+                                  : make_smem_desc(a_base + k * 32, 16, 1024, 2);
+      const uint64_t bdesc = B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024, 2)
+                                  : make_smem_desc(b_base + k * 32, 16, 1024, 2);
+      tc_mma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+    }
+    tc_commit(&c.empty[s]);          // frees the smem stage once these MMAs have read it
+  }
+  tc_commit(&c.tmem_full[acc]);      // accumulator complete -> epilogue
+  return true;
+}
+
+// ---- epilogue ------------------------------------------------------------------------------
+MACO_DEVICE float epi_bias(const GemmEpilogue& e, int col) {
+  if (e.bias == nullptr) return 0.f;
+  if (e.bias_type == MACO_DT_F32) return reinterpret_cast<const float*>(e.bias)[col];
+  if (e.bias_type == MACO_DT_F16) return __half2float(reinterpret_cast<const __half*>(e.bias)[col]);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e.bias)[col]);
+}
+
+MACO_DEVICE uint32_t epi_pack(int out_type, float a, float b) {
+  if (out_type == MACO_DT_F16) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  return pack_bf16x2(a, b);
+}
+
+// Stores 32 consecutive columns of one row. `v` holds fp32 values already transformed.
+MACO_DEVICE void epi_store_row32(const GemmEpilogue& e, void* out_base, long long row, int col0,
+                                 int ncols_valid, const float (&v)[32]) {
+  if (e.out_type == MACO_DT_F32) {
+    float* p = reinterpret_cast<float*>(out_base) + row * e.ld_out + col0;
+    if (e.mode == MACO_EPI_F32_ACC) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        if (j + 4 <= ncols_valid) {
+          float4 o = *reinterpret_cast<float4*>(p + j);
+          o.x += v[j]; o.y += v[j + 1]; o.z += v[j + 2]; o.w += v[j + 3];
+          *reinterpret_cast<float4*>(p + j) = o;
+        } else {
+          for (int t = j; t < ncols_valid && t < j + 4; ++t) p[t] += v[t];
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        if (j + 4 <= ncols_valid) {
+          *reinterpret_cast<float4*>(p + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+          for (int t = j; t < ncols_valid && t < j + 4; ++t) p[t] = v[t];
+        }
+      }
+    }
+  } else {
+    uint16_t* p = reinterpret_cast<uint16_t*>(out_base) + row * e.ld_out + col0;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      if (j + 8 <= ncols_valid) {
+        uint4 o;
+        o.x = epi_pack(e.out_type, v[j], v[j + 1]);
+        o.y = epi_pack(e.out_type, v[j + 2], v[j + 3]);
+        o.z = epi_pack(e.out_type, v[j + 4], v[j + 5]);
+        o.w = epi_pack(e.out_type, v[j + 6], v[j + 7]);
+        *reinterpret_cast<uint4*>(p + j) = o;
+      } else {
+        for (int t = j; t < ncols_valid && t < j + 8; ++t) {
+          uint32_t w = epi_pack(e.out_type, v[t], 0.f);
+          p[t] = (uint16_t)(w & 0xffffu);
+        }
+      }
+    }
+  }
+}
+
+MACO_DEVICE float epi_load_aux(const GemmEpilogue& e, long long row, int col) {
+  const uint16_t* p = reinterpret_cast<const uint16_t*>(e.aux) + row * e.ld_aux + col;
+  if (e.aux_type == MACO_DT_F16) return __half2float(*reinterpret_cast<const __half*>(p));
+  return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(p));
+}
+
+// Consumes one finished accumulator. Called by all 32 lanes of each of the 4 epilogue warps.
+// `out_base` lets a caller redirect the tile (for example into a peer GPU's buffer);
+// `row_off` is added to the tile's row index when storing (for scatter into per-rank slabs).
+template <int BN>
+MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const GemmEpilogue& e,
+                                    void* out_base, long long row_off, int m0, int n0,
+                                    uint32_t tile_seq, uint64_t budget_ns) {
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t q = warp & 3;     // TMEM lane quarter this warp may read
+  const uint32_t acc = tile_seq & 1, acc_ph = (tile_seq >> 1) & 1;
+  uint32_t ok = 1;
+  if (lane == 0) ok = mbar_wait(&c.tmem_full[acc], acc_ph, budget_ns, c.abort_word) ? 1u : 0u;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (!ok) return false;
+  tc_fence_after();
+  const int row = m0 + q * 32 + lane;
+  const bool row_ok = row < e.M;
+  const uint32_t t_row = tmem_base + ((q * 32u) << 16) + acc * BN;
+  if (e.mode == MACO_EPI_SWIGLU) {
+    // Columns [0, BN/2) of the tile hold the gate projection, [BN/2, BN) the up projection of
+    // the same BN/2 output features (weights are interleaved that way when the graph is built).
+#pragma unroll 1
+    for (int ch = 0; ch < BN / 64; ++ch) {
+      uint32_t g[32], u[32];
+      tmem_ld_32x32(t_row + ch * 32, g);
+      tmem_ld_32x32(t_row + BN / 2 + ch * 32, u);
+      tmem_ld_wait();
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = silu(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+      const int col0 = n0 / 2 + ch * 32;
+      const int valid = min(32, e.N / 2 - col0);
+      if (row_ok && valid > 0) epi_store_row32(e, out_base, row + row_off, col0, valid, v);
+      __syncwarp();
+    }
+  } else {
+#pragma unroll 1
+    for (int ch = 0; ch < BN / 32; ++ch) {
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + ch * 32, r);
+      tmem_ld_wait();
+      const int col0 = n0 + ch * 32;
+      const int valid = min(32, e.N - col0);
+      if (row_ok && valid > 0) {
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * e.alpha;
+      if (e.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (j < valid) v[j] += epi_bias(e, col0 + j);
+      }
+      if (e.mode == MACO_EPI_GELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+      } else if (e.mode == MACO_EPI_GELU_BWD) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (j < valid) v[j] *= gelu_tanh_grad(epi_load_aux(e, row, col0 + j));
+      } else if (e.mode == MACO_EPI_SILU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = silu(v[j]);
+      } else if (e.mode == MACO_EPI_RESIDUAL) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (j < valid) v[j] += epi_load_aux(e, row, col0 + j);
+      }
+      epi_store_row32(e, out_base, row + row_off, col0, valid, v);
+      }
+      __syncwarp();
+    }
+  }
+  tc_fence_before();
+  mbar_arrive(&c.tmem_empty[acc]);
+  return true;
+}
+
+// ---- CTA set-up / tear-down shared by every kernel built on this pipeline ------------------------
+template <int BN, int STAGES>
+MACO_DEVICE uint8_t* gemm_cta_setup(uint8_t* dyn_smem, GemmCtrl& c, uint32_t& tmem_base) {
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
+  c = gemm_ctrl<BN, STAGES>(smem);
+  const uint32_t warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&c.tmem_full[a], 1); mbar_init(&c.tmem_empty[a], 128); }
+    *c.abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(c.tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  tmem_base = *c.tmem_slot;
+  return smem;
+}
+
+template <int BN>
+MACO_DEVICE void gemm_cta_teardown(const GemmCtrl& c, uint32_t tmem_base, uint32_t* status) {
+  tc_fence_before();
+  __syncthreads();
+  if ((threadIdx.x >> 5) == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+  if (threadIdx.x == 0 && *c.abort_word != 0 && status != nullptr) st_relaxed_sys_u32(status, MACO_STATUS_TIMEOUT);
+}
+
+// ---- stand-alone persistent GEMM kernel ---------------------------------------------------------
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    GemmEpilogue epi, int K, uint32_t idesc, uint64_t budget_ns, uint32_t* status) {
+  extern __shared__ uint8_t dyn_smem[];
+  GemmCtrl c;
+  uint32_t tmem_base;
+  uint8_t* smem = gemm_cta_setup<BN, STAGES>(dyn_smem, c, tmem_base);
+
+  const int m_tiles = (epi.M + kBM - 1) / kBM, n_tiles = (epi.N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + kBK - 1) / kBK;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        int mb, nb;
+        gemm_tile_coords(tile, m_tiles, n_tiles, mb, nb);
+        ok = gemm_produce_tile<BN, STAGES, A_MN, B_MN>(smem, c, &tmA, &tmB, mb * kBM, nb * BN, 0, k_blocks, it, budget_ns);
+      }
+      if (!ok) gemm_drain_loads<STAGES>(c, it);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t it = 0, seq = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++seq)
+        ok = gemm_mma_tile<BN, STAGES, A_MN, B_MN>(smem, c, tmem_base, idesc, k_blocks, it, seq, budget_ns);
+    }
+    __syncwarp();
+  } else {
+    uint32_t seq = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++seq) {
+      int mb, nb;
+      gemm_tile_coords(tile, m_tiles, n_tiles, mb, nb);
+      ok = gemm_epilogue_tile<BN>(c, tmem_base, epi, epi.out, 0, mb * kBM, nb * BN, seq, budget_ns);
+    }
+  }
+  gemm_cta_teardown<BN>(c, tmem_base, status);
+}
+
+}  // namespace maco
