@@ -1,0 +1,264 @@
+// Element-wise and row-wise operators written as *thread-group* device functions: the same body
+// runs as a task inside the persistent kernel (group = the 4 epilogue warps of a worker CTA) and
+// as a stand-alone kernel (group = one CTA).
+//
+// Covers the reference's device tasks maco/csrc/maco_worker.cuh:66-177 (vector scale,
+// LayerNorm, tanh-GELU, SiLU) and adds what the target layers need (RMSNorm, SwiGLU gate,
+// residual add, RoPE, softmax, GELU backward). The reference's LayerNorm reduces with one thread
+// over a 256-float shared buffer and strides rows by blockIdx (maco_worker.cuh:80-145); here one
+// warp owns a row, reduces with shuffles and moves 16 bytes per lane per access.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "maco_atoms.cuh"
+#include "maco_types.h"
+
+namespace maco {
+
+// ---- 8-wide typed access -------------------------------------------------------------------
+struct F8 { float v[8]; };
+
+MACO_DEVICE F8 load8(const void* base, long long idx, int dtype) {
+  F8 r;
+  if (dtype == MACO_DT_F32) {
+    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx);
+    float4 a = p[0], b = p[1];
+    r.v[0] = a.x; r.v[1] = a.y; r.v[2] = a.z; r.v[3] = a.w; r.v[4] = b.x; r.v[5] = b.y; r.v[6] = b.z; r.v[7] = b.w;
+  } else {
+    uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + idx);
+    uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (dtype == MACO_DT_BF16) {
+        float2 f = unpack_bf16x2(w[i]);
+        r.v[2 * i] = f.x; r.v[2 * i + 1] = f.y;
+      } else {
+        __half2 h = *reinterpret_cast<__half2*>(&w[i]);
+        float2 f = __half22float2(h);
+        r.v[2 * i] = f.x; r.v[2 * i + 1] = f.y;
+      }
+    }
+  }
+  return r;
+}
+
+MACO_DEVICE void store8(void* base, long long idx, int dtype, const F8& r) {
+  if (dtype == MACO_DT_F32) {
+    float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + idx);
+    p[0] = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+    p[1] = make_float4(r.v[4], r.v[5], r.v[6], r.v[7]);
+  } else {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (dtype == MACO_DT_BF16) {
+        w[i] = pack_bf16x2(r.v[2 * i], r.v[2 * i + 1]);
+      } else {
+        __half2 h = __floats2half2_rn(r.v[2 * i], r.v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(base) + idx) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+MACO_DEVICE float load1(const void* base, long long idx, int dtype) {
+  if (dtype == MACO_DT_F32) return reinterpret_cast<const float*>(base)[idx];
+  if (dtype == MACO_DT_F16) return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+}
+MACO_DEVICE void store1(void* base, long long idx, int dtype, float v) {
+  if (dtype == MACO_DT_F32) reinterpret_cast<float*>(base)[idx] = v;
+  else if (dtype == MACO_DT_F16) reinterpret_cast<__half*>(base)[idx] = __float2half_rn(v);
+  else reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
+}
+
+MACO_DEVICE int dtype_bytes(int dtype) { return dtype == MACO_DT_F32 ? 4 : 2; }
+
+MACO_DEVICE bool elt_vec_ok(const MacoEltArgs& a) {
+  const int eb = dtype_bytes(a.dtype);
+  auto al = [&](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return (a.cols % 8) == 0 && ((long long)a.ld_in * eb) % 16 == 0 && ((long long)a.ld_out * eb) % 16 == 0 &&
+         al(a.in0) && al(a.in1) && al(a.in2) && al(a.out);
+}
+
+// ---- pointwise family ----------------------------------------------------------------------
+MACO_DEVICE float elt_apply(uint32_t type, float x, float y, const MacoEltArgs& a) {
+  switch (type) {
+    case MACO_TASK_GELU: return gelu_tanh(x);
+    case MACO_TASK_SILU: return silu(x);
+    case MACO_TASK_SCALE: return x * a.f0;
+    case MACO_TASK_ADD: return x + y;
+    case MACO_TASK_SILU_GATE: return silu(x) * y;
+    case MACO_TASK_GELU_BWD: return x * gelu_tanh_grad(y);
+    case MACO_TASK_COPY: return x;
+    default: return x;
+  }
+}
+
+MACO_DEVICE bool elt_is_binary(uint32_t type) {
+  return type == MACO_TASK_ADD || type == MACO_TASK_SILU_GATE || type == MACO_TASK_GELU_BWD;
+}
+
+MACO_DEVICE void elt_pointwise(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
+  const bool bin = elt_is_binary(type);
+  if (elt_vec_ok(a)) {
+    const int vpr = a.cols / 8;                       // vectors per row
+    const long long total = (long long)a.rows * vpr;
+    for (long long i = tid; i < total; i += nthreads) {
+      const long long r = a.row0 + i / vpr;
+      const int c = (int)(i % vpr) * 8;
+      F8 x = load8(a.in0, r * a.ld_in + c, a.dtype);
+      F8 y;
+      if (bin) y = load8(a.in1, r * a.ld_in + c, a.dtype);
+      F8 o;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o.v[j] = elt_apply(type, x.v[j], bin ? y.v[j] : 0.f, a);
+      store8(a.out, r * a.ld_out + c, a.dtype, o);
+    }
+  } else {
+    const long long total = (long long)a.rows * a.cols;
+    for (long long i = tid; i < total; i += nthreads) {
+      const long long r = a.row0 + i / a.cols;
+      const int c = (int)(i % a.cols);
+      float x = load1(a.in0, r * a.ld_in + c, a.dtype);
+      float y = bin ? load1(a.in1, r * a.ld_in + c, a.dtype) : 0.f;
+      store1(a.out, r * a.ld_out + c, a.dtype, elt_apply(type, x, y, a));
+    }
+  }
+}
+
+// ---- row-wise family: one warp per row ----------------------------------------------------
+// RMSNORM: out = x * rsqrt(mean(x^2) + eps) * w          (in0 = x, in1 = w, f0 = eps)
+// LAYERNORM: out = (x - mean) * rsqrt(var + eps) * w + b  (in2 = b)
+// SOFTMAX: out = exp(x - max) / sum
+MACO_DEVICE void elt_rowwise(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
+  const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
+  const bool vec = elt_vec_ok(a);
+  for (int rr = warp; rr < a.rows; rr += nwarps) {
+    const long long r = a.row0 + rr;
+    const long long ib = r * a.ld_in, ob = r * a.ld_out;
+    float s1 = 0.f, s2 = 0.f, mx = -INFINITY;
+    if (vec) {
+      for (int c = lane * 8; c < a.cols; c += 256) {
+        F8 x = load8(a.in0, ib + c, a.dtype);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { s1 += x.v[j]; s2 += x.v[j] * x.v[j]; mx = fmaxf(mx, x.v[j]); }
+      }
+    } else {
+      for (int c = lane; c < a.cols; c += 32) {
+        float x = load1(a.in0, ib + c, a.dtype);
+        s1 += x; s2 += x * x; mx = fmaxf(mx, x);
+      }
+    }
+    float mean = 0.f, rstd = 0.f, denom = 0.f;
+    if (type == MACO_TASK_RMSNORM) {
+      s2 = warp_sum(s2);
+      rstd = rsqrtf(s2 / a.cols + a.f0);
+    } else if (type == MACO_TASK_LAYERNORM) {
+      s1 = warp_sum(s1); s2 = warp_sum(s2);
+      mean = s1 / a.cols;
+      rstd = rsqrtf(fmaxf(s2 / a.cols - mean * mean, 0.f) + a.f0);
+    } else {  // softmax
+      mx = warp_max(mx);
+      float e = 0.f;
+      if (vec) {
+        for (int c = lane * 8; c < a.cols; c += 256) {
+          F8 x = load8(a.in0, ib + c, a.dtype);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) e += __expf(x.v[j] - mx);
+        }
+      } else {
+        for (int c = lane; c < a.cols; c += 32) e += __expf(load1(a.in0, ib + c, a.dtype) - mx);
+      }
+      denom = 1.f / warp_sum(e);
+    }
+    if (vec) {
+      for (int c = lane * 8; c < a.cols; c += 256) {
+        F8 x = load8(a.in0, ib + c, a.dtype);
+        F8 o;
+        if (type == MACO_TASK_SOFTMAX) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o.v[j] = __expf(x.v[j] - mx) * denom;
+        } else {
+          F8 w = load8(a.in1, c, a.dtype);
+          if (type == MACO_TASK_RMSNORM) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o.v[j] = x.v[j] * rstd * w.v[j];
+          } else {
+            F8 b = load8(a.in2, c, a.dtype);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o.v[j] = (x.v[j] - mean) * rstd * w.v[j] + b.v[j];
+          }
+        }
+        store8(a.out, ob + c, a.dtype, o);
+      }
+    } else {
+      for (int c = lane; c < a.cols; c += 32) {
+        float x = load1(a.in0, ib + c, a.dtype), o;
+        if (type == MACO_TASK_SOFTMAX) o = __expf(x - mx) * denom;
+        else if (type == MACO_TASK_RMSNORM) o = x * rstd * load1(a.in1, c, a.dtype);
+        else o = (x - mean) * rstd * load1(a.in1, c, a.dtype) + load1(a.in2, c, a.dtype);
+        store1(a.out, ob + c, a.dtype, o);
+      }
+    }
+  }
+}
+
+// ---- RoPE (half-rotation form) -------------------------------------------------------------
+// Rows are (token, head) pairs: row = token * heads + head, cols = head_dim, i0 = heads.
+// in1 = cos [tokens, head_dim/2], in2 = sin (same dtype as x); i1 = token index of row 0's token
+// in the cos/sin tables minus row0 / heads (0 when the tables start at the first row's token).
+MACO_DEVICE void elt_rope(const MacoEltArgs& a, int tid, int nthreads) {
+  const int half = a.cols / 2;
+  const long long total = (long long)a.rows * half;
+  for (long long i = tid; i < total; i += nthreads) {
+    const long long r = a.row0 + i / half;
+    const int c = (int)(i % half);
+    const long long tok = r / a.i0 + a.i1;
+    const float cs = load1(a.in1, tok * half + c, a.dtype), sn = load1(a.in2, tok * half + c, a.dtype);
+    const float x1 = load1(a.in0, r * a.ld_in + c, a.dtype), x2 = load1(a.in0, r * a.ld_in + c + half, a.dtype);
+    store1(a.out, r * a.ld_out + c, a.dtype, x1 * cs - x2 * sn);
+    store1(a.out, r * a.ld_out + c + half, a.dtype, x2 * cs + x1 * sn);
+  }
+}
+
+// Per-head RMSNorm followed by RoPE, one warp per (token, head) row (Qwen3's QK-norm):
+// in0 = x rows [rows, head_dim], in1 = norm weight [head_dim], in2 = cos|sin packed as
+// [tokens, head_dim] (first half cos, second half sin), f0 = eps, f1 = 1 selects this fused form,
+// i0 = heads, i1 = token offset into the cos/sin table.
+MACO_DEVICE void elt_qknorm_rope(const MacoEltArgs& a, int tid, int nthreads) {
+  const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
+  const int half = a.cols / 2;
+  for (int rr = warp; rr < a.rows; rr += nwarps) {
+    const long long r = a.row0 + rr;
+    const long long tok = r / a.i0 + a.i1;
+    float s2 = 0.f;
+    for (int c = lane; c < a.cols; c += 32) { float x = load1(a.in0, r * a.ld_in + c, a.dtype); s2 += x * x; }
+    const float rstd = rsqrtf(warp_sum(s2) / a.cols + a.f0);
+    for (int c = lane; c < half; c += 32) {
+      const float x1 = load1(a.in0, r * a.ld_in + c, a.dtype) * rstd * load1(a.in1, c, a.dtype);
+      const float x2 = load1(a.in0, r * a.ld_in + c + half, a.dtype) * rstd * load1(a.in1, c + half, a.dtype);
+      const float cs = load1(a.in2, tok * a.cols + c, a.dtype), sn = load1(a.in2, tok * a.cols + half + c, a.dtype);
+      store1(a.out, r * a.ld_out + c, a.dtype, x1 * cs - x2 * sn);
+      store1(a.out, r * a.ld_out + c + half, a.dtype, x2 * cs + x1 * sn);
+    }
+  }
+}
+
+// Dispatch by task type. Returns false for a type this file does not implement.
+MACO_DEVICE bool elt_run(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
+  switch (type) {
+    case MACO_TASK_GELU: case MACO_TASK_SILU: case MACO_TASK_SCALE: case MACO_TASK_ADD:
+    case MACO_TASK_SILU_GATE: case MACO_TASK_GELU_BWD: case MACO_TASK_COPY:
+      elt_pointwise(type, a, tid, nthreads); return true;
+    case MACO_TASK_RMSNORM: case MACO_TASK_LAYERNORM: case MACO_TASK_SOFTMAX:
+      elt_rowwise(type, a, tid, nthreads); return true;
+    case MACO_TASK_ROPE:
+      if (a.f1 == 0.f) elt_rope(a, tid, nthreads); else elt_qknorm_rope(a, tid, nthreads);
+      return true;
+    default: return false;
+  }
+}
+
+}  // namespace maco
