@@ -152,13 +152,15 @@ class ProcessGroupManager:
     def heartbeat(self, step: int) -> None:
         """Publishes "rank r reached step" in the rendezvous store."""
         store = self._get_store()
+        self._last_step = int(step)
         if store is not None:
             store.set(f"{self._hb_prefix}/{self._rank}", f"{step}:{time.time():.3f}")
 
     def announce_exit(self) -> None:
+        """Publishes that this rank leaves after the last step it reported (call between steps)."""
         store = self._get_store()
         if store is not None:
-            store.set(f"{self._hb_prefix}/{self._rank}", "exit:0")
+            store.set(f"{self._hb_prefix}/{self._rank}", f"exit:{getattr(self, '_last_step', -1)}")
 
     def check_peers(self, step: int, timeout_s: float = 5.0, poll_s: float = 0.01) -> List[int]:
         """Returns the ranks that have NOT reached ``step`` within ``timeout_s`` (or announced exit)."""
@@ -176,8 +178,9 @@ class ProcessGroupManager:
                 try:
                     if store.check([key]):
                         val = store.get(key).decode()
-                        head = val.split(":")[0]
+                        head, tail = val.split(":")[0], val.split(":")[1]
                         if head == "exit":
+                            ok = int(tail) >= step      # it had reached this step before it left
                             break
                         if int(head) >= step:
                             ok = True

@@ -1,0 +1,108 @@
+"""CUDA operators against plain PyTorch fp32 references."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from tests.conftest import assert_close
+
+
+def _ops():
+    from maco_b200 import ops
+    return ops
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (200, 328, 136), (1024, 512, 2048), (64, 1280, 5120)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_tcgen05_all_majors(dtype, shape, bn):
+    ops = _ops()
+    M, N, K = shape
+    a = torch.randn(M, K, device="cuda", dtype=dtype)
+    b = torch.randn(N, K, device="cuda", dtype=dtype) * 0.1
+    ref = a.float() @ b.float().t()
+    scale = ref.abs().max().item()
+    for ta, tb in [(False, False), (False, True), (True, False), (True, True)]:
+        aa = a.t().contiguous() if ta else a
+        bb = b.t().contiguous() if tb else b
+        out = ops.gemm(aa, bb, trans_a=ta, trans_b=tb, bn=bn)
+        assert (out.float() - ref).abs().max().item() <= 1e-2 * scale, (ta, tb)
+    from maco_b200 import _native
+    assert _native.status() == 0
+
+
+def test_gemm_epilogues():
+    ops = _ops()
+    M, N, K = 512, 1024, 512
+    dt = torch.bfloat16
+    a = torch.randn(M, K, device="cuda", dtype=dt)
+    b = torch.randn(N, K, device="cuda", dtype=dt) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=dt)
+    aux = torch.randn(M, N, device="cuda", dtype=dt)
+    acc = a.float() @ b.float().t()
+    F = torch.nn.functional
+    assert_close(ops.gemm(a, b, bias=bias), acc + bias.float(), dt)
+    assert_close(ops.gemm(a, b, bias=bias, epilogue="gelu"), F.gelu(acc + bias.float(), approximate="tanh"), dt)
+    assert_close(ops.gemm(a, b, epilogue="silu"), F.silu(acc), dt)
+    assert_close(ops.gemm(a, b, aux=aux, epilogue="residual"), acc + aux.float(), dt)
+    o32 = ops.gemm(a, b, epilogue="f32", alpha=0.5)
+    torch.testing.assert_close(o32, 0.5 * acc, atol=2e-3, rtol=2e-3)
+    ops.gemm(a, b, epilogue="f32_acc", alpha=0.5, out=o32)
+    torch.testing.assert_close(o32, acc, atol=4e-3, rtol=4e-3)
+    x = aux.float().requires_grad_(True)
+    F.gelu(x, approximate="tanh").sum().backward()
+    assert_close(ops.gemm(a, b, aux=aux, epilogue="gelu_bwd"), acc * x.grad, dt)
+    wg, wu = b[: N // 2], b[N // 2:]
+    fused = ops.interleave_gate_up(wg.contiguous(), wu.contiguous())
+    ref = F.silu(a.float() @ wg.float().t()) * (a.float() @ wu.float().t())
+    assert_close(ops.gemm(a, fused, epilogue="swiglu"), ref, dt)
+
+
+def test_gemm_fp32_simt_and_odd_shapes():
+    ops = _ops()
+    a = torch.randn(33, 70, device="cuda")
+    b = torch.randn(70, 45, device="cuda")
+    torch.testing.assert_close(ops.matmul(a, b), a @ b, atol=1e-4, rtol=1e-4)
+    w = torch.randn(45, 70, device="cuda")
+    bias = torch.randn(45, device="cuda")
+    torch.testing.assert_close(ops.linear(a, w, bias), torch.nn.functional.linear(a, w, bias), atol=1e-4, rtol=1e-4)
+    # 16-bit inputs whose rows are not 16-byte aligned take the CUDA-core kernel too
+    ah, bh = a.half(), w.half()
+    assert_close(ops.linear(ah, bh), ah.float() @ bh.float().t(), torch.float16)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(37, 256), (513, 1000), (4, 8192)])
+def test_elementwise_and_rowwise(dtype, shape):
+    ops = _ops()
+    F = torch.nn.functional
+    x = torch.randn(*shape, device="cuda", dtype=dtype)
+    y = torch.randn(*shape, device="cuda", dtype=dtype)
+    w = torch.randn(shape[1], device="cuda", dtype=dtype)
+    b = torch.randn(shape[1], device="cuda", dtype=dtype)
+    xf, yf = x.float(), y.float()
+    assert_close(ops.gelu(x), F.gelu(xf, approximate="tanh"), dtype)
+    assert_close(ops.silu(x), F.silu(xf), dtype)
+    assert_close(ops.scale(x, 0.25), xf * 0.25, dtype)
+    assert_close(ops.add(x, y), xf + yf, dtype)
+    assert_close(ops.silu_gate(x, y), F.silu(xf) * yf, dtype)
+    assert_close(ops.softmax(x), torch.softmax(xf, -1), dtype)
+    assert_close(ops.rmsnorm(x, w, 1e-6), xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float(), dtype)
+    assert_close(ops.layernorm(x, w, b, 1e-5), F.layer_norm(xf, (shape[1],), w.float(), b.float(), 1e-5), dtype)
+    g = yf.clone().requires_grad_(True)
+    F.gelu(g, approximate="tanh").sum().backward()
+    assert_close(ops.gelu_bwd(x, y), xf * g.grad, dtype)
+
+
+def test_rope_and_qknorm_rope():
+    ops = _ops()
+    from maco_b200.task_graph.runtime import rope_reference
+    tokens, heads, hd = 64, 8, 128
+    x = torch.randn(tokens, heads, hd, device="cuda", dtype=torch.bfloat16)
+    ang = torch.randn(tokens, hd // 2, device="cuda")
+    cos, sin = ang.cos(), ang.sin()
+    assert_close(ops.rope(x, cos, sin), rope_reference(x.float(), cos, sin), torch.bfloat16)
+    w = torch.randn(hd, device="cuda", dtype=torch.bfloat16)
+    xn = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    cs = torch.cat([cos, sin], -1)
+    assert_close(ops.qknorm_rope(x, w, cs, 1e-6), rope_reference(xn, cos, sin), torch.bfloat16)
