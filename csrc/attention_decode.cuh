@@ -1,0 +1,161 @@
+// Split-KV decode attention for grouped-query attention (one KV head shared by G <= 8 query
+// heads, head_dim 128), as tasks of the persistent kernel, plus the merge of the split partials.
+//
+// The reference only names ATTENTION / SOFTMAX in its task enum (maco/csrc/maco_types.h:48,53)
+// and computes attention as softmax(QK^T)V with O(S^2) memory in an example
+// (examples/test_overlap_attention.py:111-113). Decode attention is bound by streaming the KV
+// cache from HBM, so the task reads every K and V row exactly once with 16-byte loads, keeps the
+// G query rows in shared memory and carries the usual running (max, sum, output) triple, which
+// also is what a ring / context-parallel merge needs.
+//
+// Task ATTENTION, arguments in MacoEltArgs:
+//   in0 = q [G, 128]   in1 = K rows [rows, ld_in]   in2 = V rows [rows, ld_in]   (bf16 or fp16)
+//   out = fp32 partial: o[G*128] (unnormalised), m[G], l[G]
+//   rows = keys in this split, cols = 128, i0 = G, f0 = softmax scale
+// Task ATTN_MERGE:
+//   in0 = partials [i1 splits][G*128 + 2G] fp32, out = o [G, 128] (dtype), i0 = G, i1 = splits
+#pragma once
+#include "elementwise.cuh"
+
+namespace maco {
+
+constexpr int kAttnD = 128;
+constexpr int kAttnMaxG = 8;
+
+__device__ __forceinline__ void attn_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratch) {
+  const int G = a.i0 < kAttnMaxG ? a.i0 : kAttnMaxG;
+  float* q_s = reinterpret_cast<float*>(scratch);                 // [G][128]
+  float* p_s = q_s + kAttnMaxG * kAttnD;                          // [G][128] probabilities of the chunk
+  float* red = p_s + kAttnMaxG * kAttnD;                          // [4][G] cross-warp scratch, then [G] results
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int i = tid; i < G * kAttnD; i += 128) q_s[i] = load1(a.in0, i, a.dtype) * a.f0;
+  float m_run[kAttnMaxG], l_run[kAttnMaxG], o[kAttnMaxG];
+#pragma unroll
+  for (int g = 0; g < kAttnMaxG; ++g) { m_run[g] = -INFINITY; l_run[g] = 0.f; o[g] = 0.f; }
+  attn_bar();
+  const uint16_t* K = reinterpret_cast<const uint16_t*>(a.in1);
+  const uint16_t* V = reinterpret_cast<const uint16_t*>(a.in2);
+  for (int base = 0; base < a.rows; base += 128) {
+    const int j = base + tid;
+    const bool valid = j < a.rows;
+    float s[kAttnMaxG];
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) s[g] = 0.f;
+    if (valid) {
+      const uint4* krow = reinterpret_cast<const uint4*>(K + (long long)j * a.ld_in);
+#pragma unroll 4
+      for (int v = 0; v < kAttnD / 8; ++v) {
+        const uint4 u = ld_global_nc_v4(krow + v);
+        float kf[8];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          float2 f = a.dtype == MACO_DT_BF16 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+          kf[2 * t] = f.x; kf[2 * t + 1] = f.y;
+        }
+#pragma unroll
+        for (int g = 0; g < kAttnMaxG; ++g) {
+          if (g < G) {
+            const float4 q0 = *reinterpret_cast<const float4*>(q_s + g * kAttnD + v * 8);
+            const float4 q1 = *reinterpret_cast<const float4*>(q_s + g * kAttnD + v * 8 + 4);
+            s[g] += q0.x * kf[0] + q0.y * kf[1] + q0.z * kf[2] + q0.w * kf[3] + q1.x * kf[4] + q1.y * kf[5] +
+                    q1.z * kf[6] + q1.w * kf[7];
+          }
+        }
+      }
+    }
+    // chunk maximum per head
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) {
+      float mx = warp_max(valid ? s[g] : -INFINITY);
+      if (lane == 0) red[warp * kAttnMaxG + g] = mx;
+    }
+    attn_bar();
+    float corr[kAttnMaxG];
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) {
+      const float cm = fmaxf(fmaxf(red[g], red[kAttnMaxG + g]), fmaxf(red[2 * kAttnMaxG + g], red[3 * kAttnMaxG + g]));
+      const float m_new = fmaxf(m_run[g], cm);
+      corr[g] = (m_run[g] == -INFINITY) ? 0.f : __expf(m_run[g] - m_new);
+      const float pj = valid ? __expf(s[g] - m_new) : 0.f;
+      p_s[g * kAttnD + tid] = pj;
+      s[g] = pj;
+      m_run[g] = m_new;
+    }
+    attn_bar();                                   // red consumed, p_s complete
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) {
+      float sm = warp_sum(s[g]);
+      if (lane == 0) red[warp * kAttnMaxG + g] = sm;
+    }
+    // P·V for this chunk: thread `tid` owns output dimension `tid` of every head
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) o[g] *= corr[g];
+    const int nk = min(128, a.rows - base);
+    const uint16_t* vcol = V + (long long)base * a.ld_in + tid;
+    int jj = 0;
+    for (; jj + 4 <= nk; jj += 4) {
+      float vv[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const uint16_t raw = vcol[(long long)(jj + t) * a.ld_in];
+        vv[t] = a.dtype == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
+      }
+#pragma unroll
+      for (int g = 0; g < kAttnMaxG; ++g) {
+        if (g < G) {
+          const float4 pp = *reinterpret_cast<const float4*>(p_s + g * kAttnD + jj);
+          o[g] += pp.x * vv[0] + pp.y * vv[1] + pp.z * vv[2] + pp.w * vv[3];
+        }
+      }
+    }
+    for (; jj < nk; ++jj) {
+      const uint16_t raw = vcol[(long long)jj * a.ld_in];
+      const float v1 = a.dtype == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
+#pragma unroll
+      for (int g = 0; g < kAttnMaxG; ++g) if (g < G) o[g] += p_s[g * kAttnD + jj] * v1;
+    }
+    attn_bar();                                   // partial sums in red complete, p_s free for the next chunk
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g)
+      l_run[g] = l_run[g] * corr[g] + red[g] + red[kAttnMaxG + g] + red[2 * kAttnMaxG + g] + red[3 * kAttnMaxG + g];
+    attn_bar();                                   // red free for the next chunk
+  }
+  float* out = reinterpret_cast<float*>(a.out);
+#pragma unroll
+  for (int g = 0; g < kAttnMaxG; ++g) if (g < G) out[g * kAttnD + tid] = o[g];
+  if (tid < G) {
+    float mg = -INFINITY, lg = 0.f;
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) if (g == tid) { mg = m_run[g]; lg = l_run[g]; }
+    out[G * kAttnD + tid] = mg;
+    out[G * kAttnD + G + tid] = lg;
+  }
+}
+
+MACO_DEVICE void attn_merge_task(const MacoEltArgs& a, int tid) {
+  const int G = a.i0, S = a.i1;
+  const int rec = G * kAttnD + 2 * G;
+  const float* part = reinterpret_cast<const float*>(a.in0);
+  for (int g = 0; g < G; ++g) {
+    float M = -INFINITY;
+    for (int s = 0; s < S; ++s) M = fmaxf(M, part[s * rec + G * kAttnD + g]);
+    float L = 0.f, acc = 0.f;
+    for (int s = 0; s < S; ++s) {
+      const float ms = part[s * rec + G * kAttnD + g];
+      const float w = (ms == -INFINITY) ? 0.f : __expf(ms - M);
+      L += part[s * rec + G * kAttnD + G + g] * w;
+      acc += part[s * rec + g * kAttnD + tid] * w;
+    }
+    store1(a.out, g * kAttnD + tid, a.dtype, L > 0.f ? acc / L : 0.f);
+  }
+}
+
+MACO_DEVICE void attn_run(uint32_t type, const MacoEltArgs& a, int tid, int nthreads, uint8_t* scratch) {
+  (void)nthreads;
+  if (type == MACO_TASK_ATTENTION) attn_decode_task(a, tid, scratch); else attn_merge_task(a, tid);
+}
+
+}  // namespace maco

@@ -30,11 +30,14 @@ constexpr int kBK = 64;        // k-block: 64 x 2 B = one 128-byte swizzle row
 constexpr int kUmmaK = 16;     // K per tcgen05.mma for 16-bit inputs
 constexpr int kGemmThreads = 192;
 
-template <int BN, int STAGES>
+// BN is the tile width a task uses; SBN (>= BN) sizes the ring's stages, so tasks of different
+// BN can share one ring with identical stage addresses and barrier phases.
+template <int BN, int STAGES, int SBN = BN>
 struct GemmSmemLayout {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kLoadBytes = kABytes + kBBytes;          // bytes one k-step brings in
+  static constexpr int kStageBytes = kABytes + SBN * kBK * 2;   // distance between stages
   static constexpr int kRingBytes = STAGES * kStageBytes;
   // after the ring: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem slot, abort word
   static constexpr int kCtrlBytes = 256;
@@ -51,9 +54,9 @@ struct GemmCtrl {
   volatile uint32_t* abort_word;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int SBN = BN>
 MACO_DEVICE GemmCtrl gemm_ctrl(uint8_t* smem_base) {
-  using L = GemmSmemLayout<BN, STAGES>;
+  using L = GemmSmemLayout<BN, STAGES, SBN>;
   GemmCtrl c;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_base + L::kRingBytes);
   c.full = bars;
@@ -81,17 +84,17 @@ MACO_DEVICE void gemm_tile_coords(int tile, int m_tiles, int n_tiles, int& m_blk
 // ---- producer ------------------------------------------------------------------------------
 // Loads one (128 x 64) A block and one (BN x 64) B block per k-step. K-major operands take one
 // box; MN-major operands take one 64-wide box per 64 rows (each box is a 64x64 swizzle panel).
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int SBN = BN>
 MACO_DEVICE bool gemm_produce_tile(uint8_t* smem, const GemmCtrl& c, const CUtensorMap* tmA,
                                    const CUtensorMap* tmB, int m0, int n0, int k0, int k_blocks,
                                    uint32_t& it, uint64_t budget_ns) {
-  using L = GemmSmemLayout<BN, STAGES>;
+  using L = GemmSmemLayout<BN, STAGES, SBN>;
   for (int kb = 0; kb < k_blocks; ++kb, ++it) {
     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
     if (!mbar_wait(&c.empty[s], ph ^ 1, budget_ns, c.abort_word)) return false;
     uint8_t* sa = smem + s * L::kStageBytes;
     uint8_t* sb = sa + L::kABytes;
-    mbar_arrive_expect_tx(&c.full[s], L::kStageBytes);
+    mbar_arrive_expect_tx(&c.full[s], L::kLoadBytes);
     const int k = k0 + kb * kBK;
     if constexpr (!A_MN) {
       tma_load_2d(sa, tmA, &c.full[s], k, m0);
@@ -123,14 +126,14 @@ MACO_DEVICE void gemm_drain_loads(const GemmCtrl& c, uint32_t issued) {
 }
 
 // ---- MMA issuer ----------------------------------------------------------------------------
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int SBN = BN>
 MACO_DEVICE bool gemm_mma_tile(uint8_t* smem, const GemmCtrl& c, uint32_t tmem_base, uint32_t idesc,
                                int k_blocks, uint32_t& it, uint32_t tile_seq, uint64_t budget_ns) {
-  using L = GemmSmemLayout<BN, STAGES>;
+  using L = GemmSmemLayout<BN, STAGES, SBN>;
   const uint32_t acc = tile_seq & 1, acc_ph = (tile_seq >> 1) & 1;
   if (!mbar_wait(&c.tmem_empty[acc], acc_ph ^ 1, budget_ns, c.abort_word)) return false;
   tc_fence_after();
-  const uint32_t d_tmem = tmem_base + acc * BN;
+  const uint32_t d_tmem = tmem_base + acc * SBN;
   for (int kb = 0; kb < k_blocks; ++kb, ++it) {
     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
     if (!mbar_wait(&c.full[s], ph, budget_ns, c.abort_word)) return false;
@@ -226,7 +229,7 @@ MACO_DEVICE float epi_load_aux(const GemmEpilogue& e, long long row, int col) {
 // Consumes one finished accumulator. Called by all 32 lanes of each of the 4 epilogue warps.
 // `out_base` lets a caller redirect the tile (for example into a peer GPU's buffer);
 // `row_off` is added to the tile's row index when storing (for scatter into per-rank slabs).
-template <int BN>
+template <int BN, int SBN = BN>
 MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const GemmEpilogue& e,
                                     void* out_base, long long row_off, int m0, int n0,
                                     uint32_t tile_seq, uint64_t budget_ns) {
@@ -240,7 +243,7 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
   tc_fence_after();
   const int row = m0 + q * 32 + lane;
   const bool row_ok = row < e.M;
-  const uint32_t t_row = tmem_base + ((q * 32u) << 16) + acc * BN;
+  const uint32_t t_row = tmem_base + ((q * 32u) << 16) + acc * SBN;
   if (e.mode == MACO_EPI_SWIGLU) {
     // Columns [0, BN/2) of the tile hold the gate projection, [BN/2, BN) the up projection of
     // the same BN/2 output features (weights are interleaved that way when the graph is built).
@@ -299,7 +302,7 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
 
 // ---- CTA set-up / tear-down shared by every kernel built on this pipeline ------------------------
 template <int BN, int STAGES>
-MACO_DEVICE uint8_t* gemm_cta_setup(uint8_t* dyn_smem, GemmCtrl& c, uint32_t& tmem_base) {
+MACO_DEVICE uint8_t* gemm_cta_setup(uint8_t* dyn_smem, GemmCtrl& c, uint32_t& tmem_base, bool alloc_tmem = true) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
   c = gemm_ctrl<BN, STAGES>(smem);
   const uint32_t warp = threadIdx.x >> 5;
@@ -309,7 +312,9 @@ MACO_DEVICE uint8_t* gemm_cta_setup(uint8_t* dyn_smem, GemmCtrl& c, uint32_t& tm
     *c.abort_word = 0;
     fence_mbar_init();
   }
-  if (warp == 1) {
+  if (threadIdx.x == 32) *c.tmem_slot = 0;
+  __syncwarp();
+  if (warp == 1 && alloc_tmem) {
     tmem_alloc(c.tmem_slot, 2 * BN);
     tmem_relinquish();
   }
@@ -321,10 +326,10 @@ MACO_DEVICE uint8_t* gemm_cta_setup(uint8_t* dyn_smem, GemmCtrl& c, uint32_t& tm
 }
 
 template <int BN>
-MACO_DEVICE void gemm_cta_teardown(const GemmCtrl& c, uint32_t tmem_base, uint32_t* status) {
+MACO_DEVICE void gemm_cta_teardown(const GemmCtrl& c, uint32_t tmem_base, uint32_t* status, bool had_tmem = true) {
   tc_fence_before();
   __syncthreads();
-  if ((threadIdx.x >> 5) == 1) {
+  if ((threadIdx.x >> 5) == 1 && had_tmem) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * BN);
   }

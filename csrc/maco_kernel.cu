@@ -1,0 +1,485 @@
+// The persistent task kernel: ONE launch executes a whole compiled task graph.
+//
+//   CTA 0 .. num_workers-1   worker CTAs (6 warps: TMA producer, MMA issuer, 4 general warps)
+//   CTA num_workers          scheduler CTA (dynamic mode only)
+//
+// What the reference describes and never launches (maco/csrc/maco_kernel.cu:36-44 has no host
+// launcher; its live kernel, :58-140, has workers only with queues the CPU fills through three
+// host syncs per task) is here the execution path of TaskGraph.execute():
+//
+//  * Tasks are tile-granular 128-byte descriptors uploaded once at compile time. Each carries up
+//    to two wait conditions (event, count) and up to two local signals plus one peer signal.
+//  * Events are monotonic 32-bit counters that are never reset: launch number `epoch` waits for
+//    events[e] >= epoch * count, so re-executing a graph needs no clearing pass and a peer GPU
+//    that runs ahead cannot be lost by a reset.
+//  * STATIC mode: every worker walks a queue written at compile time in global topological
+//    order (which makes the schedule deadlock-free as long as all CTAs are resident: the
+//    earliest unfinished task always sits at the front of its queue) and waits on the events
+//    of each task itself: tile-granular, signal-driven, no central hop.
+//  * DYNAMIC mode: the scheduler CTA polls the events of dispatch groups (a group = the tiles of
+//    one node that become ready together), and when a group's conditions hold pushes its tasks
+//    into the per-worker rings: slot written first, then the head published with st.release
+//    (the reference advances the head before writing the slot, maco_worker.cuh:342-344). Each
+//    ring has one producer (the scheduler) and one consumer CTA; workers publish their tail for
+//    back-pressure. A TERMINATE entry ends each ring.
+//  * Inside a worker the three roles read the same task sequence independently, so the
+//    producer warp prefetches operands of task i+1 while the epilogue of task i drains TMEM.
+//  * Every wait (event, ring, mbarrier) is bounded by `budget_ns`; on expiry the CTA records
+//    {status, task, event, cta} in the host-mapped status block, raises the launch-wide abort
+//    word, and all CTAs drain and return.
+#include "elementwise.cuh"
+#include "gemm_tcgen05.cuh"
+#include "comm_tasks.cuh"
+#include "attention_decode.cuh"
+#include "host_common.h"
+
+using namespace maco;
+
+namespace {
+
+constexpr int kMkBN = 256;
+constexpr int kMkStages = 4;
+using MkLayout = GemmSmemLayout<kMkBN, kMkStages>;
+constexpr int kMkExtraSmem = 1024;     // scheduler heads / current-task slots live after the GEMM control block
+constexpr int kMkScratchSmem = 12288;  // scratch of non-GEMM tasks (the operand ring is NOT free for them:
+                                       // the producer warp may already be filling it for the next GEMM task)
+constexpr int kMkSmemBytes = MkLayout::kTotalBytes + kMkExtraSmem + kMkScratchSmem;
+
+__device__ __forceinline__ void general_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ bool aborted(const MacoProgram& p) { return ld_relaxed_gpu_u32(p.abort_word) == p.epoch; }
+
+__device__ void report_failure(const MacoProgram& p, uint32_t status, uint32_t task, uint32_t event,
+                               volatile uint32_t* cta_abort) {
+  if (cta_abort != nullptr) *cta_abort = 1;
+  if (ld_relaxed_gpu_u32(p.abort_word) != p.epoch) {
+    st_relaxed_gpu_u32(p.abort_word, p.epoch);
+    if (p.status != nullptr) {
+      volatile MacoStatusBlock* s = p.status;
+      s->task = task; s->event = event; s->cta = blockIdx.x; s->rank = (uint32_t)p.rank;
+      __threadfence_system();
+      s->status = s->status | status;
+    }
+  }
+}
+
+// Bounded wait until *flag >= expect (wrap-safe). Leaves early when the launch was aborted.
+__device__ bool mk_wait(const MacoProgram& p, const uint32_t* flag, uint32_t expect, bool sys) {
+  uint32_t v = sys ? ld_acquire_sys_u32(flag) : ld_acquire_gpu_u32(flag);
+  if ((int32_t)(v - expect) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    v = sys ? ld_acquire_sys_u32(flag) : ld_acquire_gpu_u32(flag);
+    if ((int32_t)(v - expect) >= 0) return true;
+    if ((++spins & 31u) == 0) {
+      if (aborted(p)) return false;
+      if (globaltimer_ns() - t0 > p.budget_ns) return false;
+    }
+    __nanosleep(32);
+  }
+}
+
+__device__ bool wait_deps(const MacoProgram& p, const MacoTaskDesc& d, uint32_t task, volatile uint32_t* cta_abort,
+                          uint64_t* wait_ns) {
+  const uint64_t t0 = wait_ns ? globaltimer_ns() : 0;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int e = d.wait_event[j];
+    if (e < 0) continue;
+    const bool sys = (d.flags & (j == 0 ? MACO_TF_WAIT0_SYS : MACO_TF_WAIT1_SYS)) != 0;
+    const bool prev = (d.flags & (j == 0 ? MACO_TF_WAIT0_PREV : MACO_TF_WAIT1_PREV)) != 0;
+    if (!mk_wait(p, &p.events[e], (p.epoch - (prev ? 1u : 0u)) * d.wait_count[j], sys)) {
+      report_failure(p, sys ? MACO_STATUS_PEER_TIMEOUT : MACO_STATUS_TIMEOUT, task, (uint32_t)e, cta_abort);
+      return false;
+    }
+  }
+  if (wait_ns) *wait_ns += globaltimer_ns() - t0;
+  return true;
+}
+
+__device__ void signal_done(const MacoProgram& p, const MacoTaskDesc& d) {
+  const bool sys = (d.flags & MACO_TF_SIGNAL_SYS) != 0;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int e = d.signal_event[j];
+    if (e < 0) continue;
+    if (sys) red_add_release_sys_u32(&p.events[e], 1); else red_add_release_gpu_u32(&p.events[e], 1);
+  }
+  if (d.signal_peer_event >= 0) {
+    if (d.signal_peer >= 0) {
+      red_add_release_sys_u32(&p.peer_events[d.signal_peer][d.signal_peer_event], 1);
+    } else if (d.signal_peer == -2) {
+      for (int r = 0; r < p.world; ++r) red_add_release_sys_u32(&p.peer_events[r][d.signal_peer_event], 1);
+    }
+  }
+}
+
+// Next entry of this worker's queue. false = aborted / timed out.
+__device__ bool fetch_task(const MacoProgram& p, uint32_t w, uint32_t i, uint32_t q_base, uint32_t& task,
+                           volatile uint32_t* cta_abort) {
+  if (p.mode == MACO_MODE_STATIC) {
+    task = (i < p.static_count[w]) ? p.static_queue[(size_t)w * p.static_stride + i] : MACO_QUEUE_TERMINATE;
+    return true;
+  }
+  const uint32_t pos = q_base + i;
+  if (!mk_wait(p, &p.heads[w], pos + 1, false)) {
+    report_failure(p, MACO_STATUS_TIMEOUT, 0xfffffffeu, w, cta_abort);
+    return false;
+  }
+  task = ld_relaxed_gpu_u32(&p.ring[(size_t)w * MACO_WORKER_QUEUE_SIZE + (pos & (MACO_WORKER_QUEUE_SIZE - 1))]);
+  return true;
+}
+
+__device__ __forceinline__ bool is_gemm(uint32_t type) { return type == MACO_TASK_MATMUL || type == MACO_TASK_LINEAR; }
+
+__device__ __forceinline__ MacoTaskDesc load_desc(const MacoProgram& p, uint32_t task) {
+  MacoTaskDesc d;
+  const uint4* src = reinterpret_cast<const uint4*>(p.tasks + task);
+  uint4* dst = reinterpret_cast<uint4*>(&d);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dst[i] = src[i];
+  return d;
+}
+
+// ---- producer warp (lane 0) ---------------------------------------------------------------------
+__device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint8_t* smem, const GemmCtrl& c) {
+  uint32_t it = 0;
+  bool ok = true;
+  const CUtensorMap* tmaps = reinterpret_cast<const CUtensorMap*>(p.tmaps);
+  for (uint32_t i = 0; ok; ++i) {
+    uint32_t task;
+    if (!fetch_task(p, w, i, q_base, task, c.abort_word)) { ok = false; break; }
+    if (task == MACO_QUEUE_TERMINATE) break;
+    const MacoTaskDesc d = load_desc(p, task);
+    if (!is_gemm(d.type)) continue;
+    if (!wait_deps(p, d, task, c.abort_word, nullptr)) { ok = false; break; }
+    fence_proxy_async_all();           // operands were written by generic-proxy stores of other CTAs
+    const MacoGemmArgs& g = d.u.gemm;
+    const CUtensorMap* ta = tmaps + g.tmap_a;
+    const CUtensorMap* tb = tmaps + g.tmap_b;
+    const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | (g.b_mn ? 1 : 0);
+    switch (sel) {
+      case 0: ok = gemm_produce_tile<256, kMkStages, false, false, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      case 1: ok = gemm_produce_tile<256, kMkStages, false, true, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      case 2: ok = gemm_produce_tile<256, kMkStages, true, false, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      case 3: ok = gemm_produce_tile<256, kMkStages, true, true, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      case 4: ok = gemm_produce_tile<128, kMkStages, false, false, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      case 5: ok = gemm_produce_tile<128, kMkStages, false, true, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      case 6: ok = gemm_produce_tile<128, kMkStages, true, false, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      default: ok = gemm_produce_tile<128, kMkStages, true, true, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+    }
+    if (!ok) report_failure(p, MACO_STATUS_TIMEOUT, task, 0xffffffffu, c.abort_word);
+  }
+  if (!ok) gemm_drain_loads<kMkStages>(c, it);
+}
+
+// ---- MMA warp (lane 0) --------------------------------------------------------------------------
+__device__ void mma_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint8_t* smem, const GemmCtrl& c,
+                         uint32_t tmem_base) {
+  uint32_t it = 0, seq = 0;
+  bool ok = true;
+  for (uint32_t i = 0; ok; ++i) {
+    uint32_t task;
+    if (!fetch_task(p, w, i, q_base, task, c.abort_word)) break;
+    if (task == MACO_QUEUE_TERMINATE) break;
+    const MacoTaskDesc d = load_desc(p, task);
+    if (!is_gemm(d.type)) continue;
+    const MacoGemmArgs& g = d.u.gemm;
+    const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | (g.b_mn ? 1 : 0);
+    switch (sel) {
+      case 0: ok = gemm_mma_tile<256, kMkStages, false, false, kMkBN>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      case 1: ok = gemm_mma_tile<256, kMkStages, false, true, kMkBN>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      case 2: ok = gemm_mma_tile<256, kMkStages, true, false, kMkBN>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      case 3: ok = gemm_mma_tile<256, kMkStages, true, true, kMkBN>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      case 4: ok = gemm_mma_tile<128, kMkStages, false, false, kMkBN>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      case 5: ok = gemm_mma_tile<128, kMkStages, false, true, kMkBN>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      case 6: ok = gemm_mma_tile<128, kMkStages, true, false, kMkBN>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      default: ok = gemm_mma_tile<128, kMkStages, true, true, kMkBN>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+    }
+    ++seq;
+  }
+}
+
+// ---- general warps (128 threads): GEMM epilogues and every non-GEMM task -------------------------
+// Control words shared by the 128 threads are double buffered by iteration parity, so the
+// leader can prepare iteration i+1 while slower threads still read the words of iteration i.
+__device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, const GemmCtrl& c, uint32_t tmem_base,
+                             volatile uint32_t* slots, uint8_t* scratch_smem) {
+  const int tid = threadIdx.x - 64;          // 0..127
+  const bool leader = tid == 0;
+  uint32_t seq = 0, done = 0;
+  for (uint32_t i = 0;; ++i) {
+    volatile uint32_t* cur = slots + (i & 1u) * 4;     // [0] task, [1] dependencies satisfied, [2] failure
+    if (leader) {
+      uint32_t task;
+      if (!fetch_task(p, w, i, q_base, task, c.abort_word)) task = MACO_QUEUE_TERMINATE - 1;   // abort marker
+      cur[0] = task;
+      cur[2] = 0;
+    }
+    general_bar();
+    const uint32_t task = cur[0];
+    if (task >= MACO_QUEUE_TERMINATE - 1) {
+      // consume the TERMINATE entry too, so the next launch starts behind it
+      if (leader && task == MACO_QUEUE_TERMINATE && p.mode == MACO_MODE_DYNAMIC) st_release_gpu_u32(&p.tails[w], q_base + i + 1);
+      break;
+    }
+    const MacoTaskDesc d = load_desc(p, task);
+    uint64_t t_start = 0, wait_ns = 0;
+    if (leader && p.trace != nullptr) t_start = globaltimer_ns();
+    if (is_gemm(d.type)) {
+      const MacoGemmArgs& g = d.u.gemm;
+      GemmEpilogue e = p.epis[g.epi];
+      void* out_base = e.out;
+      if (g.peer >= 0) out_base = p.peer_heap[g.peer] + g.out_off;
+      bool ok;
+      if (g.bn == 128) ok = gemm_epilogue_tile<128, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns);
+      else ok = gemm_epilogue_tile<256, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns);
+      if (!ok) cur[2] = 1;
+      ++seq;
+    } else {
+      if (leader) cur[1] = wait_deps(p, d, task, c.abort_word, p.trace ? &wait_ns : nullptr) ? 1u : 0u;
+      general_bar();
+      if (cur[1] != 0) {
+        if (d.type >= 200 && d.type < 300) {
+          if (!comm_run(p, d, tid, 128)) {
+            cur[2] = 1;
+            if (leader) report_failure(p, MACO_STATUS_BAD_TASK, task, d.u.comm.op, c.abort_word);
+          }
+        } else if (d.type == MACO_TASK_ATTENTION || d.type == MACO_TASK_ATTN_MERGE) {
+          attn_run(d.type, d.u.elt, tid, 128, scratch_smem);
+        } else if (d.type != MACO_TASK_NOP) {
+          if (!elt_run(d.type, d.u.elt, tid, 128)) {
+            cur[2] = 1;
+            if (leader) report_failure(p, MACO_STATUS_BAD_TASK, task, d.type, c.abort_word);
+          }
+        }
+      } else if (leader) {
+        cur[2] = 1;
+      }
+    }
+    if (leader && *c.abort_word != 0) cur[2] = 1;
+    general_bar();                              // every thread's stores are issued, failure word final
+    if (cur[2] != 0) break;
+    if (leader) {
+      fence_proxy_async_all();                  // later TMA reads of this output by other CTAs
+      signal_done(p, d);
+      ++done;
+      if (p.mode == MACO_MODE_DYNAMIC) st_release_gpu_u32(&p.tails[w], q_base + i + 1);
+      if (p.trace != nullptr) {
+        MacoTraceRecord r;
+        r.task = task; r.type = d.type; r.sm = (uint16_t)smid(); r.t_start_ns = t_start; r.t_end_ns = globaltimer_ns();
+        r.wait_ns = wait_ns;
+        p.trace[task] = r;
+      }
+    }
+  }
+  if (leader && done != 0 && p.counters != nullptr) atomicAdd(&p.counters[0], done);
+}
+
+// ---- scheduler CTA (warp 0) ---------------------------------------------------------------------
+__device__ bool sched_push(const MacoProgram& p, uint32_t* heads_sm, uint32_t w, uint32_t task) {
+  const uint32_t head = heads_sm[w];
+  // back-pressure: never run more than a ring ahead of the consumer
+  if (!mk_wait(p, &p.tails[w], head + 1 - MACO_WORKER_QUEUE_SIZE, false)) return false;
+  st_relaxed_gpu_u32(&p.ring[(size_t)w * MACO_WORKER_QUEUE_SIZE + (head & (MACO_WORKER_QUEUE_SIZE - 1))], task);
+  st_release_gpu_u32(&p.heads[w], head + 1);
+  heads_sm[w] = head + 1;
+  return true;
+}
+
+__device__ void scheduler_role(const MacoProgram& p, uint32_t* heads_sm) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t W = p.num_workers;
+  const uint32_t n_comm = p.num_comm_workers < W ? p.num_comm_workers : 0;
+  const uint32_t n_compute = W - n_comm;
+  for (uint32_t w = lane; w < W; w += 32) heads_sm[w] = ld_relaxed_gpu_u32(&p.heads[w]);
+  __syncwarp();
+  uint32_t base = 0;                 // first group not yet dispatched
+  uint32_t window_done = 0;          // bit i: group base+i dispatched
+  uint32_t rr_compute = 0, rr_comm = 0;
+  uint64_t last_progress = globaltimer_ns();
+  bool ok = true;
+  while (ok && base < p.num_groups) {
+    const uint32_t g = base + lane;
+    bool ready = false;
+    MacoGroupDesc gd;
+    if (g < p.num_groups && !((window_done >> lane) & 1u)) {
+      gd = p.groups[g];
+      ready = true;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int e = gd.wait_event[j];
+        if (e < 0) continue;
+        const bool sys = (gd.flags & (j == 0 ? MACO_TF_WAIT0_SYS : MACO_TF_WAIT1_SYS)) != 0;
+        const bool prev = (gd.flags & (j == 0 ? MACO_TF_WAIT0_PREV : MACO_TF_WAIT1_PREV)) != 0;
+        const uint32_t v = sys ? ld_acquire_sys_u32(&p.events[e]) : ld_acquire_gpu_u32(&p.events[e]);
+        if ((int32_t)(v - (p.epoch - (prev ? 1u : 0u)) * gd.wait_count[j]) < 0) ready = false;
+      }
+    }
+    uint32_t mask = __ballot_sync(0xffffffffu, ready);
+    if (mask == 0) {
+      if (lane == 0 && (aborted(p) || globaltimer_ns() - last_progress > p.budget_ns)) {
+        report_failure(p, MACO_STATUS_TIMEOUT, 0xfffffffdu, base, nullptr);
+        ok = false;
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      __nanosleep(64);
+      continue;
+    }
+    while (mask != 0 && ok) {
+      const int b = __ffs(mask) - 1;
+      mask &= mask - 1;
+      const uint32_t first = __shfl_sync(0xffffffffu, gd.first_task, b);
+      const uint32_t count = __shfl_sync(0xffffffffu, gd.num_tasks, b);
+      const uint32_t gflags = __shfl_sync(0xffffffffu, gd.flags, b);
+      const bool to_comm = (gflags & MACO_TF_COMM_WORKER) != 0 && n_comm > 0;
+      const uint32_t n_target = to_comm ? n_comm : n_compute;
+      const uint32_t w_off = to_comm ? n_compute : 0;
+      uint32_t rr = to_comm ? rr_comm : rr_compute;
+      // 32 pushes at a time, one lane per distinct worker (fewer lanes when there are fewer workers)
+      const uint32_t par = n_target < 32 ? n_target : 32;
+      for (uint32_t t0 = 0; t0 < count && ok; t0 += par) {
+        bool lane_ok = true;
+        if (lane < par && t0 + lane < count) {
+          const uint32_t w = w_off + (rr + t0 + lane) % n_target;
+          lane_ok = sched_push(p, heads_sm, w, first + t0 + lane);
+        }
+        if (!__all_sync(0xffffffffu, lane_ok)) {
+          if (lane == 0) report_failure(p, MACO_STATUS_QUEUE_OVERFLOW, first, 0, nullptr);
+          ok = false;
+        }
+        __syncwarp();
+      }
+      rr = (rr + count) % n_target;
+      if (to_comm) rr_comm = rr; else rr_compute = rr;
+      window_done |= 1u << b;
+    }
+    last_progress = globaltimer_ns();
+    while (window_done & 1u) { window_done >>= 1; ++base; }
+  }
+  // End of program (or abort): close every ring so the workers leave.
+  for (uint32_t w = lane; w < W; w += 32) sched_push(p, heads_sm, w, MACO_QUEUE_TERMINATE);
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1) maco_persistent_kernel(const __grid_constant__ MacoProgram p) {
+  extern __shared__ uint8_t dyn_smem[];
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool is_worker = blockIdx.x < p.num_workers;
+  GemmCtrl c;
+  uint32_t tmem_base;
+  uint8_t* smem = gemm_cta_setup<kMkBN, kMkStages>(dyn_smem, c, tmem_base, is_worker);
+  uint32_t* extra = reinterpret_cast<uint32_t*>(smem + MkLayout::kRingBytes + MkLayout::kCtrlBytes);
+  if (is_worker) {
+    const uint32_t w = blockIdx.x;
+    // All roles must start from the same ring position: one thread reads it before anyone can move it.
+    if (threadIdx.x == 0) extra[16] = p.mode == MACO_MODE_DYNAMIC ? ld_relaxed_gpu_u32(&p.tails[w]) : 0;
+    __syncthreads();
+    const uint32_t q_base = extra[16];
+    if (warp == 0) {
+      if (lane == 0) producer_role(p, w, q_base, smem, c);
+      __syncwarp();
+    } else if (warp == 1) {
+      if (lane == 0) mma_role(p, w, q_base, smem, c, tmem_base);
+      __syncwarp();
+    } else {
+      general_role(p, w, q_base, c, tmem_base, extra, reinterpret_cast<uint8_t*>(extra) + kMkExtraSmem);
+    }
+  } else {
+    if (warp == 0) scheduler_role(p, extra);
+  }
+  gemm_cta_teardown<kMkBN>(c, tmem_base, nullptr, is_worker);
+}
+
+__global__ void maco_grid_barrier_demo_kernel(uint32_t* counter, uint32_t* order, float* data, int n_per_cta,
+                                              int num_tasks, uint64_t budget_ns, uint32_t* status) {
+  // Self-test of the atoms: every CTA updates its slice, then all CTAs meet at a counter barrier
+  // (atom.add.release.gpu + bounded ld.acquire.gpu spin), num_tasks times. The launcher clamps
+  // the grid to what is co-resident, which the reference's demo kernel
+  // (maco/csrc/maco_kernel.cu:154-198) does not, so that one can deadlock.
+  float* mine = data + (size_t)blockIdx.x * n_per_cta;
+  for (int t = 0; t < num_tasks; ++t) {
+    for (int i = threadIdx.x; i < n_per_cta; i += blockDim.x) mine[i] = mine[i] * 1.5f + 0.1f;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t ticket = atom_add_release_gpu_u32(counter, 1);
+      if (order != nullptr) order[ticket] = blockIdx.x;
+      if (!wait_flag_ge_u32<false>(counter, (uint32_t)(t + 1) * gridDim.x, budget_ns)) {
+        st_relaxed_sys_u32(status, MACO_STATUS_TIMEOUT);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int maco_abi_sizes(int* task, int* group, int* program, int* epilogue, int* trace, int* tmap) {
+  *task = sizeof(MacoTaskDesc); *group = sizeof(MacoGroupDesc); *program = sizeof(MacoProgram);
+  *epilogue = sizeof(GemmEpilogue); *trace = sizeof(MacoTraceRecord); *tmap = sizeof(CUtensorMap);
+  return 0;
+}
+
+int maco_persistent_smem_bytes() { return kMkSmemBytes; }
+
+// Encodes one operand tensor map into `out` (128 bytes, host memory).
+int maco_encode_operand_tmap(void* out, const void* base, int rows_or_k, int cols, long long ld_elems, int mn_major,
+                             int box_rows) {
+  CUtensorMap* tm = reinterpret_cast<CUtensorMap*>(out);
+  // K-major operand [rows, K]: box = 64 (K) x box_rows. MN-major operand stored [K, rows]: box = 64 (rows) x 64 (K).
+  if (!mn_major) return maco_host::encode_tmap_2d(tm, base, 2, rows_or_k, cols, ld_elems * 2, kBK, box_rows);
+  return maco_host::encode_tmap_2d(tm, base, 2, rows_or_k, cols, ld_elems * 2, 64, kBK);
+}
+
+int maco_program_launch(const MacoProgram* prog, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  static bool attr_set[64] = {};
+  int dev = 0;
+  MACO_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev]) {
+    MACO_CHECK_CUDA(cudaFuncSetAttribute(maco_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMkSmemBytes));
+    attr_set[dev] = true;
+  }
+  MacoProgram p = *prog;
+  if (p.status == nullptr) p.status = reinterpret_cast<MacoStatusBlock*>(maco_host::status_device_ptr());
+  const int sms = maco_host::sm_count();
+  const int grid = (int)p.num_workers + (p.mode == MACO_MODE_DYNAMIC ? 1 : 0);
+  if (grid > sms) {
+    // All CTAs must be resident at once (1 per SM): a queued CTA could hold the task another one waits for.
+    maco_host::set_error("persistent kernel: workers + scheduler exceed the number of SMs");
+    return -1;
+  }
+  if (p.num_workers == 0 || p.num_workers > MACO_MAX_WORKERS) { maco_host::set_error("bad worker count"); return -1; }
+  maco_persistent_kernel<<<grid, kGemmThreads, kMkSmemBytes, stream>>>(p);
+  MACO_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Runs the barrier self-test; returns elapsed milliseconds (device-timed) or a negative error.
+float maco_run_sm_scheduling_demo(float* data, int n_total, int num_ctas, int threads, int num_tasks,
+                                  uint32_t* order_out_dev, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int sms = maco_host::sm_count();
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, maco_grid_barrier_demo_kernel, threads, 0) != cudaSuccess) return -1.f;
+  if (num_ctas > sms * per_sm) { maco_host::set_error("demo: more CTAs than can be co-resident"); return -2.f; }
+  uint32_t* counter = nullptr;
+  if (cudaMalloc(&counter, sizeof(uint32_t)) != cudaSuccess) return -1.f;
+  cudaMemsetAsync(counter, 0, sizeof(uint32_t), stream);
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0); cudaEventCreate(&e1);
+  cudaEventRecord(e0, stream);
+  maco_grid_barrier_demo_kernel<<<num_ctas, threads, 0, stream>>>(counter, order_out_dev, data, n_total / num_ctas, num_tasks,
+                                                                 2000000000ull, maco_host::status_device_ptr());
+  cudaEventRecord(e1, stream);
+  cudaError_t err = cudaEventSynchronize(e1);
+  float ms = -1.f;
+  if (err == cudaSuccess) cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0); cudaEventDestroy(e1);
+  cudaFree(counter);
+  return ms;
+}
+
+}  // extern "C"

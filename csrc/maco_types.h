@@ -99,9 +99,11 @@ struct MacoGemmArgs {             /* one output tile */
   uint8_t a_mn, b_mn;             /* operand majors */
   int32_t m0, n0, k0, k_blocks;
   uint32_t idesc;
-  int32_t peer;                   /* -1: store to epilogue.out; else store into peer_out[peer] */
+  int32_t peer;                   /* -1: store to the epilogue's out; else into that rank's heap at out_off */
   long long row_off;              /* added to the row index on store */
-  void* out_override;             /* non-null: store here instead of epilogue.out */
+  uint64_t out_off;               /* with peer >= 0: byte offset of the destination inside the peer's heap */
+  uint32_t bn;                    /* tile width: 128 or 256 */
+  uint32_t _pad;
 };
 
 struct MacoEltArgs {              /* row-wise / element-wise task over rows [row0, row0+rows) */
@@ -116,34 +118,92 @@ struct MacoEltArgs {              /* row-wise / element-wise task over rows [row
   int32_t i0, i1;
 };
 
-struct MacoCommArgs {             /* chunk [off, off+bytes) of a symmetric buffer */
-  uint64_t sym_off_src;           /* byte offset inside the symmetric heap */
-  uint64_t sym_off_dst;
-  uint64_t bytes;
-  int32_t dtype;
-  int32_t peer;                   /* destination / source rank, -1 = all */
-  int32_t op;                     /* 0 sum, 1 avg, 2 max, 3 min */
-  int32_t flag_event;             /* peer event bumped per chunk, -1 none */
-  void* local_out;                /* optional non-symmetric destination */
-  float scale;
+struct MacoCommArgs {             /* 2-D block (rows x row_bytes) of a buffer in the symmetric heap */
+  uint64_t src_off;               /* byte offset of the source inside a rank's heap */
+  uint64_t dst_off;               /* byte offset of the destination inside a rank's heap */
+  uint64_t src_stride, dst_stride;/* bytes between rows */
+  uint32_t row_bytes, rows;
+  int32_t dtype;                  /* element type for reductions */
+  int32_t peer;                   /* push: destination rank (-1 = every other rank, -3 = every rank incl. self) */
+  int32_t op;                     /* MacoCommOp */
+  int32_t nslots;                 /* local reduce: number of slots summed */
+  uint64_t slot_stride;           /* local reduce: bytes between slots */
+  void* local_ptr;                /* optional destination outside the heap (reductions) */
+  float scale;                    /* applied to reduced values (1/world for an average) */
   int32_t _pad;
 };
 
+enum MacoCommOp {
+  MACO_COMM_PUSH = 0,             /* copy my block into peer heap(s) */
+  MACO_COMM_REDUCE_LOCAL = 1,     /* out = scale * sum of nslots blocks of my own heap */
+  MACO_COMM_REDUCE_PULL = 2,      /* out = scale * sum over ranks of heap[r] + src_off (reads peers) */
+  MACO_COMM_ALLREDUCE = 3,        /* pull-reduce one block from every rank, store the result to every rank */
+  MACO_COMM_ALLREDUCE_MC = 4,     /* same through the NVSwitch multicast address (multimem) */
+  MACO_COMM_PULL = 5              /* copy a block of peer `peer`'s heap into my heap */
+};
+
 struct MacoTaskDesc {
-  uint32_t type;
+  uint16_t type;                  /* MacoTaskType */
+  uint16_t flags;                 /* MACO_TF_* */
   uint32_t node_id;
-  int32_t wait_event[2];          /* -1: no condition */
+  int32_t wait_event[2];          /* -1: no condition; else wait until events[e] >= epoch * wait_count */
   uint32_t wait_count[2];
-  int32_t signal_event;           /* local event bumped by 1 at completion, -1 none */
-  int32_t signal_peer;            /* rank whose event table is bumped, -1 none, -2 all ranks */
+  int32_t signal_event[2];        /* local events bumped by 1 at completion, -1 none */
+  int32_t signal_peer;            /* rank whose event table is bumped, -1 none, -2 every rank */
   int32_t signal_peer_event;
-  uint32_t flags;                 /* bit0: waits are on .sys-scope (peer-written) counters */
   union {
     MacoGemmArgs gemm;
     MacoEltArgs elt;
     MacoCommArgs comm;
     uint8_t raw[88];
   } u;
+};
+
+enum MacoTaskFlags {
+  MACO_TF_WAIT0_SYS = 1,          /* wait_event[0] is bumped by other GPUs: poll with .sys scope */
+  MACO_TF_WAIT1_SYS = 2,
+  MACO_TF_COMM_WORKER = 4,        /* prefers a communication worker */
+  MACO_TF_SIGNAL_SYS = 8,         /* local signals use .sys scope (another GPU polls them) */
+  MACO_TF_WAIT0_PREV = 16,        /* wait_event[0] refers to the previous launch: (epoch-1) * count */
+  MACO_TF_WAIT1_PREV = 32
+};
+
+/* A dispatch group for the scheduler CTA: a run of consecutive tasks that becomes ready together. */
+struct MacoGroupDesc {
+  uint32_t first_task, num_tasks;
+  int32_t wait_event[2];
+  uint32_t wait_count[2];
+  uint32_t flags;                 /* MACO_TF_* */
+  uint32_t _pad;
+};
+
+#define MACO_QUEUE_TERMINATE 0xffffffffu
+
+enum MacoKernelMode { MACO_MODE_STATIC = 0, MACO_MODE_DYNAMIC = 1 };
+
+/* Everything one launch of the persistent kernel needs; passed by value. */
+struct MacoProgram {
+  const struct MacoTaskDesc* tasks;
+  const void* tmaps;              /* CUtensorMap[ ] (128 bytes each, 64-byte aligned) */
+  const struct GemmEpilogue* epis;
+  uint32_t* events;               /* monotonic counters, never reset; threshold scales with epoch */
+  uint32_t* peer_events[MACO_MAX_PEERS];
+  uint8_t* peer_heap[MACO_MAX_PEERS];
+  const uint32_t* static_queue;   /* [num_workers][static_stride] task indices */
+  const uint32_t* static_count;   /* [num_workers] */
+  uint32_t* ring;                 /* [num_workers][MACO_WORKER_QUEUE_SIZE] (dynamic mode) */
+  uint32_t* heads;                /* [num_workers] published by the scheduler */
+  uint32_t* tails;                /* [num_workers] published by the workers */
+  const struct MacoGroupDesc* groups;
+  uint32_t* abort_word;           /* == epoch when some wait of this launch gave up */
+  uint32_t* counters;             /* [0] tasks completed (all launches); may be null */
+  uint8_t* mc_heap;               /* multicast (NVLS) address of the symmetric heap, or null */
+  struct MacoStatusBlock* status;
+  struct MacoTraceRecord* trace;  /* [num_tasks] or null */
+  unsigned long long budget_ns;
+  uint32_t num_tasks, num_groups, num_workers, num_comm_workers;
+  uint32_t static_stride, mode, epoch;
+  int32_t rank, world;
 };
 
 #ifdef __cplusplus

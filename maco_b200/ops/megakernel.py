@@ -1,0 +1,666 @@
+"""Host side of the persistent task kernel: program builder, graph lowering, launch.
+
+``ProgramBuilder`` turns operations into tile-granular task descriptors with (event, count) wait
+conditions and signals; ``Program`` owns the device tables and launches ``maco_persistent_kernel``
+once per ``run()``; ``lower_graph`` maps a compiled ``TaskGraph`` onto a builder.
+
+The reference's ``MacoRuntime`` (maco/task_graph/runtime.py:21-144) re-uploads every task on every
+execute with three host syncs each and forwards only the first input and first dependency. Here
+the whole table is built at compile time, uploaded in one copy, and ``run()`` is: bump the epoch,
+one launch.
+"""
+from __future__ import annotations
+
+import ctypes
+import struct
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import _native as N
+from ..task_graph.nodes import TaskNode, TaskType
+
+BM, BK = 128, 64
+QUEUE_TERMINATE = 0xFFFFFFFF
+MODE_STATIC, MODE_DYNAMIC = 0, 1
+TF_WAIT0_SYS, TF_WAIT1_SYS, TF_COMM_WORKER, TF_SIGNAL_SYS, TF_WAIT0_PREV, TF_WAIT1_PREV = 1, 2, 4, 8, 16, 32
+COMM_PUSH, COMM_REDUCE_LOCAL, COMM_REDUCE_PULL, COMM_ALLREDUCE, COMM_ALLREDUCE_MC, COMM_PULL = range(6)
+MAX_PEERS = 16
+WORKER_QUEUE_SIZE = 1024
+
+EPI = {None: 0, "none": 0, "gelu": 1, "swiglu": 2, "f32": 3, "f32_acc": 4, "gelu_bwd": 5, "silu": 6, "residual": 7}
+
+TASK_DTYPE = np.dtype([
+    ("type", "<u2"), ("flags", "<u2"), ("node_id", "<u4"), ("wait_event", "<i4", 2), ("wait_count", "<u4", 2),
+    ("signal_event", "<i4", 2), ("signal_peer", "<i4"), ("signal_peer_event", "<i4"), ("raw", "u1", 88),
+])
+GROUP_DTYPE = np.dtype([
+    ("first_task", "<u4"), ("num_tasks", "<u4"), ("wait_event", "<i4", 2), ("wait_count", "<u4", 2),
+    ("flags", "<u4"), ("_pad", "<u4"),
+])
+TRACE_DTYPE = np.dtype([("task", "<u4"), ("type", "<u2"), ("sm", "<u2"), ("t_start_ns", "<u8"), ("t_end_ns", "<u8"),
+                        ("wait_ns", "<u8")])
+
+
+class _ProgramStruct(ctypes.Structure):
+    _fields_ = [
+        ("tasks", ctypes.c_void_p), ("tmaps", ctypes.c_void_p), ("epis", ctypes.c_void_p), ("events", ctypes.c_void_p),
+        ("peer_events", ctypes.c_void_p * MAX_PEERS), ("peer_heap", ctypes.c_void_p * MAX_PEERS),
+        ("static_queue", ctypes.c_void_p), ("static_count", ctypes.c_void_p), ("ring", ctypes.c_void_p),
+        ("heads", ctypes.c_void_p), ("tails", ctypes.c_void_p), ("groups", ctypes.c_void_p),
+        ("abort_word", ctypes.c_void_p), ("counters", ctypes.c_void_p), ("mc_heap", ctypes.c_void_p),
+        ("status", ctypes.c_void_p), ("trace", ctypes.c_void_p), ("budget_ns", ctypes.c_ulonglong),
+        ("num_tasks", ctypes.c_uint32), ("num_groups", ctypes.c_uint32), ("num_workers", ctypes.c_uint32),
+        ("num_comm_workers", ctypes.c_uint32), ("static_stride", ctypes.c_uint32), ("mode", ctypes.c_uint32),
+        ("epoch", ctypes.c_uint32), ("rank", ctypes.c_int32), ("world", ctypes.c_int32),
+    ]
+
+
+_abi_checked = False
+
+
+def _lib():
+    global _abi_checked
+    lib = N.lib()
+    if not _abi_checked:
+        I, P, LL = ctypes.c_int, ctypes.c_void_p, ctypes.c_longlong
+        lib.maco_abi_sizes.restype = I
+        lib.maco_abi_sizes.argtypes = [ctypes.POINTER(I)] * 6
+        lib.maco_encode_operand_tmap.restype = I
+        lib.maco_encode_operand_tmap.argtypes = [P, P, I, I, LL, I, I]
+        lib.maco_program_launch.restype = I
+        lib.maco_program_launch.argtypes = [ctypes.POINTER(_ProgramStruct), P]
+        lib.maco_persistent_smem_bytes.restype = I
+        sizes = [I() for _ in range(6)]
+        lib.maco_abi_sizes(*[ctypes.byref(s) for s in sizes])
+        got = [s.value for s in sizes]
+        want = [TASK_DTYPE.itemsize, GROUP_DTYPE.itemsize, ctypes.sizeof(_ProgramStruct), 72, TRACE_DTYPE.itemsize, 128]
+        if got != want:
+            raise RuntimeError(f"ABI mismatch between the Python tables and libmaco_b200: native {got}, python {want}")
+        _abi_checked = True
+    return lib
+
+
+def _pack_gemm(tmap_a, tmap_b, epi, a_mn, b_mn, m0, n0, k0, k_blocks, idesc, peer, row_off, out_off, bn) -> bytes:
+    return struct.pack("<HHHBBiiiiIiqQII", tmap_a, tmap_b, epi, a_mn, b_mn, m0, n0, k0, k_blocks, idesc, peer, row_off,
+                       out_off, bn, 0)
+
+
+def _pack_elt(in0, in1, in2, out, row0, rows, cols, dtype, ld_in, ld_out, f0=0.0, f1=0.0, i0=0, i1=0) -> bytes:
+    return struct.pack("<QQQQiiiiiiffii", in0 or 0, in1 or 0, in2 or 0, out or 0, row0, rows, cols, dtype, ld_in, ld_out,
+                       f0, f1, i0, i1)
+
+
+def _pack_comm(src_off, dst_off, src_stride, dst_stride, row_bytes, rows, dtype, peer, op, nslots=0, slot_stride=0,
+               local_ptr=0, scale=1.0) -> bytes:
+    return struct.pack("<QQQQIIiiiiQQfi", src_off, dst_off, src_stride, dst_stride, row_bytes, rows, dtype, peer, op,
+                       nslots, slot_stride, local_ptr or 0, scale, 0)
+
+
+def _pack_epilogue(out, bias, aux, ld_out, ld_aux, mode, out_type, bias_type, aux_type, M, Nn, alpha) -> bytes:
+    return struct.pack("<QQQqqiiiiiifi", out or 0, bias or 0, aux or 0, ld_out, ld_aux, mode, out_type, bias_type,
+                       aux_type, M, Nn, alpha, 0)
+
+
+def make_idesc(ab_format: int, m: int, n: int, a_mn: int, b_mn: int) -> int:
+    return (1 << 4) | (ab_format << 7) | (ab_format << 10) | (a_mn << 15) | (b_mn << 16) | ((n >> 3) << 17) | ((m >> 4) << 24)
+
+
+Wait = Tuple[int, int, int]   # (event, count, flags among SYS/PREV expressed for slot 0)
+
+
+@dataclass
+class RowEvents:
+    """Completion events of a produced 2-D tensor: one per ``block`` rows plus one for the whole tensor."""
+    rows: int
+    block: int
+    row_events: List[Tuple[int, int]]          # (event, count) per row block
+    all_event: Tuple[int, int]                 # (event, count) of the whole node
+    sys: bool = False                          # signalled by other GPUs
+
+    def for_rows(self, r0: int, r1: int) -> Tuple[int, int]:
+        b0, b1 = r0 // self.block, (max(r0 + 1, r1) - 1) // self.block
+        if b0 == b1 and b0 < len(self.row_events):
+            return self.row_events[b0]
+        return self.all_event
+
+
+class ProgramBuilder:
+    """Accumulates tasks, events, tensor maps and epilogues; ``build()`` uploads them."""
+
+    def __init__(self, device: torch.device, num_workers: Optional[int] = None, mode: str = "static",
+                 num_comm_workers: int = 0, heap=None, trace: bool = False, wait_budget_ms: Optional[float] = None):
+        self.device = torch.device(device)
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.mode = MODE_DYNAMIC if mode == "dynamic" else MODE_STATIC
+        limit = sms - (1 if self.mode == MODE_DYNAMIC else 0)
+        self.num_workers = max(1, min(int(num_workers) if num_workers else limit, limit, 256))
+        self.num_comm_workers = max(0, min(int(num_comm_workers), self.num_workers - 1))
+        self.heap = heap
+        self.trace = trace
+        from ..config import config
+        self.wait_budget_ms = float(wait_budget_ms if wait_budget_ms is not None else config.wait_budget_ms)
+        self.tasks: List[dict] = []
+        self.groups: List[dict] = []
+        self.tmaps: List[bytes] = []
+        self._tmap_cache: Dict[tuple, int] = {}
+        self.epis: List[bytes] = []
+        self.num_events = 0
+        self.keepalive: List[torch.Tensor] = []
+        self._node_counter = 0
+
+    # ------------------------------------------------------------------ primitives
+    def new_event(self) -> int:
+        e = self.num_events
+        self.num_events += 1
+        return e
+
+    def new_node_id(self) -> int:
+        self._node_counter += 1
+        return self._node_counter - 1
+
+    def add_task(self, ttype: int, raw: bytes, waits: Sequence[Tuple[int, int, bool, bool]] = (),
+                 signals: Sequence[int] = (), signal_peer: int = -1, signal_peer_event: int = -1, node_id: int = 0,
+                 comm_worker: bool = False, signal_sys: bool = False) -> int:
+        """``waits``: up to two (event, count, sys_scope, previous_epoch)."""
+        if len(waits) > 2 or len(signals) > 2:
+            raise ValueError("a task takes at most two wait conditions and two local signals")
+        flags = 0
+        we, wc = [-1, -1], [0, 0]
+        for j, (ev, cnt, sys_scope, prev) in enumerate(waits):
+            we[j], wc[j] = ev, cnt
+            if sys_scope:
+                flags |= TF_WAIT0_SYS if j == 0 else TF_WAIT1_SYS
+            if prev:
+                flags |= TF_WAIT0_PREV if j == 0 else TF_WAIT1_PREV
+        if comm_worker:
+            flags |= TF_COMM_WORKER
+        if signal_sys:
+            flags |= TF_SIGNAL_SYS
+        se = list(signals) + [-1] * (2 - len(signals))
+        self.tasks.append(dict(type=ttype, flags=flags, node_id=node_id, wait_event=we, wait_count=wc, signal_event=se,
+                               signal_peer=signal_peer, signal_peer_event=signal_peer_event, raw=raw))
+        return len(self.tasks) - 1
+
+    def join(self, waits: List[Tuple[int, int, bool, bool]], node_id: int = 0) -> List[Tuple[int, int, bool, bool]]:
+        """Reduces a list of wait conditions to at most two by chaining NOP tasks."""
+        waits = list(dict.fromkeys(waits))
+        while len(waits) > 2:
+            ev = self.new_event()
+            self.add_task(int(TaskType.NOP), b"", waits=waits[:2], signals=[ev], node_id=node_id)
+            waits = [(ev, 1, False, False)] + waits[2:]
+        return waits
+
+    def _tmap(self, t: torch.Tensor, rows: int, cols: int, ld: int, mn_major: bool, box_rows: int) -> int:
+        key = (t.data_ptr(), rows, cols, ld, mn_major, box_rows)
+        idx = self._tmap_cache.get(key)
+        if idx is not None:
+            return idx
+        buf = ctypes.create_string_buffer(128)
+        rc = _lib().maco_encode_operand_tmap(buf, t.data_ptr(), rows, cols, ld, int(mn_major), box_rows)
+        N.check(rc, "maco_encode_operand_tmap")
+        self.tmaps.append(buf.raw)
+        self._tmap_cache[key] = len(self.tmaps) - 1
+        return len(self.tmaps) - 1
+
+    # ------------------------------------------------------------------ GEMM node
+    def gemm(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor], *, trans_a: bool = False,
+             trans_b: bool = False, epilogue: Optional[str] = None, bias: Optional[torch.Tensor] = None,
+             aux: Optional[torch.Tensor] = None, alpha: float = 1.0, bn: int = 0,
+             a_ready: Optional[RowEvents] = None, extra_waits: Sequence[Tuple[int, int, bool, bool]] = (),
+             per_tile=None, m_blocks: Optional[Sequence[int]] = None, signal_sys: bool = False,
+             row_wait=None) -> RowEvents:
+        """Adds the tiles of ``out = epilogue(alpha * A · B^T)`` (A logically [M,K], B logically [N,K]).
+
+        ``a_ready`` gives row-block events of A (a tile waits only for its 128 rows); ``extra_waits``
+        apply to every tile. ``per_tile(mb, nb) -> dict`` may override ``peer``, ``out_off``,
+        ``row_off``, ``signal_peer``, ``signal_peer_event`` per tile (fused GEMM -> reduce-scatter).
+        ``row_wait(mb) -> wait`` supplies a per-row-block wait instead of ``a_ready``.
+        """
+        for t in (a, b):
+            if t.dim() != 2 or t.stride(1) != 1 or t.dtype not in (torch.bfloat16, torch.float16):
+                raise ValueError("tcgen05 GEMM tasks need row-major 2-D bf16/fp16 operands")
+            if t.data_ptr() % 16 or (t.stride(0) * 2) % 16:
+                raise ValueError("tcgen05 GEMM tasks need 16-byte aligned operand rows")
+        M, K = (a.shape[1], a.shape[0]) if trans_a else (a.shape[0], a.shape[1])
+        Nn, Kb = (b.shape[1], b.shape[0]) if trans_b else (b.shape[0], b.shape[1])
+        if K != Kb:
+            raise ValueError("inner dimensions differ")
+        mode = EPI[epilogue]
+        if bn == 0:
+            m_tiles = (M + BM - 1) // BM
+            bn = 128 if (Nn <= 128 or (m_tiles * ((Nn + 255) // 256) < self.num_workers and mode != 2)) else 256
+        if mode == 2:
+            bn = 256
+        ab = 1 if a.dtype == torch.bfloat16 else 0
+        idesc = make_idesc(ab, BM, bn, int(trans_a), int(trans_b))
+        ta = self._tmap(a, a.shape[0], a.shape[1], a.stride(0), trans_a, BM)
+        tb = self._tmap(b, b.shape[0], b.shape[1], b.stride(0), trans_b, bn)
+        out_ptr = out.data_ptr() if out is not None else 0
+        ld_out = out.stride(0) if out is not None else 0
+        out_type = N.DTYPE_CODE[out.dtype] if out is not None else N.DTYPE_CODE[a.dtype]
+        self.epis.append(_pack_epilogue(out_ptr, N.ptr(bias), N.ptr(aux), ld_out, aux.stride(0) if aux is not None else 0,
+                                        mode, out_type, N.DTYPE_CODE[bias.dtype] if bias is not None else 0,
+                                        N.DTYPE_CODE[aux.dtype] if aux is not None else 0, M, Nn, float(alpha)))
+        epi = len(self.epis) - 1
+        if epi > 0xFFFF or len(self.tmaps) > 0xFFFF:
+            raise ValueError("too many epilogues / tensor maps in one program")
+        self.keepalive += [t for t in (a, b, out, bias, aux) if t is not None]
+        node_id = self.new_node_id()
+        m_tiles, n_tiles, k_blocks = (M + BM - 1) // BM, (Nn + bn - 1) // bn, (K + BK - 1) // BK
+        mbs = list(m_blocks) if m_blocks is not None else list(range(m_tiles))
+        all_ev = self.new_event()
+        row_events = {mb: self.new_event() for mb in mbs}
+        base_waits = self.join(list(extra_waits), node_id)
+        G = 8
+        for g0 in range(0, len(mbs), G):
+            grp = mbs[g0:g0 + G]
+            # tiles of `G` row blocks sweep all column tiles: operands stay in L2, row blocks finish in order
+            for nb in range(n_tiles):
+                for mb in grp:
+                    waits = list(base_waits)
+                    if row_wait is not None:
+                        w = row_wait(mb)
+                        if w is not None:
+                            waits.append(w)
+                    elif a_ready is not None:
+                        ev, cnt = a_ready.for_rows(mb * BM, min(M, (mb + 1) * BM))
+                        waits.append((ev, cnt, a_ready.sys, False))
+                    waits = list(dict.fromkeys(waits))
+                    if len(waits) > 2:
+                        waits = self.join(waits, node_id)
+                    ov = per_tile(mb, nb) if per_tile is not None else {}
+                    raw = _pack_gemm(ta, tb, epi, int(trans_a), int(trans_b), mb * BM, nb * bn, 0, k_blocks, idesc,
+                                     ov.get("peer", -1), ov.get("row_off", 0), ov.get("out_off", 0), bn)
+                    self.add_task(int(TaskType.LINEAR), raw, waits=waits, signals=[row_events[mb], all_ev],
+                                  signal_peer=ov.get("signal_peer", -1), signal_peer_event=ov.get("signal_peer_event", -1),
+                                  node_id=node_id, signal_sys=signal_sys)
+        total = len(mbs) * n_tiles
+        return RowEvents(rows=M, block=BM, row_events=[(row_events.get(mb, all_ev), n_tiles) if mb in row_events
+                                                       else (all_ev, total) for mb in range(m_tiles)],
+                         all_event=(all_ev, total), sys=signal_sys)
+
+    def _emit_groups(self) -> None:
+        """Dispatch groups of the scheduler CTA: maximal runs of consecutive tasks with identical wait
+        conditions and worker class (so a group becomes ready as a whole)."""
+        self.groups = []
+        i, n = 0, len(self.tasks)
+        mask = TF_WAIT0_SYS | TF_WAIT1_SYS | TF_COMM_WORKER | TF_WAIT0_PREV | TF_WAIT1_PREV
+
+        def key(t):
+            return (tuple(t["wait_event"]), tuple(t["wait_count"]), t["flags"] & mask)
+
+        while i < n:
+            k = key(self.tasks[i])
+            j = i + 1
+            while j < n and key(self.tasks[j]) == k:
+                j += 1
+            t = self.tasks[i]
+            self.groups.append(dict(first_task=i, num_tasks=j - i, wait_event=list(t["wait_event"]),
+                                    wait_count=list(t["wait_count"]), flags=t["flags"] & mask))
+            i = j
+
+    # ------------------------------------------------------------------ element-wise / row-wise node
+    def elementwise(self, ttype: int, in0: torch.Tensor, out: torch.Tensor, *, in1: Optional[torch.Tensor] = None,
+                    in2: Optional[torch.Tensor] = None, rows: int, cols: int, f0: float = 0.0, f1: float = 0.0,
+                    i0: int = 0, i1: int = 0, in_ready: Sequence[Optional[RowEvents]] = (),
+                    extra_waits: Sequence[Tuple[int, int, bool, bool]] = (), rows_per_task: Optional[int] = None,
+                    in1_rowwise: bool = True) -> RowEvents:
+        """Row-chunked task list for an operator of csrc/elementwise.cuh over a [rows, cols] view."""
+        dt = N.DTYPE_CODE[in0.dtype]
+        esz = in0.element_size()
+        if rows_per_task is None:
+            target = max(1, (256 * 1024) // max(1, cols * esz))       # ~256 KiB of input per task
+            rows_per_task = 1
+            while rows_per_task * 2 <= min(target, BM):
+                rows_per_task *= 2
+        self.keepalive += [t for t in (in0, in1, in2, out) if t is not None]
+        node_id = self.new_node_id()
+        all_ev = self.new_event()
+        n_blocks = (rows + BM - 1) // BM
+        row_events = [self.new_event() for _ in range(n_blocks)]
+        counts = [0] * n_blocks
+        base_waits = self.join(list(extra_waits), node_id)
+        total = 0
+        for r0 in range(0, rows, rows_per_task):
+            r1 = min(rows, r0 + rows_per_task)
+            waits = list(base_waits)
+            for re_ in in_ready:
+                if re_ is not None:
+                    ev, cnt = re_.for_rows(r0, r1) if re_.rows == rows else re_.all_event
+                    waits.append((ev, cnt, re_.sys, False))
+            waits = list(dict.fromkeys(waits))
+            if len(waits) > 2:
+                waits = self.join(waits, node_id)
+            raw = _pack_elt(in0.data_ptr(), N.ptr(in1), N.ptr(in2), out.data_ptr(), r0, r1 - r0, cols, dt, cols, cols,
+                            f0, f1, i0, i1)
+            blk = r0 // BM
+            self.add_task(ttype, raw, waits=waits, signals=[row_events[blk], all_ev], node_id=node_id)
+            counts[blk] += 1
+            total += 1
+        return RowEvents(rows=rows, block=BM, row_events=list(zip(row_events, counts)), all_event=(all_ev, total))
+
+    # ------------------------------------------------------------------ build
+    def build(self) -> "Program":
+        self._emit_groups()
+        return Program(self)
+
+
+class Program:
+    """Device tables of a built program plus the launch call."""
+
+    def __init__(self, b: ProgramBuilder):
+        lib = _lib()
+        self.device = b.device
+        self.mode = b.mode
+        self.num_workers = b.num_workers
+        self.num_comm_workers = b.num_comm_workers
+        self.keepalive = b.keepalive
+        self.heap = b.heap
+        n = len(b.tasks)
+        self.num_tasks = n
+        tasks = np.zeros(max(n, 1), dtype=TASK_DTYPE)
+        for i, t in enumerate(b.tasks):
+            rec = tasks[i]
+            rec["type"], rec["flags"], rec["node_id"] = t["type"], t["flags"], t["node_id"]
+            rec["wait_event"], rec["wait_count"], rec["signal_event"] = t["wait_event"], t["wait_count"], t["signal_event"]
+            rec["signal_peer"], rec["signal_peer_event"] = t["signal_peer"], t["signal_peer_event"]
+            raw = t["raw"]
+            rec["raw"][: len(raw)] = np.frombuffer(raw, dtype=np.uint8)
+        self._tasks_np = tasks
+        self.task_types = tasks["type"].copy()
+        dev = self.device
+
+        def up(arr: np.ndarray) -> torch.Tensor:
+            return torch.from_numpy(arr.view(np.uint8).reshape(-1).copy()).to(dev)
+
+        self.d_tasks = up(tasks)
+        self.d_tmaps = up(np.frombuffer(b"".join(b.tmaps) or bytes(128), dtype=np.uint8))
+        self.d_epis = up(np.frombuffer(b"".join(b.epis) or bytes(72), dtype=np.uint8))
+        groups = np.zeros(max(len(b.groups), 1), dtype=GROUP_DTYPE)
+        for i, g in enumerate(b.groups):
+            rec = groups[i]
+            rec["first_task"], rec["num_tasks"] = g["first_task"], g["num_tasks"]
+            rec["wait_event"], rec["wait_count"], rec["flags"] = g["wait_event"], g["wait_count"], g["flags"]
+        self.num_groups = len(b.groups)
+        self.d_groups = up(groups)
+        # events live in the symmetric heap when peers must reach them
+        self.num_events = max(1, b.num_events)
+        if b.heap is not None:
+            self.d_events = b.heap.alloc((self.num_events + 64,), torch.int32, zero=True)
+        else:
+            self.d_events = torch.zeros(self.num_events + 64, dtype=torch.int32, device=dev)
+        self.d_ctrl = torch.zeros(8, dtype=torch.int32, device=dev)        # [0] abort word, [1] task counter
+        # static queues: global order, round-robin over the worker class the task prefers
+        W, Wc = self.num_workers, self.num_comm_workers
+        n_compute = W - Wc
+        queues: List[List[int]] = [[] for _ in range(W)]
+        rr_c = rr_m = 0
+        for i, t in enumerate(b.tasks):
+            if (t["flags"] & TF_COMM_WORKER) and Wc > 0:
+                queues[n_compute + rr_m % Wc].append(i)
+                rr_m += 1
+            else:
+                queues[rr_c % n_compute].append(i)
+                rr_c += 1
+        stride = max(1, max(len(q) for q in queues))
+        sq = np.full((W, stride), QUEUE_TERMINATE, dtype=np.uint32)
+        for w, q in enumerate(queues):
+            sq[w, : len(q)] = q
+        self.static_stride = stride
+        self.d_static_queue = up(sq)
+        self.d_static_count = up(np.array([len(q) for q in queues], dtype=np.uint32))
+        if self.mode == MODE_DYNAMIC:
+            self.d_ring = torch.zeros(W * WORKER_QUEUE_SIZE, dtype=torch.int32, device=dev)
+            self.d_heads = torch.zeros(W, dtype=torch.int32, device=dev)
+            self.d_tails = torch.zeros(W, dtype=torch.int32, device=dev)
+        else:
+            self.d_ring = self.d_heads = self.d_tails = None
+        self.d_trace = torch.zeros(max(n, 1) * TRACE_DTYPE.itemsize, dtype=torch.uint8, device=dev) if b.trace else None
+        self.epoch = 0
+        ps = _ProgramStruct()
+        ps.tasks, ps.tmaps, ps.epis = self.d_tasks.data_ptr(), self.d_tmaps.data_ptr(), self.d_epis.data_ptr()
+        ps.events = self.d_events.data_ptr()
+        ps.static_queue, ps.static_count = self.d_static_queue.data_ptr(), self.d_static_count.data_ptr()
+        if self.mode == MODE_DYNAMIC:
+            ps.ring, ps.heads, ps.tails = self.d_ring.data_ptr(), self.d_heads.data_ptr(), self.d_tails.data_ptr()
+        ps.groups = self.d_groups.data_ptr()
+        ps.abort_word = self.d_ctrl.data_ptr()
+        ps.counters = self.d_ctrl.data_ptr() + 4
+        ps.status = None
+        ps.trace = self.d_trace.data_ptr() if self.d_trace is not None else None
+        ps.budget_ns = int(b.wait_budget_ms * 1e6)
+        ps.num_tasks, ps.num_groups, ps.num_workers, ps.num_comm_workers = n, self.num_groups, W, Wc
+        ps.static_stride, ps.mode, ps.epoch = stride, self.mode, 0
+        ps.rank, ps.world = 0, 1
+        if b.heap is not None:
+            ps.rank, ps.world = b.heap.rank, b.heap.world
+            ev_off = b.heap.offset_of(self.d_events)
+            for r in range(b.heap.world):
+                ps.peer_heap[r] = b.heap.peer_base(r)
+                ps.peer_events[r] = b.heap.peer_base(r) + ev_off
+            ps.mc_heap = b.heap.multicast_base() or None
+        else:
+            ps.peer_heap[0] = 0
+            ps.peer_events[0] = self.d_events.data_ptr()
+        self._ps = ps
+        self._lib = lib
+        torch.cuda.synchronize(dev)
+
+    def run(self, stream: Optional[torch.cuda.Stream] = None) -> None:
+        """One launch of the persistent kernel on ``stream`` (default: the current stream)."""
+        if self.num_tasks == 0:
+            return
+        self.epoch += 1
+        self._ps.epoch = self.epoch
+        rc = self._lib.maco_program_launch(ctypes.byref(self._ps), N.current_stream_ptr(stream))
+        N.check(rc, "maco_program_launch")
+
+    def reset_after_failure(self) -> None:
+        """Re-zeroes the control state after an aborted launch (events restart from epoch 0)."""
+        torch.cuda.synchronize(self.device)
+        self.d_events.zero_()
+        self.d_ctrl.zero_()
+        if self.mode == MODE_DYNAMIC:
+            self.d_heads.zero_(); self.d_tails.zero_()
+        self.epoch = 0
+        N.status(clear=True)
+
+    def tasks_completed(self) -> int:
+        return int(self.d_ctrl[1].item())
+
+    def trace_records(self) -> np.ndarray:
+        if self.d_trace is None:
+            return np.zeros(0, dtype=TRACE_DTYPE)
+        return self.d_trace.cpu().numpy().view(TRACE_DTYPE)[: self.num_tasks]
+
+    def stats(self) -> dict:
+        rec = self.trace_records()
+        if rec.size == 0:
+            return {}
+        rec = rec[rec["t_end_ns"] > 0]
+        if rec.size == 0:
+            return {}
+        t0, t1 = rec["t_start_ns"].min(), rec["t_end_ns"].max()
+        out = {"span_us": float(t1 - t0) / 1e3, "tasks": int(rec.size), "by_type": {}}
+        for ty in np.unique(rec["type"]):
+            sel = rec[rec["type"] == ty]
+            name = TaskType(int(ty)).name if int(ty) in TaskType._value2member_map_ else str(int(ty))
+            busy = (sel["t_end_ns"] - sel["t_start_ns"]).astype(np.float64)
+            out["by_type"][name] = {"count": int(sel.size), "busy_us": float(busy.sum()) / 1e3,
+                                    "wait_us": float(sel["wait_ns"].sum()) / 1e3, "mean_us": float(busy.mean()) / 1e3}
+        return out
+
+    def chrome_trace(self) -> List[dict]:
+        """Trace records as Chrome-trace events (one row per SM)."""
+        rec = self.trace_records()
+        rec = rec[rec["t_end_ns"] > 0]
+        if rec.size == 0:
+            return []
+        t0 = int(rec["t_start_ns"].min())
+        ev = []
+        for r in rec:
+            ty = int(r["type"])
+            name = TaskType(ty).name if ty in TaskType._value2member_map_ else str(ty)
+            ev.append({"name": name, "ph": "X", "pid": 0, "tid": int(r["sm"]), "ts": (int(r["t_start_ns"]) - t0) / 1e3,
+                       "dur": (int(r["t_end_ns"]) - int(r["t_start_ns"])) / 1e3, "args": {"task": int(r["task"]),
+                                                                                         "wait_us": int(r["wait_ns"]) / 1e3}})
+        return ev
+
+    def describe(self) -> str:
+        kind = "dynamic (scheduler CTA)" if self.mode == MODE_DYNAMIC else "static queues"
+        return (f"Persistent kernel: {self.num_tasks} tile tasks, {self.num_groups} dispatch groups, "
+                f"{self.num_events} events, {self.num_workers} workers ({self.num_comm_workers} comm), {kind}")
+
+
+# ---------------------------------------------------------------------------------------------------
+# TaskGraph lowering
+# ---------------------------------------------------------------------------------------------------
+_ELT_TYPES = {TaskType.GELU, TaskType.SILU, TaskType.SOFTMAX, TaskType.SCALE, TaskType.ADD, TaskType.SILU_GATE,
+              TaskType.RMSNORM, TaskType.LAYERNORM, TaskType.ROPE}
+_F16 = (torch.bfloat16, torch.float16)
+
+
+def _flat2d(t: torch.Tensor) -> Optional[torch.Tensor]:
+    if t.dim() == 0 or not t.is_contiguous():
+        return None
+    return t.view(-1, t.shape[-1])
+
+
+def _gemm_ok(node: TaskNode) -> bool:
+    ins = node.inputs
+    x, w = ins[0], ins[1]
+    if x.dtype not in _F16 or w.dtype != x.dtype:
+        return False
+    x2 = _flat2d(x)
+    if x2 is None or w.dim() != 2 or w.stride(1) != 1:
+        return False
+    out = node.outputs[0]
+    if not out.is_contiguous():
+        return False
+    for t in (x2, w):
+        if t.numel() and (t.data_ptr() % 16 or (t.stride(0) * 2) % 16):
+            return False
+    if out.numel() and (out.data_ptr() % 16 or (out.shape[-1] * 2) % 16):
+        return False
+    return True
+
+
+def can_lower(graph) -> bool:
+    """True when every node has a task form. Custom host callables and collectives over more than
+    one rank (outside the symmetric heap) are run by the stream runtime instead."""
+    from ..comm.process_group import get_world_size
+    if not graph._nodes:
+        return False
+    world = get_world_size()
+    for n in graph._nodes:
+        t = n.task_type
+        if t in (TaskType.LINEAR, TaskType.MATMUL):
+            if not _gemm_ok(n):
+                return False
+        elif t in _ELT_TYPES:
+            if any(not x.is_contiguous() for x in n.inputs + n.outputs) or n.inputs[0].dtype not in N.DTYPE_CODE:
+                return False
+            if any(x.dtype != n.inputs[0].dtype for x in n.inputs):
+                return False
+        elif t in (TaskType.ALLREDUCE, TaskType.BROADCAST, TaskType.NOP):
+            if world > 1:
+                return False
+        elif t in (TaskType.ALL_TO_ALL, TaskType.ALLGATHER, TaskType.REDUCE_SCATTER):
+            if world > 1 or any(not x.is_contiguous() for x in n.inputs + n.outputs):
+                return False
+        else:
+            return False
+    return True
+
+
+def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None) -> Program:
+    """Lowers a TaskGraph (dependencies already inferred) to a persistent-kernel program."""
+    import os
+    from ..config import config
+    mode = mode or os.environ.get("MACO_PERSISTENT_MODE", "static")
+    trace = config.profile if trace is None else trace
+    sms = torch.cuda.get_device_properties(graph.device).multi_processor_count
+    workers = min(graph.num_workers, sms - (1 if mode == "dynamic" else 0))
+    b = ProgramBuilder(graph.device, num_workers=workers, mode=mode, trace=trace)
+    produced: Dict[int, Tuple[TaskNode, RowEvents]] = {}       # node id -> events of its output
+
+    def ready_of(node: TaskNode, t: torch.Tensor, rows: int) -> Tuple[Optional[RowEvents], List[tuple]]:
+        """Row-aligned events for tensor ``t`` if one dependency produced exactly this view; every other
+        dependency becomes a whole-node wait."""
+        aligned, extra = None, []
+        for dep in node.depends_on:
+            ent = produced.get(dep._node_id)
+            if ent is None:
+                continue
+            dnode, ev = ent
+            o = dnode.outputs[0]
+            if (aligned is None and t is not None and o.data_ptr() == t.data_ptr() and o.numel() == t.numel()
+                    and ev.rows == rows and o.numel() > 0):
+                aligned = ev
+            else:
+                extra.append((ev.all_event[0], ev.all_event[1], ev.sys, False))
+        return aligned, extra
+
+    for node in graph._schedule.order if graph._schedule is not None else graph._nodes:
+        t = node.task_type
+        out = node.outputs[0] if node.outputs else None
+        if out is None or out.numel() == 0:
+            continue
+        if t in (TaskType.LINEAR, TaskType.MATMUL):
+            x2 = _flat2d(node.inputs[0])
+            w = node.inputs[1]
+            aligned, extra = ready_of(node, node.inputs[0], x2.shape[0])
+            act = node.attrs.get("activation")
+            bias = node.inputs[2] if node.attrs.get("has_bias") else None
+            ev = b.gemm(x2, w, out.view(-1, out.shape[-1]), trans_b=(t == TaskType.MATMUL), epilogue=act, bias=bias,
+                        a_ready=aligned, extra_waits=extra)
+            produced[node._node_id] = (node, ev)
+        elif t in _ELT_TYPES:
+            x = node.inputs[0]
+            cols = x.shape[-1]
+            rows = x.numel() // cols
+            kw = {}
+            in1 = node.inputs[1] if len(node.inputs) > 1 else None
+            in2 = node.inputs[2] if len(node.inputs) > 2 else None
+            if t in (TaskType.RMSNORM, TaskType.LAYERNORM):
+                kw["f0"] = node.attrs["eps"]
+            elif t == TaskType.SCALE:
+                kw["f0"] = node.attrs["factor"]
+            elif t == TaskType.ROPE:
+                tokens, heads, hd = x.shape
+                rows, cols = tokens * heads, hd
+                kw.update(i0=heads, i1=0)
+            aligned, extra = ready_of(node, x, rows)
+            readies = [aligned]
+            if t in (TaskType.ADD, TaskType.SILU_GATE) and in1 is not None:
+                # second operand: look for its own row-aligned producer among the remaining dependencies
+                for dep in node.depends_on:
+                    ent = produced.get(dep._node_id)
+                    if ent and ent[0].outputs[0].data_ptr() == in1.data_ptr() and ent[1].rows == rows and ent[1] is not aligned:
+                        readies.append(ent[1])
+                        extra = [e for e in extra if e[0] != ent[1].all_event[0]]
+                        break
+            ev = b.elementwise(int(t), x, out, in1=in1, in2=in2, rows=rows, cols=cols, in_ready=readies,
+                               extra_waits=extra, **kw)
+            produced[node._node_id] = (node, ev)
+        elif t in (TaskType.ALL_TO_ALL, TaskType.ALLGATHER, TaskType.REDUCE_SCATTER):
+            # world size 1: the collective degenerates to a copy
+            x = node.inputs[0]
+            cols = x.shape[-1] if x.dim() else 1
+            rows = x.numel() // max(1, cols)
+            aligned, extra = ready_of(node, x, rows)
+            ev = b.elementwise(300, x, out, rows=rows, cols=cols, in_ready=[aligned], extra_waits=extra)
+            produced[node._node_id] = (node, ev)
+        elif t in (TaskType.ALLREDUCE, TaskType.BROADCAST, TaskType.NOP):
+            # in place and a no-op at world size 1: consumers inherit the producers of the tensor
+            aligned, extra = ready_of(node, node.inputs[0] if node.inputs else None, -1)
+            waits = b.join(extra, 0)
+            e = b.new_event()
+            b.add_task(int(TaskType.NOP), b"", waits=waits, signals=[e])
+            produced[node._node_id] = (node, RowEvents(rows=-1, block=BM, row_events=[], all_event=(e, 1)))
+        else:
+            raise NotImplementedError(f"no task form for {t.name}")
+    return b.build()

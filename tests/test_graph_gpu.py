@@ -24,6 +24,8 @@ def _runtimes():
 def test_linear_chain(kind, dtype):
     if kind not in _runtimes():
         pytest.skip("runtime not built")
+    if kind == "persistent" and dtype == torch.float32:
+        pytest.skip("the persistent kernel's GEMM tasks are tcgen05 tiles: 16-bit inputs only")
     g = maco.TaskGraph(num_workers=8)
     x = torch.randn(32, 512, device="cuda", dtype=dtype)
     w1 = (torch.randn(1024, 512, device="cuda") / 512 ** 0.5).to(dtype)

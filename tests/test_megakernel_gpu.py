@@ -1,0 +1,126 @@
+"""The persistent task kernel: static and dynamic scheduling, tile-level dependencies, tracing,
+and the bounded-wait failure path (a wait that nothing satisfies returns a status; nothing hangs)."""
+import pytest
+import torch
+
+import maco_b200 as maco
+from maco_b200 import _native
+from tests.conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _mlp_program(mode, tokens=1024, hidden=1024, ffn=2048, workers=None, trace=False):
+    from maco_b200.ops import interleave_gate_up, megakernel as mk
+    dt = torch.bfloat16
+    x = torch.randn(tokens, hidden, device="cuda", dtype=dt)
+    nw = torch.randn(hidden, device="cuda", dtype=dt)
+    wg = torch.randn(ffn, hidden, device="cuda", dtype=dt) * 0.03
+    wu = torch.randn(ffn, hidden, device="cuda", dtype=dt) * 0.03
+    wd = torch.randn(hidden, ffn, device="cuda", dtype=dt) * 0.03
+    wgu = interleave_gate_up(wg, wu)
+    xn = torch.empty_like(x)
+    h = torch.empty(tokens, ffn, device="cuda", dtype=dt)
+    y = torch.empty(tokens, hidden, device="cuda", dtype=dt)
+    b = mk.ProgramBuilder(torch.device("cuda"), num_workers=workers, mode=mode, trace=trace)
+    e0 = b.elementwise(104, x, xn, in1=nw, rows=tokens, cols=hidden, f0=1e-6)
+    e1 = b.gemm(xn, wgu, h, epilogue="swiglu", a_ready=e0)
+    b.gemm(h, wd, y, epilogue="residual", aux=x, a_ready=e1)
+    prog = b.build()
+    xf = x.float()
+    nf = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()).to(dt).float()
+    hf = (torch.nn.functional.silu(nf @ wg.float().t()) * (nf @ wu.float().t())).to(dt).float()
+    ref = hf @ wd.float().t() + xf
+    return prog, y, ref
+
+
+@pytest.mark.parametrize("mode", ["static", "dynamic"])
+@pytest.mark.parametrize("workers", [None, 5])
+def test_fused_mlp_program(mode, workers):
+    prog, y, ref = _mlp_program(mode, workers=workers)
+    for _ in range(3):                      # re-execution: events are monotonic, nothing is reset
+        y.zero_()
+        prog.run()
+    torch.cuda.synchronize()
+    assert _native.status() == 0
+    assert_close(y, ref, torch.bfloat16)
+    assert prog.tasks_completed() == 3 * prog.num_tasks
+    assert "tile tasks" in prog.describe()
+
+
+def test_trace_and_stats():
+    prog, y, ref = _mlp_program("static", trace=True)
+    prog.run()
+    torch.cuda.synchronize()
+    st = prog.stats()
+    assert st["tasks"] == prog.num_tasks and "LINEAR" in st["by_type"] and "RMSNORM" in st["by_type"]
+    ev = prog.chrome_trace()
+    assert len(ev) == prog.num_tasks and all(e["dur"] >= 0 for e in ev)
+
+
+@pytest.mark.parametrize("mode", ["static", "dynamic"])
+def test_unsatisfied_wait_times_out_and_context_survives(mode):
+    """A task that waits on an event nothing signals: the kernel gives up after its budget, reports
+    TIMEOUT with the task and event, returns normally, and the device stays usable."""
+    from maco_b200.ops import megakernel as mk
+    x = torch.randn(256, 256, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros_like(x)
+    b = mk.ProgramBuilder(torch.device("cuda"), num_workers=4, mode=mode, wait_budget_ms=20.0)
+    orphan = b.new_event()
+    b.elementwise(105, x, out, rows=256, cols=256, extra_waits=[(orphan, 1, False, False)])
+    prog = b.build()
+    _native.status(clear=True)
+    prog.run()
+    torch.cuda.synchronize()                # returns: nothing hangs
+    st = _native.status(clear=True)
+    assert st & _native.STATUS_TIMEOUT
+    assert torch.all(out == 0)              # the blocked task never ran
+    prog.reset_after_failure()
+    # the context is intact: a normal program runs right after
+    prog2, y, ref = _mlp_program("static", tokens=256, hidden=256, ffn=512)
+    prog2.run()
+    torch.cuda.synchronize()
+    assert _native.status() == 0
+    assert_close(y, ref, torch.bfloat16)
+
+
+def test_graph_lowering_modes(monkeypatch):
+    for mode in ("static", "dynamic"):
+        monkeypatch.setenv("MACO_PERSISTENT_MODE", mode)
+        g = maco.TaskGraph()
+        x = torch.randn(300, 512, device="cuda", dtype=torch.float16)
+        w1 = torch.randn(768, 512, device="cuda", dtype=torch.float16) * 0.05
+        w2 = torch.randn(512, 768, device="cuda", dtype=torch.float16) * 0.05
+        a = g.linear(x, w1, activation="gelu")
+        b = g.linear(a.output, w2)
+        c = g.add(b.output, x)
+        s = g.softmax(c.output)
+        g.compile(runtime="persistent")
+        g.execute(); g.execute()
+        torch.cuda.synchronize()
+        F = torch.nn.functional
+        af = F.gelu(x.float() @ w1.float().t(), approximate="tanh").half().float()
+        cf = ((af @ w2.float().t()).half().float() + x.float()).half().float()
+        assert_close(s.output, torch.softmax(cf, -1), torch.float16)
+        assert "Persistent kernel" in g.summary()
+    assert _native.status() == 0
+
+
+def test_sm_scheduling_demo_barrier():
+    import ctypes
+    lib = _native.lib()
+    lib.maco_run_sm_scheduling_demo.restype = ctypes.c_float
+    lib.maco_run_sm_scheduling_demo.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                ctypes.c_void_p, ctypes.c_void_p]
+    n, ctas, tasks = 1 << 20, 8, 10
+    data = torch.ones(n, device="cuda")
+    order = torch.zeros(ctas * tasks, dtype=torch.int32, device="cuda")
+    ms = lib.maco_run_sm_scheduling_demo(data.data_ptr(), n, ctas, 128, tasks, order.data_ptr(), None)
+    assert ms > 0
+    ref = torch.ones(1, dtype=torch.float64)
+    for _ in range(tasks):
+        ref = (ref.float() * 1.5 + 0.1).double()
+    torch.testing.assert_close(data, torch.full_like(data, float(ref)), rtol=1e-5, atol=1e-5)
+    o = order.cpu().view(tasks, ctas)
+    assert all(sorted(row.tolist()) == list(range(ctas)) for row in o)   # every barrier round saw each CTA once
+    assert _native.status() == 0
