@@ -1,0 +1,294 @@
+#!/usr/bin/env python
+"""Headline benchmark: latency of the tensor-parallel SwiGLU MLP layer (forward), TP = number of GPUs.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Config (fixed total work, so scaling is "strong"): 8192 tokens, hidden 4096, ffn 14336, bf16,
+x ~ N(0,1), weights ~ N(0, 0.02), sequence-parallel input and output (all-gather -> GEMM in,
+GEMM -> reduce-scatter out), synthetic seeded data, random-init weights.
+
+Default arm: this package - the whole layer is one launch of the persistent kernel per rank.
+``--impl reference``: the unmodified reference package (installed under baseline/_ref) through its
+own API: TaskGraph.linear / custom + StreamRuntime for the GEMMs, maco.comm.patterns allgather /
+reduce_scatter (NCCL) for the collectives.
+
+Rank 0 prints exactly one JSON line. ``value`` is the device-timed layer latency in microseconds
+(CUDA events around K back-to-back steps, max over ranks); ``e2e`` is the same layer driven through
+the public API with, every step, the host->device copy of that step's input from pinned memory
+and a device->host read of a result metric inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import contextlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+TOKENS, HIDDEN, FFN = 8192, 4096, 14336
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="maco_b200", choices=["maco_b200", "reference"])
+    ap.add_argument("--mode", default=os.environ.get("MACO_PERSISTENT_MODE", "static"), choices=["static", "dynamic"])
+    ap.add_argument("--tokens", type=int, default=TOKENS)
+    ap.add_argument("--hidden", type=int, default=HIDDEN)
+    ap.add_argument("--ffn", type=int, default=FFN)
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, f"/tmp/maco_bench_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.05)
+        self.proc.terminate()          # the exact child started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 8:
+                    continue
+                try:
+                    sm.append(float(f[0])); mx.append(float(f[1]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, f[4:8]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def maybe_relaunch(args):
+    """`python bench.py --gpus N` with N > 1 outside torchrun: start the ranks ourselves."""
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 2000), os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+
+
+def timed_region(torch, dist, world, steps, step_fn, sampler=None):
+    """K steps between CUDA events, barrier + synchronize on both sides; returns max-over-ranks ms."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step_fn()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, clocks
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    rank, local_rank, world = dist_env()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    sys.path.insert(0, REPO)
+    import maco_b200 as maco
+    from maco_b200 import _native
+    from maco_b200.models.tp_mlp import TPSwiGLUMLP
+    from maco_b200.parallel import symm_heap
+    heap = None
+    if world > 1:
+        act = args.tokens * args.hidden * 2
+        maco.config.set(comm_buffer_size=str(int(act * (2 + 1.0 / world)) + (64 << 20)), backend="peer")
+        maco.init(backend="nccl")
+        heap = symm_heap.current_heap()
+    layer = TPSwiGLUMLP(args.tokens, args.hidden, args.ffn, rank=rank, world=world, heap=heap, seed=0, mode=args.mode)
+    rows = args.tokens // world
+    g = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    x_host = torch.randn(rows, args.hidden, generator=g).to(torch.bfloat16).pin_memory()
+    layer.x_shard.copy_(x_host)
+    metric_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+    def step():
+        layer.forward(None)
+
+    def step_e2e():
+        y = layer.forward(x_host)                     # H2D copy of this step's input, then one launch
+        metric_host.copy_(y[0, :1].float(), non_blocking=True)
+        torch.cuda.current_stream().synchronize()     # the host has the result of this step
+
+    for _ in range(args.warmup):
+        step()
+    ms, clocks = timed_region(torch, dist, world, args.steps, step, ClockSampler(local_rank) if rank == 0 else None)
+    for _ in range(max(3, args.warmup // 2)):
+        step_e2e()
+    ms_e2e, _ = timed_region(torch, dist, world, args.steps, step_e2e)
+    status = _native.status(clear=False)
+    us = ms * 1e3 / args.steps
+    us_e2e = ms_e2e * 1e3 / args.steps
+    flops = 2.0 * args.tokens * args.hidden * args.ffn * 3
+    if rank == 0:
+        print(json.dumps({
+            "metric": "layer latency (us, device-timed, max over ranks)", "value": round(us, 2), "unit": "us",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5),
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "maco_b200",
+            "config": {"model": "TP SwiGLU MLP forward (all-gather->GEMM, GEMM->reduce-scatter)", "global_batch": args.tokens,
+                       "seq_len": args.tokens, "hidden": args.hidden, "ffn": args.ffn, "parallelism": f"tp{world}",
+                       "l2": "per-GPU working set (activations + weights) exceeds the 126 MB L2; no flush",
+                       "scheduler": args.mode},
+            "tflops_per_gpu": round(flops / world / (us * 1e-6) / 1e12, 1),
+            "clocks": clocks,
+            "e2e": {"value": round(us_e2e, 2), "unit": "us", "h2d_bytes_per_step": x_host.numel() * 2,
+                    "d2h_bytes_per_step": 4},
+            "gpu_launches": args.steps,
+            "kernel_status": status,
+        }), flush=True)
+    if world > 1:
+        maco.cleanup()
+
+
+def run_reference(args):
+    ref_dir = os.path.join(REPO, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "maco")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/maco is not installed"}), flush=True)
+        return
+    import torch
+    import torch.distributed as dist
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    sys.path.insert(0, ref_dir)
+    with contextlib.redirect_stdout(sys.stderr):          # the reference prints banners on stdout
+        import maco
+        if world > 1:
+            maco.init(backend="nccl")
+        from maco.comm import patterns
+    dev = torch.device("cuda", local_rank)
+    dt = torch.bfloat16
+    rows, f_local = args.tokens // world, args.ffn // world
+    g = torch.Generator(device="cpu").manual_seed(1000 * 0 + rank)
+    mk = lambda *s: (torch.randn(*s, generator=g) * 0.02).to(dt).to(dev)
+    w_gate, w_up, w_down = mk(f_local, args.hidden), mk(f_local, args.hidden), mk(args.hidden, f_local)
+    gx = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    x_host = torch.randn(rows, args.hidden, generator=gx).to(dt).pin_memory()
+    x_shard = x_host.to(dev)
+    x_full = torch.empty(args.tokens, args.hidden, device=dev, dtype=dt)
+    h = torch.empty(args.tokens, f_local, device=dev, dtype=dt)
+    with contextlib.redirect_stdout(sys.stderr):
+        graph = maco.TaskGraph(num_workers=8)
+        t_gate = graph.linear(x_full, w_gate, name="gate")
+        t_up = graph.linear(x_full, w_up, name="up")
+        graph.custom(lambda a, b: torch.nn.functional.silu(a) * b, [t_gate.output, t_up.output], [h], name="swiglu")
+        t_down = graph.linear(h, w_down, name="down")
+        graph.compile()
+    metric_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+    def step():
+        if world > 1:
+            x_full.copy_(patterns.allgather(x_shard).view(args.tokens, args.hidden))
+        else:
+            x_full.copy_(x_shard)
+        graph.execute()
+        return patterns.reduce_scatter(t_down.output) if world > 1 else t_down.output
+
+    def step_e2e():
+        x_shard.copy_(x_host, non_blocking=True)
+        y = step()
+        metric_host.copy_(y[0, :1].float(), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    with contextlib.redirect_stdout(sys.stderr):
+        for _ in range(args.warmup):
+            step()
+        ms, clocks = timed_region(torch, dist, world, args.steps, step, ClockSampler(local_rank) if rank == 0 else None)
+        for _ in range(max(3, args.warmup // 2)):
+            step_e2e()
+        ms_e2e, _ = timed_region(torch, dist, world, args.steps, step_e2e)
+    us, us_e2e = ms * 1e3 / args.steps, ms_e2e * 1e3 / args.steps
+    flops = 2.0 * args.tokens * args.hidden * args.ffn * 3
+    if rank == 0:
+        print(json.dumps({
+            "metric": "layer latency (us, device-timed, max over ranks)", "value": round(us, 2), "unit": "us",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5),
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "reference",
+            "config": {"model": "TP SwiGLU MLP forward (all-gather->GEMM, GEMM->reduce-scatter)", "global_batch": args.tokens,
+                       "seq_len": args.tokens, "hidden": args.hidden, "ffn": args.ffn, "parallelism": f"tp{world}",
+                       "l2": "per-GPU working set (activations + weights) exceeds the 126 MB L2; no flush",
+                       "path": "reference TaskGraph + StreamRuntime (torch.mm) + maco.comm.patterns (NCCL)"},
+            "tflops_per_gpu": round(flops / world / (us * 1e-6) / 1e12, 1),
+            "clocks": clocks,
+            "e2e": {"value": round(us_e2e, 2), "unit": "us", "h2d_bytes_per_step": x_host.numel() * 2,
+                    "d2h_bytes_per_step": 4},
+            "gpu_launches": 0,
+        }), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    maybe_relaunch(args)
+    if args.impl == "reference":
+        try:
+            run_reference(args)
+        except Exception as exc:  # the arm must not take the round down
+            rank, _, _ = dist_env()
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"}), flush=True)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -389,7 +389,9 @@ class Program:
         # events live in the symmetric heap when peers must reach them
         self.num_events = max(1, b.num_events)
         if b.heap is not None:
-            self.d_events = b.heap.alloc((self.num_events + 64,), torch.int32, zero=True)
+            # Not cleared here: heap memory is zero from creation and never recycled for events, and a
+            # peer that built this program earlier may already have bumped these counters.
+            self.d_events = b.heap.alloc((self.num_events + 64,), torch.int32)
         else:
             self.d_events = torch.zeros(self.num_events + 64, dtype=torch.int32, device=dev)
         self.d_ctrl = torch.zeros(8, dtype=torch.int32, device=dev)        # [0] abort word, [1] task counter

@@ -1,0 +1,166 @@
+"""Fused compute + collective task patterns for the persistent kernel.
+
+Each helper appends tasks to a ``ProgramBuilder`` so that the transfer over NVLink overlaps the
+tensor-core tiles inside ONE kernel, tile by tile:
+
+* ``allgather_push``        shard rows are pushed into every rank's gathered buffer in chunks; each
+                            128-row block of the gathered buffer has its own event, so a GEMM tile
+                            starts as soon as the rows it reads have landed (all-gather -> GEMM).
+* ``gemm_reduce_scatter``   the GEMM epilogue stores each partial tile straight into the staging slot
+                            of the rank that owns those rows and bumps that rank's per-block counter;
+                            the owner sums the slots when the counter is full (GEMM -> reduce-scatter).
+* ``allreduce_tasks``       two-shot all-reduce in chunks: the chunk's owner pulls it from every rank,
+                            reduces in fp32 and writes the result back to every rank.
+* ``epoch_fence``           end-of-launch signal that keeps a faster rank's next launch from
+                            overwriting buffers a slower rank still reads.
+
+The reference has no such path: its tensor-parallel example all-reduces a column-parallel output
+(examples/tensor_parallel.py:55-61) and every collective is a separate NCCL call.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import _native as N
+from ..ops.megakernel import (BM, COMM_ALLREDUCE, COMM_PUSH, COMM_REDUCE_LOCAL, ProgramBuilder, RowEvents, _pack_comm)
+from ..task_graph.nodes import TaskType
+
+
+def epoch_fence_event(b: ProgramBuilder) -> Tuple[int, int, bool, bool]:
+    """Allocates the cross-rank "previous launch finished everywhere" condition: an event every
+    rank bumps once at the end of a launch; waited on with the previous epoch's threshold."""
+    ev = b.new_event()
+    b._fence_event = ev
+    return (ev, b.heap.world, True, True)
+
+
+def epoch_fence_signal(b: ProgramBuilder, waits: Sequence[Tuple[int, int, bool, bool]]) -> None:
+    """Final task of a program: when ``waits`` hold, tell every rank this rank is done."""
+    waits = b.join(list(waits))
+    b.add_task(int(TaskType.NOP), b"", waits=waits, signal_peer=-2, signal_peer_event=b._fence_event)
+
+
+def allgather_push(b: ProgramBuilder, shard: torch.Tensor, gathered: torch.Tensor, *, chunk_rows: int = 32,
+                   fence: Optional[Tuple[int, int, bool, bool]] = None,
+                   src_ready: Optional[RowEvents] = None) -> RowEvents:
+    """Pushes this rank's ``shard`` [rows, cols] into rows ``[rank*rows, (rank+1)*rows)`` of every
+    rank's ``gathered`` [world*rows, cols]. Returns row-block events of ``gathered``."""
+    heap = b.heap
+    rank, world = heap.rank, heap.world
+    rows, cols = shard.shape
+    if rows % BM:
+        raise ValueError("all-gather shards must be a multiple of 128 rows")
+    if BM % chunk_rows:
+        raise ValueError("chunk_rows must divide 128")
+    row_bytes = cols * shard.element_size()
+    s_off, g_off = heap.offset_of(shard), heap.offset_of(gathered)
+    blocks = world * rows // BM
+    events = [b.new_event() for _ in range(blocks)]
+    all_ev = b.new_event()
+    per_block = BM // chunk_rows
+    for c0 in range(0, rows, chunk_rows):
+        waits = []
+        if fence is not None:
+            waits.append(fence)
+        if src_ready is not None:
+            ev, cnt = src_ready.for_rows(c0, c0 + chunk_rows)
+            waits.append((ev, cnt, src_ready.sys, False))
+        grow = rank * rows + c0
+        raw = _pack_comm(s_off + c0 * row_bytes, g_off + grow * row_bytes, row_bytes, row_bytes, row_bytes, chunk_rows,
+                         N.DTYPE_CODE[shard.dtype], -3, COMM_PUSH)
+        b.add_task(int(TaskType.ALLGATHER), raw, waits=waits, signal_peer=-2, signal_peer_event=events[grow // BM],
+                   comm_worker=True)
+    b.keepalive += [shard, gathered]
+    return RowEvents(rows=world * rows, block=BM, row_events=[(e, per_block) for e in events],
+                     all_event=(all_ev, 0), sys=True)
+
+
+def rotated_blocks(rank: int, world: int, blocks_per_rank: int) -> List[int]:
+    """Row blocks ordered own shard first, then rank+1, rank+2, ...: the order data arrives in and
+    the order in which partial results should leave, so that at any moment the ranks talk to
+    different peers."""
+    out: List[int] = []
+    for k in range(world):
+        r = (rank + k) % world
+        out += list(range(r * blocks_per_rank, (r + 1) * blocks_per_rank))
+    return out
+
+
+def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, staging: torch.Tensor,
+                        out: torch.Tensor, *, a_ready: Optional[RowEvents] = None, bn: int = 256,
+                        reduce_rows: int = 32, scale: float = 1.0) -> Tuple[RowEvents, RowEvents]:
+    """``out[rows_local, N] = reduce_scatter(a @ w.T)`` with the partial tiles leaving through the
+    GEMM epilogue. ``staging`` is a heap tensor [world, rows_local, N] (slot = source rank).
+    Returns (events of the GEMM tiles, events of ``out``)."""
+    heap = b.heap
+    rank, world = heap.rank, heap.world
+    M, K = a.shape
+    Nn = w.shape[0]
+    rows_local = M // world
+    if M % (world * BM):
+        raise ValueError("rows must be a multiple of world * 128")
+    blocks_per_rank = rows_local // BM
+    n_tiles = (Nn + bn - 1) // bn
+    st_off = heap.offset_of(staging)
+    slot_bytes = rows_local * Nn * staging.element_size()
+    part_events = [b.new_event() for _ in range(blocks_per_rank)]
+
+    def per_tile(mb: int, nb: int) -> dict:
+        owner = mb // blocks_per_rank
+        return dict(peer=owner, out_off=st_off + rank * slot_bytes, row_off=-(owner * rows_local), signal_peer=owner,
+                    signal_peer_event=part_events[mb % blocks_per_rank])
+
+    gemm_ev = b.gemm(a, w, staging[0], a_ready=a_ready, bn=bn, per_tile=per_tile,
+                     m_blocks=rotated_blocks(rank, world, blocks_per_rank))
+    # owner-side reduction of the `world` slots, fp32 accumulation
+    row_bytes = Nn * staging.element_size()
+    out_events = [b.new_event() for _ in range(blocks_per_rank)]
+    all_ev = b.new_event()
+    total = 0
+    for j in range(blocks_per_rank):
+        for r0 in range(j * BM, (j + 1) * BM, reduce_rows):
+            raw = _pack_comm(st_off + r0 * row_bytes, 0, row_bytes, row_bytes, row_bytes, reduce_rows,
+                             N.DTYPE_CODE[staging.dtype], -1, COMM_REDUCE_LOCAL, nslots=world, slot_stride=slot_bytes,
+                             local_ptr=out.data_ptr() + r0 * out.stride(0) * out.element_size(), scale=scale)
+            b.add_task(int(TaskType.REDUCE_SCATTER), raw, waits=[(part_events[j], world * n_tiles, True, False)],
+                       signals=[out_events[j], all_ev])
+            total += 1
+    b.keepalive += [staging, out]
+    per_block = BM // reduce_rows
+    return gemm_ev, RowEvents(rows=rows_local, block=BM, row_events=[(e, per_block) for e in out_events],
+                              all_event=(all_ev, total))
+
+
+def allreduce_tasks(b: ProgramBuilder, buf: torch.Tensor, *, avg: bool = False, chunk_bytes: int = 1 << 20,
+                    ready_waits: Sequence[Tuple[int, int, bool, bool]] = (),
+                    ready_event: Optional[int] = None, comm_worker: bool = True) -> Tuple[int, int]:
+    """In-place all-reduce of heap tensor ``buf`` in chunks. Chunk c is owned by rank c % world, which
+    pulls it from every rank, reduces and writes it back everywhere. ``ready_event`` (bumped once
+    by every rank when its data is complete) gates the pulls; when None a NOP task with
+    ``ready_waits`` announces readiness. Returns (completion event, count) local to every rank."""
+    heap = b.heap
+    rank, world = heap.rank, heap.world
+    nbytes = buf.numel() * buf.element_size()
+    if nbytes % 16:
+        raise ValueError("all-reduce buffers must be a multiple of 16 bytes")
+    off = heap.offset_of(buf)
+    if ready_event is None:
+        ready_event = b.new_event()
+        b.add_task(int(TaskType.NOP), b"", waits=b.join(list(ready_waits)), signal_peer=-2, signal_peer_event=ready_event)
+    done = b.new_event()
+    row = 16384 if nbytes >= 16384 and nbytes % 16384 == 0 else 16
+    chunk_bytes = max(row, chunk_bytes // row * row)
+    n_chunks = (nbytes + chunk_bytes - 1) // chunk_bytes
+    for c in range(n_chunks):
+        if c % world != rank:
+            continue
+        c0 = c * chunk_bytes
+        cb = min(chunk_bytes, nbytes - c0)
+        raw = _pack_comm(off + c0, off + c0, row, row, row, cb // row, N.DTYPE_CODE[buf.dtype], -1, COMM_ALLREDUCE,
+                         scale=(1.0 / world if avg else 1.0))
+        b.add_task(int(TaskType.ALLREDUCE), raw, waits=[(ready_event, world, True, False)], signal_peer=-2,
+                   signal_peer_event=done, comm_worker=comm_worker)
+    b.keepalive.append(buf)
+    return done, n_chunks

@@ -159,5 +159,7 @@ def destroy_heap() -> None:
             barrier()
         except Exception:
             pass
+        from . import collectives
+        collectives.clear_cache()
         _current.close()
         _current = None

@@ -1,0 +1,101 @@
+"""Peer-memory collectives and the fused tensor-parallel layer on 2 GPUs (one process per GPU)."""
+import pytest
+import torch
+
+from tests._dist import run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+ENV = {"NCCL_NVLS_ENABLE": "0"}
+
+
+def _setup(rank, world, heap_mb=256):
+    import maco_b200 as maco
+    maco.config.set(comm_buffer_size=f"{heap_mb}MB", backend="peer")
+    maco.init(backend="nccl")
+    from maco_b200.parallel import symm_heap
+    return maco, symm_heap.current_heap()
+
+
+def _collectives(rank, world):
+    maco, heap = _setup(rank, world)
+    from maco_b200 import _native
+    from maco_b200.parallel import collectives
+    assert heap is not None and heap.world == world and maco.is_nvshmem_available()
+    # all-reduce, closed form P(P+1)/2; repeated to exercise the epoch logic
+    for dtype, n in ((torch.float32, 1 << 20), (torch.bfloat16, 3 << 16)):
+        t = heap.alloc((n,), dtype)
+        for it in range(3):
+            t.fill_(float(rank + 1))
+            collectives.all_reduce(t)
+            torch.cuda.synchronize()
+            assert torch.all(t.float() == world * (world + 1) / 2), (dtype, it)
+    t = heap.alloc((4096,), torch.float32)
+    t.fill_(float(rank + 1))
+    collectives.all_reduce(t, avg=True)
+    torch.cuda.synchronize()
+    assert torch.allclose(t, torch.full_like(t, (world + 1) / 2))
+    # through the public patterns API and the nvshmem-compatible names
+    from maco_b200.comm import patterns
+    u = heap.alloc((1000 * 8,), torch.float32)
+    u.fill_(float(rank))
+    patterns.allreduce(u)
+    torch.cuda.synchronize()
+    assert torch.all(u == sum(range(world)))
+    v = torch.full((333,), float(rank + 1), device="cuda")          # outside the heap, odd size
+    maco.nvshmem_allreduce(v)
+    torch.cuda.synchronize()
+    assert torch.all(v == world * (world + 1) / 2)
+    maco.nvshmem_barrier()
+    # all-gather
+    shard = heap.alloc((256, 512), torch.bfloat16)
+    full = heap.alloc((256 * world, 512), torch.bfloat16)
+    shard.fill_(float(rank + 1))
+    collectives.all_gather(shard, full)
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert torch.all(full[r * 256:(r + 1) * 256].float() == r + 1)
+    # 4-D Ulysses exchange, value-checked, and its inverse
+    B, s, H, D = 2, 8, 4 * world, 64
+    whole = torch.arange(B * s * world * H * D, dtype=torch.float32, device="cuda").reshape(B, s * world, H, D)
+    mine = heap.alloc((B, s, H, D), torch.float32)
+    mine.copy_(whole[:, rank * s:(rank + 1) * s])
+    y = collectives.all_to_all_4d(mine, 2, 1)
+    torch.cuda.synchronize()
+    hp = H // world
+    assert torch.equal(y, whole[:, :, rank * hp:(rank + 1) * hp])
+    z = collectives.all_to_all_4d(y, 1, 2)
+    torch.cuda.synchronize()
+    assert torch.equal(z, mine)
+    assert _native.status() == 0
+    maco.cleanup()
+
+
+def test_peer_collectives():
+    run_ranks(_collectives, 2, env=ENV, timeout=240)
+
+
+def _tp_mlp(rank, world):
+    maco, heap = _setup(rank, world, heap_mb=128)
+    import torch.distributed as dist
+    from maco_b200 import _native
+    from maco_b200.models.tp_mlp import TPSwiGLUMLP
+    tokens, hidden, ffn = 1024, 1024, 2048
+    layer = TPSwiGLUMLP(tokens, hidden, ffn, rank=rank, world=world, heap=heap, seed=3)
+    torch.manual_seed(7)
+    x_full = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)      # same on every rank
+    rows = tokens // world
+    partial = layer.reference(x_full)
+    dist.all_reduce(partial)
+    ref = partial[rank * rows:(rank + 1) * rows]
+    for it in range(3):
+        y = layer(x_full[rank * rows:(rank + 1) * rows])
+        torch.cuda.synchronize()
+        err = (y.float() - ref).abs().max().item()
+        assert err < 3e-2 * max(1.0, ref.abs().max().item()), (it, err)
+    assert _native.status() == 0
+    maco.cleanup()
+
+
+def test_fused_tp_mlp_matches_reference():
+    run_ranks(_tp_mlp, 2, env=ENV, timeout=240)
