@@ -91,13 +91,14 @@ MACO_DEVICE float elt_apply(uint32_t type, float x, float y, const MacoEltArgs& 
     case MACO_TASK_ADD: return x + y;
     case MACO_TASK_SILU_GATE: return silu(x) * y;
     case MACO_TASK_GELU_BWD: return x * gelu_tanh_grad(y);
+    case MACO_TASK_AXPBY: return a.f0 * x + a.f1 * y;
     case MACO_TASK_COPY: return x;
     default: return x;
   }
 }
 
 MACO_DEVICE bool elt_is_binary(uint32_t type) {
-  return type == MACO_TASK_ADD || type == MACO_TASK_SILU_GATE || type == MACO_TASK_GELU_BWD;
+  return type == MACO_TASK_ADD || type == MACO_TASK_SILU_GATE || type == MACO_TASK_GELU_BWD || type == MACO_TASK_AXPBY;
 }
 
 MACO_DEVICE void elt_pointwise(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
@@ -250,7 +251,7 @@ MACO_DEVICE void elt_qknorm_rope(const MacoEltArgs& a, int tid, int nthreads) {
 MACO_DEVICE bool elt_run(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
   switch (type) {
     case MACO_TASK_GELU: case MACO_TASK_SILU: case MACO_TASK_SCALE: case MACO_TASK_ADD:
-    case MACO_TASK_SILU_GATE: case MACO_TASK_GELU_BWD: case MACO_TASK_COPY:
+    case MACO_TASK_SILU_GATE: case MACO_TASK_GELU_BWD: case MACO_TASK_COPY: case MACO_TASK_AXPBY:
       elt_pointwise(type, a, tid, nthreads); return true;
     case MACO_TASK_RMSNORM: case MACO_TASK_LAYERNORM: case MACO_TASK_SOFTMAX:
       elt_rowwise(type, a, tid, nthreads); return true;

@@ -35,6 +35,7 @@ enum MacoTaskType {
   MACO_TASK_SCALE = 112,
   MACO_TASK_ADD = 113,
   MACO_TASK_GELU_BWD = 114,
+  MACO_TASK_AXPBY = 115,         /* out = f0 * in0 + f1 * in1 */
   MACO_TASK_CUSTOM_COMPUTE = 150,
   MACO_TASK_ALLREDUCE = 200,     /* reduce one chunk over all peers' buffers, write to all */
   MACO_TASK_ALLGATHER = 201,     /* push one chunk of the local shard to every peer */

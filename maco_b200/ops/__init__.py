@@ -1,7 +1,8 @@
 """CUDA operators of the package (stand-alone launches of the kernels under csrc/)."""
-from .elementwise import (add, gelu, gelu_bwd, layernorm, qknorm_rope, rmsnorm, rope, scale, silu, silu_gate,
+from .attention import attention_decode
+from .elementwise import (add, axpby, gelu, gelu_bwd, layernorm, qknorm_rope, rmsnorm, rope, scale, silu, silu_gate,
                           softmax)
 from .gemm import gemm, interleave_gate_up, linear, matmul
 
-__all__ = ["gemm", "linear", "matmul", "interleave_gate_up", "gelu", "silu", "softmax", "scale", "add", "silu_gate",
-           "gelu_bwd", "rmsnorm", "layernorm", "rope", "qknorm_rope"]
+__all__ = ["attention_decode", "gemm", "linear", "matmul", "interleave_gate_up", "gelu", "silu", "softmax", "scale", "add", "silu_gate",
+           "gelu_bwd", "axpby", "rmsnorm", "layernorm", "rope", "qknorm_rope"]

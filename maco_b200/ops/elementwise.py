@@ -13,7 +13,7 @@ import torch
 from .. import _native as N
 
 T_LAYERNORM, T_RMSNORM, T_GELU, T_SILU, T_SOFTMAX, T_SILU_GATE, T_ROPE = 103, 104, 105, 106, 107, 108, 109
-T_SCALE, T_ADD, T_GELU_BWD, T_COPY = 112, 113, 114, 300
+T_SCALE, T_ADD, T_GELU_BWD, T_AXPBY, T_COPY = 112, 113, 114, 115, 300
 
 _declared = False
 
@@ -66,6 +66,7 @@ def scale(x, factor: float, out=None): return _launch(T_SCALE, x, out=out, f0=fa
 def add(a, b, out=None): return _launch(T_ADD, a, in1=b, out=out)
 def silu_gate(gate, up, out=None): return _launch(T_SILU_GATE, gate, in1=up, out=out)
 def gelu_bwd(dy, pre, out=None): return _launch(T_GELU_BWD, dy, in1=pre, out=out)
+def axpby(x, y, a: float, b: float, out=None): return _launch(T_AXPBY, x, in1=y, out=out, f0=a, f1=b)
 def rmsnorm(x, weight, eps: float = 1e-6, out=None): return _launch(T_RMSNORM, x, in1=weight, out=out, f0=eps)
 def layernorm(x, weight, bias, eps: float = 1e-5, out=None):
     return _launch(T_LAYERNORM, x, in1=weight, in2=bias, out=out, f0=eps)

@@ -32,6 +32,7 @@ class TaskType(IntEnum):
     SCALE = 112
     ADD = 113
     GELU_BWD = 114
+    AXPBY = 115
     CUSTOM_COMPUTE = 150
     # communication: 200 <= v < 300
     ALLREDUCE = 200

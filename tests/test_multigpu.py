@@ -99,3 +99,27 @@ def _tp_mlp(rank, world):
 
 def test_fused_tp_mlp_matches_reference():
     run_ranks(_tp_mlp, 2, env=ENV, timeout=240)
+
+
+def _dp_backward(rank, world):
+    maco, heap = _setup(rank, world, heap_mb=192)
+    import torch.distributed as dist
+    from maco_b200 import _native
+    from maco_b200.models.dp_mlp_stack import DPMLPStackBackward
+    m = DPMLPStackBackward(layers=3, hidden=512, tokens=1024, rank=rank, world=world, heap=heap, seed=5, weight_std=0.05,
+                           comm_workers=4)
+    ref = m.reference_grads()
+    dist.all_reduce(ref)
+    ref /= world
+    for it in range(2):
+        m.forward()
+        grads = m.backward()
+        torch.cuda.synchronize()
+        err = (grads - ref).abs().max().item()
+        assert err < 3e-2 * ref.abs().max().item() + 1e-7, (it, err, ref.abs().max().item())
+    assert _native.status() == 0
+    maco.cleanup()
+
+
+def test_dp_backward_with_tilewise_allreduce():
+    run_ranks(_dp_backward, 2, env=ENV, timeout=240)

@@ -106,3 +106,19 @@ def test_rope_and_qknorm_rope():
     xn = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
     cs = torch.cat([cos, sin], -1)
     assert_close(ops.qknorm_rope(x, w, cs, 1e-6), rope_reference(xn, cos, sin), torch.bfloat16)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("cfg", [(4, 8, 1, 1000, 4), (2, 16, 2, 4097, None), (3, 4, 4, 130, 1)])
+def test_attention_decode(dtype, cfg):
+    ops = _ops()
+    B, Hq, Hkv, S, splits = cfg
+    q = torch.randn(B, Hq, 128, device="cuda", dtype=dtype)
+    k = torch.randn(B, Hkv, S, 128, device="cuda", dtype=dtype)
+    v = torch.randn(B, Hkv, S, 128, device="cuda", dtype=dtype)
+    out = ops.attention_decode(q, k, v, splits=splits)
+    G = Hq // Hkv
+    qf = q.float().view(B, Hkv, G, 128)
+    s = torch.einsum("bhgd,bhsd->bhgs", qf, k.float()) * 128 ** -0.5
+    ref = torch.einsum("bhgs,bhsd->bhgd", torch.softmax(s, -1), v.float()).reshape(B, Hq, 128)
+    assert_close(out, ref, dtype)
