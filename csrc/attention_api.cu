@@ -94,3 +94,64 @@ int maco_attention_decode(const void* q, const void* k, const void* v, void* out
 }
 
 }  // extern "C"
+
+// ---- no-allocation variant ---------------------------------------------------------------------
+// See maco_no_alloc.h for the contract. The scratch of the split-KV partials lives in this
+// file-scope device array; the name below is only a host-side handle for it, so host code asks the
+// runtime for the real device address once per device and hands that pointer to the kernels.
+#include "maco_no_alloc.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_static_attn_scratch[MACO_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+namespace {
+std::mutex g_static_mu;
+float* g_static_ptr[64] = {};
+
+// Device address of the static scratch on the current device (looked up on first use).
+int static_scratch_ptr(float** out) {
+  int dev = 0;
+  MACO_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) { maco_host::set_error("attention_decode_static: device index out of range"); return -1; }
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_attn_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      maco_host::set_error(std::string("attention_decode_static: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
+      return -1;
+    }
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int maco_attention_decode_static(const void* q, const void* k, const void* v, void* out, int B, int Hq,
+                                            int Hkv, int S, int head_dim, int splits, int dtype,
+                                            long long kv_batch_stride, long long kv_head_stride, float scale,
+                                            void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AttnParams p;
+  int rc = check_and_fill(p, q, k, v, out, nullptr, B, Hq, Hkv, S, head_dim, splits, dtype, kv_batch_stride,
+                          kv_head_stride, scale);
+  if (rc != 0) return rc;
+  const unsigned long long need = maco_attention_decode_scratch_bytes(B, Hq, Hkv, splits);
+  if (need > MACO_STATIC_SCRATCH_BYTES) {
+    char buf[200];
+    snprintf(buf, sizeof buf,
+             "attention_decode_static: needs %llu bytes of scratch, the built-in array holds %u; use fewer splits "
+             "or maco_attention_decode with your own scratch", need, (unsigned)MACO_STATIC_SCRATCH_BYTES);
+    maco_host::set_error(buf);
+    return -3;
+  }
+  float* scratch = nullptr;
+  rc = static_scratch_ptr(&scratch);
+  if (rc != 0) return rc;
+  p.scratch = scratch;
+  attn_decode_kernel<<<B * Hkv * splits, 128, 0, stream>>>(p);
+  attn_merge_kernel<<<B * Hkv, 128, 0, stream>>>(p);
+  MACO_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
