@@ -177,7 +177,7 @@ def run_ours(args):
     us_e2e = ms_e2e * 1e3 / args.steps
     flops = 2.0 * args.tokens * args.hidden * args.ffn * 3
     if rank == 0:
-        print(json.dumps({
+        emit(({
             "metric": "layer latency (us, device-timed, max over ranks)", "value": round(us, 2), "unit": "us",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5),
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -192,7 +192,7 @@ def run_ours(args):
                     "d2h_bytes_per_step": 4},
             "gpu_launches": args.steps,
             "kernel_status": status,
-        }), flush=True)
+        }))
     if world > 1:
         maco.cleanup()
 
@@ -200,7 +200,7 @@ def run_ours(args):
 def run_reference(args):
     ref_dir = os.path.join(REPO, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_dir, "maco")):
-        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/maco is not installed"}), flush=True)
+        emit({"impl": "reference", "unavailable": "baseline/_ref/maco is not installed"})
         return
     import torch
     import torch.distributed as dist
@@ -256,7 +256,7 @@ def run_reference(args):
     us, us_e2e = ms * 1e3 / args.steps, ms_e2e * 1e3 / args.steps
     flops = 2.0 * args.tokens * args.hidden * args.ffn * 3
     if rank == 0:
-        print(json.dumps({
+        emit(({
             "metric": "layer latency (us, device-timed, max over ranks)", "value": round(us, 2), "unit": "us",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5),
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -270,22 +270,36 @@ def run_reference(args):
             "e2e": {"value": round(us_e2e, 2), "unit": "us", "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": 4},
             "gpu_launches": 0,
-        }), flush=True)
+        }))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
+_REAL_STDOUT = None
+
+
+def emit(obj) -> None:
+    """Writes the one JSON line to the real stdout (fd 1 is pointed at stderr while the benchmark runs,
+    because native libraries such as NCCL print banners straight to fd 1)."""
+    line = json.dumps(obj) + "\n"
+    os.write(_REAL_STDOUT if _REAL_STDOUT is not None else 1, line.encode())
+
+
 def main():
+    global _REAL_STDOUT
     args = parse_args()
     maybe_relaunch(args)
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         try:
             run_reference(args)
         except Exception as exc:  # the arm must not take the round down
             rank, _, _ = dist_env()
             if rank == 0:
-                print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"}), flush=True)
+                emit({"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"})
     else:
         run_ours(args)
 

@@ -1,0 +1,215 @@
+#!/usr/bin/env python
+"""Device-timed latency of the target layer configurations, this package vs the library path.
+
+    python benchmarks/bench_layers.py --config {tp_mlp,dp_backward,qwen3_decode} --gpus N [--steps K --warmup W]
+    (N > 1: starts one rank per GPU with torch.distributed.run on 127.0.0.1)
+
+"ours" is one launch of the persistent kernel per step. "library" is the same math as separate
+launches of the kernels the reference's live runtime calls (torch.mm / cuBLAS, torch element-wise
+ops, torch.distributed / NCCL collectives), with the reference's two-stream overlap where it
+offers one. Times are CUDA events around K steps, max over ranks; rank 0 prints one JSON line per arm
+with the achieved fraction of the roofline (slower of FLOPs / measured GEMM peak and bytes / bandwidth).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, REPO)
+
+
+def peaks():
+    p = {"bf16_tflops_sustained": 1400.0, "bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+    try:
+        d = json.load(open(os.path.join(REPO, "MEASURED_PEAKS.json")))
+        p.update({k: d[k] for k in ("bf16_tflops_sustained", "bf16_tflops", "hbm_gbs") if k in d})
+        p["source"] = "measured"
+    except Exception:
+        pass
+    p["nvlink_gbs"] = 770.0
+    return p
+
+
+def timed(torch, dist, world, steps, fn):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms * 1e3 / steps
+
+
+# ---------------------------------------------------------------------------------------------------
+# configurations: each returns (step_ours, step_library, roofline dict)
+# ---------------------------------------------------------------------------------------------------
+def cfg_tp_mlp(torch, dist, rank, world, heap, args):
+    from maco_b200.models.tp_mlp import TPSwiGLUMLP
+    T, H, F = 8192, 4096, 14336
+    layer = TPSwiGLUMLP(T, H, F, rank=rank, world=world, heap=heap, mode=args.mode)
+    layer.x_shard.normal_()
+    rows = T // world
+    x_shard = layer.x_shard.clone()
+    x_full = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+    y_shard = torch.empty(rows, H, device="cuda", dtype=torch.bfloat16)
+
+    def library():
+        if world > 1:
+            dist.all_gather_into_tensor(x_full, x_shard)
+        else:
+            x_full.copy_(x_shard)
+        h = torch.nn.functional.silu(x_full @ layer.w_gate.t()) * (x_full @ layer.w_up.t())
+        y = h @ layer.w_down.t()
+        if world > 1:
+            dist.reduce_scatter_tensor(y_shard, y)
+
+    p = peaks()
+    flops = 2.0 * T * H * F * 3 / world
+    link = (T * H * 2) * (world - 1) / world                       # bytes in (all-gather) = bytes out (partials)
+    roof = {"compute_us": flops / (p["bf16_tflops_sustained"] * 1e12) * 1e6, "nvlink_us": link / (p["nvlink_gbs"] * 1e9) * 1e6}
+    return (lambda: layer.forward(None)), library, roof
+
+
+def cfg_dp_backward(torch, dist, rank, world, heap, args):
+    from maco_b200.models.dp_mlp_stack import DPMLPStackBackward
+    L, H, T = args.layers, 4096, 8192
+    m = DPMLPStackBackward(L, H, T, rank=rank, world=world, heap=heap, mode=args.mode)
+    m.forward()
+    grads = [torch.empty(H, H, device="cuda", dtype=torch.float32) for _ in range(L)]
+    comm = torch.cuda.Stream()
+    F = torch.nn.functional
+
+    def gelu_grad(z):
+        zf = z.float()
+        k0, k1 = 0.7978845608028654, 0.044715
+        t = torch.tanh(k0 * (zf + k1 * zf ** 3))
+        return 0.5 * (1 + t) + 0.5 * zf * (1 - t * t) * k0 * (1 + 3 * k1 * zf * zf)
+
+    def library():
+        # the reference's overlap pattern: backward GEMMs on the compute stream, each layer's fp32
+        # gradient all-reduce on a second stream behind an event
+        cur = torch.cuda.current_stream()
+        dz = ((m.a[-1].float() - m.target.float()) * (2.0 / (T * H)) * gelu_grad(m.z[-1])).to(torch.bfloat16)
+        for l in range(L - 1, -1, -1):
+            inp = m.a[l - 1] if l > 0 else m.x
+            grads[l].copy_((dz.t() @ inp).float() / world)
+            if world > 1:
+                ev = torch.cuda.Event(); ev.record(cur)
+                comm.wait_event(ev)
+                with torch.cuda.stream(comm):
+                    dist.all_reduce(grads[l])
+            if l > 0:
+                dz = ((dz @ m.weights[l]).float() * gelu_grad(m.z[l - 1])).to(torch.bfloat16)
+        cur.wait_stream(comm)
+
+    p = peaks()
+    flops = m.flops()
+    link = L * H * H * 4 * 2.0 * (world - 1) / world               # two-shot all-reduce: reduce-scatter + all-gather
+    roof = {"compute_us": flops / (p["bf16_tflops_sustained"] * 1e12) * 1e6, "nvlink_us": link / (p["nvlink_gbs"] * 1e9) * 1e6}
+    return m.backward, library, roof
+
+
+def cfg_qwen3_decode(torch, dist, rank, world, heap, args):
+    from maco_b200.models.qwen3_layer import Qwen3DecodeLayer
+    layer = Qwen3DecodeLayer(rank=rank, world=world, heap=heap, mode=args.mode)
+    layer.x.normal_()
+    F = torch.nn.functional
+    B, D, hq, hkv, G = layer.batch, layer.D, layer.hq, layer.hkv, layer.G
+    rms = lambda t, w: (t.float() * torch.rsqrt(t.float().pow(2).mean(-1, keepdim=True) + layer.eps) * w.float()).to(t.dtype)
+    cs = layer.cos_sin.float()
+    cos, sin = cs[:, : D // 2].unsqueeze(1), cs[:, D // 2:].unsqueeze(1)
+
+    def norm_rope(t, w):
+        t = rms(t, w).float()
+        t1, t2 = t[..., : D // 2], t[..., D // 2:]
+        return torch.cat([t1 * cos - t2 * sin, t2 * cos + t1 * sin], -1).to(torch.bfloat16)
+
+    def library():
+        x = layer.x
+        qkv = rms(x, layer.w_in) @ layer.w_qkv.t()
+        q = norm_rope(qkv[:, : hq * D].view(B, hq, D), layer.q_norm)
+        k = norm_rope(qkv[:, hq * D:(hq + hkv) * D].view(B, hkv, D), layer.k_norm)
+        layer.k_cache[:, :, layer.pos] = k
+        layer.v_cache[:, :, layer.pos] = qkv[:, (hq + hkv) * D:].view(B, hkv, D)
+        a = F.scaled_dot_product_attention(q.view(B, hkv, G, D), layer.k_cache, layer.v_cache).reshape(B, hq * D)
+        o = a @ layer.w_o.t()
+        if world > 1:
+            dist.all_reduce(o)
+        y1 = o + x
+        h2 = rms(y1, layer.w_post)
+        act = F.silu(h2 @ layer.w_gate.t()) * (h2 @ layer.w_up.t())
+        d = act @ layer.w_down.t()
+        if world > 1:
+            dist.all_reduce(d)
+        return d + y1
+
+    p = peaks()
+    roof = {"hbm_us": layer.bytes_streamed() / (p["hbm_gbs"] * 1e9) * 1e6,
+            "compute_us": 2.0 * B * sum(t.numel() for t in (layer.w_qkv, layer.w_o, layer.w_gate_up, layer.w_down)) / (p["bf16_tflops_sustained"] * 1e12) * 1e6}
+    return (lambda: layer.forward(None)), library, roof
+
+
+CONFIGS = {"tp_mlp": cfg_tp_mlp, "dp_backward": cfg_dp_backward, "qwen3_decode": cfg_qwen3_decode}
+HEAP_MB = {"tp_mlp": 256, "dp_backward": 1400, "qwen3_decode": 64}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", required=True, choices=sorted(CONFIGS))
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--layers", type=int, default=16)
+    ap.add_argument("--mode", default="static", choices=["static", "dynamic"])
+    ap.add_argument("--arms", default="library,ours")
+    args = ap.parse_args()
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 2000), os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)                         # native libraries print banners on fd 1
+    import torch
+    import torch.distributed as dist
+    rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(local_rank)
+    import maco_b200 as maco
+    from maco_b200 import _native
+    from maco_b200.parallel import symm_heap
+    heap = None
+    if world > 1:
+        maco.config.set(comm_buffer_size=f"{HEAP_MB[args.config]}MB", backend="peer")
+        maco.init(backend="nccl")
+        heap = symm_heap.current_heap()
+    ours, library, roof = CONFIGS[args.config](torch, dist, rank, world, heap, args)
+    p = peaks()
+    bound = max(roof.values())
+    for arm, fn in (("library", library), ("ours", ours)):
+        if arm not in args.arms.split(","):
+            continue
+        for _ in range(args.warmup):
+            fn()
+        us = timed(torch, dist, world, args.steps, fn)
+        if rank == 0:
+            line = {"config": args.config, "impl": arm, "n_gpus": world, "latency_us": round(us, 2), "steps": args.steps,
+                    "warmup": args.warmup, "roofline_us": {k: round(v, 1) for k, v in roof.items()},
+                    "fraction_of_roofline": round(bound / us, 3), "peaks": p["source"], "kernel_status": _native.status(clear=False)}
+            os.write(real_stdout, (json.dumps(line) + "\n").encode())
+    if world > 1:
+        maco.cleanup()
+
+
+if __name__ == "__main__":
+    main()

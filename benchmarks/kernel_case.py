@@ -1,0 +1,72 @@
+#!/usr/bin/env python
+"""Small, self-ending single-GPU cases of the hot kernels, for profiler captures and quick timing.
+
+    python benchmarks/kernel_case.py gemm        # stand-alone tcgen05 GEMM, 8192 x 4096 x 4096 bf16
+    python benchmarks/kernel_case.py mlp         # persistent kernel: fused SwiGLU MLP, 4096 tokens, 4096 -> 14336/4
+    python benchmarks/kernel_case.py attention   # split-KV decode attention, batch 32, 4096 keys
+    python benchmarks/kernel_case.py rmsnorm     # row-wise kernel, 16384 x 8192 bf16
+
+Each case holds well under 1 GB on the device, uses inputs larger than the 126 MB L2 where DRAM
+figures matter, warms up twice and then runs the kernel three times between CUDA events, printing
+the mean time and the achieved rate.
+"""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import torch
+
+from maco_b200 import _native, ops
+
+
+def timed(fn, iters=3, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3
+
+
+def main():
+    case = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    dt = torch.bfloat16
+    if case == "gemm":
+        M, N, K = 8192, 4096, 4096
+        a = torch.randn(M, K, device="cuda", dtype=dt)
+        b = torch.randn(N, K, device="cuda", dtype=dt) * 0.02
+        out = torch.empty(M, N, device="cuda", dtype=dt)
+        us = timed(lambda: ops.gemm(a, b, out=out, bn=256))
+        print(f"gemm {M}x{N}x{K}: {us:.1f} us, {2 * M * N * K / us / 1e6:.0f} TFLOP/s")
+    elif case == "mlp":
+        from maco_b200.models.tp_mlp import TPSwiGLUMLP
+        layer = TPSwiGLUMLP(4096, 4096, 3584)
+        layer.x_shard.normal_()
+        us = timed(lambda: layer.forward(None))
+        print(f"persistent fused MLP 4096 tok 4096->3584: {us:.1f} us, {layer.flops() / us / 1e6:.0f} TFLOP/s")
+    elif case == "attention":
+        B, Hq, Hkv, S = 32, 8, 1, 4096
+        q = torch.randn(B, Hq, 128, device="cuda", dtype=dt)
+        k = torch.randn(B, Hkv, S, 128, device="cuda", dtype=dt)
+        v = torch.randn(B, Hkv, S, 128, device="cuda", dtype=dt)
+        out = torch.empty_like(q)
+        scratch = torch.empty(1 << 20, device="cuda", dtype=torch.float32)
+        us = timed(lambda: ops.attention_decode(q, k, v, out=out, scratch=scratch))
+        print(f"attention decode B{B} S{S}: {us:.1f} us, {2 * k.numel() * 2 / us / 1e3:.0f} GB/s of KV")
+    elif case == "rmsnorm":
+        x = torch.randn(16384, 8192, device="cuda", dtype=dt)
+        w = torch.randn(8192, device="cuda", dtype=dt)
+        out = torch.empty_like(x)
+        us = timed(lambda: ops.rmsnorm(x, w, 1e-6, out=out))
+        print(f"rmsnorm 16384x8192: {us:.1f} us, {2 * x.numel() * 2 / us / 1e3:.0f} GB/s")
+    else:
+        raise SystemExit(f"unknown case {case}")
+    assert _native.status() == 0
+
+
+if __name__ == "__main__":
+    main()

@@ -48,76 +48,204 @@ MACO_DEVICE uint4 pack8(const float (&acc)[8], float scale, int dtype) {
   return o;
 }
 
-// Block geometry: `rows` rows of `row_bytes` (a multiple of 16) bytes.
-template <typename Program>
-MACO_DEVICE bool comm_run(const Program& p, const MacoTaskDesc& d, int tid, int nthreads) {
-  const MacoCommArgs& a = d.u.comm;
-  const uint32_t vpr = a.row_bytes >> 4;                     // 16-byte vectors per row
-  const uint64_t total = (uint64_t)a.rows * vpr;
+// Block geometry: `rows` rows of `row_bytes` (a multiple of 16) bytes. Every loop keeps kU
+// independent 16-byte accesses per thread in flight: with 128 threads per task the copies are
+// latency-bound otherwise.
+constexpr int kU = 8;
+
+// Data loads are plain (weak) 16-byte loads: ordering against the producer comes from the acquire
+// on the task's event followed by the CTA barrier, so the compiler is free to batch them.
+MACO_DEVICE uint4 ldv(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+MACO_DEVICE void stv(uint8_t* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
+
+// Byte offset of 16-byte vector `i` of a block whose rows are `stride` bytes apart. 32-bit index
+// arithmetic (64-bit division is emulated and would dominate the copy loops); rows that are packed
+// back to back take the division-free path.
+MACO_DEVICE uint64_t blk_off(uint32_t i, uint32_t vpr, uint64_t stride) {
+  if (stride == ((uint64_t)vpr << 4)) return (uint64_t)i << 4;
+  const uint32_t r = i / vpr;
+  return (uint64_t)r * stride + ((uint64_t)(i - r * vpr) << 4);
+}
+
+// out = scale * (sum over n sources (+ aux)); kR vectors per thread per pass, loads of kS sources issued together.
+template <int kR, int kS, typename Program>
+MACO_DEVICE void comm_reduce(const Program& p, const MacoCommArgs& a, int n, uint32_t total, uint32_t vpr, int tid,
+                             int nthreads) {
   uint8_t* mine = p.peer_heap[p.rank];
+  const bool local = a.op == MACO_COMM_REDUCE_LOCAL;
+  uint8_t* out = a.local_ptr != nullptr ? reinterpret_cast<uint8_t*>(a.local_ptr) : mine + a.dst_off;
+  const uint32_t rstep = (uint32_t)nthreads * kR;
+  for (uint32_t base = tid; base < total; base += rstep) {
+    float acc[kR][8];
+#pragma unroll
+    for (int u = 0; u < kR; ++u)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+    uint64_t soff[kR];
+#pragma unroll
+    for (int u = 0; u < kR; ++u) {
+      const uint32_t i = base + (uint32_t)u * nthreads;
+      soff[u] = blk_off(i < total ? i : 0, vpr, a.src_stride);
+    }
+    for (int j0 = 0; j0 < n; j0 += kS) {
+      uint4 v[kS][kR];
+#pragma unroll
+      for (int jj = 0; jj < kS; ++jj) {
+        const int j = j0 + jj;
+        if (j < n) {
+          const uint8_t* src = local ? mine + a.src_off + (uint64_t)j * a.slot_stride
+                                     : p.peer_heap[(p.rank + j) % p.world] + a.src_off;
+#pragma unroll
+          for (int u = 0; u < kR; ++u) v[jj][u] = ldv(src + soff[u]);
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < kS; ++jj) {
+        if (j0 + jj < n) {
+#pragma unroll
+          for (int u = 0; u < kR; ++u) add8(acc[u], v[jj][u], a.dtype);
+        }
+      }
+    }
+    if (a.aux_ptr != nullptr) {
+#pragma unroll
+      for (int u = 0; u < kR; ++u) {
+        const uint32_t i = base + (uint32_t)u * nthreads;
+        if (i < total) add8(acc[u], ldv(reinterpret_cast<const uint8_t*>(a.aux_ptr) + blk_off(i, vpr, a.dst_stride)), a.dtype);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kR; ++u) {
+      const uint32_t i = base + (uint32_t)u * nthreads;
+      if (i >= total) continue;
+      const uint4 o = pack8(acc[u], a.scale, a.dtype);
+      if (a.op == MACO_COMM_ALLREDUCE) {
+        for (int j = 0; j < p.world; ++j)
+          stv(p.peer_heap[(p.rank + j) % p.world] + a.dst_off + blk_off(i, vpr, a.dst_stride), o);
+      } else {
+        stv(out + blk_off(i, vpr, a.dst_stride), o);
+      }
+    }
+  }
+}
+
+// Shared-memory staging for bulk pushes: only offered on workers whose operand ring is idle
+// (communication workers never receive GEMM tasks).
+struct BulkCtx {
+  uint8_t* buf;            // nbuf buffers of buf_bytes each (1024-byte aligned)
+  uint64_t* bars;          // one mbarrier per buffer, initialised with count 1
+  uint32_t nbuf, buf_bytes;
+  uint32_t phase;          // bit b = parity the next wait on bars[b] uses
+};
+
+// Contiguous push through the bulk-copy engine: one thread keeps nbuf * buf_bytes in flight
+// (load rounds into shared memory, then one bulk store per destination), which is what it takes
+// to fill an NVLink from a single SM; 128 threads with 16-byte accesses are latency-bound far below.
+template <typename Program>
+MACO_DEVICE bool comm_push_bulk(const Program& p, const MacoCommArgs& a, BulkCtx& bc, uint64_t budget_ns) {
+  const uint64_t bytes = (uint64_t)a.rows * a.row_bytes;
+  const uint8_t* src = p.peer_heap[p.rank] + a.src_off;
+  fence_proxy_async_all();
+  bool ok = true;
+  for (uint64_t pos = 0; pos < bytes && ok; pos += (uint64_t)bc.nbuf * bc.buf_bytes) {
+    uint32_t used = 0;
+    for (uint32_t b = 0; b < bc.nbuf; ++b) {
+      const uint64_t off = pos + (uint64_t)b * bc.buf_bytes;
+      if (off >= bytes) break;
+      const uint32_t n = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
+      mbar_arrive_expect_tx(&bc.bars[b], n);
+      bulk_load(bc.buf + (size_t)b * bc.buf_bytes, src + off, n, &bc.bars[b]);
+      ++used;
+    }
+    for (uint32_t b = 0; b < used; ++b) {
+      const uint64_t off = pos + (uint64_t)b * bc.buf_bytes;
+      const uint32_t n = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
+      const uint32_t parity = (bc.phase >> b) & 1u;
+      const uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_wait(&bc.bars[b], parity)) {
+        if (globaltimer_ns() - t0 > budget_ns) { ok = false; break; }
+      }
+      bc.phase ^= 1u << b;
+      if (!ok) break;
+      const uint8_t* sm = bc.buf + (size_t)b * bc.buf_bytes;
+      if (a.peer >= 0) {
+        bulk_store(p.peer_heap[a.peer] + a.dst_off + off, sm, n);
+      } else {
+        for (int k = 0; k < p.world; ++k) {
+          const int dr = (p.rank + 1 + k) % p.world;
+          if (dr == p.rank && a.peer != -3) continue;
+          bulk_store(p.peer_heap[dr] + a.dst_off + off, sm, n);
+        }
+      }
+      tma_store_commit();
+    }
+    tma_store_wait_read<0>();          // the buffers may be refilled
+  }
+  tma_store_wait<0>();                 // every store has completed before the task signals
+  return ok;
+}
+
+template <typename Program>
+MACO_DEVICE bool comm_run(const Program& p, const MacoTaskDesc& d, int tid, int nthreads, BulkCtx* bulk = nullptr) {
+  const MacoCommArgs& a = d.u.comm;
+  if (bulk != nullptr && a.op == MACO_COMM_PUSH && a.src_stride == a.row_bytes && a.dst_stride == a.row_bytes &&
+      (uint64_t)a.rows * a.row_bytes >= 65536) {
+    bool ok = true;
+    if (tid == 0) ok = comm_push_bulk(p, a, *bulk, p.budget_ns);
+    return ok;
+  }
+  const uint32_t vpr = a.row_bytes >> 4;                     // 16-byte vectors per row
+  const uint32_t total = a.rows * vpr;                      // blocks are far below 2^32 vectors
+  uint8_t* mine = p.peer_heap[p.rank];
+  const uint32_t step = (uint32_t)nthreads * kU;
   switch (a.op) {
-    case MACO_COMM_PUSH: {
+    case MACO_COMM_PUSH:
+    case MACO_COMM_PULL: {
       // Read each vector once, store it to every destination: the block leaves this GPU once per peer.
-      for (uint64_t i = tid; i < total; i += nthreads) {
-        const uint64_t r = i / vpr, c = (i % vpr) << 4;
-        const uint4 v = ld_global_v4(mine + a.src_off + r * a.src_stride + c);
-        const uint64_t doff = a.dst_off + r * a.dst_stride + c;
-        if (a.peer >= 0) {
-          st_global_v4(p.peer_heap[a.peer] + doff, v);
+      const uint8_t* src = (a.op == MACO_COMM_PULL ? p.peer_heap[a.peer] : mine) + a.src_off;
+      for (uint32_t base = tid; base < total; base += step) {
+        uint4 v[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const uint32_t i = base + (uint32_t)u * nthreads;
+          if (i < total) v[u] = ldv(src + blk_off(i, vpr, a.src_stride));
+        }
+        if (a.op == MACO_COMM_PULL || a.peer >= 0) {
+          uint8_t* dst = (a.op == MACO_COMM_PULL ? mine : p.peer_heap[a.peer]) + a.dst_off;
+#pragma unroll
+          for (int u = 0; u < kU; ++u) {
+            const uint32_t i = base + (uint32_t)u * nthreads;
+            if (i < total) stv(dst + blk_off(i, vpr, a.dst_stride), v[u]);
+          }
         } else {
           for (int k = 0; k < p.world; ++k) {
-            const int dst = (p.rank + 1 + k) % p.world;       // staggered so peers are not hit in lockstep
-            if (dst == p.rank && a.peer != -3) continue;
-            st_global_v4(p.peer_heap[dst] + doff, v);
+            const int dr = (p.rank + 1 + k) % p.world;        // staggered so peers are not hit in lockstep
+            if (dr == p.rank && a.peer != -3) continue;
+            uint8_t* dst = p.peer_heap[dr] + a.dst_off;
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+              const uint32_t i = base + (uint32_t)u * nthreads;
+              if (i < total) stv(dst + blk_off(i, vpr, a.dst_stride), v[u]);
+            }
           }
         }
       }
       return true;
     }
-    case MACO_COMM_PULL: {
-      const uint8_t* src = p.peer_heap[a.peer];
-      for (uint64_t i = tid; i < total; i += nthreads) {
-        const uint64_t r = i / vpr, c = (i % vpr) << 4;
-        st_global_v4(mine + a.dst_off + r * a.dst_stride + c, ld_global_v4(src + a.src_off + r * a.src_stride + c));
-      }
-      return true;
-    }
     case MACO_COMM_REDUCE_LOCAL:
-    case MACO_COMM_REDUCE_PULL: {
-      const bool pull = a.op == MACO_COMM_REDUCE_PULL;
-      const int n = pull ? p.world : a.nslots;
-      uint8_t* out = a.local_ptr != nullptr ? reinterpret_cast<uint8_t*>(a.local_ptr) : mine + a.dst_off;
-      const bool f32 = a.dtype == MACO_DT_F32;
-      for (uint64_t i = tid; i < total; i += nthreads) {
-        const uint64_t r = i / vpr, c = (i % vpr) << 4;
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < n; ++j) {
-          const uint8_t* src = pull ? p.peer_heap[(p.rank + j) % p.world] + a.src_off
-                                    : mine + a.src_off + (uint64_t)j * a.slot_stride;
-          add8(acc, ld_global_v4(src + r * a.src_stride + c), a.dtype);
-        }
-        (void)f32;
-        st_global_v4(out + r * a.dst_stride + c, pack8(acc, a.scale, a.dtype));
-      }
-      return true;
-    }
+    case MACO_COMM_REDUCE_PULL:
     case MACO_COMM_ALLREDUCE: {
-      for (uint64_t i = tid; i < total; i += nthreads) {
-        const uint64_t r = i / vpr, c = (i % vpr) << 4;
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < p.world; ++j)
-          add8(acc, ld_global_v4(p.peer_heap[(p.rank + j) % p.world] + a.src_off + r * a.src_stride + c), a.dtype);
-        const uint4 o = pack8(acc, a.scale, a.dtype);
-        for (int j = 0; j < p.world; ++j)
-          st_global_v4(p.peer_heap[(p.rank + j) % p.world] + a.dst_off + r * a.dst_stride + c, o);
-      }
+      const int n = a.op == MACO_COMM_REDUCE_LOCAL ? a.nslots : p.world;
+      // 8 independent 16-byte loads per thread in flight whatever the number of sources (more spills registers)
+      if (n <= 2) comm_reduce<4, 2>(p, a, n, total, vpr, tid, nthreads);
+      else if (n <= 4) comm_reduce<2, 4>(p, a, n, total, vpr, tid, nthreads);
+      else comm_reduce<1, 8>(p, a, n, total, vpr, tid, nthreads);
       return true;
     }
     case MACO_COMM_ALLREDUCE_MC: {
       if (p.mc_heap == nullptr) return false;
-      for (uint64_t i = tid; i < total; i += nthreads) {
-        const uint64_t r = i / vpr, c = (i % vpr) << 4;
-        const uint8_t* src = p.mc_heap + a.src_off + r * a.src_stride + c;
+      for (uint32_t i = tid; i < total; i += nthreads) {
+        const uint8_t* src = p.mc_heap + a.src_off + blk_off(i, vpr, a.src_stride);
         uint4 o;
         if (a.dtype == MACO_DT_F32) {
           float4 f = multimem_ld_reduce_f32x4(src);
@@ -131,7 +259,7 @@ MACO_DEVICE bool comm_run(const Program& p, const MacoTaskDesc& d, int tid, int 
             o = pack8(acc, a.scale, MACO_DT_BF16);
           }
         }
-        multimem_st_v4(p.mc_heap + a.dst_off + r * a.dst_stride + c, o);
+        multimem_st_v4(p.mc_heap + a.dst_off + blk_off(i, vpr, a.dst_stride), o);
       }
       return true;
     }

@@ -104,11 +104,12 @@ MACO_DEVICE bool elt_is_binary(uint32_t type) {
 MACO_DEVICE void elt_pointwise(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
   const bool bin = elt_is_binary(type);
   if (elt_vec_ok(a)) {
-    const int vpr = a.cols / 8;                       // vectors per row
-    const long long total = (long long)a.rows * vpr;
-    for (long long i = tid; i < total; i += nthreads) {
-      const long long r = a.row0 + i / vpr;
-      const int c = (int)(i % vpr) * 8;
+    const uint32_t vpr = a.cols / 8;                  // vectors per row
+    const uint32_t total = (uint32_t)a.rows * vpr;    // one task's rows: far below 2^32 (64-bit division is emulated)
+    for (uint32_t i = tid; i < total; i += nthreads) {
+      const uint32_t rr = i / vpr;
+      const long long r = a.row0 + rr;
+      const int c = (int)(i - rr * vpr) * 8;
       F8 x = load8(a.in0, r * a.ld_in + c, a.dtype);
       F8 y;
       if (bin) y = load8(a.in1, r * a.ld_in + c, a.dtype);
@@ -118,10 +119,11 @@ MACO_DEVICE void elt_pointwise(uint32_t type, const MacoEltArgs& a, int tid, int
       store8(a.out, r * a.ld_out + c, a.dtype, o);
     }
   } else {
-    const long long total = (long long)a.rows * a.cols;
-    for (long long i = tid; i < total; i += nthreads) {
-      const long long r = a.row0 + i / a.cols;
-      const int c = (int)(i % a.cols);
+    const uint32_t total = (uint32_t)a.rows * (uint32_t)a.cols;
+    for (uint32_t i = tid; i < total; i += nthreads) {
+      const uint32_t rr = i / (uint32_t)a.cols;
+      const long long r = a.row0 + rr;
+      const int c = (int)(i - rr * (uint32_t)a.cols);
       float x = load1(a.in0, r * a.ld_in + c, a.dtype);
       float y = bin ? load1(a.in1, r * a.ld_in + c, a.dtype) : 0.f;
       store1(a.out, r * a.ld_out + c, a.dtype, elt_apply(type, x, y, a));
@@ -207,20 +209,23 @@ MACO_DEVICE void elt_rowwise(uint32_t type, const MacoEltArgs& a, int tid, int n
 }
 
 // ---- RoPE (half-rotation form) -------------------------------------------------------------
-// Rows are (token, head) pairs: row = token * heads + head, cols = head_dim, i0 = heads.
+// Rows are (token, head) pairs: row = token * heads + head, cols = head_dim, i0 = heads;
+// ld_in / ld_out are the TOKEN strides (heads * head_dim when packed), heads are `cols` apart.
 // in1 = cos [tokens, head_dim/2], in2 = sin (same dtype as x); i1 = token index of row 0's token
 // in the cos/sin tables minus row0 / heads (0 when the tables start at the first row's token).
 MACO_DEVICE void elt_rope(const MacoEltArgs& a, int tid, int nthreads) {
   const int half = a.cols / 2;
-  const long long total = (long long)a.rows * half;
-  for (long long i = tid; i < total; i += nthreads) {
-    const long long r = a.row0 + i / half;
-    const int c = (int)(i % half);
+  const uint32_t total = (uint32_t)a.rows * (uint32_t)half;
+  for (uint32_t i = tid; i < total; i += nthreads) {
+    const uint32_t rr = i / (uint32_t)half;
+    const long long r = a.row0 + rr;
+    const int c = (int)(i - rr * (uint32_t)half);
     const long long tok = r / a.i0 + a.i1;
+    const long long ib = (r / a.i0) * a.ld_in + (r % a.i0) * a.cols, ob = (r / a.i0) * a.ld_out + (r % a.i0) * a.cols;
     const float cs = load1(a.in1, tok * half + c, a.dtype), sn = load1(a.in2, tok * half + c, a.dtype);
-    const float x1 = load1(a.in0, r * a.ld_in + c, a.dtype), x2 = load1(a.in0, r * a.ld_in + c + half, a.dtype);
-    store1(a.out, r * a.ld_out + c, a.dtype, x1 * cs - x2 * sn);
-    store1(a.out, r * a.ld_out + c + half, a.dtype, x2 * cs + x1 * sn);
+    const float x1 = load1(a.in0, ib + c, a.dtype), x2 = load1(a.in0, ib + c + half, a.dtype);
+    store1(a.out, ob + c, a.dtype, x1 * cs - x2 * sn);
+    store1(a.out, ob + c + half, a.dtype, x2 * cs + x1 * sn);
   }
 }
 
@@ -234,15 +239,16 @@ MACO_DEVICE void elt_qknorm_rope(const MacoEltArgs& a, int tid, int nthreads) {
   for (int rr = warp; rr < a.rows; rr += nwarps) {
     const long long r = a.row0 + rr;
     const long long tok = r / a.i0 + a.i1;
+    const long long ib = (r / a.i0) * a.ld_in + (r % a.i0) * a.cols, ob = (r / a.i0) * a.ld_out + (r % a.i0) * a.cols;
     float s2 = 0.f;
-    for (int c = lane; c < a.cols; c += 32) { float x = load1(a.in0, r * a.ld_in + c, a.dtype); s2 += x * x; }
+    for (int c = lane; c < a.cols; c += 32) { float x = load1(a.in0, ib + c, a.dtype); s2 += x * x; }
     const float rstd = rsqrtf(warp_sum(s2) / a.cols + a.f0);
     for (int c = lane; c < half; c += 32) {
-      const float x1 = load1(a.in0, r * a.ld_in + c, a.dtype) * rstd * load1(a.in1, c, a.dtype);
-      const float x2 = load1(a.in0, r * a.ld_in + c + half, a.dtype) * rstd * load1(a.in1, c + half, a.dtype);
+      const float x1 = load1(a.in0, ib + c, a.dtype) * rstd * load1(a.in1, c, a.dtype);
+      const float x2 = load1(a.in0, ib + c + half, a.dtype) * rstd * load1(a.in1, c + half, a.dtype);
       const float cs = load1(a.in2, tok * a.cols + c, a.dtype), sn = load1(a.in2, tok * a.cols + half + c, a.dtype);
-      store1(a.out, r * a.ld_out + c, a.dtype, x1 * cs - x2 * sn);
-      store1(a.out, r * a.ld_out + c + half, a.dtype, x2 * cs + x1 * sn);
+      store1(a.out, ob + c, a.dtype, x1 * cs - x2 * sn);
+      store1(a.out, ob + c + half, a.dtype, x2 * cs + x1 * sn);
     }
   }
 }

@@ -229,10 +229,37 @@ MACO_DEVICE float epi_load_aux(const GemmEpilogue& e, long long row, int col) {
 // Consumes one finished accumulator. Called by all 32 lanes of each of the 4 epilogue warps.
 // `out_base` lets a caller redirect the tile (for example into a peer GPU's buffer);
 // `row_off` is added to the tile's row index when storing (for scatter into per-rank slabs).
+// Staged stores: tiles that leave the GPU (a peer's heap) are first written to shared memory and
+// then sent as one 128-byte bulk copy per row and 64-column group. Per-thread 16-byte stores to
+// peer memory reach only a small fraction of NVLink bandwidth; the bulk engine writes full lines.
+constexpr int kEpiStageRowBytes = 144;                       // 128 bytes of data + 16 of padding (bank spread)
+constexpr int kEpiStageWarpBytes = 32 * kEpiStageRowBytes;   // one epilogue warp: 32 rows
+constexpr int kEpiStageBytes = 4 * kEpiStageWarpBytes;
+
+MACO_DEVICE void epi_stage_chunk(uint8_t* srow, int half, int out_type, const float (&v)[32]) {
+  uint4* dst = reinterpret_cast<uint4*>(srow + half * 64);
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint4 o;
+    o.x = epi_pack(out_type, v[j], v[j + 1]); o.y = epi_pack(out_type, v[j + 2], v[j + 3]);
+    o.z = epi_pack(out_type, v[j + 4], v[j + 5]); o.w = epi_pack(out_type, v[j + 6], v[j + 7]);
+    dst[j >> 3] = o;
+  }
+}
+
+// Extra destinations of a tile: the same values are also stored at bases[k] + off for k < n
+// (used to broadcast a partial result into every rank's staging slot).
+struct EpiBroadcast {
+  int n;
+  uint8_t* const* bases;
+  unsigned long long off;
+};
+
 template <int BN, int SBN = BN>
 MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const GemmEpilogue& e,
                                     void* out_base, long long row_off, int m0, int n0,
-                                    uint32_t tile_seq, uint64_t budget_ns) {
+                                    uint32_t tile_seq, uint64_t budget_ns, const EpiBroadcast* bc = nullptr,
+                                    uint8_t* stage = nullptr) {
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t q = warp & 3;     // TMEM lane quarter this warp may read
   const uint32_t acc = tile_seq & 1, acc_ph = (tile_seq >> 1) & 1;
@@ -243,6 +270,28 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
   tc_fence_after();
   const int row = m0 + q * 32 + lane;
   const bool row_ok = row < e.M;
+  // staged path: 16-bit output, tile completely inside the output columns (uniform over the CTA)
+  const int out_cols = e.mode == MACO_EPI_SWIGLU ? e.N / 2 : e.N;
+  const int tile_col0 = e.mode == MACO_EPI_SWIGLU ? n0 / 2 : n0;
+  const int tile_cols = e.mode == MACO_EPI_SWIGLU ? BN / 2 : BN;
+  const bool staged = stage != nullptr && e.out_type != MACO_DT_F32 && tile_col0 + tile_cols <= out_cols &&
+                      e.mode != MACO_EPI_F32_ACC;
+  uint8_t* srow = stage != nullptr ? stage + q * kEpiStageWarpBytes + lane * kEpiStageRowBytes : nullptr;
+  auto flush_group = [&](int gcol) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (row_ok) {
+      const long long eoff = ((long long)(row + row_off) * e.ld_out + gcol) * 2;
+      if (bc == nullptr) {
+        bulk_store(reinterpret_cast<uint8_t*>(out_base) + eoff, srow, 128);
+      } else {
+        for (int k = 0; k < bc->n; ++k) bulk_store(bc->bases[k] + bc->off + eoff, srow, 128);
+      }
+      tma_store_commit();
+    }
+    tma_store_wait_read<0>();
+    __syncwarp();
+  };
   const uint32_t t_row = tmem_base + ((q * 32u) << 16) + acc * SBN;
   if (e.mode == MACO_EPI_SWIGLU) {
     // Columns [0, BN/2) of the tile hold the gate projection, [BN/2, BN) the up projection of
@@ -258,7 +307,13 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
       for (int j = 0; j < 32; ++j) v[j] = silu(__uint_as_float(g[j])) * __uint_as_float(u[j]);
       const int col0 = n0 / 2 + ch * 32;
       const int valid = min(32, e.N / 2 - col0);
-      if (row_ok && valid > 0) epi_store_row32(e, out_base, row + row_off, col0, valid, v);
+      if (staged) {
+        if (row_ok) epi_stage_chunk(srow, ch & 1, e.out_type, v);
+        if (ch & 1) flush_group(col0 - 32);
+      } else if (row_ok && valid > 0) {
+        if (bc == nullptr) epi_store_row32(e, out_base, row + row_off, col0, valid, v);
+        else for (int k = 0; k < bc->n; ++k) epi_store_row32(e, bc->bases[k] + bc->off, row + row_off, col0, valid, v);
+      }
       __syncwarp();
     }
   } else {
@@ -290,11 +345,16 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
 #pragma unroll
         for (int j = 0; j < 32; ++j) if (j < valid) v[j] += epi_load_aux(e, row, col0 + j);
       }
-      epi_store_row32(e, out_base, row + row_off, col0, valid, v);
+      if (staged) {
+        if (row_ok) epi_stage_chunk(srow, ch & 1, e.out_type, v);
+      } else if (bc == nullptr) epi_store_row32(e, out_base, row + row_off, col0, valid, v);
+      else for (int k = 0; k < bc->n; ++k) epi_store_row32(e, bc->bases[k] + bc->off, row + row_off, col0, valid, v);
       }
+      if (staged && (ch & 1)) flush_group(col0 - 32);
       __syncwarp();
     }
   }
+  if (staged) tma_store_wait<0>();     // bulk stores complete before the tile is signalled
   tc_fence_before();
   mbar_arrive(&c.tmem_empty[acc]);
   return true;

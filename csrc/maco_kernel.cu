@@ -41,9 +41,13 @@ constexpr int kMkBN = 256;
 constexpr int kMkStages = 4;
 using MkLayout = GemmSmemLayout<kMkBN, kMkStages>;
 constexpr int kMkExtraSmem = 1024;     // scheduler heads / current-task slots live after the GEMM control block
-constexpr int kMkScratchSmem = 12288;  // scratch of non-GEMM tasks (the operand ring is NOT free for them:
+constexpr int kMkScratchSmem = 20480;  // scratch of non-GEMM tasks (the operand ring is NOT free for them:
                                        // the producer warp may already be filling it for the next GEMM task)
 constexpr int kMkSmemBytes = MkLayout::kTotalBytes + kMkExtraSmem + kMkScratchSmem;
+static_assert(kMkScratchSmem >= kEpiStageBytes, "epilogue staging must fit the scratch block");
+constexpr uint32_t kBulkBufBytes = 16384;                                  // staging buffers of bulk pushes
+constexpr uint32_t kBulkBuffers = MkLayout::kRingBytes / kBulkBufBytes;    // the whole operand ring
+static_assert(kBulkBuffers <= 16, "phase bits / barrier slots");
 
 __device__ __forceinline__ void general_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -205,9 +209,12 @@ __device__ void mma_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint
 // Control words shared by the 128 threads are double buffered by iteration parity, so the
 // leader can prepare iteration i+1 while slower threads still read the words of iteration i.
 __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, const GemmCtrl& c, uint32_t tmem_base,
-                             volatile uint32_t* slots, uint8_t* scratch_smem) {
+                             volatile uint32_t* slots, uint8_t* scratch_smem, uint8_t* ring_smem, uint64_t* bulk_bars) {
   const int tid = threadIdx.x - 64;          // 0..127
   const bool leader = tid == 0;
+  // Communication workers never get GEMM tasks, so their operand ring is free to stage bulk copies.
+  const bool comm_worker = p.num_comm_workers > 0 && w >= p.num_workers - p.num_comm_workers;
+  BulkCtx bulk{ring_smem, bulk_bars, kBulkBuffers, kBulkBufBytes, 0u};
   uint32_t seq = 0, done = 0;
   for (uint32_t i = 0;; ++i) {
     volatile uint32_t* cur = slots + (i & 1u) * 4;     // [0] task, [1] dependencies satisfied, [2] failure
@@ -232,9 +239,12 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
       GemmEpilogue e = p.epis[g.epi];
       void* out_base = e.out;
       if (g.peer >= 0) out_base = p.peer_heap[g.peer] + g.out_off;
+      EpiBroadcast bc{p.world, p.peer_heap, g.out_off};       // peer == -2: the tile goes to every rank's heap
+      const EpiBroadcast* bcp = g.peer == -2 ? &bc : nullptr;
       bool ok;
-      if (g.bn == 128) ok = gemm_epilogue_tile<128, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns);
-      else ok = gemm_epilogue_tile<256, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns);
+      uint8_t* stage = g.peer != -1 ? scratch_smem : nullptr;  // tiles that leave the GPU go through the bulk engine
+      if (g.bn == 128) ok = gemm_epilogue_tile<128, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns, bcp, stage);
+      else ok = gemm_epilogue_tile<256, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns, bcp, stage);
       if (!ok) cur[2] = 1;
       ++seq;
     } else {
@@ -242,7 +252,7 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
       general_bar();
       if (cur[1] != 0) {
         if (d.type >= 200 && d.type < 300) {
-          if (!comm_run(p, d, tid, 128)) {
+          if (!comm_run(p, d, tid, 128, comm_worker ? &bulk : nullptr)) {
             cur[2] = 1;
             if (leader) report_failure(p, MACO_STATUS_BAD_TASK, task, d.u.comm.op, c.abort_word);
           }
@@ -373,7 +383,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) maco_persistent_kernel(const 
   if (is_worker) {
     const uint32_t w = blockIdx.x;
     // All roles must start from the same ring position: one thread reads it before anyone can move it.
-    if (threadIdx.x == 0) extra[16] = p.mode == MACO_MODE_DYNAMIC ? ld_relaxed_gpu_u32(&p.tails[w]) : 0;
+    uint64_t* bulk_bars = reinterpret_cast<uint64_t*>(extra + 32);          // bytes 128.. of the extra block
+    if (threadIdx.x == 0) {
+      extra[16] = p.mode == MACO_MODE_DYNAMIC ? ld_relaxed_gpu_u32(&p.tails[w]) : 0;
+      for (uint32_t b = 0; b < kBulkBuffers; ++b) mbar_init(&bulk_bars[b], 1);
+      fence_mbar_init();
+    }
     __syncthreads();
     const uint32_t q_base = extra[16];
     if (warp == 0) {
@@ -383,7 +398,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) maco_persistent_kernel(const 
       if (lane == 0) mma_role(p, w, q_base, smem, c, tmem_base);
       __syncwarp();
     } else {
-      general_role(p, w, q_base, c, tmem_base, extra, reinterpret_cast<uint8_t*>(extra) + kMkExtraSmem);
+      general_role(p, w, q_base, c, tmem_base, extra, reinterpret_cast<uint8_t*>(extra) + kMkExtraSmem, smem, bulk_bars);
     }
   } else {
     if (warp == 0) scheduler_role(p, extra);

@@ -100,7 +100,7 @@ struct MacoGemmArgs {             /* one output tile */
   uint8_t a_mn, b_mn;             /* operand majors */
   int32_t m0, n0, k0, k_blocks;
   uint32_t idesc;
-  int32_t peer;                   /* -1: store to the epilogue's out; else into that rank's heap at out_off */
+  int32_t peer;                   /* -1: store to the epilogue's out; >= 0: into that rank's heap at out_off; -2: into every rank's heap at out_off */
   long long row_off;              /* added to the row index on store */
   uint64_t out_off;               /* with peer >= 0: byte offset of the destination inside the peer's heap */
   uint32_t bn;                    /* tile width: 128 or 256 */
@@ -132,6 +132,7 @@ struct MacoCommArgs {             /* 2-D block (rows x row_bytes) of a buffer in
   void* local_ptr;                /* optional destination outside the heap (reductions) */
   float scale;                    /* applied to reduced values (1/world for an average) */
   int32_t _pad;
+  const void* aux_ptr;            /* reductions: optional block added to the sum (e.g. a residual), laid out like the destination */
 };
 
 enum MacoCommOp {

@@ -5,7 +5,7 @@
     y_shard = reduce_scatter(h Wd^T)   row-parallel down        [F/P -> H]
 
 The whole layer is ONE launch of the persistent kernel per rank. The all-gather is pushed in
-32-row chunks and each gate/up tile waits only for the 128 rows it reads; SwiGLU is applied in the
+128-row chunks by a few communication workers and each gate/up tile waits only for the 128 rows it reads; SwiGLU is applied in the
 GEMM epilogue (gate and up weights are interleaved per 256-column tile); the down-projection
 epilogue stores every partial tile into the staging slot of the rank that owns those rows, and
 that rank sums the slots as their per-block counters fill. With one rank the collectives
@@ -29,7 +29,8 @@ from ..parallel import fused
 class TPSwiGLUMLP:
     def __init__(self, tokens: int, hidden: int, ffn: int, *, rank: int = 0, world: int = 1, heap=None,
                  device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16, seed: int = 0,
-                 mode: str = "static", trace: bool = False, weight_std: float = 0.02, num_workers: Optional[int] = None):
+                 mode: str = "static", trace: bool = False, weight_std: float = 0.02, num_workers: Optional[int] = None,
+                 comm_workers: int = 8):
         if tokens % (world * BM) or ffn % (world * 128):
             raise ValueError("tokens must be a multiple of world*128 and ffn of world*128")
         if world > 1 and heap is None:
@@ -45,7 +46,8 @@ class TPSwiGLUMLP:
         self.w_gate, self.w_up, self.w_down = mk(f_local, hidden), mk(f_local, hidden), mk(hidden, f_local)
         self.w_gate_up = interleave_gate_up(self.w_gate, self.w_up)
         dev = self.device
-        b = ProgramBuilder(dev, num_workers=num_workers, mode=mode, heap=heap, trace=trace)
+        b = ProgramBuilder(dev, num_workers=num_workers, mode=mode, heap=heap, trace=trace,
+                           num_comm_workers=(comm_workers if world > 1 else 0))
         self.h = torch.empty(tokens, f_local, device=dev, dtype=dtype)
         if world == 1:
             self.x_shard = torch.empty(tokens, hidden, device=dev, dtype=dtype)
@@ -53,8 +55,9 @@ class TPSwiGLUMLP:
             e1 = b.gemm(self.x_shard, self.w_gate_up, self.h, epilogue="swiglu")
             b.gemm(self.h, self.w_down, self.y_shard, a_ready=e1)
         else:
-            self.x_shard = heap.alloc((self.rows_local, hidden), dtype)
             self.x_full = heap.alloc((tokens, hidden), dtype)
+            # the input shard IS this rank's slice of the gathered buffer: nothing to copy locally
+            self.x_shard = self.x_full[rank * self.rows_local:(rank + 1) * self.rows_local]
             self.staging = heap.alloc((world, self.rows_local, hidden), dtype)
             self.y_shard = torch.empty(self.rows_local, hidden, device=dev, dtype=dtype)
             fence = fused.epoch_fence_event(b)

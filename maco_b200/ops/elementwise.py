@@ -37,7 +37,7 @@ def _rows2d(t: torch.Tensor) -> torch.Tensor:
 
 
 def _launch(kind: int, x: torch.Tensor, in1=None, in2=None, out: Optional[torch.Tensor] = None, f0=0.0, f1=0.0,
-            i0=0, i1=0, rows=None, cols=None) -> torch.Tensor:
+            i0=0, i1=0, rows=None, cols=None, ld=None) -> torch.Tensor:
     if not x.is_cuda:
         raise ValueError("maco_b200 element-wise operators need CUDA tensors")
     if x.dtype not in N.DTYPE_CODE:
@@ -53,7 +53,8 @@ def _launch(kind: int, x: torch.Tensor, in1=None, in2=None, out: Optional[torch.
     r = rows if rows is not None else xc.numel() // c
     a1 = in1.contiguous() if in1 is not None else None
     a2 = in2.contiguous() if in2 is not None else None
-    rc = _fn()(kind, xc.data_ptr(), N.ptr(a1), N.ptr(a2), out.data_ptr(), r, c, N.DTYPE_CODE[x.dtype], c, c,
+    ld = ld if ld is not None else c
+    rc = _fn()(kind, xc.data_ptr(), N.ptr(a1), N.ptr(a2), out.data_ptr(), r, c, N.DTYPE_CODE[x.dtype], ld, ld,
                float(f0), float(f1), int(i0), int(i1), N.current_stream_ptr())
     N.check(rc, "maco_elementwise")
     return out
@@ -76,7 +77,7 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out=None) -> tor
     """Half-rotation RoPE on [tokens, heads, head_dim]; cos/sin are [tokens, head_dim // 2]."""
     tokens, heads, hd = x.shape
     return _launch(T_ROPE, x, in1=cos.to(x.dtype), in2=sin.to(x.dtype), out=out, i0=heads, i1=0,
-                   rows=tokens * heads, cols=hd)
+                   rows=tokens * heads, cols=hd, ld=heads * hd)
 
 
 def qknorm_rope(x: torch.Tensor, weight: torch.Tensor, cos_sin: torch.Tensor, eps: float = 1e-6, out=None,
@@ -85,4 +86,4 @@ def qknorm_rope(x: torch.Tensor, weight: torch.Tensor, cos_sin: torch.Tensor, ep
     with cos in the first half of each row and sin in the second."""
     tokens, heads, hd = x.shape
     return _launch(T_ROPE, x, in1=weight, in2=cos_sin.to(x.dtype), out=out, f0=eps, f1=1.0, i0=heads,
-                   i1=token_offset, rows=tokens * heads, cols=hd)
+                   i1=token_offset, rows=tokens * heads, cols=hd, ld=heads * hd)

@@ -26,6 +26,7 @@ BM, BK = 128, 64
 QUEUE_TERMINATE = 0xFFFFFFFF
 MODE_STATIC, MODE_DYNAMIC = 0, 1
 TF_WAIT0_SYS, TF_WAIT1_SYS, TF_COMM_WORKER, TF_SIGNAL_SYS, TF_WAIT0_PREV, TF_WAIT1_PREV = 1, 2, 4, 8, 16, 32
+TF_ANY_WORKER = 64      # host-side placement hint: spread over compute AND communication workers
 COMM_PUSH, COMM_REDUCE_LOCAL, COMM_REDUCE_PULL, COMM_ALLREDUCE, COMM_ALLREDUCE_MC, COMM_PULL = range(6)
 MAX_PEERS = 16
 WORKER_QUEUE_SIZE = 1024
@@ -94,9 +95,9 @@ def _pack_elt(in0, in1, in2, out, row0, rows, cols, dtype, ld_in, ld_out, f0=0.0
 
 
 def _pack_comm(src_off, dst_off, src_stride, dst_stride, row_bytes, rows, dtype, peer, op, nslots=0, slot_stride=0,
-               local_ptr=0, scale=1.0) -> bytes:
-    return struct.pack("<QQQQIIiiiiQQfi", src_off, dst_off, src_stride, dst_stride, row_bytes, rows, dtype, peer, op,
-                       nslots, slot_stride, local_ptr or 0, scale, 0)
+               local_ptr=0, scale=1.0, aux_ptr=0) -> bytes:
+    return struct.pack("<QQQQIIiiiiQQfiQ", src_off, dst_off, src_stride, dst_stride, row_bytes, rows, dtype, peer, op,
+                       nslots, slot_stride, local_ptr or 0, scale, 0, aux_ptr or 0)
 
 
 def _pack_epilogue(out, bias, aux, ld_out, ld_aux, mode, out_type, bias_type, aux_type, M, Nn, alpha) -> bytes:
@@ -163,7 +164,7 @@ class ProgramBuilder:
 
     def add_task(self, ttype: int, raw: bytes, waits: Sequence[Tuple[int, int, bool, bool]] = (),
                  signals: Sequence[int] = (), signal_peer: int = -1, signal_peer_event: int = -1, node_id: int = 0,
-                 comm_worker: bool = False, signal_sys: bool = False) -> int:
+                 comm_worker: bool = False, signal_sys: bool = False, any_worker: bool = False) -> int:
         """``waits``: up to two (event, count, sys_scope, previous_epoch)."""
         if len(waits) > 2 or len(signals) > 2:
             raise ValueError("a task takes at most two wait conditions and two local signals")
@@ -179,6 +180,8 @@ class ProgramBuilder:
             flags |= TF_COMM_WORKER
         if signal_sys:
             flags |= TF_SIGNAL_SYS
+        if any_worker:
+            flags |= TF_ANY_WORKER
         se = list(signals) + [-1] * (2 - len(signals))
         self.tasks.append(dict(type=ttype, flags=flags, node_id=node_id, wait_event=we, wait_count=wc, signal_event=se,
                                signal_peer=signal_peer, signal_peer_event=signal_peer_event, raw=raw))
@@ -231,9 +234,10 @@ class ProgramBuilder:
         mode = EPI[epilogue]
         if bn == 0:
             m_tiles = (M + BM - 1) // BM
+            # the SwiGLU epilogue needs the weight interleaved for the tile width; 256 unless told otherwise
             bn = 128 if (Nn <= 128 or (m_tiles * ((Nn + 255) // 256) < self.num_workers and mode != 2)) else 256
-        if mode == 2:
-            bn = 256
+        if bn not in (128, 256):
+            raise ValueError("bn must be 128 or 256")
         ab = 1 if a.dtype == torch.bfloat16 else 0
         idesc = make_idesc(ab, BM, bn, int(trans_a), int(trans_b))
         ta = self._tmap(a, a.shape[0], a.shape[1], a.stride(0), trans_a, BM)
@@ -307,7 +311,7 @@ class ProgramBuilder:
                     in2: Optional[torch.Tensor] = None, rows: int, cols: int, f0: float = 0.0, f1: float = 0.0,
                     i0: int = 0, i1: int = 0, in_ready: Sequence[Optional[RowEvents]] = (),
                     extra_waits: Sequence[Tuple[int, int, bool, bool]] = (), rows_per_task: Optional[int] = None,
-                    in1_rowwise: bool = True) -> RowEvents:
+                    ld_in: Optional[int] = None, ld_out: Optional[int] = None) -> RowEvents:
         """Row-chunked task list for an operator of csrc/elementwise.cuh over a [rows, cols] view."""
         dt = N.DTYPE_CODE[in0.dtype]
         esz = in0.element_size()
@@ -334,8 +338,8 @@ class ProgramBuilder:
             waits = list(dict.fromkeys(waits))
             if len(waits) > 2:
                 waits = self.join(waits, node_id)
-            raw = _pack_elt(in0.data_ptr(), N.ptr(in1), N.ptr(in2), out.data_ptr(), r0, r1 - r0, cols, dt, cols, cols,
-                            f0, f1, i0, i1)
+            raw = _pack_elt(in0.data_ptr(), N.ptr(in1), N.ptr(in2), out.data_ptr(), r0, r1 - r0, cols, dt,
+                            ld_in if ld_in is not None else cols, ld_out if ld_out is not None else cols, f0, f1, i0, i1)
             blk = r0 // BM
             self.add_task(ttype, raw, waits=waits, signals=[row_events[blk], all_ev], node_id=node_id)
             counts[blk] += 1
@@ -399,9 +403,12 @@ class Program:
         W, Wc = self.num_workers, self.num_comm_workers
         n_compute = W - Wc
         queues: List[List[int]] = [[] for _ in range(W)]
-        rr_c = rr_m = 0
+        rr_c = rr_m = rr_a = 0
         for i, t in enumerate(b.tasks):
-            if (t["flags"] & TF_COMM_WORKER) and Wc > 0:
+            if (t["flags"] & TF_ANY_WORKER) and Wc > 0:
+                queues[(W - 1 - rr_a) % W].append(i)       # communication workers (highest indices) first
+                rr_a += 1
+            elif (t["flags"] & TF_COMM_WORKER) and Wc > 0:
                 queues[n_compute + rr_m % Wc].append(i)
                 rr_m += 1
             else:
@@ -634,7 +641,7 @@ def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None)
             elif t == TaskType.ROPE:
                 tokens, heads, hd = x.shape
                 rows, cols = tokens * heads, hd
-                kw.update(i0=heads, i1=0)
+                kw.update(i0=heads, i1=0, ld_in=heads * hd, ld_out=heads * hd)
             aligned, extra = ready_of(node, x, rows)
             readies = [aligned]
             if t in (TaskType.ADD, TaskType.SILU_GATE) and in1 is not None:

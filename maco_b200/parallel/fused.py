@@ -42,11 +42,16 @@ def epoch_fence_signal(b: ProgramBuilder, waits: Sequence[Tuple[int, int, bool, 
     b.add_task(int(TaskType.NOP), b"", waits=waits, signal_peer=-2, signal_peer_event=b._fence_event)
 
 
-def allgather_push(b: ProgramBuilder, shard: torch.Tensor, gathered: torch.Tensor, *, chunk_rows: int = 32,
+def allgather_push(b: ProgramBuilder, shard: torch.Tensor, gathered: torch.Tensor, *, chunk_rows: int = 128,
                    fence: Optional[Tuple[int, int, bool, bool]] = None,
                    src_ready: Optional[RowEvents] = None) -> RowEvents:
     """Pushes this rank's ``shard`` [rows, cols] into rows ``[rank*rows, (rank+1)*rows)`` of every
-    rank's ``gathered`` [world*rows, cols]. Returns row-block events of ``gathered``."""
+    rank's ``gathered`` [world*rows, cols]. Returns row-block events of ``gathered``.
+
+    ``shard`` may BE that slice of this rank's ``gathered`` (no local copy is made then, and the
+    local blocks carry an always-true condition). One task per (destination, chunk), ordered by when
+    the destination needs the rows: rank r-1 consumes this shard first, then r-2, ...
+    """
     heap = b.heap
     rank, world = heap.rank, heap.world
     rows, cols = shard.shape
@@ -56,33 +61,41 @@ def allgather_push(b: ProgramBuilder, shard: torch.Tensor, gathered: torch.Tenso
         raise ValueError("chunk_rows must divide 128")
     row_bytes = cols * shard.element_size()
     s_off, g_off = heap.offset_of(shard), heap.offset_of(gathered)
+    in_place = s_off == g_off + rank * rows * row_bytes
     blocks = world * rows // BM
     events = [b.new_event() for _ in range(blocks)]
     all_ev = b.new_event()
     per_block = BM // chunk_rows
-    for c0 in range(0, rows, chunk_rows):
-        waits = []
-        if fence is not None:
-            waits.append(fence)
-        if src_ready is not None:
-            ev, cnt = src_ready.for_rows(c0, c0 + chunk_rows)
-            waits.append((ev, cnt, src_ready.sys, False))
-        grow = rank * rows + c0
-        raw = _pack_comm(s_off + c0 * row_bytes, g_off + grow * row_bytes, row_bytes, row_bytes, row_bytes, chunk_rows,
-                         N.DTYPE_CODE[shard.dtype], -3, COMM_PUSH)
-        b.add_task(int(TaskType.ALLGATHER), raw, waits=waits, signal_peer=-2, signal_peer_event=events[grow // BM],
-                   comm_worker=True)
+    dests = [(rank - k) % world for k in range(1, world)]
+    if not in_place:
+        dests = [rank] + dests
+    for dst in dests:
+        for c0 in range(0, rows, chunk_rows):
+            waits = []
+            if fence is not None:
+                waits.append(fence)
+            if src_ready is not None:
+                ev, cnt = src_ready.for_rows(c0, c0 + chunk_rows)
+                waits.append((ev, cnt, src_ready.sys, False))
+            grow = rank * rows + c0
+            raw = _pack_comm(s_off + c0 * row_bytes, g_off + grow * row_bytes, row_bytes, row_bytes, row_bytes,
+                             chunk_rows, N.DTYPE_CODE[shard.dtype], dst, COMM_PUSH)
+            b.add_task(int(TaskType.ALLGATHER), raw, waits=waits, signal_peer=dst, signal_peer_event=events[grow // BM],
+                       comm_worker=True)
     b.keepalive += [shard, gathered]
-    return RowEvents(rows=world * rows, block=BM, row_events=[(e, per_block) for e in events],
-                     all_event=(all_ev, 0), sys=True)
+    own = range(rank * rows // BM, (rank + 1) * rows // BM)
+    row_events = [(e, 0 if (in_place and i in own) else per_block) for i, e in enumerate(events)]
+    return RowEvents(rows=world * rows, block=BM, row_events=row_events, all_event=(all_ev, 0), sys=True)
 
 
-def rotated_blocks(rank: int, world: int, blocks_per_rank: int) -> List[int]:
-    """Row blocks ordered own shard first, then rank+1, rank+2, ...: the order data arrives in and
-    the order in which partial results should leave, so that at any moment the ranks talk to
-    different peers."""
+def rotated_blocks(rank: int, world: int, blocks_per_rank: int, own_last: bool = False) -> List[int]:
+    """Row blocks ordered own shard first, then rank+1, rank+2, ... (the order gathered rows arrive
+    in); with ``own_last`` the own shard comes last (partial results for other owners leave first, and
+    the owner's reduction of a block can start right after its own tile of that block). Either way the
+    ranks talk to different peers at any moment."""
     out: List[int] = []
-    for k in range(world):
+    ks = list(range(1, world)) + [0] if own_last else list(range(world))
+    for k in ks:
         r = (rank + k) % world
         out += list(range(r * blocks_per_rank, (r + 1) * blocks_per_rank))
     return out
@@ -90,7 +103,7 @@ def rotated_blocks(rank: int, world: int, blocks_per_rank: int) -> List[int]:
 
 def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, staging: torch.Tensor,
                         out: torch.Tensor, *, a_ready: Optional[RowEvents] = None, bn: int = 256,
-                        reduce_rows: int = 32, scale: float = 1.0) -> Tuple[RowEvents, RowEvents]:
+                        reduce_rows: Optional[int] = None, scale: float = 1.0) -> Tuple[RowEvents, RowEvents]:
     """``out[rows_local, N] = reduce_scatter(a @ w.T)`` with the partial tiles leaving through the
     GEMM epilogue. ``staging`` is a heap tensor [world, rows_local, N] (slot = source rank).
     Returns (events of the GEMM tiles, events of ``out``)."""
@@ -103,6 +116,11 @@ def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, sta
         raise ValueError("rows must be a multiple of world * 128")
     blocks_per_rank = rows_local // BM
     n_tiles = (Nn + bn - 1) // bn
+    if reduce_rows is None:
+        # about one reduction task per worker, so the tail after the last GEMM tile is one short task
+        reduce_rows = 4
+        while reduce_rows * 2 <= BM and rows_local // (reduce_rows * 2) >= b.num_workers:
+            reduce_rows *= 2
     st_off = heap.offset_of(staging)
     slot_bytes = rows_local * Nn * staging.element_size()
     part_events = [b.new_event() for _ in range(blocks_per_rank)]
@@ -113,7 +131,7 @@ def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, sta
                     signal_peer_event=part_events[mb % blocks_per_rank])
 
     gemm_ev = b.gemm(a, w, staging[0], a_ready=a_ready, bn=bn, per_tile=per_tile,
-                     m_blocks=rotated_blocks(rank, world, blocks_per_rank))
+                     m_blocks=rotated_blocks(rank, world, blocks_per_rank, own_last=True))
     # owner-side reduction of the `world` slots, fp32 accumulation
     row_bytes = Nn * staging.element_size()
     out_events = [b.new_event() for _ in range(blocks_per_rank)]
@@ -125,7 +143,7 @@ def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, sta
                              N.DTYPE_CODE[staging.dtype], -1, COMM_REDUCE_LOCAL, nslots=world, slot_stride=slot_bytes,
                              local_ptr=out.data_ptr() + r0 * out.stride(0) * out.element_size(), scale=scale)
             b.add_task(int(TaskType.REDUCE_SCATTER), raw, waits=[(part_events[j], world * n_tiles, True, False)],
-                       signals=[out_events[j], all_ev])
+                       signals=[out_events[j], all_ev], any_worker=True)
             total += 1
     b.keepalive += [staging, out]
     per_block = BM // reduce_rows
@@ -164,3 +182,43 @@ def allreduce_tasks(b: ProgramBuilder, buf: torch.Tensor, *, avg: bool = False, 
                    signal_peer_event=done, comm_worker=comm_worker)
     b.keepalive.append(buf)
     return done, n_chunks
+
+
+def gemm_allreduce(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, slots: Optional[torch.Tensor],
+                   out: torch.Tensor, *, residual: Optional[torch.Tensor] = None, a_ready: Optional[RowEvents] = None,
+                   extra_waits: Sequence[Tuple[int, int, bool, bool]] = (), bn: int = 128,
+                   reduce_rows: int = 8) -> RowEvents:
+    """``out = all_reduce(a @ w.T) (+ residual)`` for small row counts (decode): the GEMM epilogue stores
+    every partial tile into slot ``rank`` of ALL ranks' ``slots`` [world, M, N] (one-shot exchange) and
+    bumps their counters; each rank then sums its slots and the residual. With one rank the residual is
+    added in the GEMM epilogue and nothing is exchanged."""
+    M, Nn = a.shape[0], w.shape[0]
+    heap = b.heap
+    if heap is None or heap.world == 1:
+        return b.gemm(a, w, out, epilogue="residual" if residual is not None else None, aux=residual, a_ready=a_ready,
+                      extra_waits=extra_waits, bn=bn)
+    rank, world = heap.rank, heap.world
+    if M > BM:
+        raise ValueError("gemm_allreduce is the one-shot form for at most 128 rows")
+    off = heap.offset_of(slots)
+    slot_bytes = M * Nn * slots.element_size()
+    arrived = b.new_event()
+    n_tiles = (Nn + bn - 1) // bn
+
+    def per_tile(mb: int, nb: int) -> dict:
+        return dict(peer=-2, out_off=off + rank * slot_bytes, signal_peer=-2, signal_peer_event=arrived)
+
+    b.gemm(a, w, slots[0], a_ready=a_ready, extra_waits=extra_waits, bn=bn, per_tile=per_tile)
+    row_bytes = Nn * slots.element_size()
+    done = b.new_event()
+    total = 0
+    for r0 in range(0, M, reduce_rows):
+        rr = min(reduce_rows, M - r0)
+        raw = _pack_comm(off + r0 * row_bytes, 0, row_bytes, row_bytes, row_bytes, rr, N.DTYPE_CODE[slots.dtype], -1,
+                         COMM_REDUCE_LOCAL, nslots=world, slot_stride=slot_bytes,
+                         local_ptr=out.data_ptr() + r0 * row_bytes,
+                         aux_ptr=(residual.data_ptr() + r0 * row_bytes) if residual is not None else 0)
+        b.add_task(int(TaskType.ALLREDUCE), raw, waits=[(arrived, world * n_tiles, True, False)], signals=[done])
+        total += 1
+    b.keepalive += [slots, out] + ([residual] if residual is not None else [])
+    return RowEvents(rows=M, block=BM, row_events=[(done, total)], all_event=(done, total))

@@ -27,3 +27,19 @@ def test_tp_mlp_single_gpu():
     torch.cuda.synchronize()
     ref = layer.reference(x)
     assert (y.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("mode", ["static", "dynamic"])
+def test_qwen3_decode_layer_single_gpu(mode):
+    from maco_b200 import _native
+    from maco_b200.models.qwen3_layer import Qwen3DecodeLayer
+    layer = Qwen3DecodeLayer(hidden=1024, q_heads=16, kv_heads=2, ffn=2048, batch=8, kv_len=300, seed=4, mode=mode, splits=3,
+                             weight_std=0.05)
+    x = torch.randn(8, 1024, device="cuda", dtype=torch.bfloat16)
+    ref = layer.reference(x)
+    for _ in range(2):
+        out = layer(x)
+        torch.cuda.synchronize()
+        err = (out.float() - ref).abs().max().item()
+        assert err < 4e-2 * max(1.0, ref.abs().max().item()), err
+    assert _native.status() == 0

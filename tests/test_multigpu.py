@@ -72,7 +72,7 @@ def _collectives(rank, world):
 
 
 def test_peer_collectives():
-    run_ranks(_collectives, 2, env=ENV, timeout=240)
+    run_ranks(_collectives, 2, env=ENV, timeout=100)
 
 
 def _tp_mlp(rank, world):
@@ -98,7 +98,7 @@ def _tp_mlp(rank, world):
 
 
 def test_fused_tp_mlp_matches_reference():
-    run_ranks(_tp_mlp, 2, env=ENV, timeout=240)
+    run_ranks(_tp_mlp, 2, env=ENV, timeout=100)
 
 
 def _dp_backward(rank, world):
@@ -122,4 +122,33 @@ def _dp_backward(rank, world):
 
 
 def test_dp_backward_with_tilewise_allreduce():
-    run_ranks(_dp_backward, 2, env=ENV, timeout=240)
+    run_ranks(_dp_backward, 2, env=ENV, timeout=100)
+
+
+def _qwen3(rank, world):
+    maco, heap = _setup(rank, world, heap_mb=64)
+    import torch.distributed as dist
+    from maco_b200 import _native
+    from maco_b200.models.qwen3_layer import Qwen3DecodeLayer
+    layer = Qwen3DecodeLayer(hidden=1024, q_heads=16, kv_heads=2, ffn=2048, batch=8, kv_len=300, rank=rank, world=world,
+                             heap=heap, seed=4, weight_std=0.05)
+    torch.manual_seed(11)
+    x = torch.randn(8, 1024, device="cuda", dtype=torch.bfloat16)        # replicated input
+
+    def ar(t):
+        t = t.clone()
+        dist.all_reduce(t)
+        return t
+
+    ref = layer.reference(x, ar)
+    for it in range(3):
+        out = layer(x)
+        torch.cuda.synchronize()
+        err = (out.float() - ref).abs().max().item()
+        assert err < 4e-2 * max(1.0, ref.abs().max().item()), (it, err)
+    assert _native.status() == 0
+    maco.cleanup()
+
+
+def test_qwen3_decode_layer_tensor_parallel():
+    run_ranks(_qwen3, 2, env=ENV, timeout=100)
