@@ -135,7 +135,7 @@ struct BulkCtx {
   uint8_t* buf;            // nbuf buffers of buf_bytes each (1024-byte aligned)
   uint64_t* bars;          // one mbarrier per buffer, initialised with count 1
   uint32_t nbuf, buf_bytes;
-  uint32_t phase;          // bit b = parity the next wait on bars[b] uses
+  volatile uint32_t* phase;  // shared word: bit b = parity the next wait on bars[b] uses (updated by the leader only)
 };
 
 // Contiguous push through the bulk-copy engine: one thread keeps nbuf * buf_bytes in flight
@@ -160,12 +160,12 @@ MACO_DEVICE bool comm_push_bulk(const Program& p, const MacoCommArgs& a, BulkCtx
     for (uint32_t b = 0; b < used; ++b) {
       const uint64_t off = pos + (uint64_t)b * bc.buf_bytes;
       const uint32_t n = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
-      const uint32_t parity = (bc.phase >> b) & 1u;
+      const uint32_t parity = (*bc.phase >> b) & 1u;
       const uint64_t t0 = globaltimer_ns();
       while (!mbar_try_wait(&bc.bars[b], parity)) {
         if (globaltimer_ns() - t0 > budget_ns) { ok = false; break; }
       }
-      bc.phase ^= 1u << b;
+      *bc.phase = *bc.phase ^ (1u << b);
       if (!ok) break;
       const uint8_t* sm = bc.buf + (size_t)b * bc.buf_bytes;
       if (a.peer >= 0) {
@@ -185,6 +185,84 @@ MACO_DEVICE bool comm_push_bulk(const Program& p, const MacoCommArgs& a, BulkCtx
   return ok;
 }
 
+// Reduction with the sources staged through shared memory by the bulk-copy engine: the leader
+// thread keeps up to nbuf * buf_bytes of loads in flight (local slots or peers' heaps), all
+// threads sum the staged vectors in fp32 and write the result (to local memory with vector stores,
+// or, for an all-reduce, back into shared memory from where one bulk store per rank sends it).
+// `bar_sync` is the barrier of the calling thread group.
+template <typename Program, typename BarFn>
+MACO_DEVICE bool comm_reduce_bulk(const Program& p, const MacoCommArgs& a, int n, int tid, int nthreads, BulkCtx& bc,
+                                  BarFn bar_sync) {
+  uint8_t* mine = p.peer_heap[p.rank];
+  const bool local = a.op == MACO_COMM_REDUCE_LOCAL;
+  const bool bcast = a.op == MACO_COMM_ALLREDUCE;
+  uint8_t* out = a.local_ptr != nullptr ? reinterpret_cast<uint8_t*>(a.local_ptr) : mine + a.dst_off;
+  const uint64_t bytes = (uint64_t)a.rows * a.row_bytes;
+  const uint32_t groups = bc.nbuf / (uint32_t)n;             // chunk positions per round
+  const uint64_t round_bytes = (uint64_t)groups * bc.buf_bytes;
+  bool ok = true;
+  if (tid == 0) fence_proxy_async_all();
+  for (uint64_t pos = 0; pos < bytes; pos += round_bytes) {
+    const uint32_t phase = *bc.phase;                         // stable: the leader flips it between the two barriers below
+    uint32_t used_mask = 0;
+    for (uint32_t g = 0; g < groups; ++g) {
+      const uint64_t off = pos + (uint64_t)g * bc.buf_bytes;
+      if (off >= bytes) break;
+      const uint32_t nb = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
+      for (int j = 0; j < n; ++j) {
+        const uint32_t b = g * n + j;
+        used_mask |= 1u << b;
+        if (tid == 0) {
+          const uint8_t* src = local ? mine + a.src_off + (uint64_t)j * a.slot_stride
+                                     : p.peer_heap[(p.rank + j) % p.world] + a.src_off;
+          mbar_arrive_expect_tx(&bc.bars[b], nb);
+          bulk_load(bc.buf + (size_t)b * bc.buf_bytes, src + off, nb, &bc.bars[b]);
+        }
+      }
+    }
+    for (uint32_t g = 0; g < groups; ++g) {
+      const uint64_t off = pos + (uint64_t)g * bc.buf_bytes;
+      if (off >= bytes) break;
+      const uint32_t nb = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
+      for (int j = 0; j < n; ++j) {
+        const uint32_t b = g * n + j;
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(&bc.bars[b], (phase >> b) & 1u)) {
+          if (globaltimer_ns() - t0 > p.budget_ns) { ok = false; break; }
+        }
+      }
+      uint8_t* g0 = bc.buf + (size_t)(g * n) * bc.buf_bytes;
+      for (uint32_t v = tid; v < (nb >> 4); v += nthreads) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < n; ++j) add8(acc, *reinterpret_cast<const uint4*>(g0 + (size_t)j * bc.buf_bytes + ((size_t)v << 4)), a.dtype);
+        if (a.aux_ptr != nullptr) add8(acc, ldv(reinterpret_cast<const uint8_t*>(a.aux_ptr) + off + ((uint64_t)v << 4)), a.dtype);
+        const uint4 o = pack8(acc, a.scale, a.dtype);
+        if (bcast) *reinterpret_cast<uint4*>(g0 + ((size_t)v << 4)) = o;      // result replaces source 0 in shared memory
+        else stv(out + off + ((uint64_t)v << 4), o);
+      }
+    }
+    if (bcast) fence_proxy_async_smem();
+    bar_sync();                                              // staged data consumed (and results staged)
+    if (tid == 0) {
+      *bc.phase = phase ^ used_mask;
+      if (bcast) {
+        for (uint32_t g = 0; g < groups; ++g) {
+          const uint64_t off = pos + (uint64_t)g * bc.buf_bytes;
+          if (off >= bytes) break;
+          const uint32_t nb = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
+          for (int j = 0; j < p.world; ++j)
+            bulk_store(p.peer_heap[(p.rank + j) % p.world] + a.dst_off + off, bc.buf + (size_t)(g * n) * bc.buf_bytes, nb);
+        }
+        tma_store_commit();
+        tma_store_wait_read<0>();
+      }
+    }
+    bar_sync();                                              // phase word and buffers are ready for the next round
+  }
+  if (tid == 0 && bcast) tma_store_wait<0>();
+  return ok;
+}
+
 template <typename Program>
 MACO_DEVICE bool comm_run(const Program& p, const MacoTaskDesc& d, int tid, int nthreads, BulkCtx* bulk = nullptr) {
   const MacoCommArgs& a = d.u.comm;
@@ -193,6 +271,12 @@ MACO_DEVICE bool comm_run(const Program& p, const MacoTaskDesc& d, int tid, int 
     bool ok = true;
     if (tid == 0) ok = comm_push_bulk(p, a, *bulk, p.budget_ns);
     return ok;
+  }
+  if (bulk != nullptr && (a.op == MACO_COMM_REDUCE_LOCAL || a.op == MACO_COMM_REDUCE_PULL || a.op == MACO_COMM_ALLREDUCE) &&
+      a.src_stride == a.row_bytes && a.dst_stride == a.row_bytes && (uint64_t)a.rows * a.row_bytes >= 32768) {
+    const int n = a.op == MACO_COMM_REDUCE_LOCAL ? a.nslots : p.world;
+    if (n >= 1 && (uint32_t)n <= bulk->nbuf)
+      return comm_reduce_bulk(p, a, n, tid, nthreads, *bulk, [] { asm volatile("bar.sync 1, 128;" ::: "memory"); });
   }
   const uint32_t vpr = a.row_bytes >> 4;                     // 16-byte vectors per row
   const uint32_t total = a.rows * vpr;                      // blocks are far below 2^32 vectors

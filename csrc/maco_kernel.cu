@@ -155,6 +155,7 @@ __device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base,
     uint32_t task;
     if (!fetch_task(p, w, i, q_base, task, c.abort_word)) { ok = false; break; }
     if (task == MACO_QUEUE_TERMINATE) break;
+    task &= MACO_QUEUE_INDEX_MASK;
     const MacoTaskDesc d = load_desc(p, task);
     if (!is_gemm(d.type)) continue;
     if (!wait_deps(p, d, task, c.abort_word, nullptr)) { ok = false; break; }
@@ -187,6 +188,7 @@ __device__ void mma_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint
     uint32_t task;
     if (!fetch_task(p, w, i, q_base, task, c.abort_word)) break;
     if (task == MACO_QUEUE_TERMINATE) break;
+    task &= MACO_QUEUE_INDEX_MASK;
     const MacoTaskDesc d = load_desc(p, task);
     if (!is_gemm(d.type)) continue;
     const MacoGemmArgs& g = d.u.gemm;
@@ -214,7 +216,7 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
   const bool leader = tid == 0;
   // Communication workers never get GEMM tasks, so their operand ring is free to stage bulk copies.
   const bool comm_worker = p.num_comm_workers > 0 && w >= p.num_workers - p.num_comm_workers;
-  BulkCtx bulk{ring_smem, bulk_bars, kBulkBuffers, kBulkBufBytes, 0u};
+  BulkCtx bulk{ring_smem, bulk_bars, kBulkBuffers, kBulkBufBytes, slots + 12};   // phase word: zeroed at kernel start
   uint32_t seq = 0, done = 0;
   for (uint32_t i = 0;; ++i) {
     volatile uint32_t* cur = slots + (i & 1u) * 4;     // [0] task, [1] dependencies satisfied, [2] failure
@@ -225,12 +227,16 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
       cur[2] = 0;
     }
     general_bar();
-    const uint32_t task = cur[0];
-    if (task >= MACO_QUEUE_TERMINATE - 1) {
+    const uint32_t raw_entry = cur[0];
+    if (raw_entry >= MACO_QUEUE_TERMINATE - 1) {
+      const uint32_t task = raw_entry;
       // consume the TERMINATE entry too, so the next launch starts behind it
       if (leader && task == MACO_QUEUE_TERMINATE && p.mode == MACO_MODE_DYNAMIC) st_release_gpu_u32(&p.tails[w], q_base + i + 1);
       break;
     }
+    // bit 31 of a static queue entry: no GEMM task follows in this worker's queue, the operand ring is idle
+    const uint32_t task = raw_entry & MACO_QUEUE_INDEX_MASK;
+    const bool ring_free = comm_worker || (raw_entry & MACO_QUEUE_RING_FREE) != 0;
     const MacoTaskDesc d = load_desc(p, task);
     uint64_t t_start = 0, wait_ns = 0;
     if (leader && p.trace != nullptr) t_start = globaltimer_ns();
@@ -252,7 +258,7 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
       general_bar();
       if (cur[1] != 0) {
         if (d.type >= 200 && d.type < 300) {
-          if (!comm_run(p, d, tid, 128, comm_worker ? &bulk : nullptr)) {
+          if (!comm_run(p, d, tid, 128, ring_free ? &bulk : nullptr)) {
             cur[2] = 1;
             if (leader) report_failure(p, MACO_STATUS_BAD_TASK, task, d.u.comm.op, c.abort_word);
           }
@@ -386,6 +392,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) maco_persistent_kernel(const 
     uint64_t* bulk_bars = reinterpret_cast<uint64_t*>(extra + 32);          // bytes 128.. of the extra block
     if (threadIdx.x == 0) {
       extra[16] = p.mode == MACO_MODE_DYNAMIC ? ld_relaxed_gpu_u32(&p.tails[w]) : 0;
+      extra[12] = 0;                                                     // parity bits of the bulk barriers
       for (uint32_t b = 0; b < kBulkBuffers; ++b) mbar_init(&bulk_bars[b], 1);
       fence_mbar_init();
     }

@@ -180,6 +180,8 @@ struct MacoGroupDesc {
 };
 
 #define MACO_QUEUE_TERMINATE 0xffffffffu
+#define MACO_QUEUE_RING_FREE 0x80000000u   /* static queue entry: no GEMM task follows in this queue */
+#define MACO_QUEUE_INDEX_MASK 0x7fffffffu
 
 enum MacoKernelMode { MACO_MODE_STATIC = 0, MACO_MODE_DYNAMIC = 1 };
 

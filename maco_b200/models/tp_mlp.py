@@ -30,7 +30,7 @@ class TPSwiGLUMLP:
     def __init__(self, tokens: int, hidden: int, ffn: int, *, rank: int = 0, world: int = 1, heap=None,
                  device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16, seed: int = 0,
                  mode: str = "static", trace: bool = False, weight_std: float = 0.02, num_workers: Optional[int] = None,
-                 comm_workers: int = 8):
+                 comm_workers: Optional[int] = None):
         if tokens % (world * BM) or ffn % (world * 128):
             raise ValueError("tokens must be a multiple of world*128 and ffn of world*128")
         if world > 1 and heap is None:
@@ -46,6 +46,10 @@ class TPSwiGLUMLP:
         self.w_gate, self.w_up, self.w_down = mk(f_local, hidden), mk(f_local, hidden), mk(hidden, f_local)
         self.w_gate_up = interleave_gate_up(self.w_gate, self.w_up)
         dev = self.device
+        if comm_workers is None:
+            # one SM pushes roughly 25-30 GB/s into a peer; the shard has to reach world-1 peers before
+            # they run out of local rows to work on
+            comm_workers = 8 if world <= 2 else 16
         b = ProgramBuilder(dev, num_workers=num_workers, mode=mode, heap=heap, trace=trace,
                            num_comm_workers=(comm_workers if world > 1 else 0))
         self.h = torch.empty(tokens, f_local, device=dev, dtype=dtype)
