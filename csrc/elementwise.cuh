@@ -261,6 +261,12 @@ MACO_DEVICE bool elt_run(uint32_t type, const MacoEltArgs& a, int tid, int nthre
       elt_pointwise(type, a, tid, nthreads); return true;
     case MACO_TASK_RMSNORM: case MACO_TASK_LAYERNORM: case MACO_TASK_SOFTMAX:
       elt_rowwise(type, a, tid, nthreads); return true;
+    case MACO_TASK_FILL: {
+      uint32_t* o = reinterpret_cast<uint32_t*>(a.out);
+      const uint32_t n = (uint32_t)a.rows * (uint32_t)a.cols;
+      for (uint32_t i = tid; i < n; i += nthreads) o[i] = (uint32_t)a.i0;
+      return true;
+    }
     case MACO_TASK_ROPE:
       if (a.f1 == 0.f) elt_rope(a, tid, nthreads); else elt_qknorm_rope(a, tid, nthreads);
       return true;

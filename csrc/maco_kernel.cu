@@ -31,6 +31,7 @@
 #include "gemm_tcgen05.cuh"
 #include "comm_tasks.cuh"
 #include "attention_decode.cuh"
+#include "moe_tasks.cuh"
 #include "host_common.h"
 
 using namespace maco;
@@ -159,8 +160,10 @@ __device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base,
     const MacoTaskDesc d = load_desc(p, task);
     if (!is_gemm(d.type)) continue;
     if (!wait_deps(p, d, task, c.abort_word, nullptr)) { ok = false; break; }
-    fence_proxy_async_all();           // operands were written by generic-proxy stores of other CTAs
     const MacoGemmArgs& g = d.u.gemm;
+    // run-time guarded tile: every role reads the same (final) count after the task's conditions hold
+    if ((d.flags & MACO_TF_COUNTED) && ld_relaxed_gpu_u32(g.count_ptr) <= g.count_base) continue;
+    fence_proxy_async_all();           // operands were written by generic-proxy stores of other CTAs
     const CUtensorMap* ta = tmaps + g.tmap_a;
     const CUtensorMap* tb = tmaps + g.tmap_b;
     const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | (g.b_mn ? 1 : 0);
@@ -192,6 +195,10 @@ __device__ void mma_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint
     const MacoTaskDesc d = load_desc(p, task);
     if (!is_gemm(d.type)) continue;
     const MacoGemmArgs& g = d.u.gemm;
+    if (d.flags & MACO_TF_COUNTED) {
+      if (!wait_deps(p, d, task, c.abort_word, nullptr)) break;
+      if (ld_relaxed_gpu_u32(g.count_ptr) <= g.count_base) continue;
+    }
     const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | (g.b_mn ? 1 : 0);
     switch (sel) {
       case 0: ok = gemm_mma_tile<256, kMkStages, false, false, kMkBN>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
@@ -240,7 +247,19 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
     const MacoTaskDesc d = load_desc(p, task);
     uint64_t t_start = 0, wait_ns = 0;
     if (leader && p.trace != nullptr) t_start = globaltimer_ns();
-    if (is_gemm(d.type)) {
+    bool skip_tile = false;
+    if (is_gemm(d.type) && (d.flags & MACO_TF_COUNTED)) {
+      if (leader) {
+        const bool okw = wait_deps(p, d, task, c.abort_word, nullptr);
+        cur[1] = !okw ? 0u : (ld_relaxed_gpu_u32(d.u.gemm.count_ptr) <= d.u.gemm.count_base ? 2u : 1u);
+      }
+      general_bar();
+      if (cur[1] == 0) cur[2] = 1;
+      skip_tile = cur[1] != 1;
+    }
+    if (is_gemm(d.type) && skip_tile) {
+      // nothing to compute: the tile's rows hold no tokens (it still signals below)
+    } else if (is_gemm(d.type)) {
       const MacoGemmArgs& g = d.u.gemm;
       GemmEpilogue e = p.epis[g.epi];
       void* out_base = e.out;
@@ -264,6 +283,12 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
           }
         } else if (d.type == MACO_TASK_ATTENTION || d.type == MACO_TASK_ATTN_MERGE) {
           attn_run(d.type, d.u.elt, tid, 128, scratch_smem);
+        } else if (d.type == MACO_TASK_TOPK) {
+          moe_topk_dispatch(p, d.u.elt, tid, scratch_smem);
+        } else if (d.type == MACO_TASK_MOE_COUNTS) {
+          moe_publish_counts(p, d.u.elt, tid);
+        } else if (d.type == MACO_TASK_MOE_RETURN) {
+          moe_return(p, d.u.elt, tid, scratch_smem);
         } else if (d.type != MACO_TASK_NOP) {
           if (!elt_run(d.type, d.u.elt, tid, 128)) {
             cur[2] = 1;

@@ -36,6 +36,8 @@ enum MacoTaskType {
   MACO_TASK_ADD = 113,
   MACO_TASK_GELU_BWD = 114,
   MACO_TASK_AXPBY = 115,         /* out = f0 * in0 + f1 * in1 */
+  MACO_TASK_MOE_RETURN = 116,    /* expert output rows -> weighted -> back to the source rank's combine buffer */
+  MACO_TASK_MOE_COUNTS = 117,    /* publish this rank's per-expert token counts to the expert owners */
   MACO_TASK_CUSTOM_COMPUTE = 150,
   MACO_TASK_ALLREDUCE = 200,     /* reduce one chunk over all peers' buffers, write to all */
   MACO_TASK_ALLGATHER = 201,     /* push one chunk of the local shard to every peer */
@@ -44,7 +46,8 @@ enum MacoTaskType {
   MACO_TASK_BROADCAST = 204,
   MACO_TASK_PEER_BARRIER = 205,
   MACO_TASK_CUSTOM_COMM = 250,
-  MACO_TASK_COPY = 300
+  MACO_TASK_COPY = 300,
+  MACO_TASK_FILL = 301           /* out[0 .. rows*cols) 32-bit words = i0 */
 };
 
 /* ---- GEMM epilogue ------------------------------------------------------------------------ */
@@ -104,7 +107,8 @@ struct MacoGemmArgs {             /* one output tile */
   long long row_off;              /* added to the row index on store */
   uint64_t out_off;               /* with peer >= 0: byte offset of the destination inside the peer's heap */
   uint32_t bn;                    /* tile width: 128 or 256 */
-  uint32_t _pad;
+  uint32_t count_base;            /* MACO_TF_COUNTED: the tile is skipped when *count_ptr <= count_base */
+  const uint32_t* count_ptr;
 };
 
 struct MacoEltArgs {              /* row-wise / element-wise task over rows [row0, row0+rows) */
@@ -167,7 +171,9 @@ enum MacoTaskFlags {
   MACO_TF_COMM_WORKER = 4,        /* prefers a communication worker */
   MACO_TF_SIGNAL_SYS = 8,         /* local signals use .sys scope (another GPU polls them) */
   MACO_TF_WAIT0_PREV = 16,        /* wait_event[0] refers to the previous launch: (epoch-1) * count */
-  MACO_TF_WAIT1_PREV = 32
+  MACO_TF_WAIT1_PREV = 32,
+  MACO_TF_ANY_WORKER = 64,        /* host-side placement hint only */
+  MACO_TF_COUNTED = 128           /* GEMM tile guarded by a row count known only at run time (MoE) */
 };
 
 /* A dispatch group for the scheduler CTA: a run of consecutive tasks that becomes ready together. */
@@ -213,6 +219,20 @@ struct MacoProgram {
 #ifdef __cplusplus
 static_assert(sizeof(MacoTaskDesc) == 128, "task descriptor must stay 128 bytes");
 #endif
+
+/* ---- mixture-of-experts layer constants (one per layer, in device memory) --------------------- */
+struct MacoMoeParams {
+  const void* logits;             /* [tokens, experts] router output (16-bit) */
+  const void* x;                  /* [tokens, hidden] */
+  uint32_t* counts;               /* [experts] slots handed out by this rank, zero at launch start */
+  void* comb;                     /* [tokens, top_k, hidden] combine buffer of this rank (inside the heap) */
+  unsigned long long recv_off;    /* heap offset: recv [experts_per_rank][world][capacity][hidden] */
+  unsigned long long meta_off;    /* heap offset: meta [experts_per_rank][world][capacity] x {token, k, weight, -} */
+  unsigned long long cnt_off;     /* heap offset: received counts [world][experts_per_rank] (uint32) */
+  unsigned long long comb_off;    /* heap offset of comb */
+  const void* y;                  /* [experts_per_rank][world][capacity][hidden] expert outputs (local) */
+  int32_t hidden, experts, top_k, experts_per_rank, capacity, tokens, dtype, _pad;
+};
 
 /* ---- device trace ring ----------------------------------------------------------------------- */
 struct MacoTraceRecord {

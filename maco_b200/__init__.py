@@ -108,17 +108,22 @@ def init(backend: str = "nccl", rank: Optional[int] = None, world_size: Optional
         log.info("initialised: world=%d backend=%s device=%s", _world_size, pgm.backend, pgm.device)
 
 
-def cleanup() -> None:
+def cleanup(abort: bool = False) -> None:
+    """Tears down the heap, the overlap manager and the process group. ``abort=True`` is the path after
+    a peer was lost: nothing collective is attempted (no barrier, no graceful group shutdown)."""
     global _initialized, _overlap_manager
     if _overlap_manager is not None:
         _overlap_manager.sync_streams()
     try:
-        finalize_nvshmem()
+        finalize_nvshmem(collective=not abort)
     except Exception:
         pass
     m = ProcessGroupManager._instance
     if m is not None:
-        m.destroy()
+        if abort:
+            ProcessGroupManager._instance = None
+        else:
+            m.destroy()
     _overlap_manager = None
     _initialized = False
 

@@ -32,9 +32,9 @@ def init_nvshmem(heap_bytes: Optional[int] = None) -> bool:
     return True
 
 
-def finalize_nvshmem() -> None:
+def finalize_nvshmem(collective: bool = True) -> None:
     from ..parallel import symm_heap
-    symm_heap.destroy_heap()
+    symm_heap.destroy_heap(collective=collective)
 
 
 def nvshmem_my_pe() -> int:

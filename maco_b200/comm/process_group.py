@@ -195,6 +195,17 @@ class ProcessGroupManager:
         return lost
 
 
+def ensure_peers(step: int, timeout_s: float = 5.0) -> None:
+    """Publishes this rank's heartbeat for ``step`` and raises PeerLostError when a peer has not reached
+    it (or has announced that it left). Call between steps, before launching anything that waits on peers."""
+    from ..task_graph.exceptions import PeerLostError
+    m = ProcessGroupManager()
+    m.heartbeat(step)
+    lost = m.check_peers(step, timeout_s=timeout_s)
+    if lost:
+        raise PeerLostError(lost[0], f"ranks {lost} did not reach step {step}")
+
+
 def _mgr() -> ProcessGroupManager:
     return ProcessGroupManager()
 

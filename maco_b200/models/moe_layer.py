@@ -1,0 +1,188 @@
+"""Expert-parallel mixture-of-experts layer (softmax top-k routing, SwiGLU experts) in one launch.
+
+Per rank, inside the persistent kernel:
+
+1. router GEMM (tcgen05): ``logits = x Wr^T``
+2. TOPK tasks: per token the top-k experts and their renormalised softmax weights; a slot in the
+   chosen expert's receive slab is taken with an atomic counter and the token row goes, by one bulk
+   copy per expert, straight into that slab on the GPU that owns the expert (dispatch all-to-all
+   fused with the router permute), with a {token, k, weight} record beside it
+3. the per-expert counts are published to the expert owners
+4. grouped expert GEMMs over the slabs: gate/up with SwiGLU in the epilogue, then down; tiles whose
+   128-row block holds no tokens are skipped by all roles of the worker (run-time counted tiles)
+5. MOE_RETURN tasks scale every valid output row by its routing weight and send it back into the
+   source rank's combine buffer at [token, k] (combine all-to-all)
+6. the source sums the k rows of every token.
+
+Receive slabs have a fixed capacity per (source rank, expert); routed pairs that do not fit are
+dropped for that expert (zero contribution) and counted in ``dropped()``.
+
+The reference simulates expert parallelism with equal splits on one GPU and a dummy all_to_all node
+(examples/benchmark_all_to_all.py:31-127): no router, no top-k, no permute, no variable splits.
+"""
+from __future__ import annotations
+
+import ctypes
+import struct
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import _native as N
+from ..ops import interleave_gate_up
+from ..ops.megakernel import BM, COMM_REDUCE_LOCAL, ProgramBuilder, RowEvents, _pack_comm, _pack_elt
+from ..parallel import fused
+from ..parallel.symm_heap import LocalHeap
+from ..task_graph.nodes import TaskType
+
+T_TOPK, T_MOE_RETURN, T_MOE_COUNTS, T_FILL = 110, 116, 117, 301
+
+
+def heap_bytes_needed(hidden: int, experts: int, top_k: int, tokens: int, world: int, capacity: int) -> int:
+    el = experts // world
+    return (el * world * capacity * (hidden * 2 + 16) + world * el * 4 + tokens * top_k * hidden * 2 + (8 << 20))
+
+
+class MoEEPLayer:
+    def __init__(self, hidden: int = 2048, experts: int = 128, top_k: int = 8, inter: int = 768, tokens: int = 4096, *,
+                 rank: int = 0, world: int = 1, heap=None, device: Optional[torch.device] = None,
+                 dtype: torch.dtype = torch.bfloat16, capacity_factor: float = 2.0, seed: int = 0, mode: str = "static",
+                 trace: bool = False, weight_std: float = 0.02, router_std: float = 0.02):
+        if experts % world or tokens % BM or inter % 128 or hidden % 256:
+            raise ValueError("experts % world, tokens % 128, inter % 128 and hidden % 256 must be 0")
+        if top_k > 8 or experts > 256 or hidden * 2 * 4 > 20480:
+            raise ValueError("supported: top_k <= 8, experts <= 256, hidden <= 2560")
+        dev = self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.hidden, self.experts, self.top_k, self.inter, self.tokens = hidden, experts, top_k, inter, tokens
+        self.rank, self.world, self.dtype = rank, world, dtype
+        self.el = experts // world
+        mean = tokens * top_k / experts
+        self.capacity = max(BM, int(-(-mean * capacity_factor // BM)) * BM)
+        if heap is None:
+            if world > 1:
+                raise ValueError("world > 1 needs the symmetric heap")
+            heap = LocalHeap(heap_bytes_needed(hidden, experts, top_k, tokens, world, self.capacity), dev)
+        self.heap = heap
+        EL, W, C, H, I, T, K = self.el, world, self.capacity, hidden, inter, tokens, top_k
+        g_shared = torch.Generator(device="cpu").manual_seed(seed * 131 + 7)
+        self.w_router = (torch.randn(experts, H, generator=g_shared) * router_std).to(dtype).to(dev)
+        # every expert's weights come from its own seed, so any rank can rebuild them for a check
+        self._seed, self._wstd = seed, weight_std
+        w1, w2 = [], []
+        self.w_gate, self.w_up, self.w_down = [], [], []
+        for el in range(EL):
+            wg, wu, wd = self.expert_weights(rank * EL + el)
+            self.w_gate.append(wg); self.w_up.append(wu); self.w_down.append(wd)
+            w1.append(interleave_gate_up(wg, wu))
+            w2.append(wd)
+        self.w1 = torch.stack(w1)                                   # [EL, 2I, H], gate/up interleaved per 256 rows
+        self.w2 = torch.stack(w2)                                   # [EL, H, I]
+        self.x = torch.empty(T, H, device=dev, dtype=dtype)
+        self.logits = torch.empty(T, experts, device=dev, dtype=dtype)
+        self.counts = torch.zeros(experts + 1, device=dev, dtype=torch.int32)
+        self.recv = heap.alloc((EL, W, C, H), dtype)
+        self.meta = heap.alloc((EL, W, C, 4), torch.int32)
+        self.cnt = heap.alloc((W, EL), torch.int32)
+        self.comb = heap.alloc((T, K, H), dtype)
+        self.act = torch.zeros(EL, W, C, I, device=dev, dtype=dtype)
+        self.y = torch.zeros(EL, W, C, H, device=dev, dtype=dtype)
+        self.out = torch.empty(T, H, device=dev, dtype=dtype)
+        params = struct.pack("<QQQQQQQQQiiiiiiii", self.logits.data_ptr(), self.x.data_ptr(), self.counts.data_ptr(),
+                             self.comb.data_ptr(), heap.offset_of(self.recv), heap.offset_of(self.meta),
+                             heap.offset_of(self.cnt), heap.offset_of(self.comb), self.y.data_ptr(), H, experts, K, EL, C, T,
+                             N.DTYPE_CODE[dtype], 0)
+        self.d_params = torch.from_numpy(np.frombuffer(params, dtype=np.uint8).copy()).to(dev)
+        self._build(mode, trace)
+
+    def expert_weights(self, e: int):
+        g = torch.Generator(device="cpu").manual_seed(self._seed * 100003 + 17 * e + 1)
+        mk = lambda *s: (torch.randn(*s, generator=g) * self._wstd).to(self.dtype).to(self.device)
+        return mk(self.inter, self.hidden), mk(self.inter, self.hidden), mk(self.hidden, self.inter)
+
+    # ------------------------------------------------------------------ program
+    def _build(self, mode: str, trace: bool) -> None:
+        EL, W, C, H, I, T, K = self.el, self.world, self.capacity, self.hidden, self.inter, self.tokens, self.top_k
+        dt = N.DTYPE_CODE[self.dtype]
+        b = ProgramBuilder(self.device, mode=mode, heap=self.heap, trace=trace)
+        pp = self.d_params.data_ptr()
+        fence = fused.epoch_fence_event(b)
+        # 0. clear this rank's slot counters (first task of the launch; everything that follows is ordered behind it)
+        e_fill = b.new_event()
+        b.add_task(T_FILL, _pack_elt(0, 0, 0, self.counts.data_ptr(), 0, 1, self.experts + 1, 2, 0, 0, i0=0), waits=[fence],
+                   signals=[e_fill])
+        # 1. router
+        e_log = b.gemm(self.x, self.w_router, self.logits, bn=128, extra_waits=[(e_fill, 1, False, False)])
+        # 2. top-k + dispatch, 32 tokens per task
+        e_disp_local = b.new_event()
+        n_disp = 0
+        for t0 in range(0, T, 32):
+            ev, cnt = e_log.for_rows(t0, t0 + 32)
+            b.add_task(T_TOPK, _pack_elt(0, 0, pp, 0, t0, 32, H, dt, 0, 0), waits=[(ev, cnt, False, False)],
+                       signals=[e_disp_local])
+            n_disp += 1
+        # 3. counts to the expert owners; every rank learns that every rank has dispatched
+        e_disp = b.new_event()
+        b.add_task(T_MOE_COUNTS, _pack_elt(0, 0, pp, 0, 0, 0, 0, dt, 0, 0), waits=[(e_disp_local, n_disp, False, False)],
+                   signal_peer=-2, signal_peer_event=e_disp)
+        arrived = (e_disp, W, True, False)
+        # 4. expert GEMMs over the slabs, tiles guarded by the received counts; 5. weighted return
+        e_ret = b.new_event()
+        cnt_base = self.cnt.data_ptr()
+        for el in range(EL):
+            for s in range(W):
+                cptr = cnt_base + (s * EL + el) * 4
+                guard = lambda mb, nb, cptr=cptr: dict(count_ptr=cptr, count_base=mb * BM)
+                e_act = b.gemm(self.recv[el, s], self.w1[el], self.act[el, s], epilogue="swiglu", bn=256,
+                               extra_waits=[arrived], per_tile=guard)
+                e_y = b.gemm(self.act[el, s], self.w2[el], self.y[el, s], bn=256, a_ready=e_act, per_tile=guard)
+                for rb in range(C // BM):
+                    ev, cnt = e_y.for_rows(rb * BM, (rb + 1) * BM)
+                    b.add_task(T_MOE_RETURN, _pack_elt(0, 0, pp, 0, rb * BM, BM, H, dt, 0, 0, i0=el, i1=s),
+                               waits=[(ev, cnt, False, False)], signal_peer=s, signal_peer_event=e_ret)
+        n_ret = W * EL * (C // BM)
+        # 6. combine: sum the k rows of every token
+        row_bytes = H * 2
+        comb_off = self.heap.offset_of(self.comb)
+        e_out = b.new_event()
+        n_out = 0
+        for t0 in range(0, T, 32):
+            raw = _pack_comm(comb_off + t0 * K * row_bytes, 0, K * row_bytes, row_bytes, row_bytes, 32, dt, -1,
+                             COMM_REDUCE_LOCAL, nslots=K, slot_stride=row_bytes,
+                             local_ptr=self.out.data_ptr() + t0 * row_bytes)
+            b.add_task(int(TaskType.REDUCE_SCATTER), raw, waits=[(e_ret, n_ret, True, False)], signals=[e_out])
+            n_out += 1
+        fused.epoch_fence_signal(b, [(e_out, n_out, False, False)])
+        self.program = b.build()
+
+    def forward(self, x: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        if x is not None:
+            self.x.copy_(x, non_blocking=True)
+        self.program.run(stream=stream)
+        return self.out
+
+    __call__ = forward
+
+    def dropped(self) -> int:
+        """(token, expert) pairs of the last step that exceeded a slab's capacity."""
+        return int(self.counts[self.experts].item())
+
+    # ------------------------------------------------------------------ oracle
+    def reference(self, x: torch.Tensor) -> torch.Tensor:
+        """fp32 PyTorch result for this rank's tokens (rebuilds every expert's weights from its seed)."""
+        F = torch.nn.functional
+        bf = lambda t: t.to(self.dtype).float()
+        xf = x.float()
+        logits = bf(xf @ self.w_router.float().t())
+        # same tie rule as the kernel: larger logit first, lower expert index on equal logits
+        sval, sidx = torch.sort(logits, dim=-1, descending=True, stable=True)
+        val, idx = sval[:, : self.top_k], sidx[:, : self.top_k]
+        w = torch.softmax(val, dim=-1)
+        out = torch.zeros_like(xf)
+        for e in torch.unique(idx).tolist():
+            wg, wu, wd = self.expert_weights(e)
+            tok, k = (idx == e).nonzero(as_tuple=True)
+            h = bf(F.silu(xf[tok] @ wg.float().t()) * (xf[tok] @ wu.float().t()))
+            y = bf(h @ wd.float().t())
+            out.index_add_(0, tok, bf(y * w[tok, k].unsqueeze(1)))
+        return out

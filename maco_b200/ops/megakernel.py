@@ -27,6 +27,7 @@ QUEUE_TERMINATE = 0xFFFFFFFF
 MODE_STATIC, MODE_DYNAMIC = 0, 1
 TF_WAIT0_SYS, TF_WAIT1_SYS, TF_COMM_WORKER, TF_SIGNAL_SYS, TF_WAIT0_PREV, TF_WAIT1_PREV = 1, 2, 4, 8, 16, 32
 TF_ANY_WORKER = 64      # host-side placement hint: spread over compute AND communication workers
+TF_COUNTED = 128        # GEMM tile guarded by a run-time row count
 COMM_PUSH, COMM_REDUCE_LOCAL, COMM_REDUCE_PULL, COMM_ALLREDUCE, COMM_ALLREDUCE_MC, COMM_PULL = range(6)
 MAX_PEERS = 16
 WORKER_QUEUE_SIZE = 1024
@@ -84,9 +85,10 @@ def _lib():
     return lib
 
 
-def _pack_gemm(tmap_a, tmap_b, epi, a_mn, b_mn, m0, n0, k0, k_blocks, idesc, peer, row_off, out_off, bn) -> bytes:
-    return struct.pack("<HHHBBiiiiIiqQII", tmap_a, tmap_b, epi, a_mn, b_mn, m0, n0, k0, k_blocks, idesc, peer, row_off,
-                       out_off, bn, 0)
+def _pack_gemm(tmap_a, tmap_b, epi, a_mn, b_mn, m0, n0, k0, k_blocks, idesc, peer, row_off, out_off, bn, count_base=0,
+               count_ptr=0) -> bytes:
+    return struct.pack("<HHHBBiiiiIiqQIIQ", tmap_a, tmap_b, epi, a_mn, b_mn, m0, n0, k0, k_blocks, idesc, peer, row_off,
+                       out_off, bn, count_base, count_ptr or 0)
 
 
 def _pack_elt(in0, in1, in2, out, row0, rows, cols, dtype, ld_in, ld_out, f0=0.0, f1=0.0, i0=0, i1=0) -> bytes:
@@ -164,7 +166,8 @@ class ProgramBuilder:
 
     def add_task(self, ttype: int, raw: bytes, waits: Sequence[Tuple[int, int, bool, bool]] = (),
                  signals: Sequence[int] = (), signal_peer: int = -1, signal_peer_event: int = -1, node_id: int = 0,
-                 comm_worker: bool = False, signal_sys: bool = False, any_worker: bool = False) -> int:
+                 comm_worker: bool = False, signal_sys: bool = False, any_worker: bool = False,
+                 counted: bool = False) -> int:
         """``waits``: up to two (event, count, sys_scope, previous_epoch)."""
         if len(waits) > 2 or len(signals) > 2:
             raise ValueError("a task takes at most two wait conditions and two local signals")
@@ -182,6 +185,8 @@ class ProgramBuilder:
             flags |= TF_SIGNAL_SYS
         if any_worker:
             flags |= TF_ANY_WORKER
+        if counted:
+            flags |= TF_COUNTED
         se = list(signals) + [-1] * (2 - len(signals))
         self.tasks.append(dict(type=ttype, flags=flags, node_id=node_id, wait_event=we, wait_count=wc, signal_event=se,
                                signal_peer=signal_peer, signal_peer_event=signal_peer_event, raw=raw))
@@ -277,10 +282,11 @@ class ProgramBuilder:
                         waits = self.join(waits, node_id)
                     ov = per_tile(mb, nb) if per_tile is not None else {}
                     raw = _pack_gemm(ta, tb, epi, int(trans_a), int(trans_b), mb * BM, nb * bn, 0, k_blocks, idesc,
-                                     ov.get("peer", -1), ov.get("row_off", 0), ov.get("out_off", 0), bn)
+                                     ov.get("peer", -1), ov.get("row_off", 0), ov.get("out_off", 0), bn,
+                                     ov.get("count_base", 0), ov.get("count_ptr", 0))
                     self.add_task(int(TaskType.LINEAR), raw, waits=waits, signals=[row_events[mb], all_ev],
                                   signal_peer=ov.get("signal_peer", -1), signal_peer_event=ov.get("signal_peer_event", -1),
-                                  node_id=node_id, signal_sys=signal_sys)
+                                  node_id=node_id, signal_sys=signal_sys, counted=bool(ov.get("count_ptr", 0)))
         total = len(mbs) * n_tiles
         return RowEvents(rows=M, block=BM, row_events=[(row_events.get(mb, all_ev), n_tiles) if mb in row_events
                                                        else (all_ev, total) for mb in range(m_tiles)],

@@ -130,6 +130,37 @@ class SymmetricHeap:
         self._closed = True
 
 
+class LocalHeap:
+    """A one-rank stand-in with the interface of :class:`SymmetricHeap`: programs whose tasks address
+    buffers as "heap base + offset" (the MoE and fused-collective tasks) run unchanged on a single GPU."""
+
+    def __init__(self, nbytes: int, device: Optional[torch.device] = None):
+        self.rank, self.world = 0, 1
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.nbytes = (int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN
+        self._whole = torch.zeros(self.nbytes, dtype=torch.uint8, device=self.device)
+        self._base = self._whole.data_ptr()
+        self._cursor = 0
+
+    alloc = SymmetricHeap.alloc
+    owns = SymmetricHeap.owns
+    offset_of = SymmetricHeap.offset_of
+    mark = SymmetricHeap.mark
+    release_to = SymmetricHeap.release_to
+
+    def peer_base(self, r: int) -> int:
+        return self._base
+
+    def multicast_base(self) -> int:
+        return 0
+
+    def peer_view(self, t: torch.Tensor, r: int) -> torch.Tensor:
+        return t
+
+    def close(self) -> None:
+        self._whole = None
+
+
 def init_heap(nbytes: Optional[int] = None) -> SymmetricHeap:
     """Creates the process-wide heap over the current process group (idempotent)."""
     global _current
@@ -151,12 +182,15 @@ def current_heap() -> Optional[SymmetricHeap]:
     return _current
 
 
-def destroy_heap() -> None:
+def destroy_heap(collective: bool = True) -> None:
+    """Unmaps the peers and frees the heap. ``collective=False`` skips the barrier (use it after a peer
+    was lost: a barrier with a dead rank would never return)."""
     global _current
     if _current is not None:
         from ..comm.process_group import barrier
         try:
-            barrier()
+            if collective:
+                barrier()
         except Exception:
             pass
         from . import collectives

@@ -43,3 +43,20 @@ def test_qwen3_decode_layer_single_gpu(mode):
         err = (out.float() - ref).abs().max().item()
         assert err < 4e-2 * max(1.0, ref.abs().max().item()), err
     assert _native.status() == 0
+
+
+@pytest.mark.parametrize("mode", ["static", "dynamic"])
+def test_moe_layer_single_gpu(mode):
+    from maco_b200 import _native
+    from maco_b200.models.moe_layer import MoEEPLayer
+    layer = MoEEPLayer(hidden=256, experts=8, top_k=2, inter=128, tokens=256, capacity_factor=4.0, seed=3, mode=mode,
+                       weight_std=0.05, router_std=0.5)
+    x = torch.randn(256, 256, device="cuda", dtype=torch.bfloat16)
+    ref = layer.reference(x)
+    for _ in range(2):
+        out = layer(x)
+        torch.cuda.synchronize()
+        assert layer.dropped() == 0
+        err = (out.float() - ref).abs().max().item()
+        assert err < 4e-2 * max(1.0, ref.abs().max().item()), err
+    assert _native.status() == 0

@@ -152,3 +152,62 @@ def _qwen3(rank, world):
 
 def test_qwen3_decode_layer_tensor_parallel():
     run_ranks(_qwen3, 2, env=ENV, timeout=100)
+
+
+def _moe(rank, world):
+    maco, heap = _setup(rank, world, heap_mb=64)
+    from maco_b200 import _native
+    from maco_b200.models.moe_layer import MoEEPLayer
+    layer = MoEEPLayer(hidden=256, experts=8, top_k=2, inter=128, tokens=256, rank=rank, world=world, heap=heap,
+                       capacity_factor=4.0, seed=3, weight_std=0.05, router_std=0.5)
+    torch.manual_seed(100 + rank)
+    x = torch.randn(256, 256, device="cuda", dtype=torch.bfloat16)          # every rank has its own tokens
+    ref = layer.reference(x)
+    for it in range(3):
+        out = layer(x)
+        torch.cuda.synchronize()
+        assert layer.dropped() == 0
+        err = (out.float() - ref).abs().max().item()
+        assert err < 4e-2 * max(1.0, ref.abs().max().item()), (it, err)
+    assert _native.status() == 0
+    maco.cleanup()
+
+
+def test_moe_expert_parallel_dispatch_combine():
+    run_ranks(_moe, 2, env=ENV, timeout=100)
+
+
+def _peer_loss(rank, world):
+    """Rank 1 leaves between steps with nothing in flight; rank 0 learns of it on the host (heartbeat in
+    the rendezvous store) before its next launch, raises PeerLostError and shuts down without collectives."""
+    import os
+    maco, heap = _setup(rank, world, heap_mb=32)
+    from maco_b200 import PeerLostError, _native
+    from maco_b200.comm.process_group import ProcessGroupManager, ensure_peers
+    from maco_b200.parallel import collectives
+    t = heap.alloc((1 << 16,), torch.float32)
+    for step in (1, 2):
+        ensure_peers(step, timeout_s=20.0)
+        t.fill_(float(rank + 1))
+        collectives.all_reduce(t)
+        torch.cuda.synchronize()
+        assert torch.all(t == world * (world + 1) / 2)
+    pgm = ProcessGroupManager()
+    if rank == 1:
+        pgm.heartbeat(2)
+        pgm.announce_exit()
+        torch.cuda.synchronize()
+        os._exit(0)                       # gone; no kernel or collective of this rank is in flight
+    lost = None
+    try:
+        ensure_peers(3, timeout_s=10.0)
+    except PeerLostError as exc:
+        lost = exc.rank
+    assert lost == 1
+    assert _native.status() == 0
+    maco.cleanup(abort=True)
+    os._exit(0)
+
+
+def test_peer_loss_detected_before_the_next_launch():
+    run_ranks(_peer_loss, 2, env=ENV, timeout=100)
