@@ -58,7 +58,8 @@ def timed(torch, dist, world, steps, fn):
 def cfg_tp_mlp(torch, dist, rank, world, heap, args):
     from maco_b200.models.tp_mlp import TPSwiGLUMLP
     T, H, F = 8192, 4096, 14336
-    layer = TPSwiGLUMLP(T, H, F, rank=rank, world=world, heap=heap, mode=args.mode)
+    layer = TPSwiGLUMLP(T, H, F, rank=rank, world=world, heap=heap, mode=args.mode, trace=args.trace)
+    args.program = layer.program
     layer.x_shard.normal_()
     rows = T // world
     x_shard = layer.x_shard.clone()
@@ -85,7 +86,8 @@ def cfg_tp_mlp(torch, dist, rank, world, heap, args):
 def cfg_dp_backward(torch, dist, rank, world, heap, args):
     from maco_b200.models.dp_mlp_stack import DPMLPStackBackward
     L, H, T = args.layers, 4096, 8192
-    m = DPMLPStackBackward(L, H, T, rank=rank, world=world, heap=heap, mode=args.mode)
+    m = DPMLPStackBackward(L, H, T, rank=rank, world=world, heap=heap, mode=args.mode, trace=args.trace)
+    args.program = m.program
     m.forward()
     grads = [torch.empty(H, H, device="cuda", dtype=torch.float32) for _ in range(L)]
     comm = torch.cuda.Stream()
@@ -123,7 +125,8 @@ def cfg_dp_backward(torch, dist, rank, world, heap, args):
 
 def cfg_qwen3_decode(torch, dist, rank, world, heap, args):
     from maco_b200.models.qwen3_layer import Qwen3DecodeLayer
-    layer = Qwen3DecodeLayer(rank=rank, world=world, heap=heap, mode=args.mode)
+    layer = Qwen3DecodeLayer(rank=rank, world=world, heap=heap, mode=args.mode, trace=args.trace)
+    args.program = layer.program
     layer.x.normal_()
     F = torch.nn.functional
     B, D, hq, hkv, G = layer.batch, layer.D, layer.hq, layer.hkv, layer.G
@@ -161,8 +164,63 @@ def cfg_qwen3_decode(torch, dist, rank, world, heap, args):
     return (lambda: layer.forward(None)), library, roof
 
 
-CONFIGS = {"tp_mlp": cfg_tp_mlp, "dp_backward": cfg_dp_backward, "qwen3_decode": cfg_qwen3_decode}
-HEAP_MB = {"tp_mlp": 256, "dp_backward": 1400, "qwen3_decode": 64}
+def cfg_moe(torch, dist, rank, world, heap, args):
+    from maco_b200.models.moe_layer import MoEEPLayer
+    H, E, K, I, T = 2048, 128, 8, 768, 4096
+    layer = MoEEPLayer(H, E, K, I, T, rank=rank, world=world, heap=heap if world > 1 else None, mode=args.mode, trace=args.trace)
+    args.program = layer.program
+    layer.x.normal_()
+    F = torch.nn.functional
+    EL = E // world
+    wg, wu, wd = torch.stack(layer.w_gate), torch.stack(layer.w_up), torch.stack(layer.w_down)
+
+    def library():
+        # the usual library formulation: top-k, sort by expert, variable-split all-to-all, per-expert GEMMs, return
+        x = layer.x
+        val, idx = torch.topk(x @ layer.w_router.t(), K, dim=-1)
+        w = torch.softmax(val.float(), -1)
+        flat = idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        send = x[order // K]
+        counts = torch.bincount(flat, minlength=E)
+        if world > 1:
+            recv_counts = torch.empty_like(counts)
+            dist.all_to_all_single(recv_counts, counts)
+            in_splits = counts.view(world, EL).sum(1).tolist()
+            out_splits = recv_counts.view(world, EL).sum(1).tolist()
+            recv = torch.empty(sum(out_splits), H, device=x.device, dtype=x.dtype)
+            dist.all_to_all_single(recv, send, out_splits, in_splits)
+            per = recv_counts.view(world, EL)
+        else:
+            recv, per, in_splits, out_splits = send, counts.view(1, EL), None, None
+        # rows arrive grouped by source rank, then by expert: walk the (source, expert) segments
+        out_rows = torch.empty_like(recv)
+        seg = per.reshape(-1).tolist()
+        pos = 0
+        for i, n in enumerate(seg):
+            if n:
+                el = i % EL
+                xs = recv[pos:pos + n]
+                out_rows[pos:pos + n] = (F.silu(xs @ wg[el].t()) * (xs @ wu[el].t())) @ wd[el].t()
+            pos += n
+        if world > 1:
+            back = torch.empty_like(send)
+            dist.all_to_all_single(back, out_rows, in_splits, out_splits)
+        else:
+            back = out_rows
+        res = torch.zeros(T, H, device=x.device, dtype=torch.float32)
+        res.index_add_(0, order // K, back.float() * w.reshape(-1)[order].unsqueeze(1))
+        return res.to(x.dtype)
+
+    p = peaks()
+    flops = T * K * 2.0 * (3 * H * I) + 2.0 * T * H * E
+    link = T * K * H * 2 * (world - 1) / world
+    roof = {"compute_us": flops / (p["bf16_tflops_sustained"] * 1e12) * 1e6, "nvlink_us": 2 * link / (p["nvlink_gbs"] * 1e9) * 1e6}
+    return (lambda: layer.forward(None)), library, roof
+
+
+CONFIGS = {"tp_mlp": cfg_tp_mlp, "dp_backward": cfg_dp_backward, "qwen3_decode": cfg_qwen3_decode, "moe": cfg_moe}
+HEAP_MB = {"tp_mlp": 256, "dp_backward": 1400, "qwen3_decode": 64, "moe": 700}
 
 
 def main():
@@ -174,6 +232,7 @@ def main():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--mode", default="static", choices=["static", "dynamic"])
     ap.add_argument("--arms", default="library,ours")
+    ap.add_argument("--trace", action="store_true", help="record the device task trace of one step and print per-type statistics")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
@@ -207,6 +266,8 @@ def main():
                     "warmup": args.warmup, "roofline_us": {k: round(v, 1) for k, v in roof.items()},
                     "fraction_of_roofline": round(bound / us, 3), "peaks": p["source"], "kernel_status": _native.status(clear=False)}
             os.write(real_stdout, (json.dumps(line) + "\n").encode())
+            if arm == "ours" and args.trace:
+                os.write(real_stdout, (json.dumps({"config": args.config, "trace": args.program.stats()}) + "\n").encode())
     if world > 1:
         maco.cleanup()
 

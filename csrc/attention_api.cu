@@ -21,7 +21,7 @@ struct AttnParams {
 };
 
 __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
-  __shared__ __align__(16) uint8_t scratch_smem[(2 * kAttnMaxG * kAttnD + 8 * kAttnMaxG) * 4];
+  __shared__ __align__(16) uint8_t scratch_smem[kAttnScratchBytes];
   const int split = blockIdx.x % p.splits;
   const int bh = blockIdx.x / p.splits;            // b * Hkv + kvh
   const int b = bh / p.Hkv, kvh = bh % p.Hkv;

@@ -24,11 +24,16 @@ constexpr int kAttnMaxG = 8;
 
 __device__ __forceinline__ void attn_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// Shared memory needed by attn_decode_task.
+constexpr int kAttnVStageKeys = 64;
+constexpr int kAttnScratchBytes = (2 * kAttnMaxG * kAttnD + 8 * kAttnMaxG) * 4 + kAttnVStageKeys * kAttnD * 2;
+
 MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratch) {
   const int G = a.i0 < kAttnMaxG ? a.i0 : kAttnMaxG;
   float* q_s = reinterpret_cast<float*>(scratch);                 // [G][128]
   float* p_s = q_s + kAttnMaxG * kAttnD;                          // [G][128] probabilities of the chunk
-  float* red = p_s + kAttnMaxG * kAttnD;                          // [4][G] cross-warp scratch, then [G] results
+  float* red = p_s + kAttnMaxG * kAttnD;                          // [4][G] cross-warp scratch
+  uint16_t* v_s = reinterpret_cast<uint16_t*>(red + 8 * kAttnMaxG);   // [64][128] staged V rows (16-byte aligned)
   const int warp = tid >> 5, lane = tid & 31;
   for (int i = tid; i < G * kAttnD; i += 128) q_s[i] = load1(a.in0, i, a.dtype) * a.f0;
   float m_run[kAttnMaxG], l_run[kAttnMaxG], o[kAttnMaxG];
@@ -43,26 +48,27 @@ MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratc
     float s[kAttnMaxG];
 #pragma unroll
     for (int g = 0; g < kAttnMaxG; ++g) s[g] = 0.f;
-    if (valid) {
-      const uint4* krow = reinterpret_cast<const uint4*>(K + (long long)j * a.ld_in);
-#pragma unroll 4
-      for (int v = 0; v < kAttnD / 8; ++v) {
-        const uint4 u = ld_global_nc_v4(krow + v);
-        float kf[8];
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    // one key row per thread: all 16 vector loads of the row are issued before the first use
+    uint4 kr[kAttnD / 8];
+    const uint4* krow = reinterpret_cast<const uint4*>(K + (long long)(valid ? j : 0) * a.ld_in);
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          float2 f = a.dtype == MACO_DT_BF16 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
-          kf[2 * t] = f.x; kf[2 * t + 1] = f.y;
-        }
+    for (int v = 0; v < kAttnD / 8; ++v) kr[v] = valid ? ld_global_nc_v4(krow + v) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int g = 0; g < kAttnMaxG; ++g) {
-          if (g < G) {
-            const float4 q0 = *reinterpret_cast<const float4*>(q_s + g * kAttnD + v * 8);
-            const float4 q1 = *reinterpret_cast<const float4*>(q_s + g * kAttnD + v * 8 + 4);
-            s[g] += q0.x * kf[0] + q0.y * kf[1] + q0.z * kf[2] + q0.w * kf[3] + q1.x * kf[4] + q1.y * kf[5] +
-                    q1.z * kf[6] + q1.w * kf[7];
-          }
+    for (int v = 0; v < kAttnD / 8; ++v) {
+      float kf[8];
+      const uint32_t w[4] = {kr[v].x, kr[v].y, kr[v].z, kr[v].w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        float2 f = a.dtype == MACO_DT_BF16 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+        kf[2 * t] = f.x; kf[2 * t + 1] = f.y;
+      }
+#pragma unroll
+      for (int g = 0; g < kAttnMaxG; ++g) {
+        if (g < G) {
+          const float4 q0 = *reinterpret_cast<const float4*>(q_s + g * kAttnD + v * 8);
+          const float4 q1 = *reinterpret_cast<const float4*>(q_s + g * kAttnD + v * 8 + 4);
+          s[g] += q0.x * kf[0] + q0.y * kf[1] + q0.z * kf[2] + q0.w * kf[3] + q1.x * kf[4] + q1.y * kf[5] +
+                  q1.z * kf[6] + q1.w * kf[7];
         }
       }
     }
@@ -90,38 +96,54 @@ MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratc
       float sm = warp_sum(s[g]);
       if (lane == 0) red[warp * kAttnMaxG + g] = sm;
     }
-    // P·V for this chunk: thread `tid` owns output dimension `tid` of every head
 #pragma unroll
     for (int g = 0; g < kAttnMaxG; ++g) o[g] *= corr[g];
+    // P·V: V rows are staged 64 at a time with coalesced 16-byte loads (8 per thread in flight);
+    // thread `tid` then owns output dimension `tid` of every head and reads the staged rows.
     const int nk = min(128, a.rows - base);
-    const uint16_t* vcol = V + (long long)base * a.ld_in + tid;
-    int jj = 0;
-    for (; jj + 4 <= nk; jj += 4) {
-      float vv[4];
+    for (int h0 = 0; h0 < nk; h0 += kAttnVStageKeys) {
+      const int hk = min(kAttnVStageKeys, nk - h0);
+      const uint4* vsrc = reinterpret_cast<const uint4*>(V + (long long)(base + h0) * a.ld_in);
+      const int nvec = hk * (kAttnD / 8);
+      if (a.ld_in == kAttnD) {
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const uint16_t raw = vcol[(long long)(jj + t) * a.ld_in];
-        vv[t] = a.dtype == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
+        for (int u = 0; u < kAttnVStageKeys * (kAttnD / 8) / 128; ++u) {
+          const int i = tid + u * 128;
+          if (i < nvec) reinterpret_cast<uint4*>(v_s)[i] = ld_global_nc_v4(vsrc + i);
+        }
+      } else {
+        for (int i = tid; i < nvec; i += 128)
+          reinterpret_cast<uint4*>(v_s)[i] = ld_global_nc_v4(reinterpret_cast<const uint4*>(V + (long long)(base + h0 + i / 16) * a.ld_in) + (i & 15));
       }
+      attn_bar();
+      int jj = 0;
+      for (; jj + 4 <= hk; jj += 4) {
+        float vv[4];
 #pragma unroll
-      for (int g = 0; g < kAttnMaxG; ++g) {
-        if (g < G) {
-          const float4 pp = *reinterpret_cast<const float4*>(p_s + g * kAttnD + jj);
-          o[g] += pp.x * vv[0] + pp.y * vv[1] + pp.z * vv[2] + pp.w * vv[3];
+        for (int t = 0; t < 4; ++t) {
+          const uint16_t raw = v_s[(jj + t) * kAttnD + tid];
+          vv[t] = a.dtype == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
+        }
+#pragma unroll
+        for (int g = 0; g < kAttnMaxG; ++g) {
+          if (g < G) {
+            const float4 pp = *reinterpret_cast<const float4*>(p_s + g * kAttnD + h0 + jj);
+            o[g] += pp.x * vv[0] + pp.y * vv[1] + pp.z * vv[2] + pp.w * vv[3];
+          }
         }
       }
-    }
-    for (; jj < nk; ++jj) {
-      const uint16_t raw = vcol[(long long)jj * a.ld_in];
-      const float v1 = a.dtype == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
+      for (; jj < hk; ++jj) {
+        const uint16_t raw = v_s[jj * kAttnD + tid];
+        const float v1 = a.dtype == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
 #pragma unroll
-      for (int g = 0; g < kAttnMaxG; ++g) if (g < G) o[g] += p_s[g * kAttnD + jj] * v1;
+        for (int g = 0; g < kAttnMaxG; ++g) if (g < G) o[g] += p_s[g * kAttnD + h0 + jj] * v1;
+      }
+      attn_bar();                                 // v_s free for the next half
     }
-    attn_bar();                                   // partial sums in red complete, p_s free for the next chunk
 #pragma unroll
     for (int g = 0; g < kAttnMaxG; ++g)
       l_run[g] = l_run[g] * corr[g] + red[g] + red[kAttnMaxG + g] + red[2 * kAttnMaxG + g] + red[3 * kAttnMaxG + g];
-    attn_bar();                                   // red free for the next chunk
+    attn_bar();                                   // red and p_s free for the next chunk
   }
   float* out = reinterpret_cast<float*>(a.out);
 #pragma unroll

@@ -42,6 +42,33 @@ MACO_DEVICE F8 load8(const void* base, long long idx, int dtype) {
   return r;
 }
 
+// Raw 8-element fetch (one 16-byte vector for 16-bit types, two for fp32) and its conversion, kept
+// apart so that a loop can issue several fetches before it touches the first value.
+MACO_DEVICE void load8_raw(const void* base, long long idx, int dtype, uint4& lo, uint4& hi) {
+  if (dtype == MACO_DT_F32) {
+    const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(base) + idx);
+    lo = p[0]; hi = p[1];
+  } else {
+    lo = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + idx);
+    hi = lo;
+  }
+}
+MACO_DEVICE F8 cvt8(int dtype, uint4 lo, uint4 hi) {
+  F8 r;
+  if (dtype == MACO_DT_F32) {
+    r.v[0] = __uint_as_float(lo.x); r.v[1] = __uint_as_float(lo.y); r.v[2] = __uint_as_float(lo.z); r.v[3] = __uint_as_float(lo.w);
+    r.v[4] = __uint_as_float(hi.x); r.v[5] = __uint_as_float(hi.y); r.v[6] = __uint_as_float(hi.z); r.v[7] = __uint_as_float(hi.w);
+  } else {
+    uint32_t w[4] = {lo.x, lo.y, lo.z, lo.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = dtype == MACO_DT_BF16 ? unpack_bf16x2(w[i]) : __half22float2(*reinterpret_cast<__half2*>(&w[i]));
+      r.v[2 * i] = f.x; r.v[2 * i + 1] = f.y;
+    }
+  }
+  return r;
+}
+
 MACO_DEVICE void store8(void* base, long long idx, int dtype, const F8& r) {
   if (dtype == MACO_DT_F32) {
     float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + idx);
@@ -101,23 +128,52 @@ MACO_DEVICE bool elt_is_binary(uint32_t type) {
   return type == MACO_TASK_ADD || type == MACO_TASK_SILU_GATE || type == MACO_TASK_GELU_BWD || type == MACO_TASK_AXPBY;
 }
 
-MACO_DEVICE void elt_pointwise(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
-  const bool bin = elt_is_binary(type);
-  if (elt_vec_ok(a)) {
-    const uint32_t vpr = a.cols / 8;                  // vectors per row
-    const uint32_t total = (uint32_t)a.rows * vpr;    // one task's rows: far below 2^32 (64-bit division is emulated)
-    for (uint32_t i = tid; i < total; i += nthreads) {
-      const uint32_t rr = i / vpr;
+// Vector path, specialised on the element type so that the fetch loop is branch-free and the
+// compiler issues all U fetches of a pass before the first use. With only four warps per SM the
+// loop is bound by how many loads each thread keeps in flight, not by arithmetic.
+template <int DT, int U>
+MACO_DEVICE void elt_pointwise_vec(uint32_t type, const MacoEltArgs& a, int tid, int nthreads, bool bin) {
+  const uint32_t vpr = a.cols / 8;                  // vectors per row
+  const uint32_t total = (uint32_t)a.rows * vpr;    // one task's rows: far below 2^32 (64-bit division is emulated)
+  for (uint32_t base = tid; base < total; base += (uint32_t)nthreads * U) {
+    uint4 xl[U], xh[U], yl[U], yh[U];
+    long long io[U], oo[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t i = base + (uint32_t)u * nthreads;
+      const uint32_t ii = i < total ? i : 0;
+      const uint32_t rr = ii / vpr;
       const long long r = a.row0 + rr;
-      const int c = (int)(i - rr * vpr) * 8;
-      F8 x = load8(a.in0, r * a.ld_in + c, a.dtype);
+      const int c = (int)(ii - rr * vpr) * 8;
+      io[u] = r * a.ld_in + c; oo[u] = r * a.ld_out + c;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) load8_raw(a.in0, io[u], DT, xl[u], xh[u]);
+    if (bin) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) load8_raw(a.in1, io[u], DT, yl[u], yh[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t i = base + (uint32_t)u * nthreads;
+      if (i >= total) continue;
+      const F8 x = cvt8(DT, xl[u], xh[u]);
       F8 y;
-      if (bin) y = load8(a.in1, r * a.ld_in + c, a.dtype);
+      if (bin) y = cvt8(DT, yl[u], yh[u]);
       F8 o;
 #pragma unroll
       for (int j = 0; j < 8; ++j) o.v[j] = elt_apply(type, x.v[j], bin ? y.v[j] : 0.f, a);
-      store8(a.out, r * a.ld_out + c, a.dtype, o);
+      store8(a.out, oo[u], DT, o);
     }
+  }
+}
+
+MACO_DEVICE void elt_pointwise(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
+  const bool bin = elt_is_binary(type);
+  if (elt_vec_ok(a)) {
+    if (a.dtype == MACO_DT_BF16) elt_pointwise_vec<MACO_DT_BF16, 8>(type, a, tid, nthreads, bin);
+    else if (a.dtype == MACO_DT_F16) elt_pointwise_vec<MACO_DT_F16, 8>(type, a, tid, nthreads, bin);
+    else elt_pointwise_vec<MACO_DT_F32, 4>(type, a, tid, nthreads, bin);
   } else {
     const uint32_t total = (uint32_t)a.rows * (uint32_t)a.cols;
     for (uint32_t i = tid; i < total; i += nthreads) {
@@ -138,15 +194,27 @@ MACO_DEVICE void elt_pointwise(uint32_t type, const MacoEltArgs& a, int tid, int
 MACO_DEVICE void elt_rowwise(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
   const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
   const bool vec = elt_vec_ok(a);
+  constexpr int U = 4;                                   // 16-byte vectors per lane fetched together
   for (int rr = warp; rr < a.rows; rr += nwarps) {
     const long long r = a.row0 + rr;
     const long long ib = r * a.ld_in, ob = r * a.ld_out;
     float s1 = 0.f, s2 = 0.f, mx = -INFINITY;
     if (vec) {
-      for (int c = lane * 8; c < a.cols; c += 256) {
-        F8 x = load8(a.in0, ib + c, a.dtype);
+      for (int c0 = lane * 8; c0 < a.cols; c0 += 256 * U) {
+        uint4 lo[U], hi[U];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { s1 += x.v[j]; s2 += x.v[j] * x.v[j]; mx = fmaxf(mx, x.v[j]); }
+        for (int u = 0; u < U; ++u) {
+          const int c = c0 + u * 256;
+          if (c < a.cols) load8_raw(a.in0, ib + c, a.dtype, lo[u], hi[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (c0 + u * 256 < a.cols) {
+            const F8 x = cvt8(a.dtype, lo[u], hi[u]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { s1 += x.v[j]; s2 += x.v[j] * x.v[j]; mx = fmaxf(mx, x.v[j]); }
+          }
+        }
       }
     } else {
       for (int c = lane; c < a.cols; c += 32) {
@@ -177,24 +245,39 @@ MACO_DEVICE void elt_rowwise(uint32_t type, const MacoEltArgs& a, int tid, int n
       denom = 1.f / warp_sum(e);
     }
     if (vec) {
-      for (int c = lane * 8; c < a.cols; c += 256) {
-        F8 x = load8(a.in0, ib + c, a.dtype);
-        F8 o;
-        if (type == MACO_TASK_SOFTMAX) {
+      // second pass: the row is in L1/L2 now; fetch row and parameters in batches again
+      for (int c0 = lane * 8; c0 < a.cols; c0 += 256 * U) {
+        uint4 lo[U], hi[U], wl[U], wh[U];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o.v[j] = __expf(x.v[j] - mx) * denom;
-        } else {
-          F8 w = load8(a.in1, c, a.dtype);
-          if (type == MACO_TASK_RMSNORM) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o.v[j] = x.v[j] * rstd * w.v[j];
-          } else {
-            F8 b = load8(a.in2, c, a.dtype);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o.v[j] = (x.v[j] - mean) * rstd * w.v[j] + b.v[j];
+        for (int u = 0; u < U; ++u) {
+          const int c = c0 + u * 256;
+          if (c < a.cols) {
+            load8_raw(a.in0, ib + c, a.dtype, lo[u], hi[u]);
+            if (type != MACO_TASK_SOFTMAX) load8_raw(a.in1, c, a.dtype, wl[u], wh[u]);
           }
         }
-        store8(a.out, ob + c, a.dtype, o);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int c = c0 + u * 256;
+          if (c >= a.cols) continue;
+          const F8 x = cvt8(a.dtype, lo[u], hi[u]);
+          F8 o;
+          if (type == MACO_TASK_SOFTMAX) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o.v[j] = __expf(x.v[j] - mx) * denom;
+          } else {
+            const F8 w = cvt8(a.dtype, wl[u], wh[u]);
+            if (type == MACO_TASK_RMSNORM) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o.v[j] = x.v[j] * rstd * w.v[j];
+            } else {
+              F8 b = load8(a.in2, c, a.dtype);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o.v[j] = (x.v[j] - mean) * rstd * w.v[j] + b.v[j];
+            }
+          }
+          store8(a.out, ob + c, a.dtype, o);
+        }
       }
     } else {
       for (int c = lane; c < a.cols; c += 32) {

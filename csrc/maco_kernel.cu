@@ -42,10 +42,12 @@ constexpr int kMkBN = 256;
 constexpr int kMkStages = 4;
 using MkLayout = GemmSmemLayout<kMkBN, kMkStages>;
 constexpr int kMkExtraSmem = 1024;     // scheduler heads / current-task slots live after the GEMM control block
-constexpr int kMkScratchSmem = 20480;  // scratch of non-GEMM tasks (the operand ring is NOT free for them:
+constexpr int kMkScratchSmem = 28672;  // scratch of non-GEMM tasks (the operand ring is NOT free for them:
                                        // the producer warp may already be filling it for the next GEMM task)
 constexpr int kMkSmemBytes = MkLayout::kTotalBytes + kMkExtraSmem + kMkScratchSmem;
 static_assert(kMkScratchSmem >= kEpiStageBytes, "epilogue staging must fit the scratch block");
+static_assert(kMkScratchSmem >= kAttnScratchBytes, "attention scratch must fit the scratch block");
+static_assert(kMkSmemBytes <= 227 * 1024, "persistent kernel exceeds the shared memory of an SM");
 constexpr uint32_t kBulkBufBytes = 16384;                                  // staging buffers of bulk pushes
 constexpr uint32_t kBulkBuffers = MkLayout::kRingBytes / kBulkBufBytes;    // the whole operand ring
 static_assert(kBulkBuffers <= 16, "phase bits / barrier slots");
@@ -214,6 +216,21 @@ __device__ void mma_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint
   }
 }
 
+// Non-GEMM task bodies are kept out of line: each gets its own register allocation, so the
+// unrolled copy / reduce / attention loops cannot push spills into the GEMM epilogue.
+__device__ __noinline__ bool run_elt(uint32_t type, const MacoEltArgs& a, int tid) { return elt_run(type, a, tid, 128); }
+__device__ __noinline__ bool run_comm(const MacoProgram& p, const MacoTaskDesc& d, int tid, BulkCtx* bulk) {
+  return comm_run(p, d, tid, 128, bulk);
+}
+__device__ __noinline__ void run_attn(uint32_t type, const MacoEltArgs& a, int tid, uint8_t* scratch) {
+  attn_run(type, a, tid, 128, scratch);
+}
+__device__ __noinline__ void run_moe(const MacoProgram& p, uint32_t type, const MacoEltArgs& a, int tid, uint8_t* scratch) {
+  if (type == MACO_TASK_TOPK) moe_topk_dispatch(p, a, tid, scratch);
+  else if (type == MACO_TASK_MOE_COUNTS) moe_publish_counts(p, a, tid);
+  else moe_return(p, a, tid, scratch);
+}
+
 // ---- general warps (128 threads): GEMM epilogues and every non-GEMM task -------------------------
 // Control words shared by the 128 threads are double buffered by iteration parity, so the
 // leader can prepare iteration i+1 while slower threads still read the words of iteration i.
@@ -277,20 +294,16 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
       general_bar();
       if (cur[1] != 0) {
         if (d.type >= 200 && d.type < 300) {
-          if (!comm_run(p, d, tid, 128, ring_free ? &bulk : nullptr)) {
+          if (!run_comm(p, d, tid, ring_free ? &bulk : nullptr)) {
             cur[2] = 1;
             if (leader) report_failure(p, MACO_STATUS_BAD_TASK, task, d.u.comm.op, c.abort_word);
           }
         } else if (d.type == MACO_TASK_ATTENTION || d.type == MACO_TASK_ATTN_MERGE) {
-          attn_run(d.type, d.u.elt, tid, 128, scratch_smem);
-        } else if (d.type == MACO_TASK_TOPK) {
-          moe_topk_dispatch(p, d.u.elt, tid, scratch_smem);
-        } else if (d.type == MACO_TASK_MOE_COUNTS) {
-          moe_publish_counts(p, d.u.elt, tid);
-        } else if (d.type == MACO_TASK_MOE_RETURN) {
-          moe_return(p, d.u.elt, tid, scratch_smem);
+          run_attn(d.type, d.u.elt, tid, scratch_smem);
+        } else if (d.type == MACO_TASK_TOPK || d.type == MACO_TASK_MOE_COUNTS || d.type == MACO_TASK_MOE_RETURN) {
+          run_moe(p, d.type, d.u.elt, tid, scratch_smem);
         } else if (d.type != MACO_TASK_NOP) {
-          if (!elt_run(d.type, d.u.elt, tid, 128)) {
+          if (!run_elt(d.type, d.u.elt, tid)) {
             cur[2] = 1;
             if (leader) report_failure(p, MACO_STATUS_BAD_TASK, task, d.type, c.abort_word);
           }

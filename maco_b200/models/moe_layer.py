@@ -129,17 +129,24 @@ class MoEEPLayer:
         # 4. expert GEMMs over the slabs, tiles guarded by the received counts; 5. weighted return
         e_ret = b.new_event()
         cnt_base = self.cnt.data_ptr()
-        for el in range(EL):
-            for s in range(W):
-                cptr = cnt_base + (s * EL + el) * 4
-                guard = lambda mb, nb, cptr=cptr: dict(count_ptr=cptr, count_base=mb * BM)
-                e_act = b.gemm(self.recv[el, s], self.w1[el], self.act[el, s], epilogue="swiglu", bn=256,
-                               extra_waits=[arrived], per_tile=guard)
-                e_y = b.gemm(self.act[el, s], self.w2[el], self.y[el, s], bn=256, a_ready=e_act, per_tile=guard)
-                for rb in range(C // BM):
-                    ev, cnt = e_y.for_rows(rb * BM, (rb + 1) * BM)
-                    b.add_task(T_MOE_RETURN, _pack_elt(0, 0, pp, 0, rb * BM, BM, H, dt, 0, 0, i0=el, i1=s),
-                               waits=[(ev, cnt, False, False)], signal_peer=s, signal_peer_event=e_ret)
+        # Phase order matters with static queues: a worker that is handed a down-projection tile right
+        # behind the gate/up tiles of the same slab would idle until those finish. All gate/up tiles come
+        # first, then all down tiles, then the returns, so a dependent task is always far behind its producers.
+        pairs = [(el, s) for el in range(EL) for s in range(W)]
+        guards, acts, ys = {}, {}, {}
+        for el, s in pairs:
+            cptr = cnt_base + (s * EL + el) * 4
+            guards[el, s] = (lambda mb, nb, cptr=cptr: dict(count_ptr=cptr, count_base=mb * BM))
+            acts[el, s] = b.gemm(self.recv[el, s], self.w1[el], self.act[el, s], epilogue="swiglu", bn=256,
+                                 extra_waits=[arrived], per_tile=guards[el, s])
+        for el, s in pairs:
+            ys[el, s] = b.gemm(self.act[el, s], self.w2[el], self.y[el, s], bn=256, a_ready=acts[el, s],
+                               per_tile=guards[el, s])
+        for el, s in pairs:
+            for rb in range(C // BM):
+                ev, cnt = ys[el, s].for_rows(rb * BM, (rb + 1) * BM)
+                b.add_task(T_MOE_RETURN, _pack_elt(0, 0, pp, 0, rb * BM, BM, H, dt, 0, 0, i0=el, i1=s),
+                           waits=[(ev, cnt, False, False)], signal_peer=s, signal_peer_event=e_ret)
         n_ret = W * EL * (C // BM)
         # 6. combine: sum the k rows of every token
         row_bytes = H * 2

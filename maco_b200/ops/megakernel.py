@@ -323,6 +323,10 @@ class ProgramBuilder:
         esz = in0.element_size()
         if rows_per_task is None:
             target = max(1, (256 * 1024) // max(1, cols * esz))       # ~256 KiB of input per task
+            if rows * cols * esz <= (4 << 20):
+                # small operands (decode): latency matters more than per-task overhead; spread the rows over
+                # as many workers as there are, one row per warp for the row-wise operators
+                target = min(target, max(4 if ttype in (103, 104, 107) else 1, -(-rows // self.num_workers)))
             rows_per_task = 1
             while rows_per_task * 2 <= min(target, BM):
                 rows_per_task *= 2
@@ -509,7 +513,10 @@ class Program:
             name = TaskType(int(ty)).name if int(ty) in TaskType._value2member_map_ else str(int(ty))
             busy = (sel["t_end_ns"] - sel["t_start_ns"]).astype(np.float64)
             out["by_type"][name] = {"count": int(sel.size), "busy_us": float(busy.sum()) / 1e3,
-                                    "wait_us": float(sel["wait_ns"].sum()) / 1e3, "mean_us": float(busy.mean()) / 1e3}
+                                    "wait_us": float(sel["wait_ns"].sum()) / 1e3, "mean_us": float(busy.mean()) / 1e3,
+                                    "max_us": float(busy.max()) / 1e3,
+                                    "first_start_us": float(sel["t_start_ns"].min() - t0) / 1e3,
+                                    "last_end_us": float(sel["t_end_ns"].max() - t0) / 1e3}
         return out
 
     def chrome_trace(self) -> List[dict]:
