@@ -232,6 +232,7 @@ def main():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--mode", default="static", choices=["static", "dynamic"])
     ap.add_argument("--arms", default="library,ours")
+    ap.add_argument("--trace-file", default="", help="with --trace: write the Chrome-trace JSON of rank 0 here")
     ap.add_argument("--trace", action="store_true", help="record the device task trace of one step and print per-type statistics")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
@@ -268,6 +269,9 @@ def main():
             os.write(real_stdout, (json.dumps(line) + "\n").encode())
             if arm == "ours" and args.trace:
                 os.write(real_stdout, (json.dumps({"config": args.config, "trace": args.program.stats()}) + "\n").encode())
+                if args.trace_file:
+                    with open(args.trace_file, "w") as f:        # Chrome-trace events, one row per SM
+                        json.dump(args.program.chrome_trace(), f)
     if world > 1:
         maco.cleanup()
 

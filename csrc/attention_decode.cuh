@@ -28,14 +28,16 @@ __device__ __forceinline__ void attn_bar() { asm volatile("bar.sync 1, 128;" :::
 constexpr int kAttnVStageKeys = 64;
 constexpr int kAttnScratchBytes = (2 * kAttnMaxG * kAttnD + 8 * kAttnMaxG) * 4 + kAttnVStageKeys * kAttnD * 2;
 
-MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratch) {
+template <int DTT>
+__device__ __noinline__ void attn_decode_task_t(const MacoEltArgs& ar, int tid, uint8_t* scratch) {
+  const MacoEltArgs a = ar;
   const int G = a.i0 < kAttnMaxG ? a.i0 : kAttnMaxG;
   float* q_s = reinterpret_cast<float*>(scratch);                 // [G][128]
   float* p_s = q_s + kAttnMaxG * kAttnD;                          // [G][128] probabilities of the chunk
   float* red = p_s + kAttnMaxG * kAttnD;                          // [4][G] cross-warp scratch
   uint16_t* v_s = reinterpret_cast<uint16_t*>(red + 8 * kAttnMaxG);   // [64][128] staged V rows (16-byte aligned)
   const int warp = tid >> 5, lane = tid & 31;
-  for (int i = tid; i < G * kAttnD; i += 128) q_s[i] = load1(a.in0, i, a.dtype) * a.f0;
+  for (int i = tid; i < G * kAttnD; i += 128) q_s[i] = load1(a.in0, i, DTT) * a.f0;
   float m_run[kAttnMaxG], l_run[kAttnMaxG], o[kAttnMaxG];
 #pragma unroll
   for (int g = 0; g < kAttnMaxG; ++g) { m_run[g] = -INFINITY; l_run[g] = 0.f; o[g] = 0.f; }
@@ -59,7 +61,7 @@ MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratc
       const uint32_t w[4] = {kr[v].x, kr[v].y, kr[v].z, kr[v].w};
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
-        float2 f = a.dtype == MACO_DT_BF16 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+        float2 f = DTT == MACO_DT_BF16 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
         kf[2 * t] = f.x; kf[2 * t + 1] = f.y;
       }
 #pragma unroll
@@ -122,7 +124,7 @@ MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratc
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           const uint16_t raw = v_s[(jj + t) * kAttnD + tid];
-          vv[t] = a.dtype == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
+          vv[t] = DTT == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
         }
 #pragma unroll
         for (int g = 0; g < kAttnMaxG; ++g) {
@@ -134,7 +136,7 @@ MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratc
       }
       for (; jj < hk; ++jj) {
         const uint16_t raw = v_s[jj * kAttnD + tid];
-        const float v1 = a.dtype == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
+        const float v1 = DTT == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
 #pragma unroll
         for (int g = 0; g < kAttnMaxG; ++g) if (g < G) o[g] += p_s[g * kAttnD + h0 + jj] * v1;
       }
@@ -155,6 +157,11 @@ MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratc
     out[G * kAttnD + tid] = mg;
     out[G * kAttnD + G + tid] = lg;
   }
+}
+
+MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratch) {
+  if (a.dtype == MACO_DT_BF16) attn_decode_task_t<MACO_DT_BF16>(a, tid, scratch);
+  else attn_decode_task_t<MACO_DT_F16>(a, tid, scratch);
 }
 
 MACO_DEVICE void attn_merge_task(const MacoEltArgs& a, int tid) {

@@ -68,8 +68,8 @@ MACO_DEVICE uint64_t blk_off(uint32_t i, uint32_t vpr, uint64_t stride) {
 }
 
 // out = scale * (sum over n sources (+ aux)); kR vectors per thread per pass, loads of kS sources issued together.
-template <int kR, int kS, typename Program>
-MACO_DEVICE void comm_reduce(const Program& p, const MacoCommArgs& a, int n, uint32_t total, uint32_t vpr, int tid,
+template <int DTT, int kR, int kS, typename Program>
+__device__ __noinline__ void comm_reduce(const Program& p, const MacoCommArgs& a, int n, uint32_t total, uint32_t vpr, int tid,
                              int nthreads) {
   uint8_t* mine = p.peer_heap[p.rank];
   const bool local = a.op == MACO_COMM_REDUCE_LOCAL;
@@ -103,7 +103,7 @@ MACO_DEVICE void comm_reduce(const Program& p, const MacoCommArgs& a, int n, uin
       for (int jj = 0; jj < kS; ++jj) {
         if (j0 + jj < n) {
 #pragma unroll
-          for (int u = 0; u < kR; ++u) add8(acc[u], v[jj][u], a.dtype);
+          for (int u = 0; u < kR; ++u) add8(acc[u], v[jj][u], DTT);
         }
       }
     }
@@ -111,14 +111,14 @@ MACO_DEVICE void comm_reduce(const Program& p, const MacoCommArgs& a, int n, uin
 #pragma unroll
       for (int u = 0; u < kR; ++u) {
         const uint32_t i = base + (uint32_t)u * nthreads;
-        if (i < total) add8(acc[u], ldv(reinterpret_cast<const uint8_t*>(a.aux_ptr) + blk_off(i, vpr, a.dst_stride)), a.dtype);
+        if (i < total) add8(acc[u], ldv(reinterpret_cast<const uint8_t*>(a.aux_ptr) + blk_off(i, vpr, a.dst_stride)), DTT);
       }
     }
 #pragma unroll
     for (int u = 0; u < kR; ++u) {
       const uint32_t i = base + (uint32_t)u * nthreads;
       if (i >= total) continue;
-      const uint4 o = pack8(acc[u], a.scale, a.dtype);
+      const uint4 o = pack8(acc[u], a.scale, DTT);
       if (a.op == MACO_COMM_ALLREDUCE) {
         for (int j = 0; j < p.world; ++j)
           stv(p.peer_heap[(p.rank + j) % p.world] + a.dst_off + blk_off(i, vpr, a.dst_stride), o);
@@ -190,8 +190,8 @@ MACO_DEVICE bool comm_push_bulk(const Program& p, const MacoCommArgs& a, BulkCtx
 // threads sum the staged vectors in fp32 and write the result (to local memory with vector stores,
 // or, for an all-reduce, back into shared memory from where one bulk store per rank sends it).
 // `bar_sync` is the barrier of the calling thread group.
-template <typename Program, typename BarFn>
-MACO_DEVICE bool comm_reduce_bulk(const Program& p, const MacoCommArgs& a, int n, int tid, int nthreads, BulkCtx& bc,
+template <int DTT, typename Program, typename BarFn>
+__device__ __noinline__ bool comm_reduce_bulk(const Program& p, const MacoCommArgs& a, int n, int tid, int nthreads, BulkCtx& bc,
                                   BarFn bar_sync) {
   uint8_t* mine = p.peer_heap[p.rank];
   const bool local = a.op == MACO_COMM_REDUCE_LOCAL;
@@ -234,9 +234,9 @@ MACO_DEVICE bool comm_reduce_bulk(const Program& p, const MacoCommArgs& a, int n
       uint8_t* g0 = bc.buf + (size_t)(g * n) * bc.buf_bytes;
       for (uint32_t v = tid; v < (nb >> 4); v += nthreads) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < n; ++j) add8(acc, *reinterpret_cast<const uint4*>(g0 + (size_t)j * bc.buf_bytes + ((size_t)v << 4)), a.dtype);
-        if (a.aux_ptr != nullptr) add8(acc, ldv(reinterpret_cast<const uint8_t*>(a.aux_ptr) + off + ((uint64_t)v << 4)), a.dtype);
-        const uint4 o = pack8(acc, a.scale, a.dtype);
+        for (int j = 0; j < n; ++j) add8(acc, *reinterpret_cast<const uint4*>(g0 + (size_t)j * bc.buf_bytes + ((size_t)v << 4)), DTT);
+        if (a.aux_ptr != nullptr) add8(acc, ldv(reinterpret_cast<const uint8_t*>(a.aux_ptr) + off + ((uint64_t)v << 4)), DTT);
+        const uint4 o = pack8(acc, a.scale, DTT);
         if (bcast) *reinterpret_cast<uint4*>(g0 + ((size_t)v << 4)) = o;      // result replaces source 0 in shared memory
         else stv(out + off + ((uint64_t)v << 4), o);
       }
@@ -275,8 +275,12 @@ MACO_DEVICE bool comm_run(const Program& p, const MacoTaskDesc& d, int tid, int 
   if (bulk != nullptr && (a.op == MACO_COMM_REDUCE_LOCAL || a.op == MACO_COMM_REDUCE_PULL || a.op == MACO_COMM_ALLREDUCE) &&
       a.src_stride == a.row_bytes && a.dst_stride == a.row_bytes && (uint64_t)a.rows * a.row_bytes >= 32768) {
     const int n = a.op == MACO_COMM_REDUCE_LOCAL ? a.nslots : p.world;
-    if (n >= 1 && (uint32_t)n <= bulk->nbuf)
-      return comm_reduce_bulk(p, a, n, tid, nthreads, *bulk, [] { asm volatile("bar.sync 1, 128;" ::: "memory"); });
+    if (n >= 1 && (uint32_t)n <= bulk->nbuf) {
+      auto bar = [] { asm volatile("bar.sync 1, 128;" ::: "memory"); };
+      if (a.dtype == MACO_DT_F32) return comm_reduce_bulk<MACO_DT_F32>(p, a, n, tid, nthreads, *bulk, bar);
+      if (a.dtype == MACO_DT_F16) return comm_reduce_bulk<MACO_DT_F16>(p, a, n, tid, nthreads, *bulk, bar);
+      return comm_reduce_bulk<MACO_DT_BF16>(p, a, n, tid, nthreads, *bulk, bar);
+    }
   }
   const uint32_t vpr = a.row_bytes >> 4;                     // 16-byte vectors per row
   const uint32_t total = a.rows * vpr;                      // blocks are far below 2^32 vectors
@@ -321,9 +325,14 @@ MACO_DEVICE bool comm_run(const Program& p, const MacoTaskDesc& d, int tid, int 
     case MACO_COMM_ALLREDUCE: {
       const int n = a.op == MACO_COMM_REDUCE_LOCAL ? a.nslots : p.world;
       // 8 independent 16-byte loads per thread in flight whatever the number of sources (more spills registers)
-      if (n <= 2) comm_reduce<4, 2>(p, a, n, total, vpr, tid, nthreads);
-      else if (n <= 4) comm_reduce<2, 4>(p, a, n, total, vpr, tid, nthreads);
-      else comm_reduce<1, 8>(p, a, n, total, vpr, tid, nthreads);
+#define MACO_REDUCE_DT(DT)                                                         \
+      if (n <= 2) comm_reduce<DT, 4, 2>(p, a, n, total, vpr, tid, nthreads);       \
+      else if (n <= 4) comm_reduce<DT, 2, 4>(p, a, n, total, vpr, tid, nthreads);  \
+      else comm_reduce<DT, 2, 8>(p, a, n, total, vpr, tid, nthreads);
+      if (a.dtype == MACO_DT_F32) { MACO_REDUCE_DT(MACO_DT_F32) }
+      else if (a.dtype == MACO_DT_F16) { MACO_REDUCE_DT(MACO_DT_F16) }
+      else { MACO_REDUCE_DT(MACO_DT_BF16) }
+#undef MACO_REDUCE_DT
       return true;
     }
     case MACO_COMM_ALLREDUCE_MC: {

@@ -128,11 +128,30 @@ MACO_DEVICE bool elt_is_binary(uint32_t type) {
   return type == MACO_TASK_ADD || type == MACO_TASK_SILU_GATE || type == MACO_TASK_GELU_BWD || type == MACO_TASK_AXPBY;
 }
 
-// Vector path, specialised on the element type so that the fetch loop is branch-free and the
-// compiler issues all U fetches of a pass before the first use. With only four warps per SM the
-// loop is bound by how many loads each thread keeps in flight, not by arithmetic.
-template <int DT, int U>
-MACO_DEVICE void elt_pointwise_vec(uint32_t type, const MacoEltArgs& a, int tid, int nthreads, bool bin) {
+// Vector path, specialised on element type AND operator: the fetch loop is branch-free, the
+// operator is resolved at compile time, and the descriptor fields are copied into registers
+// first (stores through `out` could alias the descriptor otherwise, forcing reloads). Each
+// instance is its own function, so its register allocation is independent of the others.
+template <int OP>
+MACO_DEVICE float elt_op(float x, float y, float f0, float f1) {
+  if constexpr (OP == MACO_TASK_GELU) return gelu_tanh(x);
+  else if constexpr (OP == MACO_TASK_SILU) return silu(x);
+  else if constexpr (OP == MACO_TASK_SCALE) return x * f0;
+  else if constexpr (OP == MACO_TASK_ADD) return x + y;
+  else if constexpr (OP == MACO_TASK_SILU_GATE) return silu(x) * y;
+  else if constexpr (OP == MACO_TASK_GELU_BWD) return x * gelu_tanh_grad(y);
+  else if constexpr (OP == MACO_TASK_AXPBY) return f0 * x + f1 * y;
+  else return x;
+}
+
+template <int DT, int U, int OP>
+__device__ __noinline__ void elt_pointwise_vec(const MacoEltArgs& a, int tid, int nthreads) {
+  constexpr bool bin = OP == MACO_TASK_ADD || OP == MACO_TASK_SILU_GATE || OP == MACO_TASK_GELU_BWD || OP == MACO_TASK_AXPBY;
+  const void* in0 = a.in0;
+  const void* in1 = a.in1;
+  void* out = a.out;
+  const float f0 = a.f0, f1 = a.f1;
+  const long long row0 = a.row0, ld_in = a.ld_in, ld_out = a.ld_out;
   const uint32_t vpr = a.cols / 8;                  // vectors per row
   const uint32_t total = (uint32_t)a.rows * vpr;    // one task's rows: far below 2^32 (64-bit division is emulated)
   for (uint32_t base = tid; base < total; base += (uint32_t)nthreads * U) {
@@ -143,15 +162,14 @@ MACO_DEVICE void elt_pointwise_vec(uint32_t type, const MacoEltArgs& a, int tid,
       const uint32_t i = base + (uint32_t)u * nthreads;
       const uint32_t ii = i < total ? i : 0;
       const uint32_t rr = ii / vpr;
-      const long long r = a.row0 + rr;
       const int c = (int)(ii - rr * vpr) * 8;
-      io[u] = r * a.ld_in + c; oo[u] = r * a.ld_out + c;
+      io[u] = (row0 + rr) * ld_in + c; oo[u] = (row0 + rr) * ld_out + c;
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) load8_raw(a.in0, io[u], DT, xl[u], xh[u]);
-    if (bin) {
+    for (int u = 0; u < U; ++u) load8_raw(in0, io[u], DT, xl[u], xh[u]);
+    if constexpr (bin) {
 #pragma unroll
-      for (int u = 0; u < U; ++u) load8_raw(a.in1, io[u], DT, yl[u], yh[u]);
+      for (int u = 0; u < U; ++u) load8_raw(in1, io[u], DT, yl[u], yh[u]);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -159,21 +177,35 @@ MACO_DEVICE void elt_pointwise_vec(uint32_t type, const MacoEltArgs& a, int tid,
       if (i >= total) continue;
       const F8 x = cvt8(DT, xl[u], xh[u]);
       F8 y;
-      if (bin) y = cvt8(DT, yl[u], yh[u]);
+      if constexpr (bin) y = cvt8(DT, yl[u], yh[u]);
       F8 o;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o.v[j] = elt_apply(type, x.v[j], bin ? y.v[j] : 0.f, a);
-      store8(a.out, oo[u], DT, o);
+      for (int j = 0; j < 8; ++j) o.v[j] = elt_op<OP>(x.v[j], bin ? y.v[j] : 0.f, f0, f1);
+      store8(out, oo[u], DT, o);
     }
+  }
+}
+
+template <int DT, int U>
+MACO_DEVICE void elt_pointwise_dispatch(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
+  switch (type) {
+    case MACO_TASK_GELU: elt_pointwise_vec<DT, U, MACO_TASK_GELU>(a, tid, nthreads); break;
+    case MACO_TASK_SILU: elt_pointwise_vec<DT, U, MACO_TASK_SILU>(a, tid, nthreads); break;
+    case MACO_TASK_SCALE: elt_pointwise_vec<DT, U, MACO_TASK_SCALE>(a, tid, nthreads); break;
+    case MACO_TASK_ADD: elt_pointwise_vec<DT, U, MACO_TASK_ADD>(a, tid, nthreads); break;
+    case MACO_TASK_SILU_GATE: elt_pointwise_vec<DT, U, MACO_TASK_SILU_GATE>(a, tid, nthreads); break;
+    case MACO_TASK_GELU_BWD: elt_pointwise_vec<DT, U, MACO_TASK_GELU_BWD>(a, tid, nthreads); break;
+    case MACO_TASK_AXPBY: elt_pointwise_vec<DT, U, MACO_TASK_AXPBY>(a, tid, nthreads); break;
+    default: elt_pointwise_vec<DT, U, MACO_TASK_COPY>(a, tid, nthreads); break;
   }
 }
 
 MACO_DEVICE void elt_pointwise(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
   const bool bin = elt_is_binary(type);
   if (elt_vec_ok(a)) {
-    if (a.dtype == MACO_DT_BF16) elt_pointwise_vec<MACO_DT_BF16, 8>(type, a, tid, nthreads, bin);
-    else if (a.dtype == MACO_DT_F16) elt_pointwise_vec<MACO_DT_F16, 8>(type, a, tid, nthreads, bin);
-    else elt_pointwise_vec<MACO_DT_F32, 4>(type, a, tid, nthreads, bin);
+    if (a.dtype == MACO_DT_BF16) elt_pointwise_dispatch<MACO_DT_BF16, 8>(type, a, tid, nthreads);
+    else if (a.dtype == MACO_DT_F16) elt_pointwise_dispatch<MACO_DT_F16, 8>(type, a, tid, nthreads);
+    else elt_pointwise_dispatch<MACO_DT_F32, 4>(type, a, tid, nthreads);
   } else {
     const uint32_t total = (uint32_t)a.rows * (uint32_t)a.cols;
     for (uint32_t i = tid; i < total; i += nthreads) {
@@ -191,7 +223,9 @@ MACO_DEVICE void elt_pointwise(uint32_t type, const MacoEltArgs& a, int tid, int
 // RMSNORM: out = x * rsqrt(mean(x^2) + eps) * w          (in0 = x, in1 = w, f0 = eps)
 // LAYERNORM: out = (x - mean) * rsqrt(var + eps) * w + b  (in2 = b)
 // SOFTMAX: out = exp(x - max) / sum
-MACO_DEVICE void elt_rowwise(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
+template <int DTT, int type>
+__device__ __noinline__ void elt_rowwise_t(const MacoEltArgs& ar, int tid, int nthreads) {
+  const MacoEltArgs a = ar;                              // private copy: stores cannot alias it
   const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
   const bool vec = elt_vec_ok(a);
   constexpr int U = 4;                                   // 16-byte vectors per lane fetched together
@@ -205,12 +239,12 @@ MACO_DEVICE void elt_rowwise(uint32_t type, const MacoEltArgs& a, int tid, int n
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const int c = c0 + u * 256;
-          if (c < a.cols) load8_raw(a.in0, ib + c, a.dtype, lo[u], hi[u]);
+          if (c < a.cols) load8_raw(a.in0, ib + c, DTT, lo[u], hi[u]);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           if (c0 + u * 256 < a.cols) {
-            const F8 x = cvt8(a.dtype, lo[u], hi[u]);
+            const F8 x = cvt8(DTT, lo[u], hi[u]);
 #pragma unroll
             for (int j = 0; j < 8; ++j) { s1 += x.v[j]; s2 += x.v[j] * x.v[j]; mx = fmaxf(mx, x.v[j]); }
           }
@@ -218,7 +252,7 @@ MACO_DEVICE void elt_rowwise(uint32_t type, const MacoEltArgs& a, int tid, int n
       }
     } else {
       for (int c = lane; c < a.cols; c += 32) {
-        float x = load1(a.in0, ib + c, a.dtype);
+        float x = load1(a.in0, ib + c, DTT);
         s1 += x; s2 += x * x; mx = fmaxf(mx, x);
       }
     }
@@ -235,12 +269,12 @@ MACO_DEVICE void elt_rowwise(uint32_t type, const MacoEltArgs& a, int tid, int n
       float e = 0.f;
       if (vec) {
         for (int c = lane * 8; c < a.cols; c += 256) {
-          F8 x = load8(a.in0, ib + c, a.dtype);
+          F8 x = load8(a.in0, ib + c, DTT);
 #pragma unroll
           for (int j = 0; j < 8; ++j) e += __expf(x.v[j] - mx);
         }
       } else {
-        for (int c = lane; c < a.cols; c += 32) e += __expf(load1(a.in0, ib + c, a.dtype) - mx);
+        for (int c = lane; c < a.cols; c += 32) e += __expf(load1(a.in0, ib + c, DTT) - mx);
       }
       denom = 1.f / warp_sum(e);
     }
@@ -252,43 +286,59 @@ MACO_DEVICE void elt_rowwise(uint32_t type, const MacoEltArgs& a, int tid, int n
         for (int u = 0; u < U; ++u) {
           const int c = c0 + u * 256;
           if (c < a.cols) {
-            load8_raw(a.in0, ib + c, a.dtype, lo[u], hi[u]);
-            if (type != MACO_TASK_SOFTMAX) load8_raw(a.in1, c, a.dtype, wl[u], wh[u]);
+            load8_raw(a.in0, ib + c, DTT, lo[u], hi[u]);
+            if (type != MACO_TASK_SOFTMAX) load8_raw(a.in1, c, DTT, wl[u], wh[u]);
           }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const int c = c0 + u * 256;
           if (c >= a.cols) continue;
-          const F8 x = cvt8(a.dtype, lo[u], hi[u]);
+          const F8 x = cvt8(DTT, lo[u], hi[u]);
           F8 o;
           if (type == MACO_TASK_SOFTMAX) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) o.v[j] = __expf(x.v[j] - mx) * denom;
           } else {
-            const F8 w = cvt8(a.dtype, wl[u], wh[u]);
+            const F8 w = cvt8(DTT, wl[u], wh[u]);
             if (type == MACO_TASK_RMSNORM) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) o.v[j] = x.v[j] * rstd * w.v[j];
             } else {
-              F8 b = load8(a.in2, c, a.dtype);
+              F8 b = load8(a.in2, c, DTT);
 #pragma unroll
               for (int j = 0; j < 8; ++j) o.v[j] = (x.v[j] - mean) * rstd * w.v[j] + b.v[j];
             }
           }
-          store8(a.out, ob + c, a.dtype, o);
+          store8(a.out, ob + c, DTT, o);
         }
       }
     } else {
       for (int c = lane; c < a.cols; c += 32) {
-        float x = load1(a.in0, ib + c, a.dtype), o;
+        float x = load1(a.in0, ib + c, DTT), o;
         if (type == MACO_TASK_SOFTMAX) o = __expf(x - mx) * denom;
-        else if (type == MACO_TASK_RMSNORM) o = x * rstd * load1(a.in1, c, a.dtype);
-        else o = (x - mean) * rstd * load1(a.in1, c, a.dtype) + load1(a.in2, c, a.dtype);
-        store1(a.out, ob + c, a.dtype, o);
+        else if (type == MACO_TASK_RMSNORM) o = x * rstd * load1(a.in1, c, DTT);
+        else o = (x - mean) * rstd * load1(a.in1, c, DTT) + load1(a.in2, c, DTT);
+        store1(a.out, ob + c, DTT, o);
       }
     }
   }
+}
+
+MACO_DEVICE void elt_rowwise(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
+#define MACO_ROWWISE_CASE(T)                                                              \
+  case T:                                                                                 \
+    if (a.dtype == MACO_DT_BF16) elt_rowwise_t<MACO_DT_BF16, T>(a, tid, nthreads);        \
+    else if (a.dtype == MACO_DT_F16) elt_rowwise_t<MACO_DT_F16, T>(a, tid, nthreads);     \
+    else elt_rowwise_t<MACO_DT_F32, T>(a, tid, nthreads);                                 \
+    break;
+  switch (type) {
+    MACO_ROWWISE_CASE(MACO_TASK_RMSNORM)
+    MACO_ROWWISE_CASE(MACO_TASK_LAYERNORM)
+    default:
+    MACO_ROWWISE_CASE(MACO_TASK_SOFTMAX)
+  }
+#undef MACO_ROWWISE_CASE
 }
 
 // ---- RoPE (half-rotation form) -------------------------------------------------------------

@@ -6,7 +6,7 @@ using namespace maco;
 
 namespace {
 
-__global__ void __launch_bounds__(256) elt_kernel(uint32_t type, MacoEltArgs a, int rows_per_cta) {
+__global__ void __launch_bounds__(128, 4) elt_kernel(uint32_t type, MacoEltArgs a, int rows_per_cta) {
   MacoEltArgs mine = a;
   mine.row0 = a.row0 + blockIdx.x * rows_per_cta;
   int left = a.rows - blockIdx.x * rows_per_cta;
@@ -26,15 +26,15 @@ extern "C" int maco_elementwise(int type, const void* in0, const void* in1, cons
   a.in0 = in0; a.in1 = in1; a.in2 = in2; a.out = out; a.row0 = 0; a.rows = rows; a.cols = cols; a.dtype = dtype;
   a.ld_in = ld_in; a.ld_out = ld_out; a.f0 = f0; a.f1 = f1; a.i0 = i0; a.i1 = i1;
   const int sms = maco_host::sm_count();
-  // Aim for ~8 CTAs per SM worth of chunks, at least 8 rows (one per warp) per CTA for row-wise ops.
+  // 128-thread CTAs, four resident per SM; several waves so that the tail is short.
   long long work = (long long)rows * cols;
   int target_ctas = (int)((work + 16383) / 16384);
-  if (target_ctas > sms * 8) target_ctas = sms * 8;
+  if (target_ctas > sms * 16) target_ctas = sms * 16;
   if (target_ctas < 1) target_ctas = 1;
   int rows_per_cta = (rows + target_ctas - 1) / target_ctas;
   if (rows_per_cta < 1) rows_per_cta = 1;
   int grid = (rows + rows_per_cta - 1) / rows_per_cta;
-  elt_kernel<<<grid, 256, 0, stream>>>((uint32_t)type, a, rows_per_cta);
+  elt_kernel<<<grid, 128, 0, stream>>>((uint32_t)type, a, rows_per_cta);
   MACO_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

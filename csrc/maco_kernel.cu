@@ -159,7 +159,7 @@ __device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base,
     if (!fetch_task(p, w, i, q_base, task, c.abort_word)) { ok = false; break; }
     if (task == MACO_QUEUE_TERMINATE) break;
     task &= MACO_QUEUE_INDEX_MASK;
-    const MacoTaskDesc d = load_desc(p, task);
+    const MacoTaskDesc& d = p.tasks[task];   // read in place (L1/L2 resident): a register copy would cost 32 registers
     if (!is_gemm(d.type)) continue;
     if (!wait_deps(p, d, task, c.abort_word, nullptr)) { ok = false; break; }
     const MacoGemmArgs& g = d.u.gemm;
@@ -194,7 +194,7 @@ __device__ void mma_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint
     if (!fetch_task(p, w, i, q_base, task, c.abort_word)) break;
     if (task == MACO_QUEUE_TERMINATE) break;
     task &= MACO_QUEUE_INDEX_MASK;
-    const MacoTaskDesc d = load_desc(p, task);
+    const MacoTaskDesc& d = p.tasks[task];   // read in place (L1/L2 resident): a register copy would cost 32 registers
     if (!is_gemm(d.type)) continue;
     const MacoGemmArgs& g = d.u.gemm;
     if (d.flags & MACO_TF_COUNTED) {
@@ -261,7 +261,7 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
     // bit 31 of a static queue entry: no GEMM task follows in this worker's queue, the operand ring is idle
     const uint32_t task = raw_entry & MACO_QUEUE_INDEX_MASK;
     const bool ring_free = comm_worker || (raw_entry & MACO_QUEUE_RING_FREE) != 0;
-    const MacoTaskDesc d = load_desc(p, task);
+    const MacoTaskDesc& d = p.tasks[task];   // read in place (L1/L2 resident): a register copy would cost 32 registers
     uint64_t t_start = 0, wait_ns = 0;
     if (leader && p.trace != nullptr) t_start = globaltimer_ns();
     bool skip_tile = false;
@@ -278,7 +278,7 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
       // nothing to compute: the tile's rows hold no tokens (it still signals below)
     } else if (is_gemm(d.type)) {
       const MacoGemmArgs& g = d.u.gemm;
-      GemmEpilogue e = p.epis[g.epi];
+      const GemmEpilogue& e = p.epis[g.epi];
       void* out_base = e.out;
       if (g.peer >= 0) out_base = p.peer_heap[g.peer] + g.out_off;
       EpiBroadcast bc{p.world, p.peer_heap, g.out_off};       // peer == -2: the tile goes to every rank's heap
