@@ -159,6 +159,168 @@ __device__ __noinline__ void attn_decode_task_t(const MacoEltArgs& ar, int tid, 
   }
 }
 
+// ---- pipelined form (persistent kernel) ---------------------------------------------------------
+// The worker's TMA warp streams the split's K and V rows through the operand ring with bulk copies
+// (one 128-key chunk of K, then of V, per stage; several stages in flight), and the four general
+// warps consume them from shared memory. With four warps per SM a load -> compute -> load loop is
+// bound by memory latency; the ring keeps well over 100 KB in flight instead.
+//   ring stage i of the task: stage_base(i) gives the shared-memory address, full[i] / empty[i] the
+//   barriers; `it` is the worker's running stage counter (same convention as the GEMM pipeline).
+struct AttnPipe {
+  uint8_t* ring;
+  uint64_t* full;
+  uint64_t* empty;
+  uint32_t stage_bytes, stages;
+  uint64_t budget_ns;
+  volatile uint32_t* abort_word;
+};
+
+MACO_DEVICE bool attn_pipelined(const MacoEltArgs& a) { return a.ld_in == kAttnD && a.rows > 0; }
+MACO_DEVICE uint32_t attn_stage_uses(const MacoEltArgs& a) { return 2u * (uint32_t)((a.rows + 127) / 128); }
+
+// Producer side: called by one thread.
+MACO_DEVICE bool attn_produce(const MacoEltArgs& a, const AttnPipe& pp, uint32_t& it) {
+  const uint8_t* K = reinterpret_cast<const uint8_t*>(a.in1);
+  const uint8_t* V = reinterpret_cast<const uint8_t*>(a.in2);
+  for (int base = 0; base < a.rows; base += 128) {
+    const uint32_t bytes = (uint32_t)min(128, a.rows - base) * kAttnD * 2;
+#pragma unroll
+    for (int kv = 0; kv < 2; ++kv, ++it) {
+      const uint32_t s = it % pp.stages, ph = (it / pp.stages) & 1;
+      if (!mbar_wait(&pp.empty[s], ph ^ 1, pp.budget_ns, pp.abort_word)) return false;
+      mbar_arrive_expect_tx(&pp.full[s], bytes);
+      bulk_load(pp.ring + (size_t)s * pp.stage_bytes, (kv == 0 ? K : V) + (size_t)base * kAttnD * 2, bytes, &pp.full[s]);
+    }
+  }
+  return true;
+}
+
+// Consumer side: all 128 general threads. scratch: q_s [G][128] f32, p_s [G][128] f32, red [4][G] f32.
+template <int DTT>
+__device__ __noinline__ bool attn_consume_t(const MacoEltArgs& ar, int tid, uint8_t* scratch, const AttnPipe& pp, uint32_t it) {
+  const MacoEltArgs a = ar;
+  const int G = a.i0 < kAttnMaxG ? a.i0 : kAttnMaxG;
+  float* q_s = reinterpret_cast<float*>(scratch);
+  float* p_s = q_s + kAttnMaxG * kAttnD;
+  float* red = p_s + kAttnMaxG * kAttnD;
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int i = tid; i < G * kAttnD; i += 128) q_s[i] = load1(a.in0, i, DTT) * a.f0;
+  float m_run[kAttnMaxG], l_run[kAttnMaxG], o[kAttnMaxG];
+#pragma unroll
+  for (int g = 0; g < kAttnMaxG; ++g) { m_run[g] = -INFINITY; l_run[g] = 0.f; o[g] = 0.f; }
+  attn_bar();
+  bool ok = true;
+  for (int base = 0; base < a.rows; base += 128, it += 2) {
+    const int nk = min(128, a.rows - base);
+    const bool valid = tid < nk;
+    const uint32_t sk = it % pp.stages, phk = (it / pp.stages) & 1;
+    const uint32_t sv = (it + 1) % pp.stages, phv = ((it + 1) / pp.stages) & 1;
+    if (!mbar_wait(&pp.full[sk], phk, pp.budget_ns, pp.abort_word)) ok = false;
+    // scores: one key row per thread, vectors visited in a per-thread rotated order (bank spread)
+    float s[kAttnMaxG];
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) s[g] = 0.f;
+    const uint8_t* krow = pp.ring + (size_t)sk * pp.stage_bytes + (size_t)tid * (kAttnD * 2);
+    if (valid && ok) {
+#pragma unroll
+      for (int v = 0; v < kAttnD / 8; ++v) {
+        const int dv = (v + tid) & 15;
+        const uint4 u = *reinterpret_cast<const uint4*>(krow + dv * 16);
+        float kf[8];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          float2 f = DTT == MACO_DT_BF16 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
+          kf[2 * t] = f.x; kf[2 * t + 1] = f.y;
+        }
+#pragma unroll
+        for (int g = 0; g < kAttnMaxG; ++g) {
+          if (g < G) {
+            const float4 q0 = *reinterpret_cast<const float4*>(q_s + g * kAttnD + dv * 8);
+            const float4 q1 = *reinterpret_cast<const float4*>(q_s + g * kAttnD + dv * 8 + 4);
+            s[g] += q0.x * kf[0] + q0.y * kf[1] + q0.z * kf[2] + q0.w * kf[3] + q1.x * kf[4] + q1.y * kf[5] +
+                    q1.z * kf[6] + q1.w * kf[7];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) {
+      float mx = warp_max(valid ? s[g] : -INFINITY);
+      if (lane == 0) red[warp * kAttnMaxG + g] = mx;
+    }
+    attn_bar();                                   // K stage consumed by everybody, maxima published
+    if (tid == 0) mbar_arrive(&pp.empty[sk]);
+    float corr[kAttnMaxG];
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) {
+      const float cm = fmaxf(fmaxf(red[g], red[kAttnMaxG + g]), fmaxf(red[2 * kAttnMaxG + g], red[3 * kAttnMaxG + g]));
+      const float m_new = fmaxf(m_run[g], cm);
+      corr[g] = (m_run[g] == -INFINITY) ? 0.f : __expf(m_run[g] - m_new);
+      const float pj = valid ? __expf(s[g] - m_new) : 0.f;
+      p_s[g * kAttnD + tid] = pj;
+      s[g] = pj;
+      m_run[g] = m_new;
+      o[g] *= corr[g];
+    }
+    attn_bar();                                   // red consumed, p_s complete
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) {
+      float sm = warp_sum(s[g]);
+      if (lane == 0) red[warp * kAttnMaxG + g] = sm;
+    }
+    if (!mbar_wait(&pp.full[sv], phv, pp.budget_ns, pp.abort_word)) ok = false;
+    // P.V: thread `tid` owns output dimension `tid`; the staged V rows are read straight from the ring
+    const uint16_t* vcol = reinterpret_cast<const uint16_t*>(pp.ring + (size_t)sv * pp.stage_bytes) + tid;
+    if (ok) {
+      int jj = 0;
+      for (; jj + 4 <= nk; jj += 4) {
+        float vv[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const uint16_t raw = vcol[(jj + t) * kAttnD];
+          vv[t] = DTT == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
+        }
+#pragma unroll
+        for (int g = 0; g < kAttnMaxG; ++g) {
+          if (g < G) {
+            const float4 pp4 = *reinterpret_cast<const float4*>(p_s + g * kAttnD + jj);
+            o[g] += pp4.x * vv[0] + pp4.y * vv[1] + pp4.z * vv[2] + pp4.w * vv[3];
+          }
+        }
+      }
+      for (; jj < nk; ++jj) {
+        const uint16_t raw = vcol[jj * kAttnD];
+        const float v1 = DTT == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
+#pragma unroll
+        for (int g = 0; g < kAttnMaxG; ++g) if (g < G) o[g] += p_s[g * kAttnD + jj] * v1;
+      }
+    }
+    attn_bar();                                   // V stage and p_s consumed, sums published
+    if (tid == 0) mbar_arrive(&pp.empty[sv]);
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g)
+      l_run[g] = l_run[g] * corr[g] + red[g] + red[kAttnMaxG + g] + red[2 * kAttnMaxG + g] + red[3 * kAttnMaxG + g];
+    attn_bar();                                   // red free for the next chunk
+  }
+  float* out = reinterpret_cast<float*>(a.out);
+#pragma unroll
+  for (int g = 0; g < kAttnMaxG; ++g) if (g < G) out[g * kAttnD + tid] = o[g];
+  if (tid < G) {
+    float mg = -INFINITY, lg = 0.f;
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) if (g == tid) { mg = m_run[g]; lg = l_run[g]; }
+    out[G * kAttnD + tid] = mg;
+    out[G * kAttnD + G + tid] = lg;
+  }
+  return ok;
+}
+
+MACO_DEVICE bool attn_consume(const MacoEltArgs& a, int tid, uint8_t* scratch, const AttnPipe& pp, uint32_t it) {
+  if (a.dtype == MACO_DT_BF16) return attn_consume_t<MACO_DT_BF16>(a, tid, scratch, pp, it);
+  return attn_consume_t<MACO_DT_F16>(a, tid, scratch, pp, it);
+}
+
 MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratch) {
   if (a.dtype == MACO_DT_BF16) attn_decode_task_t<MACO_DT_BF16>(a, tid, scratch);
   else attn_decode_task_t<MACO_DT_F16>(a, tid, scratch);

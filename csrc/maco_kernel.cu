@@ -160,6 +160,15 @@ __device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base,
     if (task == MACO_QUEUE_TERMINATE) break;
     task &= MACO_QUEUE_INDEX_MASK;
     const MacoTaskDesc& d = p.tasks[task];   // read in place (L1/L2 resident): a register copy would cost 32 registers
+    if (d.type == MACO_TASK_ATTENTION && attn_pipelined(d.u.elt)) {
+      // K / V rows of the split stream through the operand ring; the general warps consume them
+      if (!wait_deps(p, d, task, c.abort_word, nullptr)) { ok = false; break; }
+      fence_proxy_async_all();
+      const AttnPipe pipe{smem, c.full, c.empty, (uint32_t)MkLayout::kStageBytes, (uint32_t)kMkStages, p.budget_ns, c.abort_word};
+      ok = attn_produce(d.u.elt, pipe, it);
+      if (!ok) report_failure(p, MACO_STATUS_TIMEOUT, task, 0xffffffffu, c.abort_word);
+      continue;
+    }
     if (!is_gemm(d.type)) continue;
     if (!wait_deps(p, d, task, c.abort_word, nullptr)) { ok = false; break; }
     const MacoGemmArgs& g = d.u.gemm;
@@ -186,8 +195,8 @@ __device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base,
 
 // ---- MMA warp (lane 0) --------------------------------------------------------------------------
 __device__ void mma_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint8_t* smem, const GemmCtrl& c,
-                         uint32_t tmem_base) {
-  uint32_t it = 0, seq = 0;
+                         uint32_t tmem_base, volatile uint32_t* attn_done) {
+  uint32_t it = 0, seq = 0, attn_seen = 0;
   bool ok = true;
   for (uint32_t i = 0; ok; ++i) {
     uint32_t task;
@@ -195,6 +204,19 @@ __device__ void mma_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint
     if (task == MACO_QUEUE_TERMINATE) break;
     task &= MACO_QUEUE_INDEX_MASK;
     const MacoTaskDesc& d = p.tasks[task];   // read in place (L1/L2 resident): a register copy would cost 32 registers
+    if (d.type == MACO_TASK_ATTENTION && attn_pipelined(d.u.elt)) {
+      // The ring barriers carry one parity bit: this warp must not wait on a stage for a later GEMM while
+      // the attention task's chunks are still cycling through the same stages. Wait until the general
+      // warps have finished the task (CTA-local counter), then continue behind it.
+      it += attn_stage_uses(d.u.elt);
+      ++attn_seen;
+      const uint64_t t0 = globaltimer_ns();
+      while ((int32_t)(*attn_done - attn_seen) < 0) {
+        if (*c.abort_word != 0 || globaltimer_ns() - t0 > p.budget_ns) { ok = false; break; }
+        __nanosleep(64);
+      }
+      continue;
+    }
     if (!is_gemm(d.type)) continue;
     const MacoGemmArgs& g = d.u.gemm;
     if (d.flags & MACO_TF_COUNTED) {
@@ -241,7 +263,7 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
   // Communication workers never get GEMM tasks, so their operand ring is free to stage bulk copies.
   const bool comm_worker = p.num_comm_workers > 0 && w >= p.num_workers - p.num_comm_workers;
   BulkCtx bulk{ring_smem, bulk_bars, kBulkBuffers, kBulkBufBytes, slots + 12};   // phase word: zeroed at kernel start
-  uint32_t seq = 0, done = 0;
+  uint32_t seq = 0, done = 0, it = 0;      // it: ring stages consumed so far (kept in step with the TMA and MMA warps)
   for (uint32_t i = 0;; ++i) {
     volatile uint32_t* cur = slots + (i & 1u) * 4;     // [0] task, [1] dependencies satisfied, [2] failure
     if (leader) {
@@ -289,6 +311,7 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
       else ok = gemm_epilogue_tile<256, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns, bcp, stage);
       if (!ok) cur[2] = 1;
       ++seq;
+      it += (uint32_t)g.k_blocks;
     } else {
       if (leader) cur[1] = wait_deps(p, d, task, c.abort_word, p.trace ? &wait_ns : nullptr) ? 1u : 0u;
       general_bar();
@@ -298,6 +321,12 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
             cur[2] = 1;
             if (leader) report_failure(p, MACO_STATUS_BAD_TASK, task, d.u.comm.op, c.abort_word);
           }
+        } else if (d.type == MACO_TASK_ATTENTION && attn_pipelined(d.u.elt)) {
+          const AttnPipe pipe{ring_smem, c.full, c.empty, (uint32_t)MkLayout::kStageBytes, (uint32_t)kMkStages, p.budget_ns, c.abort_word};
+          if (!attn_consume(d.u.elt, tid, scratch_smem, pipe, it)) cur[2] = 1;
+          it += attn_stage_uses(d.u.elt);
+          general_bar();
+          if (leader) slots[13] = slots[13] + 1;                 // lets the MMA warp move past this task
         } else if (d.type == MACO_TASK_ATTENTION || d.type == MACO_TASK_ATTN_MERGE) {
           run_attn(d.type, d.u.elt, tid, scratch_smem);
         } else if (d.type == MACO_TASK_TOPK || d.type == MACO_TASK_MOE_COUNTS || d.type == MACO_TASK_MOE_RETURN) {
@@ -431,6 +460,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) maco_persistent_kernel(const 
     if (threadIdx.x == 0) {
       extra[16] = p.mode == MACO_MODE_DYNAMIC ? ld_relaxed_gpu_u32(&p.tails[w]) : 0;
       extra[12] = 0;                                                     // parity bits of the bulk barriers
+      extra[13] = 0;                                                     // pipelined attention tasks finished
       for (uint32_t b = 0; b < kBulkBuffers; ++b) mbar_init(&bulk_bars[b], 1);
       fence_mbar_init();
     }
@@ -440,7 +470,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) maco_persistent_kernel(const 
       if (lane == 0) producer_role(p, w, q_base, smem, c);
       __syncwarp();
     } else if (warp == 1) {
-      if (lane == 0) mma_role(p, w, q_base, smem, c, tmem_base);
+      if (lane == 0) mma_role(p, w, q_base, smem, c, tmem_base, extra + 13);
       __syncwarp();
     } else {
       general_role(p, w, q_base, c, tmem_base, extra, reinterpret_cast<uint8_t*>(extra) + kMkExtraSmem, smem, bulk_bars);

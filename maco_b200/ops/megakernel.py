@@ -428,9 +428,9 @@ class Program:
         sq = np.full((W, stride), QUEUE_TERMINATE, dtype=np.uint32)
         for w, q in enumerate(queues):
             sq[w, : len(q)] = q
-            # entries behind the queue's last GEMM task carry bit 31: the worker's operand ring is idle
-            # from there on, and communication tasks may stage bulk copies in it
-            last_gemm = max((k for k, t in enumerate(q) if b.tasks[t]["type"] in (100, 101)), default=-1)
+            # entries behind the queue's last ring user (GEMM tiles, pipelined attention) carry bit 31: the
+            # worker's operand ring is idle from there on, and communication tasks may stage bulk copies in it
+            last_gemm = max((k for k, t in enumerate(q) if b.tasks[t]["type"] in (100, 101, 102)), default=-1)
             sq[w, last_gemm + 1: len(q)] |= np.uint32(0x80000000)
         self.static_stride = stride
         self.d_static_queue = up(sq)

@@ -33,7 +33,8 @@ def test_tp_mlp_single_gpu():
 def test_qwen3_decode_layer_single_gpu(mode):
     from maco_b200 import _native
     from maco_b200.models.qwen3_layer import Qwen3DecodeLayer
-    layer = Qwen3DecodeLayer(hidden=1024, q_heads=16, kv_heads=2, ffn=2048, batch=8, kv_len=300, seed=4, mode=mode, splits=3,
+    # 1400 cached keys in 2 splits: 6 chunks of 128 keys per task, so the K/V ring wraps several times
+    layer = Qwen3DecodeLayer(hidden=1024, q_heads=16, kv_heads=2, ffn=2048, batch=8, kv_len=1400, seed=4, mode=mode, splits=2,
                              weight_std=0.05)
     x = torch.randn(8, 1024, device="cuda", dtype=torch.bfloat16)
     ref = layer.reference(x)
