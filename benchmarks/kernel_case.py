@@ -4,6 +4,7 @@
     python benchmarks/kernel_case.py gemm        # stand-alone tcgen05 GEMM, 8192 x 4096 x 4096 bf16
     python benchmarks/kernel_case.py mlp         # persistent kernel: fused SwiGLU MLP, 4096 tokens, 4096 -> 14336/4
     python benchmarks/kernel_case.py attention   # split-KV decode attention, batch 32, 4096 keys
+    python benchmarks/kernel_case.py attention_tc  # persistent kernel: tensor-core decode attention, 512 tasks, 537 MB of KV
     python benchmarks/kernel_case.py rmsnorm     # row-wise kernel, 16384 x 8192 bf16
 
 Each case holds well under 1 GB on the device, uses inputs larger than the 126 MB L2 where DRAM
@@ -57,6 +58,25 @@ def main():
         scratch = torch.empty(1 << 20, device="cuda", dtype=torch.float32)
         us = timed(lambda: ops.attention_decode(q, k, v, out=out, scratch=scratch))
         print(f"attention decode B{B} S{S}: {us:.1f} us, {2 * k.numel() * 2 / us / 1e3:.0f} GB/s of KV")
+    elif case == "attention_tc":
+        from maco_b200.ops.megakernel import ProgramBuilder
+        B, Hq, Hkv, S, splits = 64, 32, 4, 4096, 2
+        q = torch.randn(B, Hq, 128, device="cuda", dtype=dt)
+        k = torch.randn(B, Hkv, S, 128, device="cuda", dtype=dt)
+        v = torch.randn(B, Hkv, S, 128, device="cuda", dtype=dt)
+        out = torch.empty_like(q)
+        pb = ProgramBuilder(torch.device("cuda"), )
+        pb.attention_decode(q, k, v, out, splits=splits)
+        prog = pb.build()
+        us = timed(prog.run)
+        print(f"persistent tensor-core attention B{B} hq{Hq} hkv{Hkv} S{S} splits{splits}: {us:.1f} us, "
+              f"{2 * k.numel() * 2 / us / 1e3:.0f} GB/s of KV")
+        G = Hq // Hkv
+        ref = torch.softmax(torch.einsum("bhgd,bhsd->bhgs", q[:4].float().view(4, Hkv, G, 128), k[:4].float()) * 128 ** -0.5, -1)
+        ref = torch.einsum("bhgs,bhsd->bhgd", ref, v[:4].float()).reshape(4, Hq, 128)
+        err = (out[:4].float() - ref).abs().max().item()
+        print(f"max abs error against fp32 PyTorch (4 sequences): {err:.2e}")
+        assert err < 2e-2
     elif case == "rmsnorm":
         x = torch.randn(16384, 8192, device="cuda", dtype=dt)
         w = torch.randn(8192, device="cuda", dtype=dt)

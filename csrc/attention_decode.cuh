@@ -15,6 +15,7 @@
 // Task ATTN_MERGE:
 //   in0 = partials [i1 splits][G*128 + 2G] fp32, out = o [G, 128] (dtype), i0 = G, i1 = splits
 #pragma once
+#include <cuda.h>
 #include "elementwise.cuh"
 
 namespace maco {
@@ -159,166 +160,306 @@ __device__ __noinline__ void attn_decode_task_t(const MacoEltArgs& ar, int tid, 
   }
 }
 
-// ---- pipelined form (persistent kernel) ---------------------------------------------------------
-// The worker's TMA warp streams the split's K and V rows through the operand ring with bulk copies
-// (one 128-key chunk of K, then of V, per stage; several stages in flight), and the four general
-// warps consume them from shared memory. With four warps per SM a load -> compute -> load loop is
-// bound by memory latency; the ring keeps well over 100 KB in flight instead.
-//   ring stage i of the task: stage_base(i) gives the shared-memory address, full[i] / empty[i] the
-//   barriers; `it` is the worker's running stage counter (same convention as the GEMM pipeline).
+// ---- tensor-core form (persistent kernel) -------------------------------------------------------
+// Decode attention of one (sequence, kv head, split) on the 5th-generation tensor cores, fed by the
+// worker's TMA warp:
+//
+//   per 128-key chunk   S^T[key, head]  = K[key, :] . Q[head, :]^T      tcgen05.mma 128 x 16 x 128
+//                       P = exp(S * scale - m_ref)  (registers -> bf16/fp16 tile in shared memory)
+//                       O^T[dim, head] += V[key, dim]^T . P[head, key]  tcgen05.mma 128 x 16 x 128
+//
+// The keys (then the head dimensions) take the M = 128 rows of the instruction and the G <= 8 query
+// heads of the group, padded to 16, its N columns, so the big operand of both products is the K / V
+// chunk exactly as TMA delivers it: K rows as a K-major A operand (two 64-dim boxes), V rows as an
+// MN-major A operand (four 64 x 64 panels). Only the small operands are built by threads: Q once per
+// task, P once per chunk, both written in the 128-byte-swizzled K-major layout the descriptors expect.
+//
+// Memory latency, not bandwidth, bounds one SM here (a split is read once, nothing is reused), so the
+// K / V chunks go through their own ring of six 32 KB stages over the worker's operand memory
+// (192 KB in flight per SM) with barriers of their own, and the per-chunk dependency chain is kept
+// short:
+//   * scores run one chunk ahead (S double buffered in TMEM columns 0-15 / 16-31);
+//   * the softmax reference m_ref is lazy: it only moves when some score exceeds it by more than
+//     kAttnLazyMargin, which one barrier with an OR-reduction (also the "P complete" barrier) decides.
+//     While it stands still P.V accumulates in TMEM (columns 32-47) across chunks and nothing is read
+//     back; when it moves, the accumulator is drained into registers, rescaled, and restarted;
+//   * the softmax denominator is kept per thread (one key per thread) and summed once per task.
+//
+// The reference has no attention task at all (maco/csrc/maco_types.h:24-40 lists ATTENTION, the
+// worker never implements it).
 struct AttnPipe {
   uint8_t* ring;
-  uint64_t* full;
-  uint64_t* empty;
-  uint32_t stage_bytes, stages;
+  uint64_t* full;         // [kAttnStages]
+  uint64_t* empty;        // [kAttnStages]
   uint64_t budget_ns;
   volatile uint32_t* abort_word;
+  const CUtensorMap* tmaps;
+  uint64_t* mma_bars;     // [4]: scores ready (two buffers), P.V issued from P buffer 0 / 1 finished
+  uint32_t tmem_base;
 };
 
-MACO_DEVICE bool attn_pipelined(const MacoEltArgs& a) { return a.ld_in == kAttnD && a.rows > 0; }
+constexpr int kAttnStages = 6;
+constexpr int kAttnStageBytes = 32768;               // one 128-key chunk of K or of V
+constexpr int kAttnTileBytes = 4096;                 // 16 rows x 128 columns of 16-bit values, swizzled
+constexpr int kAttnTcScratchBytes = 1024 + 3 * kAttnTileBytes + 4 * kAttnMaxG * 4;
+constexpr float kAttnLazyMargin = 8.f;               // P <= e^8 between two moves of the reference
+
+// ld_out carries the tensor-map indices of the K and V caches (+1 each, 16 bits each); row0 is the first
+// key's row in the flattened [rows, 128] view both maps describe.
+MACO_DEVICE bool attn_pipelined(const MacoEltArgs& a) { return a.ld_in == kAttnD && a.rows > 0 && a.ld_out != 0; }
 MACO_DEVICE uint32_t attn_stage_uses(const MacoEltArgs& a) { return 2u * (uint32_t)((a.rows + 127) / 128); }
 
-// Producer side: called by one thread.
-MACO_DEVICE bool attn_produce(const MacoEltArgs& a, const AttnPipe& pp, uint32_t& it) {
-  const uint8_t* K = reinterpret_cast<const uint8_t*>(a.in1);
-  const uint8_t* V = reinterpret_cast<const uint8_t*>(a.in2);
+// Producer side: called by one thread. `ait` counts the stage uses of the attention ring on this worker.
+MACO_DEVICE bool attn_produce(const MacoEltArgs& a, const AttnPipe& pp, uint32_t& ait) {
+  const CUtensorMap* tmK = pp.tmaps + ((a.ld_out & 0xffff) - 1);
+  const CUtensorMap* tmV = pp.tmaps + (((uint32_t)a.ld_out >> 16) - 1);
   for (int base = 0; base < a.rows; base += 128) {
-    const uint32_t bytes = (uint32_t)min(128, a.rows - base) * kAttnD * 2;
-#pragma unroll
-    for (int kv = 0; kv < 2; ++kv, ++it) {
-      const uint32_t s = it % pp.stages, ph = (it / pp.stages) & 1;
+    const int y = a.row0 + base;
+    {
+      const uint32_t s = ait % kAttnStages, ph = (ait / kAttnStages) & 1;
       if (!mbar_wait(&pp.empty[s], ph ^ 1, pp.budget_ns, pp.abort_word)) return false;
-      mbar_arrive_expect_tx(&pp.full[s], bytes);
-      bulk_load(pp.ring + (size_t)s * pp.stage_bytes, (kv == 0 ? K : V) + (size_t)base * kAttnD * 2, bytes, &pp.full[s]);
+      uint8_t* st = pp.ring + (size_t)s * kAttnStageBytes;
+      mbar_arrive_expect_tx(&pp.full[s], kAttnStageBytes);
+      tma_load_2d(st, tmK, &pp.full[s], 0, y);               // dims 0..63 of 128 keys
+      tma_load_2d(st + 16384, tmK, &pp.full[s], 64, y);      // dims 64..127
+      ++ait;
+    }
+    {
+      const uint32_t s = ait % kAttnStages, ph = (ait / kAttnStages) & 1;
+      if (!mbar_wait(&pp.empty[s], ph ^ 1, pp.budget_ns, pp.abort_word)) return false;
+      uint8_t* st = pp.ring + (size_t)s * kAttnStageBytes;
+      mbar_arrive_expect_tx(&pp.full[s], kAttnStageBytes);
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb)                         // 64 keys per k-block, two 64-dim panels each
+#pragma unroll
+        for (int j = 0; j < 2; ++j) tma_load_2d(st + kb * 16384 + j * 8192, tmV, &pp.full[s], j * 64, y + kb * 64);
+      ++ait;
     }
   }
   return true;
 }
 
-// Consumer side: all 128 general threads. scratch: q_s [G][128] f32, p_s [G][128] f32, red [4][G] f32.
+// Waits (bounded) until the last uses of the attention ring have been released by the consumer: the
+// operand memory may then be handed to another pipeline.
+MACO_DEVICE bool attn_ring_drained(const AttnPipe& pp, uint32_t ait) {
+  for (uint32_t u = ait > (uint32_t)kAttnStages ? ait - kAttnStages : 0; u < ait; ++u)
+    if (!mbar_wait(&pp.empty[u % kAttnStages], (u / kAttnStages) & 1, pp.budget_ns, pp.abort_word)) return false;
+  return true;
+}
+
+// After an abort: loads still in flight get a bounded time to land (their destination is this CTA's memory).
+MACO_DEVICE void attn_drain_loads(const AttnPipe& pp, uint32_t ait) {
+  for (uint32_t u = ait > (uint32_t)kAttnStages ? ait - kAttnStages : 0; u < ait; ++u) {
+    const uint64_t t0 = globaltimer_ns();
+    while (!mbar_try_wait(&pp.full[u % kAttnStages], (u / kAttnStages) & 1)) {
+      if (globaltimer_ns() - t0 > 2000000ull) break;
+    }
+  }
+}
+
+// Byte offset of element (row, col) inside a 16-row x 128-column K-major tile of 16-bit values stored
+// as two 64-column atoms with the 128-byte swizzle (the tile's base is 1024-byte aligned).
+MACO_DEVICE uint32_t attn_tile_off(int row, int col) {
+  return (uint32_t)((col >> 6) * 2048 + (row >> 3) * 1024 + (row & 7) * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4) + (col & 7) * 2);
+}
+
+// Maximum over the warp in one instruction (sm_100a).
+MACO_DEVICE float warp_max_redux(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// Barrier of the 128 general threads that also ORs a predicate over them.
+MACO_DEVICE bool attn_bar_or(bool pred) {
+  uint32_t r;
+  asm volatile("{\n .reg .pred p, q;\n setp.ne.u32 q, %1, 0;\n bar.red.or.pred p, 1, 128, q;\n selp.u32 %0, 1, 0, p;\n}"
+               : "=r"(r) : "r"((uint32_t)pred) : "memory");
+  return r != 0;
+}
+
+// Consumer side: all 128 general threads. `ait`: this task's first use of the attention ring.
+// `chunk_seq` counts the chunks this worker has processed (buffer index and parity of the MMA
+// barriers); every thread keeps its own copy.
 template <int DTT>
-__device__ __noinline__ bool attn_consume_t(const MacoEltArgs& ar, int tid, uint8_t* scratch, const AttnPipe& pp, uint32_t it) {
+__device__ __noinline__ bool attn_consume_t(const MacoEltArgs& ar, int tid, uint8_t* scratch, const AttnPipe& pp, uint32_t ait,
+                                            uint32_t& chunk_seq) {
   const MacoEltArgs a = ar;
   const int G = a.i0 < kAttnMaxG ? a.i0 : kAttnMaxG;
-  float* q_s = reinterpret_cast<float*>(scratch);
-  float* p_s = q_s + kAttnMaxG * kAttnD;
-  float* red = p_s + kAttnMaxG * kAttnD;
-  const int warp = tid >> 5, lane = tid & 31;
-  for (int i = tid; i < G * kAttnD; i += 128) q_s[i] = load1(a.in0, i, DTT) * a.f0;
-  float m_run[kAttnMaxG], l_run[kAttnMaxG], o[kAttnMaxG];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(scratch) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_t = tiles;                                  // Q  [16 heads][128 dims]
+  uint8_t* p_t = tiles + kAttnTileBytes;                 // P  [2][16 heads][128 keys]
+  float* red_m = reinterpret_cast<float*>(tiles + 3 * kAttnTileBytes);
+  const int lane = tid & 31;
+  const int quarter = ((tid >> 5) + 2) & 3;              // TMEM lane quarter this warp may read (warp id mod 4)
+  const int row = quarter * 32 + lane;                   // key of the chunk, then output dimension, of this thread
+  const int wslot = tid >> 5;
+  // Q: 16 x 16 vectors of 16 bytes; rows >= G are zero. P: zero everywhere (rows >= G stay zero).
+  for (int i = tid; i < 256; i += 128) {
+    const int r = i >> 4, v = i & 15;
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (r < G) u = reinterpret_cast<const uint4*>(a.in0)[r * 16 + v];
+    *reinterpret_cast<uint4*>(q_t + attn_tile_off(r, v * 8)) = u;
+    *reinterpret_cast<uint4*>(p_t + i * 16) = make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4*>(p_t + kAttnTileBytes + i * 16) = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async_smem();
+  float m_ref[kAttnMaxG], l_thr[kAttnMaxG], o[kAttnMaxG];
 #pragma unroll
-  for (int g = 0; g < kAttnMaxG; ++g) { m_run[g] = -INFINITY; l_run[g] = 0.f; o[g] = 0.f; }
+  for (int g = 0; g < kAttnMaxG; ++g) { m_ref[g] = -INFINITY; l_thr[g] = 0.f; o[g] = 0.f; }
   attn_bar();
   bool ok = true;
-  for (int base = 0; base < a.rows; base += 128, it += 2) {
-    const int nk = min(128, a.rows - base);
-    const bool valid = tid < nk;
-    const uint32_t sk = it % pp.stages, phk = (it / pp.stages) & 1;
-    const uint32_t sv = (it + 1) % pp.stages, phv = ((it + 1) / pp.stages) & 1;
-    if (!mbar_wait(&pp.full[sk], phk, pp.budget_ns, pp.abort_word)) ok = false;
-    // scores: one key row per thread, vectors visited in a per-thread rotated order (bank spread)
-    float s[kAttnMaxG];
+  bool acc_live = false;                                 // TMEM holds P.V sums not yet drained (same in every thread)
+  const uint32_t fmt = DTT == MACO_DT_BF16 ? 1u : 0u;
+  const uint32_t idesc_s = make_idesc(fmt, 128, 16, 0, 0);
+  const uint32_t idesc_o = make_idesc(fmt, 128, 16, 1, 0);
+  const uint32_t q_addr = smem_u32(q_t), p_addr = smem_u32(p_t);
+  const uint32_t t_lane = (uint32_t)(quarter * 32) << 16;
+  const uint32_t t_o = pp.tmem_base + 32;
+  const int chunks = (a.rows + 127) / 128;
+
+  // thread 0: scores of chunk `c` (ring use ait + 2c) into S buffer (seq & 1)
+  auto issue_scores = [&](int c, uint32_t seq) {
+    const uint32_t u = ait + 2u * (uint32_t)c, sk = u % kAttnStages, phk = (u / kAttnStages) & 1;
+    if (ok && mbar_wait(&pp.full[sk], phk, pp.budget_ns, pp.abort_word)) {
+      tc_fence_after();
+      const uint32_t k_addr = smem_u32(pp.ring + (size_t)sk * kAttnStageBytes);
+      const uint32_t t_s = pp.tmem_base + (seq & 1) * 16;
 #pragma unroll
-    for (int g = 0; g < kAttnMaxG; ++g) s[g] = 0.f;
-    const uint8_t* krow = pp.ring + (size_t)sk * pp.stage_bytes + (size_t)tid * (kAttnD * 2);
-    if (valid && ok) {
-#pragma unroll
-      for (int v = 0; v < kAttnD / 8; ++v) {
-        const int dv = (v + tid) & 15;
-        const uint4 u = *reinterpret_cast<const uint4*>(krow + dv * 16);
-        float kf[8];
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          float2 f = DTT == MACO_DT_BF16 ? unpack_bf16x2(w[t]) : __half22float2(*reinterpret_cast<const __half2*>(&w[t]));
-          kf[2 * t] = f.x; kf[2 * t + 1] = f.y;
-        }
-#pragma unroll
-        for (int g = 0; g < kAttnMaxG; ++g) {
-          if (g < G) {
-            const float4 q0 = *reinterpret_cast<const float4*>(q_s + g * kAttnD + dv * 8);
-            const float4 q1 = *reinterpret_cast<const float4*>(q_s + g * kAttnD + dv * 8 + 4);
-            s[g] += q0.x * kf[0] + q0.y * kf[1] + q0.z * kf[2] + q0.w * kf[3] + q1.x * kf[4] + q1.y * kf[5] +
-                    q1.z * kf[6] + q1.w * kf[7];
-          }
-        }
+      for (int k = 0; k < kAttnD / 16; ++k) {
+        const uint64_t adesc = make_smem_desc(k_addr + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024, 2);
+        const uint64_t bdesc = make_smem_desc(q_addr + (k >> 2) * 2048 + (k & 3) * 32, 16, 1024, 2);
+        tc_mma_f16(t_s, adesc, bdesc, idesc_s, k != 0 ? 1u : 0u);
       }
+      tc_commit(&pp.empty[sk]);
+      tc_commit(&pp.mma_bars[seq & 1]);
+    } else {
+      ok = false;
     }
+  };
+  // every thread: waits for the P.V of chunk `seq` (and all before it), then o += accumulator
+  auto drain_output = [&](uint32_t seq) {
+    if (!mbar_wait(&pp.mma_bars[2 + (seq & 1)], (seq >> 1) & 1, pp.budget_ns, pp.abort_word)) ok = false;
+    tc_fence_after();
+    uint32_t r[16];
+    if (ok) { tmem_ld_32x16(t_o + t_lane, r); tmem_ld_wait(); }
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) o[g] += (ok && g < G) ? __uint_as_float(r[g]) : 0.f;
+    tc_fence_before();
+  };
+  // every thread: P[g][row] = exp(s - m_ref) rounded to the operand type; returns the rounded values
+  auto store_p = [&](uint8_t* p_buf, const float (&s)[kAttnMaxG], float (&pr)[kAttnMaxG]) {
 #pragma unroll
     for (int g = 0; g < kAttnMaxG; ++g) {
-      float mx = warp_max(valid ? s[g] : -INFINITY);
-      if (lane == 0) red[warp * kAttnMaxG + g] = mx;
-    }
-    attn_bar();                                   // K stage consumed by everybody, maxima published
-    if (tid == 0) mbar_arrive(&pp.empty[sk]);
-    float corr[kAttnMaxG];
-#pragma unroll
-    for (int g = 0; g < kAttnMaxG; ++g) {
-      const float cm = fmaxf(fmaxf(red[g], red[kAttnMaxG + g]), fmaxf(red[2 * kAttnMaxG + g], red[3 * kAttnMaxG + g]));
-      const float m_new = fmaxf(m_run[g], cm);
-      corr[g] = (m_run[g] == -INFINITY) ? 0.f : __expf(m_run[g] - m_new);
-      const float pj = valid ? __expf(s[g] - m_new) : 0.f;
-      p_s[g * kAttnD + tid] = pj;
-      s[g] = pj;
-      m_run[g] = m_new;
-      o[g] *= corr[g];
-    }
-    attn_bar();                                   // red consumed, p_s complete
-#pragma unroll
-    for (int g = 0; g < kAttnMaxG; ++g) {
-      float sm = warp_sum(s[g]);
-      if (lane == 0) red[warp * kAttnMaxG + g] = sm;
-    }
-    if (!mbar_wait(&pp.full[sv], phv, pp.budget_ns, pp.abort_word)) ok = false;
-    // P.V: thread `tid` owns output dimension `tid`; the staged V rows are read straight from the ring
-    const uint16_t* vcol = reinterpret_cast<const uint16_t*>(pp.ring + (size_t)sv * pp.stage_bytes) + tid;
-    if (ok) {
-      int jj = 0;
-      for (; jj + 4 <= nk; jj += 4) {
-        float vv[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const uint16_t raw = vcol[(jj + t) * kAttnD];
-          vv[t] = DTT == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
-        }
-#pragma unroll
-        for (int g = 0; g < kAttnMaxG; ++g) {
-          if (g < G) {
-            const float4 pp4 = *reinterpret_cast<const float4*>(p_s + g * kAttnD + jj);
-            o[g] += pp4.x * vv[0] + pp4.y * vv[1] + pp4.z * vv[2] + pp4.w * vv[3];
-          }
+      float pj = (g < G && m_ref[g] != -INFINITY) ? __expf(s[g] - m_ref[g]) : 0.f;
+      if (g < G) {
+        // the product uses the rounded value; the denominator sums the same one, so the two agree
+        if (DTT == MACO_DT_BF16) {
+          const __nv_bfloat16 h = __float2bfloat16_rn(pj);
+          *reinterpret_cast<__nv_bfloat16*>(p_buf + attn_tile_off(g, row)) = h;
+          pj = __bfloat162float(h);
+        } else {
+          const __half h = __float2half_rn(pj);
+          *reinterpret_cast<__half*>(p_buf + attn_tile_off(g, row)) = h;
+          pj = __half2float(h);
         }
       }
-      for (; jj < nk; ++jj) {
-        const uint16_t raw = vcol[jj * kAttnD];
-        const float v1 = DTT == MACO_DT_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(*reinterpret_cast<const __half*>(&raw));
+      pr[g] = pj;
+    }
+    fence_proxy_async_smem();
+  };
+
+  if (tid == 0) issue_scores(0, chunk_seq);
+  for (int c = 0; c < chunks; ++c, ++chunk_seq) {
+    const int nk = min(128, a.rows - c * 128);
+    const bool valid = row < nk;
+    const uint32_t seq = chunk_seq, buf = seq & 1, par = (seq >> 1) & 1;
+    if (tid == 0 && c + 1 < chunks) issue_scores(c + 1, seq + 1);
+    if (!mbar_wait(&pp.mma_bars[buf], par, pp.budget_ns, pp.abort_word)) ok = false;
+    tc_fence_after();
+    float s[kAttnMaxG], pr[kAttnMaxG];
+    {
+      uint32_t r[16];
+      if (ok) { tmem_ld_32x16(pp.tmem_base + buf * 16 + t_lane, r); tmem_ld_wait(); }
 #pragma unroll
-        for (int g = 0; g < kAttnMaxG; ++g) if (g < G) o[g] += p_s[g * kAttnD + jj] * v1;
+      for (int g = 0; g < kAttnMaxG; ++g) s[g] = (ok && valid && g < G) ? __uint_as_float(r[g]) * a.f0 : -INFINITY;
+    }
+    tc_fence_before();
+    // the P buffer is free once the product issued from it two chunks ago has finished
+    if (c >= 2 && !mbar_wait(&pp.mma_bars[2 + buf], ((seq - 2) >> 1) & 1, pp.budget_ns, pp.abort_word)) ok = false;
+    uint8_t* p_buf = p_t + buf * kAttnTileBytes;
+    bool exceed = false;
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) exceed |= s[g] > m_ref[g] + kAttnLazyMargin;
+    store_p(p_buf, s, pr);
+    if (attn_bar_or(exceed)) {                    // P complete, and: does the reference have to move?
+#pragma unroll
+      for (int g = 0; g < kAttnMaxG; ++g) {
+        const float mx = warp_max_redux(s[g]);
+        if (lane == g) red_m[wslot * kAttnMaxG + g] = mx;
+      }
+      if (acc_live) drain_output(seq - 1);        // sums under the old reference leave TMEM
+      attn_bar();
+#pragma unroll
+      for (int g = 0; g < kAttnMaxG; ++g) {
+        const float cm = fmaxf(fmaxf(red_m[g], red_m[kAttnMaxG + g]), fmaxf(red_m[2 * kAttnMaxG + g], red_m[3 * kAttnMaxG + g]));
+        const float m_new = fmaxf(m_ref[g], cm);
+        const float corr = (m_ref[g] == -INFINITY) ? 0.f : __expf(m_ref[g] - m_new);
+        o[g] *= corr;
+        l_thr[g] *= corr;
+        m_ref[g] = m_new;
+      }
+      store_p(p_buf, s, pr);
+      acc_live = false;
+      attn_bar();                                 // P complete under the new reference; red_m free
+    }
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) l_thr[g] += pr[g];
+    if (tid == 0) {
+      const uint32_t u = ait + 2u * (uint32_t)c + 1u, sv = u % kAttnStages, phv = (u / kAttnStages) & 1;
+      if (ok && mbar_wait(&pp.full[sv], phv, pp.budget_ns, pp.abort_word)) {
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(pp.ring + (size_t)sv * kAttnStageBytes);
+        const uint32_t pb = p_addr + buf * kAttnTileBytes;
+#pragma unroll
+        for (int k = 0; k < 128 / 16; ++k) {
+          const uint64_t adesc = make_smem_desc(v_addr + (k >> 2) * 16384 + (k & 3) * 2048, 8192, 1024, 2);
+          const uint64_t bdesc = make_smem_desc(pb + (k >> 2) * 2048 + (k & 3) * 32, 16, 1024, 2);
+          tc_mma_f16(t_o, adesc, bdesc, idesc_o, (k != 0 || acc_live) ? 1u : 0u);
+        }
+        tc_commit(&pp.empty[sv]);
+        tc_commit(&pp.mma_bars[2 + buf]);
+      } else {
+        ok = false;
       }
     }
-    attn_bar();                                   // V stage and p_s consumed, sums published
-    if (tid == 0) mbar_arrive(&pp.empty[sv]);
-#pragma unroll
-    for (int g = 0; g < kAttnMaxG; ++g)
-      l_run[g] = l_run[g] * corr[g] + red[g] + red[kAttnMaxG + g] + red[2 * kAttnMaxG + g] + red[3 * kAttnMaxG + g];
-    attn_bar();                                   // red free for the next chunk
+    acc_live = true;
   }
+  drain_output(chunk_seq - 1);
+  // softmax denominator: one CTA-wide sum per head
+#pragma unroll
+  for (int g = 0; g < kAttnMaxG; ++g) {
+    const float sm = warp_sum(l_thr[g]);
+    if (lane == 0) red_m[wslot * kAttnMaxG + g] = sm;
+  }
+  attn_bar();
   float* out = reinterpret_cast<float*>(a.out);
 #pragma unroll
-  for (int g = 0; g < kAttnMaxG; ++g) if (g < G) out[g * kAttnD + tid] = o[g];
+  for (int g = 0; g < kAttnMaxG; ++g) if (g < G) out[g * kAttnD + row] = o[g];
   if (tid < G) {
-    float mg = -INFINITY, lg = 0.f;
+    float mg = -INFINITY;
 #pragma unroll
-    for (int g = 0; g < kAttnMaxG; ++g) if (g == tid) { mg = m_run[g]; lg = l_run[g]; }
+    for (int g = 0; g < kAttnMaxG; ++g) if (g == tid) mg = m_ref[g];
     out[G * kAttnD + tid] = mg;
-    out[G * kAttnD + G + tid] = lg;
+    out[G * kAttnD + G + tid] = red_m[tid] + red_m[kAttnMaxG + tid] + red_m[2 * kAttnMaxG + tid] + red_m[3 * kAttnMaxG + tid];
   }
+  attn_bar();                                     // red_m is free again
   return ok;
 }
 
-MACO_DEVICE bool attn_consume(const MacoEltArgs& a, int tid, uint8_t* scratch, const AttnPipe& pp, uint32_t it) {
-  if (a.dtype == MACO_DT_BF16) return attn_consume_t<MACO_DT_BF16>(a, tid, scratch, pp, it);
-  return attn_consume_t<MACO_DT_F16>(a, tid, scratch, pp, it);
+MACO_DEVICE bool attn_consume(const MacoEltArgs& a, int tid, uint8_t* scratch, const AttnPipe& pp, uint32_t it, uint32_t& chunk_seq) {
+  if (a.dtype == MACO_DT_BF16) return attn_consume_t<MACO_DT_BF16>(a, tid, scratch, pp, it, chunk_seq);
+  return attn_consume_t<MACO_DT_F16>(a, tid, scratch, pp, it, chunk_seq);
 }
 
 MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratch) {

@@ -46,7 +46,7 @@ constexpr int kMkScratchSmem = 28672;  // scratch of non-GEMM tasks (the operand
                                        // the producer warp may already be filling it for the next GEMM task)
 constexpr int kMkSmemBytes = MkLayout::kTotalBytes + kMkExtraSmem + kMkScratchSmem;
 static_assert(kMkScratchSmem >= kEpiStageBytes, "epilogue staging must fit the scratch block");
-static_assert(kMkScratchSmem >= kAttnScratchBytes, "attention scratch must fit the scratch block");
+static_assert(kMkScratchSmem >= kAttnScratchBytes && kMkScratchSmem >= kAttnTcScratchBytes, "attention scratch must fit the scratch block");
 static_assert(kMkSmemBytes <= 227 * 1024, "persistent kernel exceeds the shared memory of an SM");
 constexpr uint32_t kBulkBufBytes = 16384;                                  // staging buffers of bulk pushes
 constexpr uint32_t kBulkBuffers = MkLayout::kRingBytes / kBulkBufBytes;    // the whole operand ring
@@ -150,10 +150,13 @@ __device__ __forceinline__ MacoTaskDesc load_desc(const MacoProgram& p, uint32_t
 }
 
 // ---- producer warp (lane 0) ---------------------------------------------------------------------
-__device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint8_t* smem, const GemmCtrl& c) {
-  uint32_t it = 0;
+__device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint8_t* smem, const GemmCtrl& c,
+                              uint64_t* attn_ring_bars) {
+  uint32_t it = 0, ait = 0;          // stage uses of the GEMM ring / of the attention ring (same memory)
+  int owner = 0;                     // which pipeline used the operand memory last: 1 GEMM, 2 attention
   bool ok = true;
   const CUtensorMap* tmaps = reinterpret_cast<const CUtensorMap*>(p.tmaps);
+  const AttnPipe apipe{smem, attn_ring_bars, attn_ring_bars + kAttnStages, p.budget_ns, c.abort_word, tmaps, nullptr, 0};
   for (uint32_t i = 0; ok; ++i) {
     uint32_t task;
     if (!fetch_task(p, w, i, q_base, task, c.abort_word)) { ok = false; break; }
@@ -164,8 +167,12 @@ __device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base,
       // K / V rows of the split stream through the operand ring; the general warps consume them
       if (!wait_deps(p, d, task, c.abort_word, nullptr)) { ok = false; break; }
       fence_proxy_async_all();
-      const AttnPipe pipe{smem, c.full, c.empty, (uint32_t)MkLayout::kStageBytes, (uint32_t)kMkStages, p.budget_ns, c.abort_word};
-      ok = attn_produce(d.u.elt, pipe, it);
+      if (owner == 1) {            // the MMA warp may still be reading the last GEMM stages out of this memory
+        for (uint32_t u = it > (uint32_t)kMkStages ? it - kMkStages : 0; u < it && ok; ++u)
+          ok = mbar_wait(&c.empty[u % kMkStages], (u / kMkStages) & 1, p.budget_ns, c.abort_word);
+      }
+      owner = 2;
+      ok = ok && attn_produce(d.u.elt, apipe, ait);
       if (!ok) report_failure(p, MACO_STATUS_TIMEOUT, task, 0xffffffffu, c.abort_word);
       continue;
     }
@@ -175,6 +182,8 @@ __device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base,
     // run-time guarded tile: every role reads the same (final) count after the task's conditions hold
     if ((d.flags & MACO_TF_COUNTED) && ld_relaxed_gpu_u32(g.count_ptr) <= g.count_base) continue;
     fence_proxy_async_all();           // operands were written by generic-proxy stores of other CTAs
+    if (owner == 2 && !attn_ring_drained(apipe, ait)) { ok = false; break; }
+    owner = 1;
     const CUtensorMap* ta = tmaps + g.tmap_a;
     const CUtensorMap* tb = tmaps + g.tmap_b;
     const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | (g.b_mn ? 1 : 0);
@@ -190,7 +199,7 @@ __device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base,
     }
     if (!ok) report_failure(p, MACO_STATUS_TIMEOUT, task, 0xffffffffu, c.abort_word);
   }
-  if (!ok) gemm_drain_loads<kMkStages>(c, it);
+  if (!ok) { gemm_drain_loads<kMkStages>(c, it); attn_drain_loads(apipe, ait); }
 }
 
 // ---- MMA warp (lane 0) --------------------------------------------------------------------------
@@ -205,10 +214,9 @@ __device__ void mma_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint
     task &= MACO_QUEUE_INDEX_MASK;
     const MacoTaskDesc& d = p.tasks[task];   // read in place (L1/L2 resident): a register copy would cost 32 registers
     if (d.type == MACO_TASK_ATTENTION && attn_pipelined(d.u.elt)) {
-      // The ring barriers carry one parity bit: this warp must not wait on a stage for a later GEMM while
-      // the attention task's chunks are still cycling through the same stages. Wait until the general
-      // warps have finished the task (CTA-local counter), then continue behind it.
-      it += attn_stage_uses(d.u.elt);
+      // The attention task issues its own tensor-core products into the low TMEM columns: this warp must
+      // not start the next GEMM tile's accumulator there before the general warps have finished the task
+      // (CTA-local counter).
       ++attn_seen;
       const uint64_t t0 = globaltimer_ns();
       while ((int32_t)(*attn_done - attn_seen) < 0) {
@@ -257,13 +265,15 @@ __device__ __noinline__ void run_moe(const MacoProgram& p, uint32_t type, const 
 // Control words shared by the 128 threads are double buffered by iteration parity, so the
 // leader can prepare iteration i+1 while slower threads still read the words of iteration i.
 __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, const GemmCtrl& c, uint32_t tmem_base,
-                             volatile uint32_t* slots, uint8_t* scratch_smem, uint8_t* ring_smem, uint64_t* bulk_bars) {
+                             volatile uint32_t* slots, uint8_t* scratch_smem, uint8_t* ring_smem, uint64_t* bulk_bars,
+                             uint64_t* attn_bars) {
   const int tid = threadIdx.x - 64;          // 0..127
   const bool leader = tid == 0;
   // Communication workers never get GEMM tasks, so their operand ring is free to stage bulk copies.
   const bool comm_worker = p.num_comm_workers > 0 && w >= p.num_workers - p.num_comm_workers;
   BulkCtx bulk{ring_smem, bulk_bars, kBulkBuffers, kBulkBufBytes, slots + 12};   // phase word: zeroed at kernel start
   uint32_t seq = 0, done = 0, it = 0;      // it: ring stages consumed so far (kept in step with the TMA and MMA warps)
+  uint32_t attn_chunks = 0, ait = 0;       // attention chunks done (parity of its MMA barriers), uses of its ring
   for (uint32_t i = 0;; ++i) {
     volatile uint32_t* cur = slots + (i & 1u) * 4;     // [0] task, [1] dependencies satisfied, [2] failure
     if (leader) {
@@ -322,9 +332,10 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
             if (leader) report_failure(p, MACO_STATUS_BAD_TASK, task, d.u.comm.op, c.abort_word);
           }
         } else if (d.type == MACO_TASK_ATTENTION && attn_pipelined(d.u.elt)) {
-          const AttnPipe pipe{ring_smem, c.full, c.empty, (uint32_t)MkLayout::kStageBytes, (uint32_t)kMkStages, p.budget_ns, c.abort_word};
-          if (!attn_consume(d.u.elt, tid, scratch_smem, pipe, it)) cur[2] = 1;
-          it += attn_stage_uses(d.u.elt);
+          const AttnPipe pipe{ring_smem, attn_bars + 4, attn_bars + 4 + kAttnStages, p.budget_ns, c.abort_word,
+                              nullptr, attn_bars, tmem_base};
+          if (!attn_consume(d.u.elt, tid, scratch_smem, pipe, ait, attn_chunks)) cur[2] = 1;
+          ait += attn_stage_uses(d.u.elt);
           general_bar();
           if (leader) slots[13] = slots[13] + 1;                 // lets the MMA warp move past this task
         } else if (d.type == MACO_TASK_ATTENTION || d.type == MACO_TASK_ATTN_MERGE) {
@@ -457,23 +468,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) maco_persistent_kernel(const 
     const uint32_t w = blockIdx.x;
     // All roles must start from the same ring position: one thread reads it before anyone can move it.
     uint64_t* bulk_bars = reinterpret_cast<uint64_t*>(extra + 32);          // bytes 128.. of the extra block
+    uint64_t* attn_bars = reinterpret_cast<uint64_t*>(extra + 64);          // bytes 256..383: 4 MMA barriers, then full[6], empty[6] of the K/V ring
     if (threadIdx.x == 0) {
       extra[16] = p.mode == MACO_MODE_DYNAMIC ? ld_relaxed_gpu_u32(&p.tails[w]) : 0;
       extra[12] = 0;                                                     // parity bits of the bulk barriers
       extra[13] = 0;                                                     // pipelined attention tasks finished
       for (uint32_t b = 0; b < kBulkBuffers; ++b) mbar_init(&bulk_bars[b], 1);
+      for (int b = 0; b < 4 + 2 * kAttnStages; ++b) mbar_init(&attn_bars[b], 1);   // attention: 4 MMA barriers, ring full / empty
       fence_mbar_init();
     }
     __syncthreads();
     const uint32_t q_base = extra[16];
     if (warp == 0) {
-      if (lane == 0) producer_role(p, w, q_base, smem, c);
+      if (lane == 0) producer_role(p, w, q_base, smem, c, attn_bars + 4);
       __syncwarp();
     } else if (warp == 1) {
       if (lane == 0) mma_role(p, w, q_base, smem, c, tmem_base, extra + 13);
       __syncwarp();
     } else {
-      general_role(p, w, q_base, c, tmem_base, extra, reinterpret_cast<uint8_t*>(extra) + kMkExtraSmem, smem, bulk_bars);
+      general_role(p, w, q_base, c, tmem_base, extra, reinterpret_cast<uint8_t*>(extra) + kMkExtraSmem, smem, bulk_bars, attn_bars);
     }
   } else {
     if (warp == 0) scheduler_role(p, extra);

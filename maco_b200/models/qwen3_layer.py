@@ -78,7 +78,6 @@ class Qwen3DecodeLayer:
         e = lambda *s, dt=dtype: torch.empty(*s, device=dev, dtype=dt)
         self.x = e(B, H)
         self.h1, self.qkv, self.q_rot, self.attn = e(B, H), e(B, (hq + 2 * hkv) * D), e(B, hq, D), e(B, hq * D)
-        self.partials = e(B * hkv * self.splits, self.G * D + 2 * self.G, dt=torch.float32)
         self.y1, self.h2, self.act, self.out = e(B, H), e(B, H), e(B, self.f_local), e(B, H)
         if world > 1:
             self.slots1 = heap.alloc((world, B, H), dtype)
@@ -109,30 +108,10 @@ class Qwen3DecodeLayer:
                                 rows=B, cols=D, ld_in=qw, ld_out=hkv * S * D, extra_waits=[qkv_done])
             kv_waits += [(e_k.all_event[0], e_k.all_event[1], False, False), (e_v.all_event[0], e_v.all_event[1], False, False)]
         ready = b.join(kv_waits)
-        # split-KV attention: one task per (sequence, kv head, split), then one merge per (sequence, kv head)
-        rec = G * D + 2 * G
-        per = -(-S // self.splits)
-        es = self.q_rot.element_size()
-        merged = b.new_event()
-        for bh in range(B * hkv):
-            bi, j = divmod(bh, hkv)
-            ev = b.new_event()
-            n_split = 0
-            for s in range(self.splits):
-                s0 = s * per
-                keys = min(per, S - s0)
-                if keys <= 0:
-                    keys = 0
-                kv_off = ((bi * hkv + j) * S + s0) * D * es
-                raw = _pack_elt(self.q_rot.data_ptr() + (bi * hq + j * G) * D * es, self.k_cache.data_ptr() + kv_off,
-                                self.v_cache.data_ptr() + kv_off, self.partials.data_ptr() + (bh * self.splits + s) * rec * 4,
-                                0, keys, D, dt, D, 0, f0=D ** -0.5, i0=G)
-                b.add_task(int(TaskType.ATTENTION), raw, waits=ready, signals=[ev])
-                n_split += 1
-            raw = _pack_elt(self.partials.data_ptr() + bh * self.splits * rec * 4, 0, 0,
-                            self.attn.data_ptr() + (bi * hq + j * G) * D * es, 0, 0, D, dt, 0, 0, i0=G, i1=self.splits)
-            b.add_task(int(TaskType.ATTN_MERGE), raw, waits=[(ev, n_split, False, False)], signals=[merged])
-        e_attn = RowEvents(rows=B, block=BM, row_events=[(merged, B * hkv)], all_event=(merged, B * hkv))
+        # split-KV attention on the tensor cores: one task per (sequence, kv head, split), then the merges
+        merged, n_merged = b.attention_decode(self.q_rot.view(B, hq, D), self.k_cache, self.v_cache, self.attn.view(B, hq, D),
+                                              kv_len=S, splits=self.splits, waits=ready)
+        e_attn = RowEvents(rows=B, block=BM, row_events=[(merged, n_merged)], all_event=(merged, n_merged))
         slots1 = self.slots1 if self.world > 1 else None
         slots2 = self.slots2 if self.world > 1 else None
         e_y1 = fused.gemm_allreduce(b, self.attn, self.w_o, slots1, self.y1, residual=self.x, a_ready=e_attn)

@@ -312,6 +312,64 @@ class ProgramBuilder:
                                     wait_count=list(t["wait_count"]), flags=t["flags"] & mask))
             i = j
 
+    # ------------------------------------------------------------------ decode attention node
+    def attention_decode(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor, *,
+                         kv_len: Optional[int] = None, splits: int = 1, scale: Optional[float] = None,
+                         waits: Sequence[Tuple[int, int, bool, bool]] = ()) -> Tuple[int, int]:
+        """Split-KV decode attention: q [B, hq, D] against caches [B, hkv, S, D] -> out [B, hq, D].
+
+        One ATTENTION task per (sequence, kv head, split) writes an fp32 partial {o, m, l}; one ATTN_MERGE
+        task per (sequence, kv head) combines the splits. 16-bit caches with D = 128 run on the tensor
+        cores (csrc/attention_decode.cuh), fed by TMA through tensor maps over the flattened caches.
+        All attention tasks are emitted before the merges: with static queues a merge placed right behind
+        its splits would hold its worker idle until the neighbours finish theirs.
+        Returns (event, count) that is complete when every merge has run.
+        The reference declares ATTENTION as a task type and never implements it (maco/csrc/maco_types.h:24-40).
+        """
+        B, hq, D = q.shape
+        _, hkv, S, _ = k_cache.shape
+        G = hq // hkv
+        kv_len = S if kv_len is None else kv_len
+        if hq % hkv or G > 8 or D != 128 or kv_len > S:
+            raise ValueError("attention_decode: head_dim 128, at most 8 query heads per kv head, kv_len <= cache length")
+        if not (q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous() and out.is_contiguous()):
+            raise ValueError("attention_decode: contiguous tensors only")
+        dt = N.DTYPE_CODE[q.dtype]
+        es = q.element_size()
+        scale = D ** -0.5 if scale is None else scale
+        rec = G * D + 2 * G
+        partials = torch.empty(B * hkv * splits * rec, device=q.device, dtype=torch.float32)
+        self.keepalive += [q, k_cache, v_cache, out, partials]
+        tm_kv = 0
+        if es == 2:
+            rows_total = B * hkv * S
+            tk = self._tmap(k_cache.view(rows_total, D), rows_total, D, D, False, BM)
+            tv = self._tmap(v_cache.view(rows_total, D), rows_total, D, D, True, 64)
+            tm_kv = (tk + 1) | ((tv + 1) << 16)
+        waits = self.join(list(waits))
+        per = -(-kv_len // splits)
+        merged = self.new_event()
+        merges = []
+        for bh in range(B * hkv):
+            bi, j = divmod(bh, hkv)
+            ev = self.new_event()
+            n_split = 0
+            for sp in range(splits):
+                s0 = sp * per
+                keys = max(0, min(per, kv_len - s0))
+                row = (bi * hkv + j) * S + s0
+                raw = _pack_elt(q.data_ptr() + (bi * hq + j * G) * D * es, k_cache.data_ptr() + row * D * es,
+                                v_cache.data_ptr() + row * D * es, partials.data_ptr() + (bh * splits + sp) * rec * 4,
+                                row, keys, D, dt, D, tm_kv, f0=scale, i0=G)
+                self.add_task(int(TaskType.ATTENTION), raw, waits=waits, signals=[ev])
+                n_split += 1
+            raw = _pack_elt(partials.data_ptr() + bh * splits * rec * 4, 0, 0, out.data_ptr() + (bi * hq + j * G) * D * es,
+                            0, 0, D, dt, 0, 0, i0=G, i1=splits)
+            merges.append((raw, ev, n_split))
+        for raw, ev, n_split in merges:
+            self.add_task(int(TaskType.ATTN_MERGE), raw, waits=[(ev, n_split, False, False)], signals=[merged])
+        return merged, B * hkv
+
     # ------------------------------------------------------------------ element-wise / row-wise node
     def elementwise(self, ttype: int, in0: torch.Tensor, out: torch.Tensor, *, in1: Optional[torch.Tensor] = None,
                     in2: Optional[torch.Tensor] = None, rows: int, cols: int, f0: float = 0.0, f1: float = 0.0,
