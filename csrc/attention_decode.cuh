@@ -467,22 +467,36 @@ MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratc
   else attn_decode_task_t<MACO_DT_F16>(a, tid, scratch);
 }
 
+// Combines the S split records {o[G][128], m[G], l[G]} of one (sequence, kv head): thread `tid` owns output
+// dimension `tid` of every head. The loads of one split are independent of each other (8 heads in flight).
 MACO_DEVICE void attn_merge_task(const MacoEltArgs& a, int tid) {
-  const int G = a.i0, S = a.i1;
+  const int G = a.i0 < kAttnMaxG ? a.i0 : kAttnMaxG, S = a.i1;
   const int rec = G * kAttnD + 2 * G;
   const float* part = reinterpret_cast<const float*>(a.in0);
-  for (int g = 0; g < G; ++g) {
-    float M = -INFINITY;
-    for (int s = 0; s < S; ++s) M = fmaxf(M, part[s * rec + G * kAttnD + g]);
-    float L = 0.f, acc = 0.f;
-    for (int s = 0; s < S; ++s) {
-      const float ms = part[s * rec + G * kAttnD + g];
-      const float w = (ms == -INFINITY) ? 0.f : __expf(ms - M);
-      L += part[s * rec + G * kAttnD + G + g] * w;
-      acc += part[s * rec + g * kAttnD + tid] * w;
-    }
-    store1(a.out, g * kAttnD + tid, a.dtype, L > 0.f ? acc / L : 0.f);
+  float M[kAttnMaxG], L[kAttnMaxG], acc[kAttnMaxG];
+#pragma unroll
+  for (int g = 0; g < kAttnMaxG; ++g) { M[g] = -INFINITY; L[g] = 0.f; acc[g] = 0.f; }
+  for (int s = 0; s < S; ++s) {
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) if (g < G) M[g] = fmaxf(M[g], part[s * rec + G * kAttnD + g]);
   }
+  for (int s = 0; s < S; ++s) {
+    float ms[kAttnMaxG], ls[kAttnMaxG], os[kAttnMaxG];
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) {
+      ms[g] = g < G ? part[s * rec + G * kAttnD + g] : -INFINITY;
+      ls[g] = g < G ? part[s * rec + G * kAttnD + G + g] : 0.f;
+      os[g] = g < G ? part[s * rec + g * kAttnD + tid] : 0.f;
+    }
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) {
+      const float w = (ms[g] == -INFINITY) ? 0.f : __expf(ms[g] - M[g]);
+      L[g] += ls[g] * w;
+      acc[g] += os[g] * w;
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < kAttnMaxG; ++g) if (g < G) store1(a.out, g * kAttnD + tid, a.dtype, L[g] > 0.f ? acc[g] / L[g] : 0.f);
 }
 
 MACO_DEVICE void attn_run(uint32_t type, const MacoEltArgs& a, int tid, int nthreads, uint8_t* scratch) {

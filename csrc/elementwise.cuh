@@ -325,7 +325,59 @@ __device__ __noinline__ void elt_rowwise_t(const MacoEltArgs& ar, int tid, int n
   }
 }
 
+// RMSNorm with all 128 threads on one row (decode: fewer rows than warps in the machine). Every load of
+// the row and of the weights is issued before the first use and the row stays in registers between the
+// sum of squares and the scaling: one memory round trip per row. cols <= 8192, a multiple of 8.
+template <int DTT>
+__device__ __noinline__ void elt_rmsnorm_block_t(const MacoEltArgs& ar, int tid) {
+  const MacoEltArgs a = ar;
+  __shared__ float red[2][4];
+  constexpr int U = 8;
+  const int lane = tid & 31, warp = tid >> 5;
+  for (int rr = 0; rr < a.rows; ++rr) {
+    const long long r = a.row0 + rr;
+    const long long ib = r * a.ld_in, ob = r * a.ld_out;
+    uint4 lo[U], hi[U], wl[U], wh[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int c = (tid + u * 128) * 8;
+      if (c < a.cols) { load8_raw(a.in0, ib + c, DTT, lo[u], hi[u]); load8_raw(a.in1, c, DTT, wl[u], wh[u]); }
+    }
+    float s2 = 0.f;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if ((tid + u * 128) * 8 < a.cols) {
+        const F8 x = cvt8(DTT, lo[u], hi[u]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s2 += x.v[j] * x.v[j];
+      }
+    }
+    s2 = warp_sum(s2);
+    if (lane == 0) red[rr & 1][warp] = s2;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const float rstd = rsqrtf((red[rr & 1][0] + red[rr & 1][1] + red[rr & 1][2] + red[rr & 1][3]) / a.cols + a.f0);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int c = (tid + u * 128) * 8;
+      if (c < a.cols) {
+        const F8 x = cvt8(DTT, lo[u], hi[u]), w = cvt8(DTT, wl[u], wh[u]);
+        F8 o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.v[j] = x.v[j] * rstd * w.v[j];
+        store8(a.out, ob + c, DTT, o);
+      }
+    }
+  }
+}
+
 MACO_DEVICE void elt_rowwise(uint32_t type, const MacoEltArgs& a, int tid, int nthreads) {
+  // i1 = 1 asks for the one-row-per-CTA form of RMSNorm
+  if (type == MACO_TASK_RMSNORM && a.i1 == 1 && nthreads == 128 && a.cols <= 8192 && elt_vec_ok(a)) {
+    if (a.dtype == MACO_DT_BF16) elt_rmsnorm_block_t<MACO_DT_BF16>(a, tid);
+    else if (a.dtype == MACO_DT_F16) elt_rmsnorm_block_t<MACO_DT_F16>(a, tid);
+    else elt_rmsnorm_block_t<MACO_DT_F32>(a, tid);
+    return;
+  }
 #define MACO_ROWWISE_CASE(T)                                                              \
   case T:                                                                                 \
     if (a.dtype == MACO_DT_BF16) elt_rowwise_t<MACO_DT_BF16, T>(a, tid, nthreads);        \
@@ -369,6 +421,34 @@ MACO_DEVICE void elt_rope(const MacoEltArgs& a, int tid, int nthreads) {
 MACO_DEVICE void elt_qknorm_rope(const MacoEltArgs& a, int tid, int nthreads) {
   const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
   const int half = a.cols / 2;
+  if (a.cols == 128 && a.dtype != MACO_DT_F32) {
+    // head_dim 128, 16-bit values: a lane owns elements {2l, 2l+1} of both halves; every load of a row is
+    // issued before the first use (one memory round trip per row instead of three)
+    const bool bf = a.dtype == MACO_DT_BF16;
+    auto up = [bf](uint32_t w) { return bf ? unpack_bf16x2(w) : __half22float2(*reinterpret_cast<const __half2*>(&w)); };
+    auto pk = [bf](float x, float y) {
+      if (bf) return pack_bf16x2(x, y);
+      const __half2 h = __floats2half2_rn(x, y);
+      return *reinterpret_cast<const uint32_t*>(&h);
+    };
+    const uint32_t* wv = reinterpret_cast<const uint32_t*>(a.in1);
+    const uint32_t w1r = wv[lane], w2r = wv[32 + lane];
+    for (int rr = warp; rr < a.rows; rr += nwarps) {
+      const long long r = a.row0 + rr;
+      const long long tokr = r / a.i0, head = r - tokr * a.i0;
+      const uint32_t* x = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(a.in0) + tokr * a.ld_in + head * 128);
+      const uint32_t* cs = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(a.in2) + (tokr + a.i1) * 128);
+      uint32_t* o = reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(a.out) + tokr * a.ld_out + head * 128);
+      const uint32_t x1r = x[lane], x2r = x[32 + lane], cr = cs[lane], sr = cs[32 + lane];
+      float2 x1 = up(x1r), x2 = up(x2r);
+      const float2 c = up(cr), sn = up(sr), w1 = up(w1r), w2 = up(w2r);
+      const float rstd = rsqrtf(warp_sum(x1.x * x1.x + x1.y * x1.y + x2.x * x2.x + x2.y * x2.y) / 128.f + a.f0);
+      x1.x *= rstd * w1.x; x1.y *= rstd * w1.y; x2.x *= rstd * w2.x; x2.y *= rstd * w2.y;
+      o[lane] = pk(x1.x * c.x - x2.x * sn.x, x1.y * c.y - x2.y * sn.y);
+      o[32 + lane] = pk(x2.x * c.x + x1.x * sn.x, x2.y * c.y + x1.y * sn.y);
+    }
+    return;
+  }
   for (int rr = warp; rr < a.rows; rr += nwarps) {
     const long long r = a.row0 + rr;
     const long long tok = r / a.i0 + a.i1;

@@ -178,7 +178,18 @@ MACO_DEVICE void epi_store_row32(const GemmEpilogue& e, void* out_base, long lon
                                  int ncols_valid, const float (&v)[32]) {
   if (e.out_type == MACO_DT_F32) {
     float* p = reinterpret_cast<float*>(out_base) + row * e.ld_out + col0;
-    if (e.mode == MACO_EPI_F32_ACC) {
+    if (e.mode == MACO_EPI_F32_ATOMIC) {
+      // split-K: several tiles add into the same fp32 block; vector reductions at the L2
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        if (j + 4 <= ncols_valid) {
+          asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                       :: "l"(p + j), "f"(v[j]), "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3]) : "memory");
+        } else {
+          for (int t = j; t < ncols_valid && t < j + 4; ++t) atomicAdd(p + t, v[t]);
+        }
+      }
+    } else if (e.mode == MACO_EPI_F32_ACC) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
         if (j + 4 <= ncols_valid) {

@@ -32,6 +32,7 @@
 #include "comm_tasks.cuh"
 #include "attention_decode.cuh"
 #include "moe_tasks.cuh"
+#include "splitk_tasks.cuh"
 #include "host_common.h"
 
 using namespace maco;
@@ -256,7 +257,8 @@ __device__ __noinline__ void run_attn(uint32_t type, const MacoEltArgs& a, int t
   attn_run(type, a, tid, 128, scratch);
 }
 __device__ __noinline__ void run_moe(const MacoProgram& p, uint32_t type, const MacoEltArgs& a, int tid, uint8_t* scratch) {
-  if (type == MACO_TASK_TOPK) moe_topk_dispatch(p, a, tid, scratch);
+  if (type == MACO_TASK_SPLITK_FIN) splitk_finalize(p, a, tid);
+  else if (type == MACO_TASK_TOPK) moe_topk_dispatch(p, a, tid, scratch);
   else if (type == MACO_TASK_MOE_COUNTS) moe_publish_counts(p, a, tid);
   else moe_return(p, a, tid, scratch);
 }
@@ -340,7 +342,8 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
           if (leader) slots[13] = slots[13] + 1;                 // lets the MMA warp move past this task
         } else if (d.type == MACO_TASK_ATTENTION || d.type == MACO_TASK_ATTN_MERGE) {
           run_attn(d.type, d.u.elt, tid, scratch_smem);
-        } else if (d.type == MACO_TASK_TOPK || d.type == MACO_TASK_MOE_COUNTS || d.type == MACO_TASK_MOE_RETURN) {
+        } else if (d.type == MACO_TASK_TOPK || d.type == MACO_TASK_MOE_COUNTS || d.type == MACO_TASK_MOE_RETURN ||
+                   d.type == MACO_TASK_SPLITK_FIN) {
           run_moe(p, d.type, d.u.elt, tid, scratch_smem);
         } else if (d.type != MACO_TASK_NOP) {
           if (!run_elt(d.type, d.u.elt, tid)) {

@@ -38,6 +38,7 @@ enum MacoTaskType {
   MACO_TASK_AXPBY = 115,         /* out = f0 * in0 + f1 * in1 */
   MACO_TASK_MOE_RETURN = 116,    /* expert output rows -> weighted -> back to the source rank's combine buffer */
   MACO_TASK_MOE_COUNTS = 117,    /* publish this rank's per-expert token counts to the expert owners */
+  MACO_TASK_SPLITK_FIN = 118,    /* split-K GEMM: fp32 partial-sum buffer -> epilogue op -> 16-bit output (local or every rank) */
   MACO_TASK_CUSTOM_COMPUTE = 150,
   MACO_TASK_ALLREDUCE = 200,     /* reduce one chunk over all peers' buffers, write to all */
   MACO_TASK_ALLGATHER = 201,     /* push one chunk of the local shard to every peer */
@@ -59,7 +60,8 @@ enum MacoEpilogueMode {
   MACO_EPI_F32_ACC = 4,    /* fp32 out += alpha * acc */
   MACO_EPI_GELU_BWD = 5,   /* out = alpha * acc * gelu'(aux) */
   MACO_EPI_SILU = 6,
-  MACO_EPI_RESIDUAL = 7    /* out = alpha * acc + bias + aux */
+  MACO_EPI_RESIDUAL = 7,   /* out = alpha * acc + bias + aux */
+  MACO_EPI_F32_ATOMIC = 8  /* fp32 out += alpha * acc with atomic adds: split-K partial tiles share one buffer */
 };
 
 struct GemmEpilogue {

@@ -68,7 +68,7 @@ class Qwen3DecodeLayer:
         self.w_qkv = mk(g, (hq + 2 * hkv) * D, H)
         self.w_o = mk(g, H, hq * D)
         self.w_gate, self.w_up, self.w_down = mk(g, self.f_local, H), mk(g, self.f_local, H), mk(g, H, self.f_local)
-        self.w_gate_up = interleave_gate_up(self.w_gate, self.w_up, block=64)
+        self.w_gate_up = interleave_gate_up(self.w_gate, self.w_up, block=128)   # 256-column tiles: gate 128 | up 128
         self.S = kv_len + 1                                        # cache rows incl. the new token
         self.k_cache = mk(g, B, hkv, self.S, D, std=1.0)
         self.v_cache = mk(g, B, hkv, self.S, D, std=1.0)
@@ -93,7 +93,8 @@ class Qwen3DecodeLayer:
         qw = (hq + 2 * hkv) * D
         e_h1 = b.elementwise(int(TaskType.RMSNORM), self.x, self.h1, in1=self.w_in, rows=B, cols=H, f0=self.eps,
                              extra_waits=fence)
-        e_qkv = b.gemm(self.h1, self.w_qkv, self.qkv, a_ready=e_h1, bn=128)
+        # the four projections are weight-streaming GEMMs with 64 rows: split-K tiles over every SM
+        e_qkv = b.gemm_splitk(self.h1, self.w_qkv, self.qkv, a_ready=e_h1)
         qkv_done = (e_qkv.all_event[0], e_qkv.all_event[1], False, False)
         # QK-norm + RoPE: q into its own buffer, k straight into the cache row of the new token
         e_q = b.elementwise(int(TaskType.ROPE), self.qkv[:, : hq * D], self.q_rot, in1=self.q_norm, in2=self.cos_sin,
@@ -117,7 +118,7 @@ class Qwen3DecodeLayer:
         e_y1 = fused.gemm_allreduce(b, self.attn, self.w_o, slots1, self.y1, residual=self.x, a_ready=e_attn)
         e_h2 = b.elementwise(int(TaskType.RMSNORM), self.y1, self.h2, in1=self.w_post, rows=B, cols=H, f0=self.eps,
                              in_ready=[e_y1])
-        e_act = b.gemm(self.h2, self.w_gate_up, self.act, epilogue="swiglu", a_ready=e_h2, bn=128)
+        e_act = b.gemm_splitk(self.h2, self.w_gate_up, self.act, epilogue="swiglu", a_ready=e_h2)
         e_out = fused.gemm_allreduce(b, self.act, self.w_down, slots2, self.out, residual=self.y1, a_ready=e_act)
         if self.world > 1:
             fused.epoch_fence_signal(b, [(e_out.all_event[0], e_out.all_event[1], False, False)])

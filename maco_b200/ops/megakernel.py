@@ -31,8 +31,9 @@ TF_COUNTED = 128        # GEMM tile guarded by a run-time row count
 COMM_PUSH, COMM_REDUCE_LOCAL, COMM_REDUCE_PULL, COMM_ALLREDUCE, COMM_ALLREDUCE_MC, COMM_PULL = range(6)
 MAX_PEERS = 16
 WORKER_QUEUE_SIZE = 1024
+T_SPLITK_FIN = 118
 
-EPI = {None: 0, "none": 0, "gelu": 1, "swiglu": 2, "f32": 3, "f32_acc": 4, "gelu_bwd": 5, "silu": 6, "residual": 7}
+EPI = {None: 0, "none": 0, "gelu": 1, "swiglu": 2, "f32": 3, "f32_acc": 4, "gelu_bwd": 5, "silu": 6, "residual": 7, "f32_atomic": 8}
 
 TASK_DTYPE = np.dtype([
     ("type", "<u2"), ("flags", "<u2"), ("node_id", "<u4"), ("wait_event", "<i4", 2), ("wait_count", "<u4", 2),
@@ -312,6 +313,79 @@ class ProgramBuilder:
                                     wait_count=list(t["wait_count"]), flags=t["flags"] & mask))
             i = j
 
+    # ------------------------------------------------------------------ split-K GEMM for few rows (decode)
+    def gemm_splitk(self, a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], *, split_k: int = 0,
+                    epilogue: Optional[str] = None, aux: Optional[torch.Tensor] = None,
+                    a_ready: Optional[RowEvents] = None, extra_waits: Sequence[Tuple[int, int, bool, bool]] = (),
+                    heap_out_off: Optional[int] = None, ld_out: Optional[int] = None,
+                    signal_peer_event: int = -1, rows_per_task: int = 0) -> RowEvents:
+        """``out = op(a @ w.T)`` for at most 128 rows, bound by streaming ``w`` out of HBM.
+
+        The K dimension is cut into ``split_k`` slices (0: enough slices for every worker to hold a tile),
+        256-column tcgen05 tiles add their fp32 partial sums into one workspace with vector reductions,
+        and SPLITK_FIN tasks (csrc/splitk_tasks.cuh) apply ``epilogue`` (None, "swiglu" over the
+        interleaved gate/up layout, "residual" with ``aux``) and write the 16-bit result: into ``out``, or,
+        with ``heap_out_off``, at that byte offset of EVERY rank's symmetric heap (the exchange step of a
+        one-shot all-reduce), bumping ``signal_peer_event`` on every rank.
+        The reference runs such GEMMs as one torch.mm each (maco/task_graph/runtime.py:188-209).
+        """
+        M, K = a.shape
+        Nn = w.shape[0]
+        if M > BM or w.shape[1] != K or Nn % 256 or K % BK:
+            raise ValueError("gemm_splitk: at most 128 rows, N a multiple of 256, K a multiple of 64")
+        mode = {None: 0, "none": 0, "swiglu": 1, "residual": 2}[epilogue]
+        n_tiles, k_blocks = Nn // 256, K // BK
+        if split_k <= 0:
+            # waves of tiles over the workers x (k-blocks per tile + a fixed cost per tile: pipeline fill, reductions)
+            def cost(sp: int) -> int:
+                return -(-n_tiles * sp // self.num_workers) * (-(-k_blocks // sp) + 8)
+            split_k = min(range(1, max(1, min(16, k_blocks // 2)) + 1), key=cost)
+        split_k = max(1, min(split_k, k_blocks))
+        ws = torch.zeros(M, Nn, device=a.device, dtype=torch.float32)      # SPLITK_FIN leaves it zeroed again
+        out_dtype = out.dtype if out is not None else a.dtype
+        ab = 1 if a.dtype == torch.bfloat16 else 0
+        idesc = make_idesc(ab, BM, 256, 0, 0)
+        ta = self._tmap(a, a.shape[0], a.shape[1], a.stride(0), False, BM)
+        tb = self._tmap(w, w.shape[0], w.shape[1], w.stride(0), False, 256)
+        self.epis.append(_pack_epilogue(ws.data_ptr(), None, None, Nn, 0, EPI["f32_atomic"], N.DTYPE_CODE[torch.float32], 0, 0,
+                                        M, Nn, 1.0))
+        epi = len(self.epis) - 1
+        self.keepalive += [t for t in (a, w, out, aux, ws) if t is not None]
+        node_id = self.new_node_id()
+        waits = list(extra_waits)
+        if a_ready is not None:
+            ev, cnt = a_ready.for_rows(0, M)
+            waits.append((ev, cnt, a_ready.sys, False))
+        waits = self.join(list(dict.fromkeys(waits)), node_id)
+        e_ws = self.new_event()
+        n_parts = 0
+        for sp in range(split_k):
+            kb0 = sp * k_blocks // split_k
+            kb1 = (sp + 1) * k_blocks // split_k
+            if kb1 <= kb0:
+                continue
+            for nb in range(n_tiles):
+                raw = _pack_gemm(ta, tb, epi, 0, 0, 0, nb * 256, kb0 * BK, kb1 - kb0, idesc, -1, 0, 0, 256)
+                self.add_task(int(TaskType.LINEAR), raw, waits=waits, signals=[e_ws], node_id=node_id)
+                n_parts += 1
+        # second half: one task per few rows, spread over the workers
+        out_cols = Nn // 2 if mode == 1 else Nn
+        ld_o = ld_out if ld_out is not None else (out.stride(0) if out is not None else out_cols)
+        if rows_per_task <= 0:
+            rows_per_task = max(1, M // self.num_workers)
+        done = self.new_event()
+        n_fin = 0
+        dt = N.DTYPE_CODE[out_dtype]
+        for r0 in range(0, M, rows_per_task):
+            rr = min(rows_per_task, M - r0)
+            raw = _pack_elt(ws.data_ptr(), aux.data_ptr() if aux is not None else 0,
+                            heap_out_off if heap_out_off is not None else 0, out.data_ptr() if out is not None else 0,
+                            r0, rr, out_cols, dt, Nn, ld_o, i0=mode, i1=-2 if heap_out_off is not None else -1)
+            self.add_task(T_SPLITK_FIN, raw, waits=[(e_ws, n_parts, False, False)], signals=[done],
+                          signal_peer=-2 if signal_peer_event >= 0 else -1, signal_peer_event=signal_peer_event, node_id=node_id)
+            n_fin += 1
+        return RowEvents(rows=M, block=BM, row_events=[(done, n_fin)], all_event=(done, n_fin))
+
     # ------------------------------------------------------------------ decode attention node
     def attention_decode(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor, *,
                          kv_len: Optional[int] = None, splits: int = 1, scale: Optional[float] = None,
@@ -379,6 +453,9 @@ class ProgramBuilder:
         """Row-chunked task list for an operator of csrc/elementwise.cuh over a [rows, cols] view."""
         dt = N.DTYPE_CODE[in0.dtype]
         esz = in0.element_size()
+        if (ttype == int(TaskType.RMSNORM) and rows_per_task is None and i1 == 0 and rows <= self.num_workers
+                and cols <= 8192 and cols % 8 == 0):
+            rows_per_task, i1 = 1, 1      # decode: one row per task, all 128 threads of the worker on it
         if rows_per_task is None:
             target = max(1, (256 * 1024) // max(1, cols * esz))       # ~256 KiB of input per task
             if rows * cols * esz <= (4 << 20):

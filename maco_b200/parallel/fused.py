@@ -187,14 +187,18 @@ def allreduce_tasks(b: ProgramBuilder, buf: torch.Tensor, *, avg: bool = False, 
 def gemm_allreduce(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, slots: Optional[torch.Tensor],
                    out: torch.Tensor, *, residual: Optional[torch.Tensor] = None, a_ready: Optional[RowEvents] = None,
                    extra_waits: Sequence[Tuple[int, int, bool, bool]] = (), bn: int = 128,
-                   reduce_rows: int = 8) -> RowEvents:
+                   reduce_rows: Optional[int] = None) -> RowEvents:
     """``out = all_reduce(a @ w.T) (+ residual)`` for small row counts (decode): the GEMM epilogue stores
     every partial tile into slot ``rank`` of ALL ranks' ``slots`` [world, M, N] (one-shot exchange) and
     bumps their counters; each rank then sums its slots and the residual. With one rank the residual is
     added in the GEMM epilogue and nothing is exchanged."""
     M, Nn = a.shape[0], w.shape[0]
     heap = b.heap
+    splitk = M <= BM and Nn % 256 == 0 and a.shape[1] % 64 == 0 and (residual is None or residual.stride(0) == out.stride(0))
     if heap is None or heap.world == 1:
+        if splitk:
+            return b.gemm_splitk(a, w, out, epilogue="residual" if residual is not None else None, aux=residual,
+                                 a_ready=a_ready, extra_waits=extra_waits)
         return b.gemm(a, w, out, epilogue="residual" if residual is not None else None, aux=residual, a_ready=a_ready,
                       extra_waits=extra_waits, bn=bn)
     rank, world = heap.rank, heap.world
@@ -203,22 +207,30 @@ def gemm_allreduce(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, slots: O
     off = heap.offset_of(slots)
     slot_bytes = M * Nn * slots.element_size()
     arrived = b.new_event()
-    n_tiles = (Nn + bn - 1) // bn
+    if splitk:
+        # split-K tiles over every SM; the finishing tasks write this rank's partial into slot `rank` of every rank
+        fin = b.gemm_splitk(a, w, None, a_ready=a_ready, extra_waits=extra_waits, heap_out_off=off + rank * slot_bytes,
+                            ld_out=Nn, signal_peer_event=arrived)
+        n_arrive = fin.all_event[1]
+    else:
+        n_arrive = (Nn + bn - 1) // bn
 
-    def per_tile(mb: int, nb: int) -> dict:
-        return dict(peer=-2, out_off=off + rank * slot_bytes, signal_peer=-2, signal_peer_event=arrived)
+        def per_tile(mb: int, nb: int) -> dict:
+            return dict(peer=-2, out_off=off + rank * slot_bytes, signal_peer=-2, signal_peer_event=arrived)
 
-    b.gemm(a, w, slots[0], a_ready=a_ready, extra_waits=extra_waits, bn=bn, per_tile=per_tile)
+        b.gemm(a, w, slots[0], a_ready=a_ready, extra_waits=extra_waits, bn=bn, per_tile=per_tile)
     row_bytes = Nn * slots.element_size()
     done = b.new_event()
     total = 0
+    if reduce_rows is None:
+        reduce_rows = max(1, M // b.num_workers)     # latency-bound: spread the rows over the workers
     for r0 in range(0, M, reduce_rows):
         rr = min(reduce_rows, M - r0)
         raw = _pack_comm(off + r0 * row_bytes, 0, row_bytes, row_bytes, row_bytes, rr, N.DTYPE_CODE[slots.dtype], -1,
                          COMM_REDUCE_LOCAL, nslots=world, slot_stride=slot_bytes,
                          local_ptr=out.data_ptr() + r0 * row_bytes,
                          aux_ptr=(residual.data_ptr() + r0 * row_bytes) if residual is not None else 0)
-        b.add_task(int(TaskType.ALLREDUCE), raw, waits=[(arrived, world * n_tiles, True, False)], signals=[done])
+        b.add_task(int(TaskType.ALLREDUCE), raw, waits=[(arrived, world * n_arrive, True, False)], signals=[done])
         total += 1
     b.keepalive += [slots, out] + ([residual] if residual is not None else [])
     return RowEvents(rows=M, block=BM, row_events=[(done, total)], all_event=(done, total))

@@ -124,3 +124,61 @@ def test_sm_scheduling_demo_barrier():
     o = order.cpu().view(tasks, ctas)
     assert all(sorted(row.tolist()) == list(range(ctas)) for row in o)   # every barrier round saw each CTA once
     assert _native.status() == 0
+
+
+@pytest.mark.parametrize("mode", ["static", "dynamic"])
+@pytest.mark.parametrize("epilogue", [None, "swiglu", "residual"])
+def test_splitk_decode_gemm(mode, epilogue):
+    """Few-row GEMM as split-K tiles with fp32 vector reductions plus finishing tasks, run three times:
+    the finishing tasks must leave the workspace zeroed for the next launch."""
+    from maco_b200.ops import interleave_gate_up, megakernel as mk
+    dt = torch.bfloat16
+    M, K, Nn = 48, 1536, 1024
+    x = torch.randn(M, K, device="cuda", dtype=dt)
+    w = torch.randn(Nn, K, device="cuda", dtype=dt) * 0.03
+    xf = x.float()
+    if epilogue == "swiglu":
+        wg, wu = w[: Nn // 2], w[Nn // 2:]
+        wk = interleave_gate_up(wg.contiguous(), wu.contiguous(), block=128)
+        ref = torch.nn.functional.silu(xf @ wg.float().t()) * (xf @ wu.float().t())
+        out = torch.empty(M, Nn // 2, device="cuda", dtype=dt)
+        aux = None
+    else:
+        wk = w
+        aux = torch.randn(M, Nn, device="cuda", dtype=dt) if epilogue == "residual" else None
+        ref = xf @ w.float().t() + (aux.float() if aux is not None else 0)
+        out = torch.empty(M, Nn, device="cuda", dtype=dt)
+    b = mk.ProgramBuilder(torch.device("cuda"), mode=mode)
+    b.gemm_splitk(x, wk, out, split_k=5, epilogue=epilogue, aux=aux)
+    prog = b.build()
+    for _ in range(3):
+        out.zero_()
+        prog.run()
+    torch.cuda.synchronize()
+    assert _native.status() == 0
+    assert_close(out, ref, dt)
+
+
+def test_attention_decode_node_multi_chunk():
+    """Tensor-core decode attention node: ragged last chunk, several chunks per split (the K/V ring
+    wraps), a split whose first scores are far below later ones (the lazy softmax reference has to move)."""
+    from maco_b200.ops import megakernel as mk
+    dt = torch.bfloat16
+    B, hq, hkv, S, kv_len = 3, 16, 2, 1100, 1037
+    q = torch.randn(B, hq, 128, device="cuda", dtype=dt)
+    k = torch.randn(B, hkv, S, 128, device="cuda", dtype=dt)
+    v = torch.randn(B, hkv, S, 128, device="cuda", dtype=dt)
+    k[:, :, 600:640] *= 4.0                       # a late burst of large scores
+    out = torch.empty_like(q)
+    b = mk.ProgramBuilder(torch.device("cuda"))
+    b.attention_decode(q, k, v, out, kv_len=kv_len, splits=2)
+    prog = b.build()
+    for _ in range(2):
+        out.zero_()
+        prog.run()
+    torch.cuda.synchronize()
+    assert _native.status() == 0
+    G = hq // hkv
+    p = torch.softmax(torch.einsum("bhgd,bhsd->bhgs", q.float().view(B, hkv, G, 128), k[:, :, :kv_len].float()) * 128 ** -0.5, -1)
+    ref = torch.einsum("bhgs,bhsd->bhgd", p, v[:, :, :kv_len].float()).reshape(B, hq, 128)
+    assert_close(out, ref, dt)
