@@ -444,14 +444,66 @@ __device__ __noinline__ bool attn_consume_t(const MacoEltArgs& ar, int tid, uint
   }
   attn_bar();
   float* out = reinterpret_cast<float*>(a.out);
+  const int S = a.i1;                              // splits of this (sequence, kv head); the last one to finish merges
+  uint32_t* counter = reinterpret_cast<uint32_t*>(const_cast<void*>(a.in1));
+  if (S <= 1 && counter != nullptr) {
+    // a single split: normalise and write the final rows directly
 #pragma unroll
-  for (int g = 0; g < kAttnMaxG; ++g) if (g < G) out[g * kAttnD + row] = o[g];
-  if (tid < G) {
-    float mg = -INFINITY;
+    for (int g = 0; g < kAttnMaxG; ++g) {
+      if (g < G) {
+        const float l = red_m[g] + red_m[kAttnMaxG + g] + red_m[2 * kAttnMaxG + g] + red_m[3 * kAttnMaxG + g];
+        store1(const_cast<void*>(a.in2), g * kAttnD + row, DTT, l > 0.f ? o[g] / l : 0.f);
+      }
+    }
+  } else {
 #pragma unroll
-    for (int g = 0; g < kAttnMaxG; ++g) if (g == tid) mg = m_ref[g];
-    out[G * kAttnD + tid] = mg;
-    out[G * kAttnD + G + tid] = red_m[tid] + red_m[kAttnMaxG + tid] + red_m[2 * kAttnMaxG + tid] + red_m[3 * kAttnMaxG + tid];
+    for (int g = 0; g < kAttnMaxG; ++g) if (g < G) out[g * kAttnD + row] = o[g];
+    if (tid < G) {
+      float mg = -INFINITY;
+#pragma unroll
+      for (int g = 0; g < kAttnMaxG; ++g) if (g == tid) mg = m_ref[g];
+      out[G * kAttnD + tid] = mg;
+      out[G * kAttnD + G + tid] = red_m[tid] + red_m[kAttnMaxG + tid] + red_m[2 * kAttnMaxG + tid] + red_m[3 * kAttnMaxG + tid];
+    }
+    if (counter != nullptr) {
+      // The split that arrives last at the group's counter combines all S records (no separate merge
+      // task, no extra dependency hop). The counter only grows: S arrivals per launch.
+      __threadfence();                             // this thread's part of the record is visible GPU-wide
+      attn_bar();
+      __shared__ uint32_t s_last;
+      if (tid == 0) s_last = ((atomicAdd(counter, 1u) + 1u) % (uint32_t)S) == 0u ? 1u : 0u;
+      attn_bar();
+      if (s_last != 0u) {
+        __threadfence();
+        const int rec = G * kAttnD + 2 * G;
+        const float* part = out - (size_t)(int)a.f1 * rec;      // record of split 0 of this group
+        float M[kAttnMaxG], L[kAttnMaxG], acc[kAttnMaxG];
+#pragma unroll
+        for (int g = 0; g < kAttnMaxG; ++g) { M[g] = -INFINITY; L[g] = 0.f; acc[g] = 0.f; }
+        for (int sp = 0; sp < S; ++sp) {
+#pragma unroll
+          for (int g = 0; g < kAttnMaxG; ++g) if (g < G) M[g] = fmaxf(M[g], __ldcg(part + sp * rec + G * kAttnD + g));
+        }
+        for (int sp = 0; sp < S; ++sp) {
+          float ms[kAttnMaxG], ls[kAttnMaxG], os[kAttnMaxG];
+#pragma unroll
+          for (int g = 0; g < kAttnMaxG; ++g) {
+            ms[g] = g < G ? __ldcg(part + sp * rec + G * kAttnD + g) : -INFINITY;
+            ls[g] = g < G ? __ldcg(part + sp * rec + G * kAttnD + G + g) : 0.f;
+            os[g] = g < G ? __ldcg(part + sp * rec + g * kAttnD + row) : 0.f;
+          }
+#pragma unroll
+          for (int g = 0; g < kAttnMaxG; ++g) {
+            const float w = (ms[g] == -INFINITY) ? 0.f : __expf(ms[g] - M[g]);
+            L[g] += ls[g] * w;
+            acc[g] += os[g] * w;
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < kAttnMaxG; ++g)
+          if (g < G) store1(const_cast<void*>(a.in2), g * kAttnD + row, DTT, L[g] > 0.f ? acc[g] / L[g] : 0.f);
+      }
+    }
   }
   attn_bar();                                     // red_m is free again
   return ok;

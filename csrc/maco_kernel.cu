@@ -91,6 +91,29 @@ __device__ bool mk_wait(const MacoProgram& p, const uint32_t* flag, uint32_t exp
 __device__ bool wait_deps(const MacoProgram& p, const MacoTaskDesc& d, uint32_t task, volatile uint32_t* cta_abort,
                           uint64_t* wait_ns) {
   const uint64_t t0 = wait_ns ? globaltimer_ns() : 0;
+  {
+    // common case, both conditions already hold: read the two counters together (one round trip instead
+    // of two) and order everything that follows behind them with a single acquire fence
+    bool sat = true, any_sys = false;
+    uint32_t v[2] = {0u, 0u}, need[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int e = d.wait_event[j];
+      if (e < 0) continue;
+      const bool sys = (d.flags & (j == 0 ? MACO_TF_WAIT0_SYS : MACO_TF_WAIT1_SYS)) != 0;
+      const bool prev = (d.flags & (j == 0 ? MACO_TF_WAIT0_PREV : MACO_TF_WAIT1_PREV)) != 0;
+      need[j] = (p.epoch - (prev ? 1u : 0u)) * d.wait_count[j];
+      v[j] = sys ? ld_relaxed_sys_u32(&p.events[e]) : ld_relaxed_gpu_u32(&p.events[e]);
+      any_sys |= sys;
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) if (d.wait_event[j] >= 0 && (int32_t)(v[j] - need[j]) < 0) sat = false;
+    if (sat) {
+      if (any_sys) fence_acq_rel_sys(); else fence_acq_rel_gpu();
+      if (wait_ns) *wait_ns += globaltimer_ns() - t0;
+      return true;
+    }
+  }
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int e = d.wait_event[j];
@@ -127,7 +150,14 @@ __device__ void signal_done(const MacoProgram& p, const MacoTaskDesc& d) {
 __device__ bool fetch_task(const MacoProgram& p, uint32_t w, uint32_t i, uint32_t q_base, uint32_t& task,
                            volatile uint32_t* cta_abort) {
   if (p.mode == MACO_MODE_STATIC) {
-    task = (i < p.static_count[w]) ? p.static_queue[(size_t)w * p.static_stride + i] : MACO_QUEUE_TERMINATE;
+    const uint32_t n = p.static_count[w];
+    const uint32_t* q = p.static_queue + (size_t)w * p.static_stride;
+    task = i < n ? q[i] : MACO_QUEUE_TERMINATE;
+    if (i + 1 < n) {
+      // the next descriptor is on its way while this task runs (the three roles share the L1 line)
+      const MacoTaskDesc* nd = p.tasks + (q[i + 1] & MACO_QUEUE_INDEX_MASK);
+      asm volatile("prefetch.global.L1 [%0];" :: "l"(nd));
+    }
     return true;
   }
   const uint32_t pos = q_base + i;
@@ -256,8 +286,10 @@ __device__ __noinline__ bool run_comm(const MacoProgram& p, const MacoTaskDesc& 
 __device__ __noinline__ void run_attn(uint32_t type, const MacoEltArgs& a, int tid, uint8_t* scratch) {
   attn_run(type, a, tid, 128, scratch);
 }
-__device__ __noinline__ void run_moe(const MacoProgram& p, uint32_t type, const MacoEltArgs& a, int tid, uint8_t* scratch) {
+__device__ __noinline__ void run_moe(const MacoProgram& p, uint32_t type, const MacoEltArgs& a, int tid, uint8_t* scratch,
+                                    BulkCtx* bulk) {
   if (type == MACO_TASK_SPLITK_FIN) splitk_finalize(p, a, tid);
+  else if (type == MACO_TASK_MOE_COMBINE) moe_combine(p, a, tid, bulk);
   else if (type == MACO_TASK_TOPK) moe_topk_dispatch(p, a, tid, scratch);
   else if (type == MACO_TASK_MOE_COUNTS) moe_publish_counts(p, a, tid);
   else moe_return(p, a, tid, scratch);
@@ -343,8 +375,8 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
         } else if (d.type == MACO_TASK_ATTENTION || d.type == MACO_TASK_ATTN_MERGE) {
           run_attn(d.type, d.u.elt, tid, scratch_smem);
         } else if (d.type == MACO_TASK_TOPK || d.type == MACO_TASK_MOE_COUNTS || d.type == MACO_TASK_MOE_RETURN ||
-                   d.type == MACO_TASK_SPLITK_FIN) {
-          run_moe(p, d.type, d.u.elt, tid, scratch_smem);
+                   d.type == MACO_TASK_SPLITK_FIN || d.type == MACO_TASK_MOE_COMBINE) {
+          run_moe(p, d.type, d.u.elt, tid, scratch_smem, ring_free ? &bulk : nullptr);
         } else if (d.type != MACO_TASK_NOP) {
           if (!run_elt(d.type, d.u.elt, tid)) {
             cur[2] = 1;

@@ -38,6 +38,7 @@ enum MacoTaskType {
   MACO_TASK_AXPBY = 115,         /* out = f0 * in0 + f1 * in1 */
   MACO_TASK_MOE_RETURN = 116,    /* expert output rows -> weighted -> back to the source rank's combine buffer */
   MACO_TASK_MOE_COUNTS = 117,    /* publish this rank's per-expert token counts to the expert owners */
+  MACO_TASK_MOE_COMBINE = 119,   /* out[token] = sum of the token's k returned rows (bulk-staged when the operand ring is idle) */
   MACO_TASK_SPLITK_FIN = 118,    /* split-K GEMM: fp32 partial-sum buffer -> epilogue op -> 16-bit output (local or every rank) */
   MACO_TASK_CUSTOM_COMPUTE = 150,
   MACO_TASK_ALLREDUCE = 200,     /* reduce one chunk over all peers' buffers, write to all */

@@ -13,7 +13,8 @@
 //
 //   in0  fp32 workspace [M, ld_in]            in1  aux rows (output dtype, stride ld_out) or null
 //   in2  byte offset inside the heap (i1 = -2)  out  local destination (i1 = -1)
-//   row0, rows; cols = OUTPUT columns; dtype = output type; ld_out = output row stride (elements)
+//        (all four already offset to the task's first column)
+//   row0, rows; cols = output columns of this task; dtype = output type; ld_out = output row stride (elements)
 //   i0   0: out = sum   1: SwiGLU over 256-column blocks [gate 128 | up 128]   2: out = sum + aux
 //   i1   -1: store to `out`   -2: store to every rank's heap at in2
 #pragma once
@@ -21,55 +22,53 @@
 
 namespace maco {
 
-template <typename Program>
-__device__ __noinline__ void splitk_finalize(const Program& p, const MacoEltArgs& ar, int tid) {
-  const MacoEltArgs a = ar;
+// SW: SwiGLU layout. Four vectors per thread per pass, every load issued before the first use: the four
+// general warps of a worker reach only 10-20 GB/s with loads that wait for one another (a round trip to
+// L2 / HBM is 0.5-1 us here), so the builder also cuts each row into column chunks, one task each.
+template <bool SW, typename Program>
+MACO_DEVICE void splitk_finalize_t(const Program& p, const MacoEltArgs& a, int tid) {
   constexpr int U = 4;
   const uint32_t nv = (uint32_t)a.cols >> 3, total = (uint32_t)a.rows * nv;
   float* ws = const_cast<float*>(reinterpret_cast<const float*>(a.in0));
-  const bool swiglu = a.i0 == 1;
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
   for (uint32_t base = tid; base < total; base += 128 * U) {
-    float4 x[U][2], y[U][2];
+    float4 x[U][SW ? 4 : 2];
     uint4 ax[U];
     float* src[U];
     long long oidx[U];
+    bool live[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const uint32_t i = base + u * 128;
-      src[u] = nullptr;
-      if (i < total) {
-        const uint32_t r = i / nv, c = (i - r * nv) << 3;
-        const long long row = a.row0 + r;
-        src[u] = ws + row * a.ld_in + (swiglu ? ((c >> 7) << 8) + (c & 127) : c);
-        oidx[u] = row * a.ld_out + c;
-        x[u][0] = __ldcg(reinterpret_cast<const float4*>(src[u]));
-        x[u][1] = __ldcg(reinterpret_cast<const float4*>(src[u]) + 1);
-        if (swiglu) {
-          y[u][0] = __ldcg(reinterpret_cast<const float4*>(src[u] + 128));
-          y[u][1] = __ldcg(reinterpret_cast<const float4*>(src[u] + 128) + 1);
-        }
-        if (a.i0 == 2) ax[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.in1) + oidx[u]);
-      }
+      uint32_t i = base + u * 128;
+      live[u] = i < total;
+      if (!live[u]) i = total - 1;                      // clamped: the load is issued anyway, the result dropped
+      const uint32_t r = i / nv, c = (i - r * nv) << 3;
+      const long long row = a.row0 + r;
+      src[u] = ws + row * a.ld_in + (SW ? ((c >> 7) << 8) + (c & 127) : c);
+      oidx[u] = row * a.ld_out + c;
+      const float4* q = reinterpret_cast<const float4*>(src[u]);
+      x[u][0] = __ldcg(q); x[u][1] = __ldcg(q + 1);
+      if (SW) { x[u][2] = __ldcg(q + 32); x[u][3] = __ldcg(q + 33); }
+      ax[u] = make_uint4(0, 0, 0, 0);
+      if (a.i0 == 2) ax[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.in1) + oidx[u]);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (src[u] == nullptr) continue;
-      reinterpret_cast<float4*>(src[u])[0] = zero;
-      reinterpret_cast<float4*>(src[u])[1] = zero;
+      if (!live[u]) continue;
+      float4* q = reinterpret_cast<float4*>(src[u]);
+      q[0] = zero; q[1] = zero;
+      if (SW) { q[32] = zero; q[33] = zero; }
       F8 v;
       v.v[0] = x[u][0].x; v.v[1] = x[u][0].y; v.v[2] = x[u][0].z; v.v[3] = x[u][0].w;
       v.v[4] = x[u][1].x; v.v[5] = x[u][1].y; v.v[6] = x[u][1].z; v.v[7] = x[u][1].w;
-      if (swiglu) {
-        reinterpret_cast<float4*>(src[u] + 128)[0] = zero;
-        reinterpret_cast<float4*>(src[u] + 128)[1] = zero;
-        const float up[8] = {y[u][0].x, y[u][0].y, y[u][0].z, y[u][0].w, y[u][1].x, y[u][1].y, y[u][1].z, y[u][1].w};
+      if (SW) {
+        const float up[8] = {x[u][2].x, x[u][2].y, x[u][2].z, x[u][2].w, x[u][3].x, x[u][3].y, x[u][3].z, x[u][3].w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) v.v[j] = silu(v.v[j]) * up[j];
       } else if (a.i0 == 2) {
-        const F8 r = cvt8(a.dtype, ax[u], ax[u]);
+        const F8 rr = cvt8(a.dtype, ax[u], ax[u]);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v.v[j] += r.v[j];
+        for (int j = 0; j < 8; ++j) v.v[j] += rr.v[j];
       }
       if (a.i1 == -2) {
         const unsigned long long off = reinterpret_cast<unsigned long long>(a.in2);
@@ -79,6 +78,13 @@ __device__ __noinline__ void splitk_finalize(const Program& p, const MacoEltArgs
       }
     }
   }
+}
+
+template <typename Program>
+__device__ __noinline__ void splitk_finalize(const Program& p, const MacoEltArgs& ar, int tid) {
+  const MacoEltArgs a = ar;
+  if (a.i0 == 1) splitk_finalize_t<true>(p, a, tid);
+  else splitk_finalize_t<false>(p, a, tid);
 }
 
 }  // namespace maco

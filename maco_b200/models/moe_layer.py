@@ -36,7 +36,7 @@ from ..parallel import fused
 from ..parallel.symm_heap import LocalHeap
 from ..task_graph.nodes import TaskType
 
-T_TOPK, T_MOE_RETURN, T_MOE_COUNTS, T_FILL = 110, 116, 117, 301
+T_TOPK, T_MOE_RETURN, T_MOE_COUNTS, T_MOE_COMBINE, T_FILL = 110, 116, 117, 119, 301
 
 
 def heap_bytes_needed(hidden: int, experts: int, top_k: int, tokens: int, world: int, capacity: int) -> int:
@@ -113,12 +113,14 @@ class MoEEPLayer:
                    signals=[e_fill])
         # 1. router
         e_log = b.gemm(self.x, self.w_router, self.logits, bn=128, extra_waits=[(e_fill, 1, False, False)])
-        # 2. top-k + dispatch, 32 tokens per task
+        # 2. top-k + dispatch: about one task per worker, a multiple of 4 tokens (one warp per token)
         e_disp_local = b.new_event()
         n_disp = 0
-        for t0 in range(0, T, 32):
-            ev, cnt = e_log.for_rows(t0, t0 + 32)
-            b.add_task(T_TOPK, _pack_elt(0, 0, pp, 0, t0, 32, H, dt, 0, 0), waits=[(ev, cnt, False, False)],
+        tok_per = max(4, -(-(-(-T // b.num_workers)) // 4) * 4)
+        for t0 in range(0, T, tok_per):
+            nt = min(tok_per, T - t0)
+            ev, cnt = e_log.for_rows(t0, t0 + nt)
+            b.add_task(T_TOPK, _pack_elt(0, 0, pp, 0, t0, nt, H, dt, 0, 0), waits=[(ev, cnt, False, False)],
                        signals=[e_disp_local])
             n_disp += 1
         # 3. counts to the expert owners; every rank learns that every rank has dispatched
@@ -148,16 +150,13 @@ class MoEEPLayer:
                 b.add_task(T_MOE_RETURN, _pack_elt(0, 0, pp, 0, rb * BM, BM, H, dt, 0, 0, i0=el, i1=s),
                            waits=[(ev, cnt, False, False)], signal_peer=s, signal_peer_event=e_ret)
         n_ret = W * EL * (C // BM)
-        # 6. combine: sum the k rows of every token
-        row_bytes = H * 2
-        comb_off = self.heap.offset_of(self.comb)
+        # 6. combine: sum the k rows of every token (token blocks streamed through the idle operand ring)
         e_out = b.new_event()
         n_out = 0
-        for t0 in range(0, T, 32):
-            raw = _pack_comm(comb_off + t0 * K * row_bytes, 0, K * row_bytes, row_bytes, row_bytes, 32, dt, -1,
-                             COMM_REDUCE_LOCAL, nslots=K, slot_stride=row_bytes,
-                             local_ptr=self.out.data_ptr() + t0 * row_bytes)
-            b.add_task(int(TaskType.REDUCE_SCATTER), raw, waits=[(e_ret, n_ret, True, False)], signals=[e_out])
+        per = max(8, -(-T // b.num_workers))
+        for t0 in range(0, T, per):
+            b.add_task(T_MOE_COMBINE, _pack_elt(0, 0, pp, self.out.data_ptr(), t0, min(per, T - t0), H, dt, 0, 0),
+                       waits=[(e_ret, n_ret, True, False)], signals=[e_out])
             n_out += 1
         fused.epoch_fence_signal(b, [(e_out, n_out, False, False)])
         self.program = b.build()

@@ -96,19 +96,25 @@ class Qwen3DecodeLayer:
         # the four projections are weight-streaming GEMMs with 64 rows: split-K tiles over every SM
         e_qkv = b.gemm_splitk(self.h1, self.w_qkv, self.qkv, a_ready=e_h1)
         qkv_done = (e_qkv.all_event[0], e_qkv.all_event[1], False, False)
-        # QK-norm + RoPE: q into its own buffer, k straight into the cache row of the new token
+        # QK-norm + RoPE: q into its own buffer, k straight into the cache row of the new token, v copied
+        # beside it. All of it bumps one event, so the attention tasks carry a single wait condition; task
+        # sizes are chosen for few tasks per worker (each costs a few us of fixed latency).
+        e_rope = b.new_event()
+        n_rope = 0
         e_q = b.elementwise(int(TaskType.ROPE), self.qkv[:, : hq * D], self.q_rot, in1=self.q_norm, in2=self.cos_sin,
                             rows=B * hq, cols=D, f0=self.eps, f1=1.0, i0=hq, i1=0, ld_in=qw, ld_out=hq * D,
-                            extra_waits=[qkv_done])
-        kv_waits = [(e_q.all_event[0], e_q.all_event[1], False, False)]
+                            extra_waits=[qkv_done], rows_per_task=16 if B * hq >= 16 * b.num_workers // 2 else 4,
+                            all_event=e_rope)
+        n_rope += e_q.all_event[1]
         for j in range(hkv):
             e_k = b.elementwise(int(TaskType.ROPE), self.qkv[:, (hq + j) * D:(hq + j + 1) * D], self.k_cache[:, j, self.pos, :],
                                 in1=self.k_norm, in2=self.cos_sin, rows=B, cols=D, f0=self.eps, f1=1.0, i0=1, i1=0,
-                                ld_in=qw, ld_out=hkv * S * D, extra_waits=[qkv_done])
+                                ld_in=qw, ld_out=hkv * S * D, extra_waits=[qkv_done], rows_per_task=4, all_event=e_rope)
             e_v = b.elementwise(T_COPY, self.qkv[:, (hq + hkv + j) * D:(hq + hkv + j + 1) * D], self.v_cache[:, j, self.pos, :],
-                                rows=B, cols=D, ld_in=qw, ld_out=hkv * S * D, extra_waits=[qkv_done])
-            kv_waits += [(e_k.all_event[0], e_k.all_event[1], False, False), (e_v.all_event[0], e_v.all_event[1], False, False)]
-        ready = b.join(kv_waits)
+                                rows=B, cols=D, ld_in=qw, ld_out=hkv * S * D, extra_waits=[qkv_done], rows_per_task=B,
+                                all_event=e_rope)
+            n_rope += e_k.all_event[1] + e_v.all_event[1]
+        ready = [(e_rope, n_rope, False, False)]
         # split-KV attention on the tensor cores: one task per (sequence, kv head, split), then the merges
         merged, n_merged = b.attention_decode(self.q_rot.view(B, hq, D), self.k_cache, self.v_cache, self.attn.view(B, hq, D),
                                               kv_len=S, splits=self.splits, waits=ready)

@@ -215,6 +215,13 @@ class ProgramBuilder:
         return len(self.tmaps) - 1
 
     # ------------------------------------------------------------------ GEMM node
+    def add_epilogue(self, out_ptr: int, ld_out: int, out_dtype: torch.dtype, M: int, Nn: int, *, mode: str = None,
+                     aux_ptr: int = 0, ld_aux: int = 0, aux_dtype: Optional[torch.dtype] = None, alpha: float = 1.0) -> int:
+        """Registers an extra epilogue record (raw pointers) and returns its index for ``per_tile``'s ``epi``."""
+        self.epis.append(_pack_epilogue(out_ptr, 0, aux_ptr, ld_out, ld_aux, EPI[mode], N.DTYPE_CODE[out_dtype], 0,
+                                        N.DTYPE_CODE[aux_dtype] if aux_dtype is not None else 0, M, Nn, float(alpha)))
+        return len(self.epis) - 1
+
     def gemm(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor], *, trans_a: bool = False,
              trans_b: bool = False, epilogue: Optional[str] = None, bias: Optional[torch.Tensor] = None,
              aux: Optional[torch.Tensor] = None, alpha: float = 1.0, bn: int = 0,
@@ -225,7 +232,8 @@ class ProgramBuilder:
 
         ``a_ready`` gives row-block events of A (a tile waits only for its 128 rows); ``extra_waits``
         apply to every tile. ``per_tile(mb, nb) -> dict`` may override ``peer``, ``out_off``,
-        ``row_off``, ``signal_peer``, ``signal_peer_event`` per tile (fused GEMM -> reduce-scatter).
+        ``row_off``, ``signal_peer``, ``signal_peer_event``, ``epi`` (index from ``add_epilogue``) and add
+        ``waits`` per tile (fused GEMM -> reduce-scatter).
         ``row_wait(mb) -> wait`` supplies a per-row-block wait instead of ``a_ready``.
         """
         for t in (a, b):
@@ -282,7 +290,11 @@ class ProgramBuilder:
                     if len(waits) > 2:
                         waits = self.join(waits, node_id)
                     ov = per_tile(mb, nb) if per_tile is not None else {}
-                    raw = _pack_gemm(ta, tb, epi, int(trans_a), int(trans_b), mb * BM, nb * bn, 0, k_blocks, idesc,
+                    if ov.get("waits"):
+                        waits = list(dict.fromkeys(waits + list(ov["waits"])))
+                        if len(waits) > 2:
+                            waits = self.join(waits, node_id)
+                    raw = _pack_gemm(ta, tb, ov.get("epi", epi), int(trans_a), int(trans_b), mb * BM, nb * bn, 0, k_blocks, idesc,
                                      ov.get("peer", -1), ov.get("row_off", 0), ov.get("out_off", 0), bn,
                                      ov.get("count_base", 0), ov.get("count_ptr", 0))
                     self.add_task(int(TaskType.LINEAR), raw, waits=waits, signals=[row_events[mb], all_ev],
@@ -371,19 +383,34 @@ class ProgramBuilder:
         # second half: one task per few rows, spread over the workers
         out_cols = Nn // 2 if mode == 1 else Nn
         ld_o = ld_out if ld_out is not None else (out.stride(0) if out is not None else out_cols)
+        if aux is not None and aux.stride(0) != ld_o:
+            raise ValueError("gemm_splitk: aux must have the output's row stride")
         if rows_per_task <= 0:
             rows_per_task = max(1, M // self.num_workers)
+        # one task per (row group, column chunk): about one per worker (a task costs several us of fixed
+        # latency: descriptor, dependency check, store drain, signal), chunks whole 128-column blocks
+        n_rowtasks = -(-M // rows_per_task)
+        chunks = max(1, min(out_cols // 128, self.num_workers // n_rowtasks))
+        while out_cols % (chunks * 128):
+            chunks -= 1
+        nc = out_cols // chunks
         done = self.new_event()
         n_fin = 0
         dt = N.DTYPE_CODE[out_dtype]
+        es = 2
         for r0 in range(0, M, rows_per_task):
             rr = min(rows_per_task, M - r0)
-            raw = _pack_elt(ws.data_ptr(), aux.data_ptr() if aux is not None else 0,
-                            heap_out_off if heap_out_off is not None else 0, out.data_ptr() if out is not None else 0,
-                            r0, rr, out_cols, dt, Nn, ld_o, i0=mode, i1=-2 if heap_out_off is not None else -1)
-            self.add_task(T_SPLITK_FIN, raw, waits=[(e_ws, n_parts, False, False)], signals=[done],
-                          signal_peer=-2 if signal_peer_event >= 0 else -1, signal_peer_event=signal_peer_event, node_id=node_id)
-            n_fin += 1
+            for ch in range(chunks):
+                c0 = ch * nc
+                ws_c0 = (c0 // 128) * 256 if mode == 1 else c0
+                raw = _pack_elt(ws.data_ptr() + ws_c0 * 4, aux.data_ptr() + c0 * es if aux is not None else 0,
+                                heap_out_off + c0 * es if heap_out_off is not None else 0,
+                                out.data_ptr() + c0 * es if out is not None else 0,
+                                r0, rr, nc, dt, Nn, ld_o, i0=mode, i1=-2 if heap_out_off is not None else -1)
+                self.add_task(T_SPLITK_FIN, raw, waits=[(e_ws, n_parts, False, False)], signals=[done],
+                              signal_peer=-2 if signal_peer_event >= 0 else -1, signal_peer_event=signal_peer_event,
+                              node_id=node_id)
+                n_fin += 1
         return RowEvents(rows=M, block=BM, row_events=[(done, n_fin)], all_event=(done, n_fin))
 
     # ------------------------------------------------------------------ decode attention node
@@ -392,12 +419,13 @@ class ProgramBuilder:
                          waits: Sequence[Tuple[int, int, bool, bool]] = ()) -> Tuple[int, int]:
         """Split-KV decode attention: q [B, hq, D] against caches [B, hkv, S, D] -> out [B, hq, D].
 
-        One ATTENTION task per (sequence, kv head, split) writes an fp32 partial {o, m, l}; one ATTN_MERGE
-        task per (sequence, kv head) combines the splits. 16-bit caches with D = 128 run on the tensor
-        cores (csrc/attention_decode.cuh), fed by TMA through tensor maps over the flattened caches.
-        All attention tasks are emitted before the merges: with static queues a merge placed right behind
-        its splits would hold its worker idle until the neighbours finish theirs.
-        Returns (event, count) that is complete when every merge has run.
+        One ATTENTION task per (sequence, kv head, split) writes an fp32 partial {o, m, l}. 16-bit caches
+        run on the tensor cores (csrc/attention_decode.cuh), fed by TMA through tensor maps over the
+        flattened caches, and the split that finishes last for a (sequence, kv head) combines the records
+        itself; other element types use the CUDA-core task plus one ATTN_MERGE task per (sequence, kv
+        head), emitted after all attention tasks (with static queues a merge placed right behind its
+        splits would hold its worker idle until the neighbours finish theirs).
+        Returns (event, count) that is complete when every output row is final.
         The reference declares ATTENTION as a task type and never implements it (maco/csrc/maco_types.h:24-40).
         """
         B, hq, D = q.shape
@@ -422,7 +450,24 @@ class ProgramBuilder:
             tm_kv = (tk + 1) | ((tv + 1) << 16)
         waits = self.join(list(waits))
         per = -(-kv_len // splits)
+        splits = -(-kv_len // per)                         # every split holds at least one key
         merged = self.new_event()
+        if tm_kv:
+            # tensor-core path: the split that finishes last for a (sequence, kv head) merges the records itself
+            counters = torch.zeros(B * hkv, device=q.device, dtype=torch.int32)   # only ever grow: `splits` per launch
+            self.keepalive.append(counters)
+            for bh in range(B * hkv):
+                bi, j = divmod(bh, hkv)
+                for sp in range(splits):
+                    s0 = sp * per
+                    keys = min(per, kv_len - s0)
+                    row = (bi * hkv + j) * S + s0
+                    raw = _pack_elt(q.data_ptr() + (bi * hq + j * G) * D * es, counters.data_ptr() + bh * 4,
+                                    out.data_ptr() + (bi * hq + j * G) * D * es,
+                                    partials.data_ptr() + (bh * splits + sp) * rec * 4,
+                                    row, keys, D, dt, D, tm_kv, f0=scale, f1=float(sp), i0=G, i1=splits)
+                    self.add_task(int(TaskType.ATTENTION), raw, waits=waits, signals=[merged])
+            return merged, B * hkv * splits
         merges = []
         for bh in range(B * hkv):
             bi, j = divmod(bh, hkv)
@@ -434,7 +479,7 @@ class ProgramBuilder:
                 row = (bi * hkv + j) * S + s0
                 raw = _pack_elt(q.data_ptr() + (bi * hq + j * G) * D * es, k_cache.data_ptr() + row * D * es,
                                 v_cache.data_ptr() + row * D * es, partials.data_ptr() + (bh * splits + sp) * rec * 4,
-                                row, keys, D, dt, D, tm_kv, f0=scale, i0=G)
+                                row, keys, D, dt, D, 0, f0=scale, i0=G)
                 self.add_task(int(TaskType.ATTENTION), raw, waits=waits, signals=[ev])
                 n_split += 1
             raw = _pack_elt(partials.data_ptr() + bh * splits * rec * 4, 0, 0, out.data_ptr() + (bi * hq + j * G) * D * es,
@@ -449,8 +494,10 @@ class ProgramBuilder:
                     in2: Optional[torch.Tensor] = None, rows: int, cols: int, f0: float = 0.0, f1: float = 0.0,
                     i0: int = 0, i1: int = 0, in_ready: Sequence[Optional[RowEvents]] = (),
                     extra_waits: Sequence[Tuple[int, int, bool, bool]] = (), rows_per_task: Optional[int] = None,
-                    ld_in: Optional[int] = None, ld_out: Optional[int] = None) -> RowEvents:
-        """Row-chunked task list for an operator of csrc/elementwise.cuh over a [rows, cols] view."""
+                    ld_in: Optional[int] = None, ld_out: Optional[int] = None, all_event: Optional[int] = None) -> RowEvents:
+        """Row-chunked task list for an operator of csrc/elementwise.cuh over a [rows, cols] view.
+        ``all_event`` lets several calls bump one shared completion event (the caller adds up the counts),
+        so that a consumer of all of them needs one wait condition instead of a chain of joins."""
         dt = N.DTYPE_CODE[in0.dtype]
         esz = in0.element_size()
         if (ttype == int(TaskType.RMSNORM) and rows_per_task is None and i1 == 0 and rows <= self.num_workers
@@ -467,7 +514,7 @@ class ProgramBuilder:
                 rows_per_task *= 2
         self.keepalive += [t for t in (in0, in1, in2, out) if t is not None]
         node_id = self.new_node_id()
-        all_ev = self.new_event()
+        all_ev = self.new_event() if all_event is None else all_event
         n_blocks = (rows + BM - 1) // BM
         row_events = [self.new_event() for _ in range(n_blocks)]
         counts = [0] * n_blocks
@@ -557,7 +604,10 @@ class Program:
                 queues[n_compute + rr_m % Wc].append(i)
                 rr_m += 1
             else:
-                queues[rr_c % n_compute].append(i)
+                # rotate by one worker per wave: with a plain modulo a worker would see the same position of
+                # every periodic task pattern (the same row block of every expert slab, say) and the load
+                # would follow that pattern instead of averaging out
+                queues[(rr_c + rr_c // n_compute) % n_compute].append(i)
                 rr_c += 1
         stride = max(1, max(len(q) for q in queues))
         sq = np.full((W, stride), QUEUE_TERMINATE, dtype=np.uint32)

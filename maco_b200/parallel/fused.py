@@ -106,6 +106,14 @@ def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, sta
                         reduce_rows: Optional[int] = None, scale: float = 1.0) -> Tuple[RowEvents, RowEvents]:
     """``out[rows_local, N] = reduce_scatter(a @ w.T)`` with the partial tiles leaving through the
     GEMM epilogue. ``staging`` is a heap tensor [world, rows_local, N] (slot = source rank).
+
+    Tiles of row blocks owned by other ranks go straight into the owner's slot (bulk stores from the
+    epilogue) and bump the owner's per-block counter; the own row blocks are computed last.
+    Two ranks: by then the peer's partial for them has arrived (each rank serves the other first), so
+    the own tile's epilogue adds the peer's slot to its accumulator and writes the final rows; no
+    reduction pass runs after the last GEMM tile. More ranks: the last peer delivers only when the own
+    blocks start, so the own tiles go to the local slot and the owner sums the slots with short
+    bulk-staged tasks spread over every worker (all of them are idle by then).
     Returns (events of the GEMM tiles, events of ``out``)."""
     heap = b.heap
     rank, world = heap.rank, heap.world
@@ -116,24 +124,44 @@ def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, sta
         raise ValueError("rows must be a multiple of world * 128")
     blocks_per_rank = rows_local // BM
     n_tiles = (Nn + bn - 1) // bn
+    es = staging.element_size()
+    st_off = heap.offset_of(staging)
+    slot_bytes = rows_local * Nn * es
+    row_bytes = Nn * es
+    part_events = [b.new_event() for _ in range(blocks_per_rank)]
+    order = rotated_blocks(rank, world, blocks_per_rank, own_last=True)
+    if world == 2 and scale == 1.0:
+        own_first = rank * blocks_per_rank
+        shift = rank * rows_local          # epilogue rows are the tile's global rows: shift both bases back
+        epi_own = b.add_epilogue(out.data_ptr() - shift * out.stride(0) * out.element_size(), out.stride(0), out.dtype, M, Nn,
+                                 mode="residual", aux_ptr=staging[1 - rank].data_ptr() - shift * row_bytes, ld_aux=Nn,
+                                 aux_dtype=staging.dtype)
+
+        def per_tile2(mb: int, nb: int) -> dict:
+            owner = mb // blocks_per_rank
+            if owner == rank:
+                return dict(epi=epi_own, waits=[(part_events[mb - own_first], n_tiles, True, False)])
+            return dict(peer=owner, out_off=st_off + rank * slot_bytes, row_off=-(owner * rows_local), signal_peer=owner,
+                        signal_peer_event=part_events[mb % blocks_per_rank])
+
+        gemm_ev = b.gemm(a, w, staging[0], a_ready=a_ready, bn=bn, per_tile=per_tile2, m_blocks=order)
+        b.keepalive += [staging, out]
+        own = gemm_ev.row_events[own_first: own_first + blocks_per_rank]
+        return gemm_ev, RowEvents(rows=rows_local, block=BM, row_events=list(own), all_event=gemm_ev.all_event)
+
     if reduce_rows is None:
         # about one reduction task per worker, so the tail after the last GEMM tile is one short task
         reduce_rows = 4
         while reduce_rows * 2 <= BM and rows_local // (reduce_rows * 2) >= b.num_workers:
             reduce_rows *= 2
-    st_off = heap.offset_of(staging)
-    slot_bytes = rows_local * Nn * staging.element_size()
-    part_events = [b.new_event() for _ in range(blocks_per_rank)]
 
     def per_tile(mb: int, nb: int) -> dict:
         owner = mb // blocks_per_rank
         return dict(peer=owner, out_off=st_off + rank * slot_bytes, row_off=-(owner * rows_local), signal_peer=owner,
                     signal_peer_event=part_events[mb % blocks_per_rank])
 
-    gemm_ev = b.gemm(a, w, staging[0], a_ready=a_ready, bn=bn, per_tile=per_tile,
-                     m_blocks=rotated_blocks(rank, world, blocks_per_rank, own_last=True))
+    gemm_ev = b.gemm(a, w, staging[0], a_ready=a_ready, bn=bn, per_tile=per_tile, m_blocks=order)
     # owner-side reduction of the `world` slots, fp32 accumulation
-    row_bytes = Nn * staging.element_size()
     out_events = [b.new_event() for _ in range(blocks_per_rank)]
     all_ev = b.new_event()
     total = 0
