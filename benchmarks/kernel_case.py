@@ -5,6 +5,8 @@
     python benchmarks/kernel_case.py mlp         # persistent kernel: fused SwiGLU MLP, 4096 tokens, 4096 -> 14336/4
     python benchmarks/kernel_case.py attention   # split-KV decode attention, batch 32, 4096 keys
     python benchmarks/kernel_case.py attention_tc  # persistent kernel: tensor-core decode attention, 512 tasks, 537 MB of KV
+    python benchmarks/kernel_case.py decode_gemm # persistent kernel: split-K 64 x 5120 x 25600 gate/up projection with SwiGLU
+    python benchmarks/kernel_case.py moe         # persistent kernel: MoE layer on one GPU (32 experts, top-4, 2048 tokens)
     python benchmarks/kernel_case.py rmsnorm     # row-wise kernel, 16384 x 8192 bf16
 
 Each case holds well under 1 GB on the device, uses inputs larger than the 126 MB L2 where DRAM
@@ -77,6 +79,34 @@ def main():
         err = (out[:4].float() - ref).abs().max().item()
         print(f"max abs error against fp32 PyTorch (4 sequences): {err:.2e}")
         assert err < 2e-2
+    elif case == "decode_gemm":
+        from maco_b200.ops import interleave_gate_up
+        from maco_b200.ops.megakernel import ProgramBuilder
+        M, K, F = 64, 5120, 12800
+        x = torch.randn(M, K, device="cuda", dtype=dt)
+        wg = torch.randn(F, K, device="cuda", dtype=dt) * 0.02
+        wu = torch.randn(F, K, device="cuda", dtype=dt) * 0.02
+        w = interleave_gate_up(wg, wu, block=128)
+        out = torch.empty(M, F, device="cuda", dtype=dt)
+        pb = ProgramBuilder(torch.device("cuda"))
+        pb.gemm_splitk(x, w, out, epilogue="swiglu")
+        prog = pb.build()
+        us = timed(prog.run)
+        print(f"persistent split-K decode GEMM {M}x{K}x{2 * F} + SwiGLU: {us:.1f} us, {w.numel() * 2 / us / 1e3:.0f} GB/s of weights")
+        ref = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
+        err = ((out.float() - ref).abs().max() / ref.abs().max()).item()
+        print(f"max error relative to the largest output, against fp32 PyTorch: {err:.2e}")
+        assert err < 2e-2
+    elif case == "moe":
+        from maco_b200.models.moe_layer import MoEEPLayer
+        layer = MoEEPLayer(hidden=2048, experts=32, top_k=4, inter=768, tokens=2048, router_std=0.05)
+        x = torch.randn(2048, 2048, device="cuda", dtype=dt)
+        layer.x.copy_(x)
+        us = timed(lambda: layer.forward(None))
+        ref = layer.reference(x)
+        err = ((layer.out.float() - ref).abs().max() / ref.abs().max()).item()
+        print(f"persistent MoE layer 2048 tok, 32 experts top-4: {us:.1f} us, dropped {layer.dropped()}, max rel error {err:.2e}")
+        assert err < 3e-2
     elif case == "rmsnorm":
         x = torch.randn(16384, 8192, device="cuda", dtype=dt)
         w = torch.randn(8192, device="cuda", dtype=dt)

@@ -237,6 +237,29 @@ MACO_DEVICE float epi_load_aux(const GemmEpilogue& e, long long row, int col) {
   return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(p));
 }
 
+// The 32 aux values beside one row's 32-column chunk: four 16-byte loads issued together when the chunk is
+// whole and aligned (one 2-byte load per element otherwise). Values past `valid` are 0.
+MACO_DEVICE void epi_load_aux32(const GemmEpilogue& e, long long row, int col0, int valid, float (&a)[32]) {
+  const uint16_t* p = reinterpret_cast<const uint16_t*>(e.aux) + row * e.ld_aux + col0;
+  if (valid == 32 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+    uint4 q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = reinterpret_cast<const uint4*>(p)[i];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 f = e.aux_type == MACO_DT_F16 ? __half22float2(*reinterpret_cast<const __half2*>(&w[t])) : unpack_bf16x2(w[t]);
+        a[i * 8 + 2 * t] = f.x; a[i * 8 + 2 * t + 1] = f.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) a[j] = j < valid ? epi_load_aux(e, row, col0 + j) : 0.f;
+  }
+}
+
 // Consumes one finished accumulator. Called by all 32 lanes of each of the 4 epilogue warps.
 // `out_base` lets a caller redirect the tile (for example into a peer GPU's buffer);
 // `row_off` is added to the tile's row index when storing (for scatter into per-rank slabs).
@@ -347,14 +370,18 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
       } else if (e.mode == MACO_EPI_GELU_BWD) {
+        float ax[32];
+        epi_load_aux32(e, row, col0, valid, ax);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) if (j < valid) v[j] *= gelu_tanh_grad(epi_load_aux(e, row, col0 + j));
+        for (int j = 0; j < 32; ++j) v[j] *= gelu_tanh_grad(ax[j]);
       } else if (e.mode == MACO_EPI_SILU) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = silu(v[j]);
       } else if (e.mode == MACO_EPI_RESIDUAL) {
+        float ax[32];
+        epi_load_aux32(e, row, col0, valid, ax);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) if (j < valid) v[j] += epi_load_aux(e, row, col0 + j);
+        for (int j = 0; j < 32; ++j) v[j] += ax[j];
       }
       if (staged) {
         if (row_ok) epi_stage_chunk(srow, ch & 1, e.out_type, v);

@@ -32,7 +32,7 @@ from ..task_graph.nodes import TaskType
 class DPMLPStackBackward:
     def __init__(self, layers: int = 16, hidden: int = 4096, tokens: int = 8192, *, rank: int = 0, world: int = 1,
                  heap=None, device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16, seed: int = 0,
-                 mode: str = "static", trace: bool = False, comm_workers: int = 16, weight_std: float = 0.02):
+                 mode: str = "static", trace: bool = False, comm_workers: Optional[int] = None, weight_std: float = 0.02):
         if tokens % BM or hidden % 256:
             raise ValueError("tokens must be a multiple of 128 and hidden of 256")
         if world > 1 and heap is None:
@@ -53,6 +53,9 @@ class DPMLPStackBackward:
             self.dw = heap.alloc((layers, hidden, hidden), torch.float32)
         else:
             self.dw = torch.empty(layers, hidden, hidden, device=dev, dtype=torch.float32)
+        if comm_workers is None:
+            # the gradient traffic per rank grows with (world-1)/world; a communication worker moves 25-40 GB/s
+            comm_workers = 8 if world <= 2 else 12
         self._build(mode, trace, comm_workers if world > 1 else 0)
 
     # ------------------------------------------------------------------ forward (set-up, separate launches)

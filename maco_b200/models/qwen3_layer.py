@@ -117,7 +117,7 @@ class Qwen3DecodeLayer:
         ready = [(e_rope, n_rope, False, False)]
         # split-KV attention on the tensor cores: one task per (sequence, kv head, split), then the merges
         merged, n_merged = b.attention_decode(self.q_rot.view(B, hq, D), self.k_cache, self.v_cache, self.attn.view(B, hq, D),
-                                              kv_len=S, splits=self.splits, waits=ready)
+                                              kv_len=S, splits=self.splits, waits=ready, balance=(mode == "static"))
         e_attn = RowEvents(rows=B, block=BM, row_events=[(merged, n_merged)], all_event=(merged, n_merged))
         slots1 = self.slots1 if self.world > 1 else None
         slots2 = self.slots2 if self.world > 1 else None

@@ -168,8 +168,9 @@ class ProgramBuilder:
     def add_task(self, ttype: int, raw: bytes, waits: Sequence[Tuple[int, int, bool, bool]] = (),
                  signals: Sequence[int] = (), signal_peer: int = -1, signal_peer_event: int = -1, node_id: int = 0,
                  comm_worker: bool = False, signal_sys: bool = False, any_worker: bool = False,
-                 counted: bool = False) -> int:
-        """``waits``: up to two (event, count, sys_scope, previous_epoch)."""
+                 counted: bool = False, worker: Optional[int] = None) -> int:
+        """``waits``: up to two (event, count, sys_scope, previous_epoch). ``worker`` pins the task to a compute
+        worker's static queue (the dynamic scheduler ignores it)."""
         if len(waits) > 2 or len(signals) > 2:
             raise ValueError("a task takes at most two wait conditions and two local signals")
         flags = 0
@@ -190,7 +191,7 @@ class ProgramBuilder:
             flags |= TF_COUNTED
         se = list(signals) + [-1] * (2 - len(signals))
         self.tasks.append(dict(type=ttype, flags=flags, node_id=node_id, wait_event=we, wait_count=wc, signal_event=se,
-                               signal_peer=signal_peer, signal_peer_event=signal_peer_event, raw=raw))
+                               signal_peer=signal_peer, signal_peer_event=signal_peer_event, raw=raw, worker=worker))
         return len(self.tasks) - 1
 
     def join(self, waits: List[Tuple[int, int, bool, bool]], node_id: int = 0) -> List[Tuple[int, int, bool, bool]]:
@@ -416,7 +417,7 @@ class ProgramBuilder:
     # ------------------------------------------------------------------ decode attention node
     def attention_decode(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor, *,
                          kv_len: Optional[int] = None, splits: int = 1, scale: Optional[float] = None,
-                         waits: Sequence[Tuple[int, int, bool, bool]] = ()) -> Tuple[int, int]:
+                         waits: Sequence[Tuple[int, int, bool, bool]] = (), balance: bool = False) -> Tuple[int, int]:
         """Split-KV decode attention: q [B, hq, D] against caches [B, hkv, S, D] -> out [B, hq, D].
 
         One ATTENTION task per (sequence, kv head, split) writes an fp32 partial {o, m, l}. 16-bit caches
@@ -453,21 +454,47 @@ class ProgramBuilder:
         splits = -(-kv_len // per)                         # every split holds at least one key
         merged = self.new_event()
         if tm_kv:
-            # tensor-core path: the split that finishes last for a (sequence, kv head) merges the records itself
-            counters = torch.zeros(B * hkv, device=q.device, dtype=torch.int32)   # only ever grow: `splits` per launch
-            self.keepalive.append(counters)
-            for bh in range(B * hkv):
+            # tensor-core path: the split that finishes last for a (sequence, kv head) merges the records itself.
+            # Pieces: either `splits` equal parts per (sequence, kv head), or (balance) the whole key range cut
+            # into one equal share per worker at 128-key boundaries, so no worker runs an extra wave.
+            pieces = []                                     # (bh, first key, keys, worker or None)
+            if balance:
+                W = self.num_workers
+                target = -(-(B * hkv * kv_len) // W)
+                target = -(-target // 128) * 128
+                wk, acc = 0, 0
+                for bh in range(B * hkv):
+                    s0 = 0
+                    while s0 < kv_len:
+                        room = target - acc                 # > 0 here; cuts inside a group sit on 128-key boundaries
+                        take = min(kv_len - s0, -(-room // 128) * 128)
+                        pieces.append((bh, s0, take, min(wk, W - 1)))
+                        s0 += take
+                        acc += take
+                        if acc >= target:
+                            wk, acc = wk + 1, 0
+            else:
+                for bh in range(B * hkv):
+                    for sp in range(splits):
+                        pieces.append((bh, sp * per, min(per, kv_len - sp * per), None))
+            n_of = [0] * (B * hkv)
+            for bh, _, _, _ in pieces:
+                n_of[bh] += 1
+            partials = torch.empty(len(pieces) * rec, device=q.device, dtype=torch.float32)
+            counters = torch.zeros(B * hkv, device=q.device, dtype=torch.int32)   # only ever grow: one per piece and launch
+            self.keepalive += [partials, counters]
+            idx_in_group = [0] * (B * hkv)
+            for pi, (bh, s0, keys, wk) in enumerate(pieces):
                 bi, j = divmod(bh, hkv)
-                for sp in range(splits):
-                    s0 = sp * per
-                    keys = min(per, kv_len - s0)
-                    row = (bi * hkv + j) * S + s0
-                    raw = _pack_elt(q.data_ptr() + (bi * hq + j * G) * D * es, counters.data_ptr() + bh * 4,
-                                    out.data_ptr() + (bi * hq + j * G) * D * es,
-                                    partials.data_ptr() + (bh * splits + sp) * rec * 4,
-                                    row, keys, D, dt, D, tm_kv, f0=scale, f1=float(sp), i0=G, i1=splits)
-                    self.add_task(int(TaskType.ATTENTION), raw, waits=waits, signals=[merged])
-            return merged, B * hkv * splits
+                sp = idx_in_group[bh]
+                idx_in_group[bh] += 1
+                row = (bi * hkv + j) * S + s0
+                # records of a group are consecutive: the piece index minus its position is the group's first record
+                raw = _pack_elt(q.data_ptr() + (bi * hq + j * G) * D * es, counters.data_ptr() + bh * 4,
+                                out.data_ptr() + (bi * hq + j * G) * D * es, partials.data_ptr() + pi * rec * 4,
+                                row, keys, D, dt, D, tm_kv, f0=scale, f1=float(sp), i0=G, i1=n_of[bh])
+                self.add_task(int(TaskType.ATTENTION), raw, waits=waits, signals=[merged], worker=wk)
+            return merged, len(pieces)
         merges = []
         for bh in range(B * hkv):
             bi, j = divmod(bh, hkv)
@@ -603,6 +630,8 @@ class Program:
             elif (t["flags"] & TF_COMM_WORKER) and Wc > 0:
                 queues[n_compute + rr_m % Wc].append(i)
                 rr_m += 1
+            elif t.get("worker") is not None:
+                queues[t["worker"] % n_compute].append(i)
             else:
                 # rotate by one worker per wave: with a plain modulo a worker would see the same position of
                 # every periodic task pattern (the same row block of every expert slab, say) and the load
