@@ -220,7 +220,7 @@ def cfg_moe(torch, dist, rank, world, heap, args):
 
 
 CONFIGS = {"tp_mlp": cfg_tp_mlp, "dp_backward": cfg_dp_backward, "qwen3_decode": cfg_qwen3_decode, "moe": cfg_moe}
-HEAP_MB = {"tp_mlp": 256, "dp_backward": 1400, "qwen3_decode": 64, "moe": 700}
+HEAP_MB = {"tp_mlp": 256, "dp_backward": 2500, "qwen3_decode": 64, "moe": 700}
 
 
 def main():

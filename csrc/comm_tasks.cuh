@@ -72,7 +72,7 @@ template <int DTT, int kR, int kS, typename Program>
 __device__ __noinline__ void comm_reduce(const Program& p, const MacoCommArgs& a, int n, uint32_t total, uint32_t vpr, int tid,
                              int nthreads) {
   uint8_t* mine = p.peer_heap[p.rank];
-  const bool local = a.op == MACO_COMM_REDUCE_LOCAL;
+  const bool local = a.op == MACO_COMM_REDUCE_LOCAL || a.op == MACO_COMM_REDUCE_LOCAL_BCAST;
   uint8_t* out = a.local_ptr != nullptr ? reinterpret_cast<uint8_t*>(a.local_ptr) : mine + a.dst_off;
   const uint32_t rstep = (uint32_t)nthreads * kR;
   for (uint32_t base = tid; base < total; base += rstep) {
@@ -119,7 +119,7 @@ __device__ __noinline__ void comm_reduce(const Program& p, const MacoCommArgs& a
       const uint32_t i = base + (uint32_t)u * nthreads;
       if (i >= total) continue;
       const uint4 o = pack8(acc[u], a.scale, DTT);
-      if (a.op == MACO_COMM_ALLREDUCE) {
+      if (a.op == MACO_COMM_ALLREDUCE || a.op == MACO_COMM_REDUCE_LOCAL_BCAST) {
         for (int j = 0; j < p.world; ++j)
           stv(p.peer_heap[(p.rank + j) % p.world] + a.dst_off + blk_off(i, vpr, a.dst_stride), o);
       } else {
@@ -194,71 +194,76 @@ template <int DTT, typename Program, typename BarFn>
 __device__ __noinline__ bool comm_reduce_bulk(const Program& p, const MacoCommArgs& a, int n, int tid, int nthreads, BulkCtx& bc,
                                   BarFn bar_sync) {
   uint8_t* mine = p.peer_heap[p.rank];
-  const bool local = a.op == MACO_COMM_REDUCE_LOCAL;
-  const bool bcast = a.op == MACO_COMM_ALLREDUCE;
+  const bool local = a.op == MACO_COMM_REDUCE_LOCAL || a.op == MACO_COMM_REDUCE_LOCAL_BCAST;
+  const bool bcast = a.op == MACO_COMM_ALLREDUCE || a.op == MACO_COMM_REDUCE_LOCAL_BCAST;
   uint8_t* out = a.local_ptr != nullptr ? reinterpret_cast<uint8_t*>(a.local_ptr) : mine + a.dst_off;
   const uint64_t bytes = (uint64_t)a.rows * a.row_bytes;
-  const uint32_t groups = bc.nbuf / (uint32_t)n;             // chunk positions per round
+  const uint32_t groups = bc.nbuf / (uint32_t)n;             // chunk positions that fit the staging buffers
+  // Every chunk position is a pipeline stage of its own: while the threads sum one position, the loads of all
+  // the others (and, for an all-reduce, the stores of earlier results) are in flight, so a round trip to a
+  // peer (several microseconds) is covered by `groups - 1` stages of work.
   const uint64_t round_bytes = (uint64_t)groups * bc.buf_bytes;
   bool ok = true;
-  if (tid == 0) fence_proxy_async_all();
-  for (uint64_t pos = 0; pos < bytes; pos += round_bytes) {
-    const uint32_t phase = *bc.phase;                         // stable: the leader flips it between the two barriers below
+  // leader: loads of position g for the round that starts at byte `pos`
+  auto issue = [&](uint32_t g, uint64_t pos) {
+    const uint64_t off = pos + (uint64_t)g * bc.buf_bytes;
+    if (off >= bytes) return;
+    const uint32_t nb = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
+    for (int j = 0; j < n; ++j) {
+      const uint32_t b = g * n + j;
+      const uint8_t* src = local ? mine + a.src_off + (uint64_t)j * a.slot_stride
+                                 : p.peer_heap[(p.rank + j) % p.world] + a.src_off;
+      mbar_arrive_expect_tx(&bc.bars[b], nb);
+      bulk_load(bc.buf + (size_t)b * bc.buf_bytes, src + off, nb, &bc.bars[b]);
+    }
+  };
+  // everybody: wait for position g of the round at `pos`, sum, write (or stage) the result; then the leader
+  // sends the staged result (all-reduce) and refills the position for the next round
+  auto consume = [&](uint32_t g, uint64_t pos) {
+    const uint64_t off = pos + (uint64_t)g * bc.buf_bytes;
+    if (off >= bytes) return;                                // uniform over the thread group
+    const uint32_t nb = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
+    const uint32_t phase = *bc.phase;                        // this position's bits change only after the barrier below
     uint32_t used_mask = 0;
-    for (uint32_t g = 0; g < groups; ++g) {
-      const uint64_t off = pos + (uint64_t)g * bc.buf_bytes;
-      if (off >= bytes) break;
-      const uint32_t nb = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
-      for (int j = 0; j < n; ++j) {
-        const uint32_t b = g * n + j;
-        used_mask |= 1u << b;
-        if (tid == 0) {
-          const uint8_t* src = local ? mine + a.src_off + (uint64_t)j * a.slot_stride
-                                     : p.peer_heap[(p.rank + j) % p.world] + a.src_off;
-          mbar_arrive_expect_tx(&bc.bars[b], nb);
-          bulk_load(bc.buf + (size_t)b * bc.buf_bytes, src + off, nb, &bc.bars[b]);
-        }
+    for (int j = 0; j < n; ++j) {
+      const uint32_t b = g * n + j;
+      used_mask |= 1u << b;
+      const uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_wait(&bc.bars[b], (phase >> b) & 1u)) {
+        if (globaltimer_ns() - t0 > p.budget_ns) { ok = false; break; }
       }
     }
-    for (uint32_t g = 0; g < groups; ++g) {
-      const uint64_t off = pos + (uint64_t)g * bc.buf_bytes;
-      if (off >= bytes) break;
-      const uint32_t nb = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
-      for (int j = 0; j < n; ++j) {
-        const uint32_t b = g * n + j;
-        const uint64_t t0 = globaltimer_ns();
-        while (!mbar_try_wait(&bc.bars[b], (phase >> b) & 1u)) {
-          if (globaltimer_ns() - t0 > p.budget_ns) { ok = false; break; }
-        }
-      }
-      uint8_t* g0 = bc.buf + (size_t)(g * n) * bc.buf_bytes;
-      for (uint32_t v = tid; v < (nb >> 4); v += nthreads) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < n; ++j) add8(acc, *reinterpret_cast<const uint4*>(g0 + (size_t)j * bc.buf_bytes + ((size_t)v << 4)), DTT);
-        if (a.aux_ptr != nullptr) add8(acc, ldv(reinterpret_cast<const uint8_t*>(a.aux_ptr) + off + ((uint64_t)v << 4)), DTT);
-        const uint4 o = pack8(acc, a.scale, DTT);
-        if (bcast) *reinterpret_cast<uint4*>(g0 + ((size_t)v << 4)) = o;      // result replaces source 0 in shared memory
-        else stv(out + off + ((uint64_t)v << 4), o);
-      }
+    uint8_t* g0 = bc.buf + (size_t)(g * n) * bc.buf_bytes;
+    for (uint32_t v = tid; v < (nb >> 4); v += nthreads) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < n; ++j) add8(acc, *reinterpret_cast<const uint4*>(g0 + (size_t)j * bc.buf_bytes + ((size_t)v << 4)), DTT);
+      if (a.aux_ptr != nullptr) add8(acc, ldv(reinterpret_cast<const uint8_t*>(a.aux_ptr) + off + ((uint64_t)v << 4)), DTT);
+      const uint4 o = pack8(acc, a.scale, DTT);
+      if (bcast) *reinterpret_cast<uint4*>(g0 + ((size_t)v << 4)) = o;        // result replaces source 0 in shared memory
+      else stv(out + off + ((uint64_t)v << 4), o);
     }
     if (bcast) fence_proxy_async_smem();
-    bar_sync();                                              // staged data consumed (and results staged)
+    bar_sync();                                              // the position is consumed (and its result staged)
     if (tid == 0) {
-      *bc.phase = phase ^ used_mask;
+      // only this position's bits change; the bits of other positions, which threads may be reading, keep their value
+      *bc.phase = *bc.phase ^ used_mask;
       if (bcast) {
-        for (uint32_t g = 0; g < groups; ++g) {
-          const uint64_t off = pos + (uint64_t)g * bc.buf_bytes;
-          if (off >= bytes) break;
-          const uint32_t nb = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
-          for (int j = 0; j < p.world; ++j)
-            bulk_store(p.peer_heap[(p.rank + j) % p.world] + a.dst_off + off, bc.buf + (size_t)(g * n) * bc.buf_bytes, nb);
-        }
+        for (int j = 0; j < p.world; ++j)
+          bulk_store(p.peer_heap[(p.rank + j) % p.world] + a.dst_off + off, g0, nb);
         tma_store_commit();
-        tma_store_wait_read<0>();
+        tma_store_wait_read<0>();                            // the staged result has left shared memory
       }
+      issue(g, pos + round_bytes);
     }
-    bar_sync();                                              // phase word and buffers are ready for the next round
+    if (groups == 1) bar_sync();                             // a single position: its phase bits are read again right away
+  };
+  if (tid == 0) {
+    fence_proxy_async_all();
+    for (uint32_t g = 0; g < groups; ++g) issue(g, 0);
   }
+  for (uint64_t pos = 0; pos < bytes; pos += round_bytes)
+    for (uint32_t g = 0; g < groups; ++g) consume(g, pos);
+  bar_sync();                                                // the last phase word is visible to the next task
   if (tid == 0 && bcast) tma_store_wait<0>();
   return ok;
 }
@@ -272,9 +277,10 @@ MACO_DEVICE bool comm_run(const Program& p, const MacoTaskDesc& d, int tid, int 
     if (tid == 0) ok = comm_push_bulk(p, a, *bulk, p.budget_ns);
     return ok;
   }
-  if (bulk != nullptr && (a.op == MACO_COMM_REDUCE_LOCAL || a.op == MACO_COMM_REDUCE_PULL || a.op == MACO_COMM_ALLREDUCE) &&
+  if (bulk != nullptr && (a.op == MACO_COMM_REDUCE_LOCAL || a.op == MACO_COMM_REDUCE_PULL || a.op == MACO_COMM_ALLREDUCE ||
+                          a.op == MACO_COMM_REDUCE_LOCAL_BCAST) &&
       a.src_stride == a.row_bytes && a.dst_stride == a.row_bytes && (uint64_t)a.rows * a.row_bytes >= 32768) {
-    const int n = a.op == MACO_COMM_REDUCE_LOCAL ? a.nslots : p.world;
+    const int n = (a.op == MACO_COMM_REDUCE_LOCAL || a.op == MACO_COMM_REDUCE_LOCAL_BCAST) ? a.nslots : p.world;
     if (n >= 1 && (uint32_t)n <= bulk->nbuf) {
       auto bar = [] { asm volatile("bar.sync 1, 128;" ::: "memory"); };
       if (a.dtype == MACO_DT_F32) return comm_reduce_bulk<MACO_DT_F32>(p, a, n, tid, nthreads, *bulk, bar);
@@ -321,9 +327,10 @@ MACO_DEVICE bool comm_run(const Program& p, const MacoTaskDesc& d, int tid, int 
       return true;
     }
     case MACO_COMM_REDUCE_LOCAL:
+    case MACO_COMM_REDUCE_LOCAL_BCAST:
     case MACO_COMM_REDUCE_PULL:
     case MACO_COMM_ALLREDUCE: {
-      const int n = a.op == MACO_COMM_REDUCE_LOCAL ? a.nslots : p.world;
+      const int n = (a.op == MACO_COMM_REDUCE_LOCAL || a.op == MACO_COMM_REDUCE_LOCAL_BCAST) ? a.nslots : p.world;
       // 8 independent 16-byte loads per thread in flight whatever the number of sources (more spills registers)
 #define MACO_REDUCE_DT(DT)                                                         \
       if (n <= 2) comm_reduce<DT, 4, 2>(p, a, n, total, vpr, tid, nthreads);       \

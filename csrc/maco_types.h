@@ -148,7 +148,8 @@ enum MacoCommOp {
   MACO_COMM_REDUCE_PULL = 2,      /* out = scale * sum over ranks of heap[r] + src_off (reads peers) */
   MACO_COMM_ALLREDUCE = 3,        /* pull-reduce one block from every rank, store the result to every rank */
   MACO_COMM_ALLREDUCE_MC = 4,     /* same through the NVSwitch multicast address (multimem) */
-  MACO_COMM_PULL = 5              /* copy a block of peer `peer`'s heap into my heap */
+  MACO_COMM_PULL = 5,             /* copy a block of peer `peer`'s heap into my heap */
+  MACO_COMM_REDUCE_LOCAL_BCAST = 6 /* sum `nslots` local slots (filled by the peers' stores) and write the result to dst_off on EVERY rank */
 };
 
 struct MacoTaskDesc {

@@ -24,7 +24,7 @@ import torch
 
 from .. import _native as N
 from .. import ops
-from ..ops.megakernel import BM, COMM_ALLREDUCE, ProgramBuilder, _pack_comm
+from ..ops.megakernel import BM, COMM_REDUCE_LOCAL_BCAST, ProgramBuilder, _pack_comm
 from ..parallel import fused
 from ..task_graph.nodes import TaskType
 
@@ -50,12 +50,17 @@ class DPMLPStackBackward:
         self.dz = [torch.empty(tokens, hidden, device=dev, dtype=dtype) for _ in range(2)]   # ping-pong
         self.da = torch.empty(tokens, hidden, device=dev, dtype=dtype)
         if world > 1:
+            if (hidden // BM) % world:
+                raise ValueError("hidden / 128 must be a multiple of world")
             self.dw = heap.alloc((layers, hidden, hidden), torch.float32)
+            # staging[l][source rank] holds the partial gradient blocks this rank owns (block mb is owned by rank
+            # mb % world and sits at index mb // world); the wgrad epilogues of every rank store into it
+            self.staging = heap.alloc((layers, world, hidden // world, hidden), torch.float32)
         else:
             self.dw = torch.empty(layers, hidden, hidden, device=dev, dtype=torch.float32)
         if comm_workers is None:
             # the gradient traffic per rank grows with (world-1)/world; a communication worker moves 25-40 GB/s
-            comm_workers = 8 if world <= 2 else 12
+            comm_workers = 12
         self._build(mode, trace, comm_workers if world > 1 else 0)
 
     # ------------------------------------------------------------------ forward (set-up, separate launches)
@@ -93,11 +98,17 @@ class DPMLPStackBackward:
                 e_next = b.gemm(dz_l, self.weights[l], self.dz[(l - 1) & 1], trans_b=True, epilogue="gelu_bwd",
                                 aux=self.z[l - 1], a_ready=e_dz, bn=256, extra_waits=extra)
             ready = [b.new_event() for _ in range(n_blocks)] if world > 1 else None
+            if world > 1:
+                st_off = self.heap.offset_of(self.staging[l])
+                slot_bytes = (H // world) * row_bytes
 
-            def per_tile(mb, nb, ready=ready):
+            def per_tile(mb, nb, ready=ready, l=l):
                 if ready is None:
                     return {}
-                return dict(signal_peer=mb % world, signal_peer_event=ready[mb])
+                # the tile goes into slot `rank` of the block's owner (a peer store from the epilogue, or a local
+                # one when this rank owns the block) at the owner's index of the block
+                return dict(peer=mb % world, out_off=st_off + rank * slot_bytes, row_off=(mb // world - mb) * BM,
+                            signal_peer=mb % world, signal_peer_event=ready[mb])
 
             e_w = b.gemm(dz_l, inp, self.dw[l], trans_a=True, trans_b=True, epilogue="f32", alpha=1.0 / world, bn=256,
                          extra_waits=[(e_dz.all_event[0], e_dz.all_event[1], False, False)], per_tile=per_tile)
@@ -111,9 +122,13 @@ class DPMLPStackBackward:
                     if mb % world != rank:
                         continue
                     for s in range(split):
-                        r0 = mb * BM + s * (BM // split)
-                        raw = _pack_comm(off + r0 * row_bytes, off + r0 * row_bytes, row_bytes, row_bytes, row_bytes,
-                                         BM // split, N.DTYPE_CODE[torch.float32], -1, COMM_ALLREDUCE, scale=1.0)
+                        r_own = (mb // world) * BM + s * (BM // split)       # row inside my slots
+                        r_glob = mb * BM + s * (BM // split)                 # row of the gradient
+                        # sum the `world` local slots (no remote reads: the peers' partials were stored here by
+                        # their epilogues) and send the averaged rows to every rank's gradient buffer
+                        raw = _pack_comm(st_off + r_own * row_bytes, off + r_glob * row_bytes, row_bytes, row_bytes, row_bytes,
+                                         BM // split, N.DTYPE_CODE[torch.float32], -1, COMM_REDUCE_LOCAL_BCAST,
+                                         nslots=world, slot_stride=slot_bytes, scale=1.0)
                         b.add_task(int(TaskType.ALLREDUCE), raw, waits=[(ready[mb], world * n_tiles_w, True, False)],
                                    signal_peer=-2, signal_peer_event=done, comm_worker=True)
                 done_events.append((done, n_done, True, False))

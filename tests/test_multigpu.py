@@ -67,6 +67,54 @@ def _collectives(rank, world):
     z = collectives.all_to_all_4d(y, 1, 2)
     torch.cuda.synchronize()
     assert torch.equal(z, mine)
+    # broadcast from rank 1, repeated (the receive counter only grows)
+    bt = heap.alloc((3 << 18,), torch.float32)
+    for it in range(2):
+        bt.fill_(float(100 * rank + it))
+        collectives.broadcast(bt, src=1)
+        torch.cuda.synchronize()
+        assert torch.all(bt == 100 + it), it
+    # reduce-scatter: block r of the sum ends up on rank r
+    rin = heap.alloc((world * 512, 256), torch.bfloat16)
+    rout = heap.alloc((512, 256), torch.bfloat16)
+    for blk in range(world):
+        rin[blk * 512:(blk + 1) * 512].fill_(float((rank + 1) * (blk + 1)))
+    collectives.reduce_scatter(rin, rout)
+    torch.cuda.synchronize()
+    assert torch.all(rout.float() == (rank + 1) * world * (world + 1) / 2)
+    # all-to-all with equal and with variable splits (all_to_all_single semantics)
+    ain = heap.alloc((world * 64, 128), torch.float32)
+    aout = heap.alloc((world * 64, 128), torch.float32)
+    for d in range(world):
+        ain[d * 64:(d + 1) * 64].fill_(float(10 * rank + d))
+    collectives.all_to_all(ain, aout)
+    torch.cuda.synchronize()
+    for s_ in range(world):
+        assert torch.all(aout[s_ * 64:(s_ + 1) * 64] == 10 * s_ + rank)
+    in_splits = [8 * (1 + (rank + d) % 3) for d in range(world)]            # what I send to d
+    out_splits = [8 * (1 + (s_ + rank) % 3) for s_ in range(world)]         # what s sends to me
+    vin = heap.alloc((24 * world, 64), torch.float32)[: sum(in_splits)]      # same allocation on every rank
+    vout = heap.alloc((24 * world, 64), torch.float32)[: sum(out_splits)]
+    o = 0
+    for d in range(world):
+        vin[o:o + in_splits[d]].fill_(float(10 * rank + d))
+        o += in_splits[d]
+    vout.fill_(-1.0)
+    torch.cuda.synchronize()
+    maco.nvshmem_barrier()            # a peer's rows must not land before this rank has finished clearing vout
+    collectives.all_to_all(vin, vout, in_splits, out_splits)
+    torch.cuda.synchronize()
+    o = 0
+    for s_ in range(world):
+        assert torch.all(vout[o:o + out_splits[s_]] == 10 * s_ + rank)
+        o += out_splits[s_]
+    # point-to-point put + flag around the ring
+    ps = heap.alloc((1 << 16,), torch.float32)
+    pr = heap.alloc((1 << 16,), torch.float32)
+    ps.fill_(float(rank + 7))
+    collectives.send_recv(ps, (rank + 1) % world, pr, (rank - 1) % world)
+    torch.cuda.synchronize()
+    assert torch.all(pr == (rank - 1) % world + 7)
     assert _native.status() == 0
     maco.cleanup()
 
