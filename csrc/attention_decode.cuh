@@ -210,7 +210,8 @@ MACO_DEVICE bool attn_pipelined(const MacoEltArgs& a) { return a.ld_in == kAttnD
 MACO_DEVICE uint32_t attn_stage_uses(const MacoEltArgs& a) { return 2u * (uint32_t)((a.rows + 127) / 128); }
 
 // Producer side: called by one thread. `ait` counts the stage uses of the attention ring on this worker.
-MACO_DEVICE bool attn_produce(const MacoEltArgs& a, const AttnPipe& pp, uint32_t& ait) {
+MACO_DEVICE bool attn_produce(const MacoEltArgs& ar, const AttnPipe& pp, uint32_t& ait) {
+  const MacoEltArgs a = ar;
   const CUtensorMap* tmK = pp.tmaps + ((a.ld_out & 0xffff) - 1);
   const CUtensorMap* tmV = pp.tmaps + (((uint32_t)a.ld_out >> 16) - 1);
   for (int base = 0; base < a.rows; base += 128) {
@@ -521,7 +522,8 @@ MACO_DEVICE void attn_decode_task(const MacoEltArgs& a, int tid, uint8_t* scratc
 
 // Combines the S split records {o[G][128], m[G], l[G]} of one (sequence, kv head): thread `tid` owns output
 // dimension `tid` of every head. The loads of one split are independent of each other (8 heads in flight).
-MACO_DEVICE void attn_merge_task(const MacoEltArgs& a, int tid) {
+MACO_DEVICE void attn_merge_task(const MacoEltArgs& ar, int tid) {
+  const MacoEltArgs a = ar;                              // private copy: stores cannot alias it
   const int G = a.i0 < kAttnMaxG ? a.i0 : kAttnMaxG, S = a.i1;
   const int rec = G * kAttnD + 2 * G;
   const float* part = reinterpret_cast<const float*>(a.in0);

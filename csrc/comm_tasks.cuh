@@ -69,8 +69,9 @@ MACO_DEVICE uint64_t blk_off(uint32_t i, uint32_t vpr, uint64_t stride) {
 
 // out = scale * (sum over n sources (+ aux)); kR vectors per thread per pass, loads of kS sources issued together.
 template <int DTT, int kR, int kS, typename Program>
-__device__ __noinline__ void comm_reduce(const Program& p, const MacoCommArgs& a, int n, uint32_t total, uint32_t vpr, int tid,
+__device__ __noinline__ void comm_reduce(const Program& p, const MacoCommArgs& ar, int n, uint32_t total, uint32_t vpr, int tid,
                              int nthreads) {
+  const MacoCommArgs a = ar;     // private copy: the descriptor lives in global memory and the loop stores could alias it
   uint8_t* mine = p.peer_heap[p.rank];
   const bool local = a.op == MACO_COMM_REDUCE_LOCAL || a.op == MACO_COMM_REDUCE_LOCAL_BCAST;
   uint8_t* out = a.local_ptr != nullptr ? reinterpret_cast<uint8_t*>(a.local_ptr) : mine + a.dst_off;
@@ -142,11 +143,63 @@ struct BulkCtx {
 // (load rounds into shared memory, then one bulk store per destination), which is what it takes
 // to fill an NVLink from a single SM; 128 threads with 16-byte accesses are latency-bound far below.
 template <typename Program>
-MACO_DEVICE bool comm_push_bulk(const Program& p, const MacoCommArgs& a, BulkCtx& bc, uint64_t budget_ns) {
+MACO_DEVICE bool comm_push_bulk(const Program& p, const MacoCommArgs& ar, BulkCtx& bc, uint64_t budget_ns) {
+  const MacoCommArgs a = ar;     // private copy (the descriptor is in global memory)
   const uint64_t bytes = (uint64_t)a.rows * a.row_bytes;
   const uint8_t* src = p.peer_heap[p.rank] + a.src_off;
   fence_proxy_async_all();
   bool ok = true;
+  // Ring over the staging buffers: the load of chunk i is issued kLead chunks before its store, and a buffer
+  // is reloaded once the store that used it last has read it out (stores are committed one group per
+  // chunk, so "at most nbuf - kLead - 1 newer groups still reading" is exactly that condition).
+  constexpr uint32_t kRing = 12, kLead = 8;
+  const uint32_t n_chunks = (uint32_t)((bytes + bc.buf_bytes - 1) / bc.buf_bytes);
+  if (bc.nbuf == kRing) {
+    for (uint32_t i = 0; i < n_chunks + kLead && ok; ++i) {
+      if (i < n_chunks) {
+        const uint32_t b = i % kRing;
+        if (i >= kRing) tma_store_wait_read<kRing - kLead - 1>();
+        const uint64_t off = (uint64_t)i * bc.buf_bytes;
+        const uint32_t n = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
+        mbar_arrive_expect_tx(&bc.bars[b], n);
+        bulk_load(bc.buf + (size_t)b * bc.buf_bytes, src + off, n, &bc.bars[b]);
+      }
+      if (i >= kLead) {
+        const uint32_t c = i - kLead, b = c % kRing;
+        const uint64_t off = (uint64_t)c * bc.buf_bytes;
+        const uint32_t n = (uint32_t)(bytes - off < bc.buf_bytes ? bytes - off : bc.buf_bytes);
+        const uint32_t parity = (*bc.phase >> b) & 1u;
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(&bc.bars[b], parity)) {
+          if (globaltimer_ns() - t0 > budget_ns) { ok = false; break; }
+        }
+        *bc.phase = *bc.phase ^ (1u << b);
+        if (!ok) break;
+        const uint8_t* sm = bc.buf + (size_t)b * bc.buf_bytes;
+        if (a.peer >= 0) {
+          bulk_store(p.peer_heap[a.peer] + a.dst_off + off, sm, n);
+        } else {
+          for (int k = 0; k < p.world; ++k) {
+            const int dr = (p.rank + 1 + k) % p.world;
+            if (dr == p.rank && a.peer != -3) continue;
+            bulk_store(p.peer_heap[dr] + a.dst_off + off, sm, n);
+          }
+        }
+        tma_store_commit();
+      }
+    }
+    if (!ok) {
+      // loads that were issued and never waited for get a bounded time to land (their destination is this CTA's memory)
+      for (uint32_t b = 0; b < kRing; ++b) {
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(&bc.bars[b], (*bc.phase >> b) & 1u)) {
+          if (globaltimer_ns() - t0 > 2000000ull) break;
+        }
+      }
+    }
+    tma_store_wait<0>();               // every store has completed before the task signals
+    return ok;
+  }
   for (uint64_t pos = 0; pos < bytes && ok; pos += (uint64_t)bc.nbuf * bc.buf_bytes) {
     uint32_t used = 0;
     for (uint32_t b = 0; b < bc.nbuf; ++b) {
@@ -191,8 +244,12 @@ MACO_DEVICE bool comm_push_bulk(const Program& p, const MacoCommArgs& a, BulkCtx
 // or, for an all-reduce, back into shared memory from where one bulk store per rank sends it).
 // `bar_sync` is the barrier of the calling thread group.
 template <int DTT, typename Program, typename BarFn>
-__device__ __noinline__ bool comm_reduce_bulk(const Program& p, const MacoCommArgs& a, int n, int tid, int nthreads, BulkCtx& bc,
+__device__ __noinline__ bool comm_reduce_bulk(const Program& p, const MacoCommArgs& ar, int n, int tid, int nthreads, BulkCtx& bcr,
                                   BarFn bar_sync) {
+  // private copies: the descriptor lives in global memory; read in place, every use inside the summing loop
+  // would be a fresh load (the loop's stores could alias it), about 500 cycles per vector
+  const MacoCommArgs a = ar;
+  const BulkCtx bc = bcr;
   uint8_t* mine = p.peer_heap[p.rank];
   const bool local = a.op == MACO_COMM_REDUCE_LOCAL || a.op == MACO_COMM_REDUCE_LOCAL_BCAST;
   const bool bcast = a.op == MACO_COMM_ALLREDUCE || a.op == MACO_COMM_REDUCE_LOCAL_BCAST;
@@ -204,6 +261,9 @@ __device__ __noinline__ bool comm_reduce_bulk(const Program& p, const MacoCommAr
   // peer (several microseconds) is covered by `groups - 1` stages of work.
   const uint64_t round_bytes = (uint64_t)groups * bc.buf_bytes;
   bool ok = true;
+  bool have_prev = false;                                    // leader only: a position whose refill is still owed
+  uint32_t prev_g = 0;
+  uint64_t prev_pos = 0;
   // leader: loads of position g for the round that starts at byte `pos`
   auto issue = [&](uint32_t g, uint64_t pos) {
     const uint64_t off = pos + (uint64_t)g * bc.buf_bytes;
@@ -247,13 +307,25 @@ __device__ __noinline__ bool comm_reduce_bulk(const Program& p, const MacoCommAr
     if (tid == 0) {
       // only this position's bits change; the bits of other positions, which threads may be reading, keep their value
       *bc.phase = *bc.phase ^ used_mask;
-      if (bcast) {
+      if (bcast && groups >= 2) {
         for (int j = 0; j < p.world; ++j)
           bulk_store(p.peer_heap[(p.rank + j) % p.world] + a.dst_off + off, g0, nb);
         tma_store_commit();
-        tma_store_wait_read<0>();                            // the staged result has left shared memory
+        // The stores just issued may still be reading shared memory (a store into a peer is paced by the link):
+        // do not wait for them. Wait for the PREVIOUS position's stores instead, which had a whole stage to
+        // finish, and refill that position; this one is refilled one stage later.
+        tma_store_wait_read<1>();
+        if (have_prev) issue(prev_g, prev_pos + round_bytes);
+        have_prev = true; prev_g = g; prev_pos = pos;
+      } else {
+        if (bcast) {
+          for (int j = 0; j < p.world; ++j)
+            bulk_store(p.peer_heap[(p.rank + j) % p.world] + a.dst_off + off, g0, nb);
+          tma_store_commit();
+          tma_store_wait_read<0>();                          // the staged result has left shared memory
+        }
+        issue(g, pos + round_bytes);
       }
-      issue(g, pos + round_bytes);
     }
     if (groups == 1) bar_sync();                             // a single position: its phase bits are read again right away
   };

@@ -398,7 +398,8 @@ MACO_DEVICE void elt_rowwise(uint32_t type, const MacoEltArgs& a, int tid, int n
 // ld_in / ld_out are the TOKEN strides (heads * head_dim when packed), heads are `cols` apart.
 // in1 = cos [tokens, head_dim/2], in2 = sin (same dtype as x); i1 = token index of row 0's token
 // in the cos/sin tables minus row0 / heads (0 when the tables start at the first row's token).
-MACO_DEVICE void elt_rope(const MacoEltArgs& a, int tid, int nthreads) {
+MACO_DEVICE void elt_rope(const MacoEltArgs& ar, int tid, int nthreads) {
+  const MacoEltArgs a = ar;                              // private copy: stores cannot alias it
   const int half = a.cols / 2;
   const uint32_t total = (uint32_t)a.rows * (uint32_t)half;
   for (uint32_t i = tid; i < total; i += nthreads) {
@@ -418,7 +419,8 @@ MACO_DEVICE void elt_rope(const MacoEltArgs& a, int tid, int nthreads) {
 // in0 = x rows [rows, head_dim], in1 = norm weight [head_dim], in2 = cos|sin packed as
 // [tokens, head_dim] (first half cos, second half sin), f0 = eps, f1 = 1 selects this fused form,
 // i0 = heads, i1 = token offset into the cos/sin table.
-MACO_DEVICE void elt_qknorm_rope(const MacoEltArgs& a, int tid, int nthreads) {
+MACO_DEVICE void elt_qknorm_rope(const MacoEltArgs& ar, int tid, int nthreads) {
+  const MacoEltArgs a = ar;                              // private copy: stores cannot alias it
   const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
   const int half = a.cols / 2;
   if (a.cols == 128 && a.dtype != MACO_DT_F32) {

@@ -290,10 +290,13 @@ struct EpiBroadcast {
 };
 
 template <int BN, int SBN = BN>
-MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const GemmEpilogue& e,
+MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const GemmEpilogue& e_in,
                                     void* out_base, long long row_off, int m0, int n0,
                                     uint32_t tile_seq, uint64_t budget_ns, const EpiBroadcast* bc = nullptr,
                                     uint8_t* stage = nullptr) {
+  // private copy: the record lives in global memory; read in place, its fields would be loaded again after
+  // every store of the tile (the stores could alias it)
+  const GemmEpilogue e = e_in;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t q = warp & 3;     // TMEM lane quarter this warp may read
   const uint32_t acc = tile_seq & 1, acc_ph = (tile_seq >> 1) & 1;

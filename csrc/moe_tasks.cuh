@@ -32,8 +32,11 @@ __device__ __forceinline__ void moe_bar() { asm volatile("bar.sync 1, 128;" ::: 
 // slot for choice k and sends copy k, so the K slot atomics and the K bulk copies of a token are one
 // round trip each instead of K.
 template <typename Program>
-MACO_DEVICE void moe_topk_dispatch(const Program& p, const MacoEltArgs& a, int tid, uint8_t* stage) {
-  const MacoMoeParams& m = *reinterpret_cast<const MacoMoeParams*>(a.in2);
+MACO_DEVICE void moe_topk_dispatch(const Program& p, const MacoEltArgs& ar, int tid, uint8_t* stage) {
+  // private copies: descriptor and parameter block live in global memory; read in place every use inside the
+  // loops would be a fresh load, because the loops' stores could alias them
+  const MacoEltArgs a = ar;
+  const MacoMoeParams m = *reinterpret_cast<const MacoMoeParams*>(a.in2);
   const int warp = tid >> 5, lane = tid & 31;
   const int E = m.experts, K = m.top_k, H = m.hidden;
   const int row_bytes = H * 2;
@@ -124,7 +127,7 @@ MACO_DEVICE void moe_topk_dispatch(const Program& p, const MacoEltArgs& a, int t
 // counts[e] of this rank -> cnt[world][experts_per_rank] on the owner of e (slot = this rank).
 template <typename Program>
 MACO_DEVICE void moe_publish_counts(const Program& p, const MacoEltArgs& a, int tid) {
-  const MacoMoeParams& m = *reinterpret_cast<const MacoMoeParams*>(a.in2);
+  const MacoMoeParams m = *reinterpret_cast<const MacoMoeParams*>(a.in2);
   for (int e = tid; e < m.experts; e += 128) {
     const int dst = e / m.experts_per_rank, el = e % m.experts_per_rank;
     uint32_t c = m.counts[e];
@@ -137,8 +140,9 @@ MACO_DEVICE void moe_publish_counts(const Program& p, const MacoEltArgs& a, int 
 // One warp per row; the next row and its record are fetched into registers before the warp waits for
 // the bulk engine to have read the current row out of shared memory.
 template <typename Program>
-MACO_DEVICE void moe_return(const Program& p, const MacoEltArgs& a, int tid, uint8_t* stage) {
-  const MacoMoeParams& m = *reinterpret_cast<const MacoMoeParams*>(a.in2);
+MACO_DEVICE void moe_return(const Program& p, const MacoEltArgs& ar, int tid, uint8_t* stage) {
+  const MacoEltArgs a = ar;
+  const MacoMoeParams m = *reinterpret_cast<const MacoMoeParams*>(a.in2);
   const int warp = tid >> 5, lane = tid & 31;
   const int el = a.i0, src = a.i1, H = m.hidden, K = m.top_k;
   const int row_bytes = H * 2;
@@ -198,7 +202,7 @@ MACO_DEVICE void moe_return(const Program& p, const MacoEltArgs& a, int tid, uin
 template <typename Program>
 __device__ __noinline__ bool moe_combine(const Program& p, const MacoEltArgs& ar, int tid, BulkCtx* bc) {
   const MacoEltArgs a = ar;
-  const MacoMoeParams& m = *reinterpret_cast<const MacoMoeParams*>(a.in2);
+  const MacoMoeParams m = *reinterpret_cast<const MacoMoeParams*>(a.in2);
   const int K = m.top_k, dt = m.dtype;
   const uint32_t row_bytes = (uint32_t)m.hidden * 2, tb = row_bytes * (uint32_t)K, nvec = row_bytes >> 4;
   const uint8_t* comb = p.peer_heap[p.rank] + m.comb_off;

@@ -49,7 +49,7 @@ class TPSwiGLUMLP:
         if comm_workers is None:
             # one SM pushes roughly 25-30 GB/s into a peer; the shard has to reach world-1 peers before
             # they run out of local rows to work on
-            comm_workers = 8 if world <= 2 else 16
+            comm_workers = 6 if world <= 2 else 16
         b = ProgramBuilder(dev, num_workers=num_workers, mode=mode, heap=heap, trace=trace,
                            num_comm_workers=(comm_workers if world > 1 else 0))
         self.h = torch.empty(tokens, f_local, device=dev, dtype=dtype)

@@ -1,0 +1,60 @@
+"""Double-buffered host -> device input feed.
+
+``submit(host_tensor)`` starts the copy of the NEXT step's input from pinned host memory on a copy
+stream; ``deliver(dst)`` makes the current stream wait for the oldest submitted copy and moves it
+into the layer's input buffer with a device-to-device copy (tens of microseconds for tens of MB). A
+step that submits the next input right after launching its kernel hides the PCIe transfer behind
+the compute, so the end-to-end step time approaches the device time.
+
+The reference offers the building blocks for this (a communication stream and events:
+maco/sync/stream_manager.py:41-110) and leaves the pattern to the user.
+"""
+from __future__ import annotations
+
+from collections import deque
+from typing import Deque, Optional, Tuple
+
+import torch
+
+
+class InputPrefetcher:
+    def __init__(self, like: torch.Tensor, depth: int = 2, stream: Optional[torch.cuda.Stream] = None):
+        if not like.is_cuda:
+            raise ValueError("InputPrefetcher stages into CUDA memory")
+        self.stream = stream if stream is not None else torch.cuda.Stream(device=like.device)
+        self._bufs = [torch.empty_like(like) for _ in range(depth)]
+        self._free = [torch.cuda.Event() for _ in range(depth)]
+        self._ready = [torch.cuda.Event() for _ in range(depth)]
+        self._used = [False] * depth
+        self._next = 0
+        self._queue: Deque[int] = deque()
+
+    @property
+    def pending(self) -> int:
+        return len(self._queue)
+
+    def submit(self, host: torch.Tensor) -> None:
+        """Starts copying ``host`` (pinned) into the next staging buffer on the copy stream."""
+        if len(self._queue) == len(self._bufs):
+            raise RuntimeError("every staging buffer holds an undelivered input")
+        i = self._next
+        self._next = (i + 1) % len(self._bufs)
+        with torch.cuda.stream(self.stream):
+            if self._used[i]:
+                self.stream.wait_event(self._free[i])       # the previous consumer has read this buffer
+            self._bufs[i].copy_(host, non_blocking=True)
+            self._ready[i].record(self.stream)
+        self._queue.append(i)
+
+    def deliver(self, dst: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        """Orders ``stream`` (default: current) behind the oldest submitted copy and moves it into ``dst``."""
+        if not self._queue:
+            raise RuntimeError("deliver() without a submitted input")
+        i = self._queue.popleft()
+        cur = stream if stream is not None else torch.cuda.current_stream(dst.device)
+        cur.wait_event(self._ready[i])
+        with torch.cuda.stream(cur):
+            dst.copy_(self._bufs[i], non_blocking=True)
+            self._free[i].record(cur)
+        self._used[i] = True
+        return dst
