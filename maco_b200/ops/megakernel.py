@@ -115,6 +115,34 @@ def make_idesc(ab_format: int, m: int, n: int, a_mn: int, b_mn: int) -> int:
 Wait = Tuple[int, int, int]   # (event, count, flags among SYS/PREV expressed for slot 0)
 
 
+def pick_split_k(n_tiles: int, k_blocks: int, workers: int) -> int:
+    """K slices of a few-row GEMM: minimises waves of tiles over the workers x (k-blocks per tile + a fixed
+    cost per tile for pipeline fill and the reductions)."""
+    def cost(sp: int) -> int:
+        return -(-n_tiles * sp // workers) * (-(-k_blocks // sp) + 8)
+    return min(range(1, max(1, min(16, k_blocks // 2)) + 1), key=cost)
+
+
+def attention_pieces(groups: int, kv_len: int, workers: int) -> List[Tuple[int, int, int, int]]:
+    """Cuts ``groups`` key ranges of ``kv_len`` keys into one (nearly) equal share per worker.
+    Returns (group, first key, keys, worker); cuts inside a group sit on 128-key boundaries."""
+    target = -(-(groups * kv_len) // workers)
+    target = -(-target // 128) * 128
+    pieces, wk, acc = [], 0, 0
+    for g in range(groups):
+        s0 = 0
+        while s0 < kv_len:
+            room = target - acc                     # > 0 here
+            take = min(kv_len - s0, -(-room // 128) * 128)
+            pieces.append((g, s0, take, min(wk, workers - 1)))
+            s0 += take
+            acc += take
+            if acc >= target:
+                wk, acc = wk + 1, 0
+    return pieces
+
+
+
 @dataclass
 class RowEvents:
     """Completion events of a produced 2-D tensor: one per ``block`` rows plus one for the whole tensor."""
@@ -349,10 +377,7 @@ class ProgramBuilder:
         mode = {None: 0, "none": 0, "swiglu": 1, "residual": 2}[epilogue]
         n_tiles, k_blocks = Nn // 256, K // BK
         if split_k <= 0:
-            # waves of tiles over the workers x (k-blocks per tile + a fixed cost per tile: pipeline fill, reductions)
-            def cost(sp: int) -> int:
-                return -(-n_tiles * sp // self.num_workers) * (-(-k_blocks // sp) + 8)
-            split_k = min(range(1, max(1, min(16, k_blocks // 2)) + 1), key=cost)
+            split_k = pick_split_k(n_tiles, k_blocks, self.num_workers)
         split_k = max(1, min(split_k, k_blocks))
         ws = torch.zeros(M, Nn, device=a.device, dtype=torch.float32)      # SPLITK_FIN leaves it zeroed again
         out_dtype = out.dtype if out is not None else a.dtype
@@ -459,20 +484,7 @@ class ProgramBuilder:
             # into one equal share per worker at 128-key boundaries, so no worker runs an extra wave.
             pieces = []                                     # (bh, first key, keys, worker or None)
             if balance:
-                W = self.num_workers
-                target = -(-(B * hkv * kv_len) // W)
-                target = -(-target // 128) * 128
-                wk, acc = 0, 0
-                for bh in range(B * hkv):
-                    s0 = 0
-                    while s0 < kv_len:
-                        room = target - acc                 # > 0 here; cuts inside a group sit on 128-key boundaries
-                        take = min(kv_len - s0, -(-room // 128) * 128)
-                        pieces.append((bh, s0, take, min(wk, W - 1)))
-                        s0 += take
-                        acc += take
-                        if acc >= target:
-                            wk, acc = wk + 1, 0
+                pieces = attention_pieces(B * hkv, kv_len, self.num_workers)
             else:
                 for bh in range(B * hkv):
                     for sp in range(splits):
@@ -855,8 +867,15 @@ def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None)
             aligned, extra = ready_of(node, node.inputs[0], x2.shape[0])
             act = node.attrs.get("activation")
             bias = node.inputs[2] if node.attrs.get("has_bias") else None
-            ev = b.gemm(x2, w, out.view(-1, out.shape[-1]), trans_b=(t == TaskType.MATMUL), epilogue=act, bias=bias,
-                        a_ready=aligned, extra_waits=extra)
+            out2 = out.view(-1, out.shape[-1])
+            few_rows = (t == TaskType.LINEAR and bias is None and act in (None, "none", "swiglu") and x2.shape[0] <= BM
+                        and w.shape[0] % 256 == 0 and x2.shape[1] % BK == 0 and w.shape[0] * w.shape[1] >= (1 << 22))
+            if few_rows:
+                # decode-shaped linear: a weight stream, cut along K over every SM (csrc/splitk_tasks.cuh)
+                ev = b.gemm_splitk(x2, w, out2, epilogue=act if act == "swiglu" else None, a_ready=aligned, extra_waits=extra)
+            else:
+                ev = b.gemm(x2, w, out2, trans_b=(t == TaskType.MATMUL), epilogue=act, bias=bias,
+                            a_ready=aligned, extra_waits=extra)
             produced[node._node_id] = (node, ev)
         elif t in _ELT_TYPES:
             x = node.inputs[0]

@@ -121,3 +121,26 @@ def test_sync_primitives_on_gpu():
     res, comm = maco.overlap_compute_and_comm(lambda: a @ a, c, "allreduce")
     torch.cuda.synchronize()
     assert res.shape == (512, 512) and comm is c
+
+
+def test_decode_shaped_linear_takes_the_split_k_path():
+    """A few-row linear with a large weight is lowered to split-K tiles plus finishing tasks; chained with a
+    row-wise op and a second linear, executed twice (the partial-sum workspace must come back clean)."""
+    g = maco.TaskGraph()
+    dt = torch.bfloat16
+    x = torch.randn(16, 2048, device="cuda", dtype=dt)
+    nw = torch.randn(2048, device="cuda", dtype=dt)
+    w1 = (torch.randn(2048, 2048, device="cuda") * 0.03).to(dt)
+    w2 = (torch.randn(2304, 2048, device="cuda") * 0.03).to(dt)
+    h = g.rmsnorm(x, nw, eps=1e-6)
+    t1 = g.linear(h.output, w1)
+    t2 = g.linear(t1.output, w2)
+    g.compile(runtime="persistent")
+    assert g.runtime_kind == "persistent"
+    for _ in range(2):
+        g.execute()
+    torch.cuda.synchronize()
+    xf = x.float()
+    hf = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()).to(dt).float()
+    ref = (hf @ w1.float().t()).to(dt).float() @ w2.float().t()
+    assert_close(t2.output, ref, dt)
