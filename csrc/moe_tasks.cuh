@@ -40,10 +40,10 @@ MACO_DEVICE void moe_topk_dispatch(const Program& p, const MacoEltArgs& ar, int 
   const int warp = tid >> 5, lane = tid & 31;
   const int E = m.experts, K = m.top_k, H = m.hidden;
   const int row_bytes = H * 2;
-  const int nvec = row_bytes >> 4;                    // 16-byte vectors per row (<= 160: 5 per lane)
+  const int nvec = row_bytes >> 4;                    // 16-byte vectors per row (<= 320: 10 per lane)
   uint8_t* srow = stage + (size_t)warp * row_bytes;
   const int per_lane = (E + 31) / 32;                 // logits held by each lane (<= 8: up to 256 experts)
-  constexpr int kVecPerLane = 5;
+  constexpr int kVecPerLane = 10;                      // 16-byte vectors of a row per lane: hidden <= 2560
   float v[8];
   uint4 xr[kVecPerLane];
   auto fetch = [&](int t) {
@@ -147,7 +147,7 @@ MACO_DEVICE void moe_return(const Program& p, const MacoEltArgs& ar, int tid, ui
   const int el = a.i0, src = a.i1, H = m.hidden, K = m.top_k;
   const int row_bytes = H * 2;
   const int nvec = row_bytes >> 4;
-  constexpr int kVecPerLane = 5;
+  constexpr int kVecPerLane = 10;                      // 16-byte vectors of a row per lane: hidden <= 2560
   const uint32_t count = reinterpret_cast<const uint32_t*>(p.peer_heap[p.rank] + m.cnt_off)[src * m.experts_per_rank + el];
   uint8_t* srow = stage + (size_t)warp * row_bytes;
   const size_t slab = ((size_t)el * p.world + src) * m.capacity;

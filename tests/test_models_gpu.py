@@ -46,6 +46,24 @@ def test_qwen3_decode_layer_single_gpu(mode):
     assert _native.status() == 0
 
 
+def test_moe_layer_full_row_width():
+    """hidden 2048: a token row is 256 16-byte vectors, more than one pass of a warp; every vector of the
+    dispatched and of the returned rows has to arrive (checked against the fp32 reference, two launches)."""
+    from maco_b200 import _native
+    from maco_b200.models.moe_layer import MoEEPLayer
+    layer = MoEEPLayer(hidden=2048, experts=16, top_k=4, inter=256, tokens=512, capacity_factor=4.0, seed=5,
+                       weight_std=0.03, router_std=0.3)
+    x = torch.randn(512, 2048, device="cuda", dtype=torch.bfloat16)
+    ref = layer.reference(x)
+    for _ in range(2):
+        out = layer(x)
+        torch.cuda.synchronize()
+        assert layer.dropped() == 0
+        err = (out.float() - ref).abs().max().item()
+        assert err < 4e-2 * max(1.0, ref.abs().max().item()), err
+    assert _native.status() == 0
+
+
 @pytest.mark.parametrize("mode", ["static", "dynamic"])
 def test_moe_layer_single_gpu(mode):
     from maco_b200 import _native
