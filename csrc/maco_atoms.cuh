@@ -62,6 +62,9 @@ MACO_DEVICE uint32_t atom_add_relaxed_gpu_u32(uint32_t* p, uint32_t v) {
 MACO_DEVICE void red_add_release_gpu_u32(uint32_t* p, uint32_t v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
 }
+MACO_DEVICE void red_add_relaxed_gpu_u32(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
 
 // .sys scope: flags that another GPU (over NVLink) or the host reads or writes.
 MACO_DEVICE uint64_t ld_acquire_sys_u64(const uint64_t* p) {

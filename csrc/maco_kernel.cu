@@ -130,18 +130,21 @@ __device__ bool wait_deps(const MacoProgram& p, const MacoTaskDesc& d, uint32_t 
 }
 
 __device__ void signal_done(const MacoProgram& p, const MacoTaskDesc& d) {
-  const bool sys = (d.flags & MACO_TF_SIGNAL_SYS) != 0;
+  // One release fence for the whole task, then relaxed counter bumps: a release per destination would
+  // repeat the fence (a round trip over NVLink once a peer is involved) for every rank that is signalled.
+  const bool sys = (d.flags & MACO_TF_SIGNAL_SYS) != 0 || d.signal_peer_event >= 0;
+  if (sys) fence_acq_rel_sys(); else fence_acq_rel_gpu();
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int e = d.signal_event[j];
     if (e < 0) continue;
-    if (sys) red_add_release_sys_u32(&p.events[e], 1); else red_add_release_gpu_u32(&p.events[e], 1);
+    if (sys) red_add_relaxed_sys_u32(&p.events[e], 1); else red_add_relaxed_gpu_u32(&p.events[e], 1);
   }
   if (d.signal_peer_event >= 0) {
     if (d.signal_peer >= 0) {
-      red_add_release_sys_u32(&p.peer_events[d.signal_peer][d.signal_peer_event], 1);
+      red_add_relaxed_sys_u32(&p.peer_events[d.signal_peer][d.signal_peer_event], 1);
     } else if (d.signal_peer == -2) {
-      for (int r = 0; r < p.world; ++r) red_add_release_sys_u32(&p.peer_events[r][d.signal_peer_event], 1);
+      for (int r = 0; r < p.world; ++r) red_add_relaxed_sys_u32(&p.peer_events[r][d.signal_peer_event], 1);
     }
   }
 }
