@@ -8,8 +8,9 @@ The whole layer is ONE launch of the persistent kernel per rank. The all-gather 
 128-row chunks by a few communication workers and each gate/up tile waits only for the 128 rows it reads; SwiGLU is applied in the
 GEMM epilogue (gate and up weights are interleaved per 256-column tile); the down-projection
 epilogue stores every partial tile into the staging slot of the rank that owns those rows, and
-that rank sums the slots as their per-block counters fill. With one rank the collectives
-vanish and the same two fused GEMMs run.
+that rank sums the slots as their per-block counters fill (with two ranks the own tiles add the
+peer's slot in their epilogue and write final rows). With one rank the collectives vanish and the
+same two fused GEMMs run.
 
 The reference expresses this layer as separate torch.mm launches plus NCCL calls
 (maco/task_graph/runtime.py:188-234, maco/comm/patterns.py:80-175) and its own tensor-parallel

@@ -38,12 +38,16 @@ def all_reduce(t: torch.Tensor, avg: bool = False) -> torch.Tensor:
     key = ("ar", heap.offset_of(t), t.numel(), t.dtype, avg)
     prog = _cache.get(key)
     if prog is None:
-        b = _builder(heap, workers=max(1, min(32, (t.numel() * t.element_size()) >> 18)))
+        nbytes = t.numel() * t.element_size()
+        chunk = 256 << 10
+        n_chunks = -(-nbytes // chunk)
+        per_owner = -(-n_chunks // heap.world)
+        # staging of its own per program: two programs sharing it could overlap across ranks (each program's
+        # fence only orders its own launches)
+        staging = _scratch[("ar_stage",) + key] = heap.alloc((heap.world * per_owner * chunk,), torch.uint8)
+        b = _builder(heap, workers=max(1, min(32, nbytes >> 18)))
         fence = fused.epoch_fence_event(b)
-        ready = b.new_event()
-        b.add_task(int(TaskType.NOP), b"", waits=[fence], signal_peer=-2, signal_peer_event=ready)
-        flat = t.view(-1)
-        done, n = fused.allreduce_tasks(b, flat, avg=avg, chunk_bytes=256 << 10, ready_event=ready, comm_worker=False)
+        done, n = fused.allreduce_push_tasks(b, t.view(-1), staging, avg=avg, chunk_bytes=chunk, fence=fence)
         fused.epoch_fence_signal(b, [(done, n, True, False)])
         prog = _cache[key] = b.build()
     prog.run()

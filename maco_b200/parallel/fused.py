@@ -8,7 +8,10 @@ tensor-core tiles inside ONE kernel, tile by tile:
                             starts as soon as the rows it reads have landed (all-gather -> GEMM).
 * ``gemm_reduce_scatter``   the GEMM epilogue stores each partial tile straight into the staging slot
                             of the rank that owns those rows and bumps that rank's per-block counter;
-                            the owner sums the slots when the counter is full (GEMM -> reduce-scatter).
+                            the owner sums the slots when the counter is full, or, with two ranks,
+                            adds the peer's slot in the epilogue of its own tiles (GEMM -> reduce-scatter).
+* ``gemm_allreduce``        few-row GEMM as split-K tiles whose finishing tasks store the partial rows
+                            into every rank's slot; each rank sums its slots plus the residual.
 * ``allreduce_tasks``       two-shot all-reduce in chunks: the chunk's owner pulls it from every rank,
                             reduces in fp32 and writes the result back to every rank.
 * ``epoch_fence``           end-of-launch signal that keeps a faster rank's next launch from
@@ -24,7 +27,8 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 
 from .. import _native as N
-from ..ops.megakernel import (BM, COMM_ALLREDUCE, COMM_PUSH, COMM_REDUCE_LOCAL, ProgramBuilder, RowEvents, _pack_comm)
+from ..ops.megakernel import (BM, COMM_ALLREDUCE, COMM_PUSH, COMM_REDUCE_LOCAL, COMM_REDUCE_LOCAL_BCAST, ProgramBuilder,
+                              RowEvents, _pack_comm)
 from ..task_graph.nodes import TaskType
 
 
@@ -209,6 +213,46 @@ def allreduce_tasks(b: ProgramBuilder, buf: torch.Tensor, *, avg: bool = False, 
         b.add_task(int(TaskType.ALLREDUCE), raw, waits=[(ready_event, world, True, False)], signal_peer=-2,
                    signal_peer_event=done, comm_worker=comm_worker)
     b.keepalive.append(buf)
+    return done, n_chunks
+
+
+def allreduce_push_tasks(b: ProgramBuilder, buf: torch.Tensor, staging: torch.Tensor, *, avg: bool = False,
+                         chunk_bytes: int = 256 << 10,
+                         fence: Optional[Tuple[int, int, bool, bool]] = None) -> Tuple[int, int]:
+    """In-place all-reduce of heap tensor ``buf`` without remote reads (one SM reads a peer's memory
+    several times slower than it writes it). Chunk c belongs to rank c % world: every rank stores its
+    copy of the chunk into slot ``rank`` of the owner's ``staging`` ([world, ceil(chunks / world) *
+    chunk_bytes] bytes, in the heap), the owner sums the ``world`` local slots in fp32 and stores the
+    result into ``buf`` on every rank. Returns (completion event, count) local to every rank."""
+    heap = b.heap
+    rank, world = heap.rank, heap.world
+    nbytes = buf.numel() * buf.element_size()
+    if nbytes % 16:
+        raise ValueError("all-reduce buffers must be a multiple of 16 bytes")
+    off, st_off = heap.offset_of(buf), heap.offset_of(staging)
+    row = 16384 if chunk_bytes % 16384 == 0 and nbytes % 16384 == 0 else 16
+    chunk_bytes = max(row, chunk_bytes // row * row)
+    n_chunks = (nbytes + chunk_bytes - 1) // chunk_bytes
+    per_owner = (n_chunks + world - 1) // world
+    slot_bytes = per_owner * chunk_bytes
+    if staging.numel() * staging.element_size() < world * slot_bytes:
+        raise ValueError("all-reduce staging buffer too small")
+    done = b.new_event()
+    dt = N.DTYPE_CODE[buf.dtype]
+    for c in range(n_chunks):
+        owner, j = c % world, c // world
+        c0 = c * chunk_bytes
+        cb = min(chunk_bytes, nbytes - c0)
+        arrived = b.new_event()
+        raw = _pack_comm(off + c0, st_off + rank * slot_bytes + j * chunk_bytes, row, row, row, cb // row, dt, owner, COMM_PUSH)
+        b.add_task(int(TaskType.ALLREDUCE), raw, waits=[fence] if fence is not None else [], signal_peer=owner,
+                   signal_peer_event=arrived)
+        if owner == rank:
+            raw = _pack_comm(st_off + j * chunk_bytes, off + c0, row, row, row, cb // row, dt, -1, COMM_REDUCE_LOCAL_BCAST,
+                             nslots=world, slot_stride=slot_bytes, scale=(1.0 / world if avg else 1.0))
+            b.add_task(int(TaskType.ALLREDUCE), raw, waits=[(arrived, world, True, False)], signal_peer=-2,
+                       signal_peer_event=done)
+    b.keepalive += [buf, staging]
     return done, n_chunks
 
 
