@@ -141,14 +141,23 @@ class MoEEPLayer:
             guards[el, s] = (lambda mb, nb, cptr=cptr: dict(count_ptr=cptr, count_base=mb * BM))
             acts[el, s] = b.gemm(self.recv[el, s], self.w1[el], self.act[el, s], epilogue="swiglu", bn=256,
                                  extra_waits=[arrived], per_tile=guards[el, s])
-        for el, s in pairs:
-            ys[el, s] = b.gemm(self.act[el, s], self.w2[el], self.y[el, s], bn=256, a_ready=acts[el, s],
-                               per_tile=guards[el, s])
-        for el, s in pairs:
+        def emit_return(el: int, s: int) -> None:
             for rb in range(C // BM):
                 ev, cnt = ys[el, s].for_rows(rb * BM, (rb + 1) * BM)
                 b.add_task(T_MOE_RETURN, _pack_elt(0, 0, pp, 0, rb * BM, BM, H, dt, 0, 0, i0=el, i1=s),
                            waits=[(ev, cnt, False, False)], signal_peer=s, signal_peer_event=e_ret)
+
+        # The return of a slab is queued `lag` slabs behind its down-projection tiles: far enough that its
+        # rows are final when a worker reaches it, early enough that the general warps (mostly idle while the
+        # expert tiles wait for weights) send rows back over NVLink under the remaining GEMM work.
+        lag = min(16, max(1, len(pairs) // 4))
+        for i, (el, s) in enumerate(pairs):
+            ys[el, s] = b.gemm(self.act[el, s], self.w2[el], self.y[el, s], bn=256, a_ready=acts[el, s],
+                               per_tile=guards[el, s])
+            if i >= lag:
+                emit_return(*pairs[i - lag])
+        for el, s in pairs[max(0, len(pairs) - lag):]:
+            emit_return(el, s)
         n_ret = W * EL * (C // BM)
         # 6. combine: sum the k rows of every token (token blocks streamed through the idle operand ring)
         e_out = b.new_event()
