@@ -18,6 +18,7 @@ example all-reduces a column-parallel output (examples/tensor_parallel.py:55-61)
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -51,6 +52,7 @@ class TPSwiGLUMLP:
             # one SM pushes roughly 25-30 GB/s into a peer; the shard has to reach world-1 peers before
             # they run out of local rows to work on
             comm_workers = 6 if world <= 2 else 16
+            comm_workers = int(os.environ.get("MACO_TP_COMM_WORKERS", comm_workers))
         b = ProgramBuilder(dev, num_workers=num_workers, mode=mode, heap=heap, trace=trace,
                            num_comm_workers=(comm_workers if world > 1 else 0))
         self.h = torch.empty(tokens, f_local, device=dev, dtype=dtype)
