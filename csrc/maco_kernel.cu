@@ -187,7 +187,6 @@ __device__ __forceinline__ MacoTaskDesc load_desc(const MacoProgram& p, uint32_t
 __device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint8_t* smem, const GemmCtrl& c,
                               uint64_t* attn_ring_bars) {
   uint32_t it = 0, ait = 0;          // stage uses of the GEMM ring / of the attention ring (same memory)
-  uint32_t pf_next = 0;              // first queue entry not yet considered for an L2 prefetch
   int owner = 0;                     // which pipeline used the operand memory last: 1 GEMM, 2 attention
   bool ok = true;
   const CUtensorMap* tmaps = reinterpret_cast<const CUtensorMap*>(p.tmaps);
@@ -219,26 +218,6 @@ __device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base,
     fence_proxy_async_all();           // operands were written by generic-proxy stores of other CTAs
     if (owner == 2 && !attn_ring_drained(apipe, ait)) { ok = false; break; }
     owner = 1;
-    if (p.mode == MACO_MODE_STATIC) {
-      // Weights that are read once per launch arrive from HBM with several microseconds of latency and the
-      // ring holds 192 KB: while this tile runs, the B operand of this worker's next flagged GEMM task is
-      // pulled into L2 (static weights: valid whatever that task's dependencies say).
-      const uint32_t n = p.static_count[w];
-      const uint32_t* q = p.static_queue + (size_t)w * p.static_stride;
-      if (pf_next <= i) pf_next = i + 1;
-      for (uint32_t scanned = 0; pf_next < n && scanned < 8; ++pf_next, ++scanned) {
-        const MacoTaskDesc& nd = p.tasks[q[pf_next] & MACO_QUEUE_INDEX_MASK];
-        if (!is_gemm(nd.type) || !(nd.flags & MACO_TF_PREFETCH_B)) continue;
-        const MacoGemmArgs& ng = nd.u.gemm;
-        const CUtensorMap* ntb = tmaps + ng.tmap_b;
-        for (int kb = 0; kb < ng.k_blocks; ++kb) {
-          if (ng.b_mn) { for (uint32_t j = 0; j < ng.bn / 64; ++j) tma_prefetch_l2_2d(ntb, ng.n0 + (int)j * 64, ng.k0 + kb * kBK); }
-          else tma_prefetch_l2_2d(ntb, ng.k0 + kb * kBK, ng.n0);
-        }
-        ++pf_next;
-        break;
-      }
-    }
     const CUtensorMap* ta = tmaps + g.tmap_a;
     const CUtensorMap* tb = tmaps + g.tmap_b;
     const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | (g.b_mn ? 1 : 0);

@@ -177,8 +177,7 @@ enum MacoTaskFlags {
   MACO_TF_WAIT0_PREV = 16,        /* wait_event[0] refers to the previous launch: (epoch-1) * count */
   MACO_TF_WAIT1_PREV = 32,
   MACO_TF_ANY_WORKER = 64,        /* host-side placement hint only */
-  MACO_TF_COUNTED = 128,          /* GEMM tile guarded by a row count known only at run time (MoE) */
-  MACO_TF_PREFETCH_B = 256        /* GEMM tile whose B operand (weights) is cold in HBM: the TMA warp prefetches it into L2 one GEMM task ahead */
+  MACO_TF_COUNTED = 128           /* GEMM tile guarded by a row count known only at run time (MoE) */
 };
 
 /* A dispatch group for the scheduler CTA: a run of consecutive tasks that becomes ready together. */

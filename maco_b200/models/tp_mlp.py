@@ -18,7 +18,6 @@ example all-reduces a column-parallel output (examples/tensor_parallel.py:55-61)
 """
 from __future__ import annotations
 
-import os
 from typing import Optional
 
 import torch
@@ -51,8 +50,8 @@ class TPSwiGLUMLP:
         if comm_workers is None:
             # one SM pushes roughly 25-30 GB/s into a peer; the shard has to reach world-1 peers before
             # they run out of local rows to work on
+            # (8 GPUs, this layer: 12 workers 493 us, 16 workers 459-482 us, 24 workers 479 us)
             comm_workers = 6 if world <= 2 else 16
-            comm_workers = int(os.environ.get("MACO_TP_COMM_WORKERS", comm_workers))
         b = ProgramBuilder(dev, num_workers=num_workers, mode=mode, heap=heap, trace=trace,
                            num_comm_workers=(comm_workers if world > 1 else 0))
         self.h = torch.empty(tokens, f_local, device=dev, dtype=dtype)

@@ -28,7 +28,6 @@ MODE_STATIC, MODE_DYNAMIC = 0, 1
 TF_WAIT0_SYS, TF_WAIT1_SYS, TF_COMM_WORKER, TF_SIGNAL_SYS, TF_WAIT0_PREV, TF_WAIT1_PREV = 1, 2, 4, 8, 16, 32
 TF_ANY_WORKER = 64      # host-side placement hint: spread over compute AND communication workers
 TF_COUNTED = 128        # GEMM tile guarded by a run-time row count
-TF_PREFETCH_B = 256     # GEMM tile whose weights are cold in HBM: prefetched into L2 one GEMM task ahead
 COMM_PUSH, COMM_REDUCE_LOCAL, COMM_REDUCE_PULL, COMM_ALLREDUCE, COMM_ALLREDUCE_MC, COMM_PULL, COMM_REDUCE_LOCAL_BCAST = range(7)
 MAX_PEERS = 16
 WORKER_QUEUE_SIZE = 1024
@@ -197,7 +196,7 @@ class ProgramBuilder:
     def add_task(self, ttype: int, raw: bytes, waits: Sequence[Tuple[int, int, bool, bool]] = (),
                  signals: Sequence[int] = (), signal_peer: int = -1, signal_peer_event: int = -1, node_id: int = 0,
                  comm_worker: bool = False, signal_sys: bool = False, any_worker: bool = False,
-                 counted: bool = False, worker: Optional[int] = None, prefetch_b: bool = False) -> int:
+                 counted: bool = False, worker: Optional[int] = None) -> int:
         """``waits``: up to two (event, count, sys_scope, previous_epoch). ``worker`` pins the task to a compute
         worker's static queue (the dynamic scheduler ignores it)."""
         if len(waits) > 2 or len(signals) > 2:
@@ -218,8 +217,6 @@ class ProgramBuilder:
             flags |= TF_ANY_WORKER
         if counted:
             flags |= TF_COUNTED
-        if prefetch_b:
-            flags |= TF_PREFETCH_B
         se = list(signals) + [-1] * (2 - len(signals))
         self.tasks.append(dict(type=ttype, flags=flags, node_id=node_id, wait_event=we, wait_count=wc, signal_event=se,
                                signal_peer=signal_peer, signal_peer_event=signal_peer_event, raw=raw, worker=worker))
@@ -259,7 +256,7 @@ class ProgramBuilder:
              aux: Optional[torch.Tensor] = None, alpha: float = 1.0, bn: int = 0,
              a_ready: Optional[RowEvents] = None, extra_waits: Sequence[Tuple[int, int, bool, bool]] = (),
              per_tile=None, m_blocks: Optional[Sequence[int]] = None, signal_sys: bool = False,
-             row_wait=None, prefetch_b: bool = False) -> RowEvents:
+             row_wait=None) -> RowEvents:
         """Adds the tiles of ``out = epilogue(alpha * A · B^T)`` (A logically [M,K], B logically [N,K]).
 
         ``a_ready`` gives row-block events of A (a tile waits only for its 128 rows); ``extra_waits``
@@ -331,8 +328,7 @@ class ProgramBuilder:
                                      ov.get("count_base", 0), ov.get("count_ptr", 0))
                     self.add_task(int(TaskType.LINEAR), raw, waits=waits, signals=[row_events[mb], all_ev],
                                   signal_peer=ov.get("signal_peer", -1), signal_peer_event=ov.get("signal_peer_event", -1),
-                                  node_id=node_id, signal_sys=signal_sys, counted=bool(ov.get("count_ptr", 0)),
-                                  prefetch_b=prefetch_b)
+                                  node_id=node_id, signal_sys=signal_sys, counted=bool(ov.get("count_ptr", 0)))
         total = len(mbs) * n_tiles
         return RowEvents(rows=M, block=BM, row_events=[(row_events.get(mb, all_ev), n_tiles) if mb in row_events
                                                        else (all_ev, total) for mb in range(m_tiles)],
