@@ -17,7 +17,9 @@ reduce_scatter (NCCL) for the collectives.
 Rank 0 prints exactly one JSON line. ``value`` is the device-timed layer latency in microseconds
 (CUDA events around K back-to-back steps, max over ranks); ``e2e`` is the same layer driven through
 the public API with, every step, the host->device copy of that step's input from pinned memory
-and a device->host read of a result metric inside the timed region.
+and a device->host read of a result metric inside the timed region. Both arms feed the input through
+a double-buffered staging copy (``maco_b200.utils.InputPrefetcher`` / the same pattern with plain
+torch streams for the reference), so the copy of step i+1 overlaps the kernels of step i.
 """
 from __future__ import annotations
 
