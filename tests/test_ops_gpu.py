@@ -122,3 +122,11 @@ def test_attention_decode(dtype, cfg):
     s = torch.einsum("bhgd,bhsd->bhgs", qf, k.float()) * 128 ** -0.5
     ref = torch.einsum("bhgs,bhsd->bhgd", torch.softmax(s, -1), v.float()).reshape(B, Hq, 128)
     assert_close(out, ref, dtype)
+    # the same call with a caller-provided output and no split count goes through the tensor-core task of the
+    # persistent kernel (fp16 and bf16; twice: the program is cached per set of buffers)
+    out2 = torch.empty_like(q)
+    for _ in range(2):
+        out2.zero_()
+        ops.attention_decode(q, k, v, out=out2)
+        torch.cuda.synchronize()
+        assert_close(out2, ref, dtype)
