@@ -56,6 +56,16 @@ constexpr int kU = 8;
 // Data loads are plain (weak) 16-byte loads: ordering against the producer comes from the acquire
 // on the task's event followed by the CTA barrier, so the compiler is free to batch them.
 MACO_DEVICE uint4 ldv(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+// Explicit shared-memory vector accesses (32-bit shared addresses): no generic-address resolution, and the
+// compiler knows they cannot alias global or local memory.
+MACO_DEVICE uint4 lds128(uint32_t saddr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
+  return v;
+}
+MACO_DEVICE void sts128(uint32_t saddr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" :: "r"(saddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 MACO_DEVICE void stv(uint8_t* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
 
 // Byte offset of 16-byte vector `i` of a block whose rows are `stride` bytes apart. 32-bit index
@@ -293,15 +303,22 @@ __device__ __noinline__ bool comm_reduce_bulk(const Program& p, const MacoCommAr
         if (globaltimer_ns() - t0 > p.budget_ns) { ok = false; break; }
       }
     }
-    uint8_t* g0 = bc.buf + (size_t)(g * n) * bc.buf_bytes;
-    for (uint32_t v = tid; v < (nb >> 4); v += nthreads) {
+    // Everything the loop needs sits in plain locals: the lambda reaches `a` and `bc` through its closure, i.e.
+    // through memory, and every store of the loop (a generic address) would force them to be read again.
+    const uint32_t g0s = smem_u32(bc.buf + (size_t)(g * n) * bc.buf_bytes), bufb = bc.buf_bytes, nvec = nb >> 4;
+    const int nn = n;
+    const float scale = a.scale;
+    const uint8_t* aux = a.aux_ptr != nullptr ? reinterpret_cast<const uint8_t*>(a.aux_ptr) + off : nullptr;
+    uint8_t* outp = out + off;
+    for (uint32_t v = tid; v < nvec; v += nthreads) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int j = 0; j < n; ++j) add8(acc, *reinterpret_cast<const uint4*>(g0 + (size_t)j * bc.buf_bytes + ((size_t)v << 4)), DTT);
-      if (a.aux_ptr != nullptr) add8(acc, ldv(reinterpret_cast<const uint8_t*>(a.aux_ptr) + off + ((uint64_t)v << 4)), DTT);
-      const uint4 o = pack8(acc, a.scale, DTT);
-      if (bcast) *reinterpret_cast<uint4*>(g0 + ((size_t)v << 4)) = o;        // result replaces source 0 in shared memory
-      else stv(out + off + ((uint64_t)v << 4), o);
+      for (int j = 0; j < nn; ++j) add8(acc, lds128(g0s + (uint32_t)j * bufb + (v << 4)), DTT);
+      if (aux != nullptr) add8(acc, ldv(aux + ((uint64_t)v << 4)), DTT);
+      const uint4 o = pack8(acc, scale, DTT);
+      if (bcast) sts128(g0s + (v << 4), o);                                  // result replaces source 0 in shared memory
+      else stv(outp + ((uint64_t)v << 4), o);
     }
+    uint8_t* g0 = bc.buf + (size_t)(g * n) * bc.buf_bytes;
     if (bcast) fence_proxy_async_smem();
     bar_sync();                                              // the position is consumed (and its result staged)
     if (tid == 0) {
