@@ -17,9 +17,11 @@ reduce_scatter (NCCL) for the collectives.
 Rank 0 prints exactly one JSON line. ``value`` is the device-timed layer latency in microseconds
 (CUDA events around K back-to-back steps, max over ranks); ``e2e`` is the same layer driven through
 the public API with, every step, the host->device copy of that step's input from pinned memory
-and a device->host read of a result metric inside the timed region. Both arms feed the input through
-a double-buffered staging copy (``maco_b200.utils.InputPrefetcher`` / the same pattern with plain
-torch streams for the reference), so the copy of step i+1 overlaps the kernels of step i.
+and a device->host read of the first output values inside the timed region. Both arms run the same
+pipelined loop (``maco_b200.utils.StepPipeline`` / the same pattern with plain torch streams and events
+for the reference): the copy of step i+1's input overlaps the kernels of step i, and the host waits for
+the result of step i-1 after it has queued step i. Outside the timed region the default arm checks its
+output rows against an fp32 PyTorch result (``max_rel_err_vs_fp32``).
 """
 from __future__ import annotations
 
@@ -111,8 +113,10 @@ def maybe_relaunch(args):
         sys.exit(subprocess.call(cmd))
 
 
-def timed_region(torch, dist, world, steps, step_fn, sampler=None):
-    """K steps between CUDA events, barrier + synchronize on both sides; returns max-over-ranks ms."""
+def timed_region(torch, dist, world, steps, step_fn, sampler=None, finish_fn=None):
+    """K steps between CUDA events, barrier + synchronize on both sides; returns max-over-ranks ms.
+    ``finish_fn`` (the pipelined end-to-end loop's drain: the host reads the last step's result) runs inside
+    the timed region."""
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -122,6 +126,8 @@ def timed_region(torch, dist, world, steps, step_fn, sampler=None):
     e0.record()
     for _ in range(steps):
         step_fn()
+    if finish_fn is not None:
+        finish_fn()
     e1.record()
     torch.cuda.synchronize()
     clocks = sampler.stop() if sampler else None
@@ -158,32 +164,28 @@ def run_ours(args):
     g = torch.Generator(device="cpu").manual_seed(1234 + rank)
     x_host = torch.randn(rows, args.hidden, generator=g).to(torch.bfloat16).pin_memory()
     layer.x_shard.copy_(x_host)
-    metric_host = torch.zeros(1, dtype=torch.float32).pin_memory()
 
     def step():
         layer.forward(None)
 
-    from maco_b200.utils import InputPrefetcher
-    feed = InputPrefetcher(layer.x_shard)
+    from maco_b200.utils import StepPipeline
+    pipe = StepPipeline(layer.x_shard, layer.y_shard[0, :2])
 
     def step_e2e():
-        # every step copies its own input from pinned host memory; the copy of step i+1 is started right after
-        # the launch of step i (double-buffered staging), so it overlaps that step's kernel
-        if not feed.pending:
-            feed.submit(x_host)
-        feed.deliver(layer.x_shard)
-        y = layer.forward(None)
-        feed.submit(x_host)
-        metric_host.copy_(y[0, :1].float(), non_blocking=True)
-        torch.cuda.current_stream().synchronize()     # the host has the result of this step
+        # Every step copies its own input from pinned host memory (started during the previous step, so it runs
+        # under that step's kernel) and its result is read on the host; the host waits for the result of step
+        # i-1 only after step i has been queued, so the GPU never idles between steps.
+        pipe.step(x_host, lambda: layer.forward(None), lambda: layer.y_shard[0, :2])
 
     for _ in range(args.warmup):
         step()
     ms, clocks = timed_region(torch, dist, world, args.steps, step, ClockSampler(local_rank) if rank == 0 else None)
     for _ in range(max(3, args.warmup // 2)):
         step_e2e()
-    ms_e2e, _ = timed_region(torch, dist, world, args.steps, step_e2e)
+    pipe.drain()
+    ms_e2e, _ = timed_region(torch, dist, world, args.steps, step_e2e, finish_fn=pipe.drain)
     status = _native.status(clear=False)
+    max_rel_err = check_output(torch, dist, layer, x_host, rank, world)
     us = ms * 1e3 / args.steps
     us_e2e = ms_e2e * 1e3 / args.steps
     flops = 2.0 * args.tokens * args.hidden * args.ffn * 3
@@ -203,9 +205,36 @@ def run_ours(args):
                     "d2h_bytes_per_step": 4},
             "gpu_launches": args.steps,
             "kernel_status": status,
+            "max_rel_err_vs_fp32": max_rel_err,
         }))
     if world > 1:
         maco.cleanup()
+
+
+def check_output(torch, dist, layer, x_host, rank, world):
+    """Outside the timed region: this rank's output rows against an fp32 PyTorch result of the same layer
+    (all-gather of the inputs and reduce-scatter of the fp32 partial products through NCCL). Returns
+    max |y - y_ref| / max |y_ref| over all ranks."""
+    dev = layer.device
+    layer.x_shard.copy_(x_host)
+    y = layer.forward(None).float().clone()
+    torch.cuda.synchronize()
+    xs = x_host.to(dev)
+    if world > 1:
+        x_full = torch.empty(world * xs.shape[0], xs.shape[1], device=dev, dtype=xs.dtype)
+        dist.all_gather_into_tensor(x_full, xs)
+    else:
+        x_full = xs
+    partial = layer.reference(x_full)
+    if world > 1:
+        y_ref = torch.empty(xs.shape[0], partial.shape[1], device=dev, dtype=torch.float32)
+        dist.reduce_scatter_tensor(y_ref, partial)
+    else:
+        y_ref = partial
+    err = ((y - y_ref).abs().max() / y_ref.abs().max().clamp_min(1e-20)).reshape(1)
+    if world > 1:
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+    return round(float(err.item()), 6)
 
 
 def run_reference(args):
@@ -241,7 +270,6 @@ def run_reference(args):
         graph.custom(lambda a, b: torch.nn.functional.silu(a) * b, [t_gate.output, t_up.output], [h], name="swiglu")
         t_down = graph.linear(h, w_down, name="down")
         graph.compile()
-    metric_host = torch.zeros(1, dtype=torch.float32).pin_memory()
 
     def step():
         if world > 1:
@@ -267,7 +295,18 @@ def run_reference(args):
             ready[i].record(copy_stream)
         state["submitted"] += 1
 
+    res_host = [torch.empty(2, dtype=dt).pin_memory() for _ in range(2)]
+    res_done = [torch.cuda.Event() for _ in range(2)]
+    pending = []
+
+    def pop_result():
+        slot = pending.pop(0)
+        res_done[slot].synchronize()
+        return res_host[slot]
+
     def step_e2e():
+        # same loop as the other arm: input of step i copied during step i-1, the host waits for the result of
+        # step i-1 after step i has been queued
         if state["submitted"] == state["delivered"]:
             submit()
         i = state["delivered"] % 2
@@ -278,8 +317,16 @@ def run_reference(args):
         state["delivered"] += 1
         y = step()
         submit()
-        metric_host.copy_(y[0, :1].float(), non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        slot = (state["delivered"] - 1) % 2
+        res_host[slot].copy_(y[0, :2], non_blocking=True)
+        res_done[slot].record(cur)
+        pending.append(slot)
+        if len(pending) >= 2:
+            pop_result()
+
+    def drain():
+        while pending:
+            pop_result()
 
     with contextlib.redirect_stdout(sys.stderr):
         for _ in range(args.warmup):
@@ -287,7 +334,8 @@ def run_reference(args):
         ms, clocks = timed_region(torch, dist, world, args.steps, step, ClockSampler(local_rank) if rank == 0 else None)
         for _ in range(max(3, args.warmup // 2)):
             step_e2e()
-        ms_e2e, _ = timed_region(torch, dist, world, args.steps, step_e2e)
+        drain()
+        ms_e2e, _ = timed_region(torch, dist, world, args.steps, step_e2e, finish_fn=drain)
     us, us_e2e = ms * 1e3 / args.steps, ms_e2e * 1e3 / args.steps
     flops = 2.0 * args.tokens * args.hidden * args.ffn * 3
     if rank == 0:

@@ -45,6 +45,40 @@ int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorM
   return launch_gemm<BN, STAGES, true, true>(tmA, tmB, epi, K, idesc, max_ctas, budget_ns, stream);
 }
 
+// Two-CTA tiles: clusters of two CTAs, 256 x BN per pair.
+template <int BN, bool A_MN, bool B_MN>
+int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmEpilogue& epi, int K, uint32_t idesc,
+                     int max_ctas, uint64_t budget_ns, cudaStream_t stream) {
+  using L = PairSmemLayout<kPairStages>;
+  auto kern = gemm_tcgen05_pair_kernel<BN, A_MN, B_MN>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  MACO_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev]) {
+    MACO_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes));
+    attr_set[dev] = true;
+  }
+  const int m_pairs = (epi.M + 2 * kBM - 1) / (2 * kBM), n_tiles = (epi.N + BN - 1) / BN;
+  int pairs = m_pairs * n_tiles;
+  int sms = maco_host::sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  if (pairs > sms / 2) pairs = sms / 2;
+  if (pairs <= 0) return 0;
+  uint32_t* status = maco_host::status_device_ptr();
+  kern<<<2 * pairs, kGemmThreads, L::kTotalBytes, stream>>>(tmA, tmB, epi, K, idesc, budget_ns, status);
+  MACO_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+template <int BN>
+int dispatch_major_pair(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmEpilogue& epi,
+                        int K, uint32_t idesc, int max_ctas, uint64_t budget_ns, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch_gemm_pair<BN, false, false>(tmA, tmB, epi, K, idesc, max_ctas, budget_ns, stream);
+  if (!a_mn && b_mn) return launch_gemm_pair<BN, false, true>(tmA, tmB, epi, K, idesc, max_ctas, budget_ns, stream);
+  if (a_mn && !b_mn) return launch_gemm_pair<BN, true, false>(tmA, tmB, epi, K, idesc, max_ctas, budget_ns, stream);
+  return launch_gemm_pair<BN, true, true>(tmA, tmB, epi, K, idesc, max_ctas, budget_ns, stream);
+}
+
 // ---- CUDA-core GEMM: 64x64 tile, 256 threads, 4x4 outputs per thread ---------------------------
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
@@ -113,7 +147,8 @@ extern "C" {
 int maco_gemm(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
               long long ldd, int a_mn, int b_mn, int ab_type, int out_type, int mode, const void* bias,
               int bias_type, const void* aux, long long ld_aux, int aux_type, float alpha, int bn, int max_ctas,
-              double wait_budget_ms, void* stream_) {
+              double wait_budget_ms, void* stream_, int cta_pair) {
+  // cta_pair: 0 = choose (two-CTA tiles when the 256 x bn tiles cover every SM pair), 1 = one-CTA tiles, 2 = two-CTA tiles
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return 0;
   if (ab_type != MACO_DT_BF16 && ab_type != MACO_DT_F16) { maco_host::set_error("maco_gemm: inputs must be bf16 or fp16"); return -2; }
@@ -131,19 +166,29 @@ int maco_gemm(const void* A, const void* B, void* D, int M, int N, int K, long l
     maco_host::set_error("maco_gemm: output base and row stride must be 16-byte aligned");
     return -2;
   }
+  bool pair = cta_pair == 2;
+  if (cta_pair == 0) {
+    const int sms = maco_host::sm_count();
+    pair = ((M + 255) / 256) * ((N + bn - 1) / bn) >= sms / 2;
+  }
   CUtensorMap tmA, tmB;
   int r;
   if (!a_mn) r = maco_host::encode_tmap_2d(&tmA, A, 2, M, K, lda * 2, kBK, kBM);
   else       r = maco_host::encode_tmap_2d(&tmA, A, 2, K, M, lda * 2, 64, kBK);
   if (r != 0) return r == -2 ? -2 : -1;
-  if (!b_mn) r = maco_host::encode_tmap_2d(&tmB, B, 2, N, K, ldb * 2, kBK, bn);
+  if (!b_mn) r = maco_host::encode_tmap_2d(&tmB, B, 2, N, K, ldb * 2, kBK, pair ? bn / 2 : bn);
   else       r = maco_host::encode_tmap_2d(&tmB, B, 2, K, N, ldb * 2, 64, kBK);
   if (r != 0) return r == -2 ? -2 : -1;
   GemmEpilogue e;
   e.out = D; e.bias = bias; e.aux = aux; e.ld_out = ldd; e.ld_aux = ld_aux; e.mode = mode; e.out_type = out_type;
   e.bias_type = bias_type; e.aux_type = aux_type; e.M = M; e.N = N; e.alpha = alpha; e._pad = 0;
-  const uint32_t idesc = make_idesc(ab_type == MACO_DT_BF16 ? 1u : 0u, kBM, bn, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
   const uint64_t budget_ns = (uint64_t)((wait_budget_ms > 0 ? wait_budget_ms : 2000.0) * 1e6);
+  if (pair) {
+    const uint32_t idesc2 = make_idesc(ab_type == MACO_DT_BF16 ? 1u : 0u, 2 * kBM, bn, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
+    if (bn == 256) return dispatch_major_pair<256>(a_mn, b_mn, tmA, tmB, e, K, idesc2, max_ctas, budget_ns, stream);
+    return dispatch_major_pair<128>(a_mn, b_mn, tmA, tmB, e, K, idesc2, max_ctas, budget_ns, stream);
+  }
+  const uint32_t idesc = make_idesc(ab_type == MACO_DT_BF16 ? 1u : 0u, kBM, bn, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
   if (bn == 256) return dispatch_major<256, 4>(a_mn, b_mn, tmA, tmB, e, K, idesc, max_ctas, budget_ns, stream);
   return dispatch_major<128, 6>(a_mn, b_mn, tmA, tmB, e, K, idesc, max_ctas, budget_ns, stream);
 }

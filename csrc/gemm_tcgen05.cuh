@@ -293,7 +293,7 @@ template <int BN, int SBN = BN>
 MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const GemmEpilogue& e_in,
                                     void* out_base, long long row_off, int m0, int n0,
                                     uint32_t tile_seq, uint64_t budget_ns, const EpiBroadcast* bc = nullptr,
-                                    uint8_t* stage = nullptr) {
+                                    uint8_t* stage = nullptr, uint32_t pair_empty_bar = 0) {
   // private copy: the record lives in global memory; read in place, its fields would be loaded again after
   // every store of the tile (the stores could alias it)
   const GemmEpilogue e = e_in;
@@ -397,7 +397,13 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
   }
   if (staged) tma_store_wait<0>();     // bulk stores complete before the tile is signalled
   tc_fence_before();
-  mbar_arrive(&c.tmem_empty[acc]);
+  if (pair_empty_bar == 0) {
+    mbar_arrive(&c.tmem_empty[acc]);
+  } else {
+    // two-CTA tile: the pair leader's barrier collects one arrival per epilogue warp of both CTAs
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster(pair_empty_bar + acc * 8);
+  }
   return true;
 }
 
@@ -435,6 +441,199 @@ MACO_DEVICE void gemm_cta_teardown(const GemmCtrl& c, uint32_t tmem_base, uint32
     tmem_dealloc(tmem_base, 2 * BN);
   }
   if (threadIdx.x == 0 && *c.abort_word != 0 && status != nullptr) st_relaxed_sys_u32(status, MACO_STATUS_TIMEOUT);
+}
+
+// ---- two-CTA tiles (cta_group::2) -----------------------------------------------------------------
+// A pair of CTAs (one cluster) computes a 256 x BN tile: each CTA loads its own 128 rows of A and its own
+// half (BN/2 rows) of B, the leader issues tcgen05.mma.cta_group::2 (M = 256), which reads both CTAs' shared
+// memory and writes each CTA's 128 accumulator rows into that CTA's TMEM. Per k-step a CTA brings in
+// 16 KB + BN/2 * 128 B instead of 16 KB + BN * 128 B: a third less shared-memory and L2 traffic per FLOP at
+// BN = 256, and six 32 KB stages where the one-CTA form has four of 48 KB. The two row blocks of a pair
+// need not be adjacent. Loads carry no multicast: each CTA fetches what it needs itself.
+template <int STAGES>
+struct PairSmemLayout {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytesMax = 128 * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytesMax;
+  static constexpr int kRingBytes = STAGES * kStageBytes;
+  static constexpr int kCtrlBytes = 256;
+  static constexpr int kTotalBytes = kRingBytes + kCtrlBytes + 1024;
+  static_assert(2 * STAGES * 8 + 4 * 8 + 16 <= kCtrlBytes, "control block too small");
+};
+
+template <int STAGES>
+MACO_DEVICE GemmCtrl pair_ctrl(uint8_t* smem_base) {
+  using L = PairSmemLayout<STAGES>;
+  GemmCtrl c;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_base + L::kRingBytes);
+  c.full = bars;
+  c.empty = bars + STAGES;
+  c.tmem_full = bars + 2 * STAGES;
+  c.tmem_empty = bars + 2 * STAGES + 2;
+  c.tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  c.abort_word = reinterpret_cast<volatile uint32_t*>(c.tmem_slot + 1);
+  return c;
+}
+
+// Producer of one CTA of the pair. `n0` is the tile's first column; this CTA loads B rows
+// [n0 + rank * BN/2, n0 + (rank + 1) * BN/2). All bytes of both CTAs are credited to the LEADER's full barrier.
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+MACO_DEVICE bool pair_produce_tile(uint8_t* smem, const GemmCtrl& c, uint32_t rank, const CUtensorMap* tmA,
+                                   const CUtensorMap* tmB, int m0, int n0, int k0, int k_blocks, uint32_t& it,
+                                   uint64_t budget_ns) {
+  using L = PairSmemLayout<STAGES>;
+  constexpr int kBHalf = BN / 2;
+  constexpr uint32_t kPairBytes = 2u * (L::kABytes + kBHalf * kBK * 2);
+  const uint32_t full0 = mapa_u32(smem_u32(&c.full[0]), 0);
+  const int nb0 = n0 + (int)rank * kBHalf;
+  for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+    if (!mbar_wait(&c.empty[s], ph ^ 1, budget_ns, c.abort_word)) return false;
+    uint8_t* sa = smem + s * L::kStageBytes;
+    uint8_t* sb = sa + L::kABytes;
+    if (rank == 0) mbar_arrive_expect_tx(&c.full[s], kPairBytes);
+    const uint32_t bar = full0 + s * 8;
+    const int k = k0 + kb * kBK;
+    if constexpr (!A_MN) {
+      tma_load_2d_pair(sa, tmA, bar, k, m0);
+    } else {
+#pragma unroll
+      for (int j = 0; j < kBM / 64; ++j) tma_load_2d_pair(sa + j * 8192, tmA, bar, m0 + j * 64, k);
+    }
+    if constexpr (!B_MN) {
+      tma_load_2d_pair(sb, tmB, bar, k, nb0);
+    } else {
+#pragma unroll
+      for (int j = 0; j < kBHalf / 64; ++j) tma_load_2d_pair(sb + j * 8192, tmB, bar, nb0 + j * 64, k);
+    }
+  }
+  return true;
+}
+
+// MMA issuer: the pair's leader only. `peer_*` are the shared::cluster addresses of the other CTA's barriers.
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+MACO_DEVICE bool pair_mma_tile(uint8_t* smem, const GemmCtrl& c, uint32_t tmem_base, uint32_t idesc, int k_blocks,
+                               uint32_t& it, uint32_t tile_seq, uint64_t budget_ns) {
+  using L = PairSmemLayout<STAGES>;
+  const uint32_t acc = tile_seq & 1, acc_ph = (tile_seq >> 1) & 1;
+  const uint32_t empty_l = smem_u32(&c.empty[0]), empty_p = mapa_u32(empty_l, 1);
+  const uint32_t tfull_l = smem_u32(&c.tmem_full[0]), tfull_p = mapa_u32(tfull_l, 1);
+  if (!mbar_wait(&c.tmem_empty[acc], acc_ph ^ 1, budget_ns, c.abort_word)) return false;
+  tc_fence_after();
+  const uint32_t d_tmem = tmem_base + acc * 256;
+  for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+    if (!mbar_wait(&c.full[s], ph, budget_ns, c.abort_word)) return false;
+    tc_fence_after();
+    const uint32_t a_base = smem_u32(smem + s * L::kStageBytes);
+    const uint32_t b_base = a_base + L::kABytes;
+#pragma unroll
+    for (int k = 0; k < kBK / kUmmaK; ++k) {
+      const uint64_t adesc = A_MN ? make_smem_desc(a_base + k * 2048, 8192, 1024, 2)
+                                  : make_smem_desc(a_base + k * 32, 16, 1024, 2);
+      const uint64_t bdesc = B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024, 2)
+                                  : make_smem_desc(b_base + k * 32, 16, 1024, 2);
+      tc_mma2_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+    }
+    tc_commit2(empty_l + s * 8);     // both CTAs may refill the stage once these MMAs have read it
+    tc_commit2(empty_p + s * 8);
+  }
+  tc_commit2(tfull_l + acc * 8);     // accumulator complete -> both CTAs' epilogues
+  tc_commit2(tfull_p + acc * 8);
+  return true;
+}
+
+template <int STAGES>
+MACO_DEVICE uint8_t* pair_cta_setup(uint8_t* dyn_smem, GemmCtrl& c, uint32_t& tmem_base) {
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
+  c = pair_ctrl<STAGES>(smem);
+  const uint32_t warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&c.tmem_full[a], 1); mbar_init(&c.tmem_empty[a], 8); }   // 4 warps x 2 CTAs
+    *c.abort_word = 0;
+    fence_mbar_init();
+  }
+  if (threadIdx.x == 32) *c.tmem_slot = 0;
+  __syncwarp();
+  if (warp == 1) {
+    tmem_alloc2(c.tmem_slot, 512);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();            // the other CTA's barriers are initialised before anything is sent to them
+  cluster_wait();
+  tc_fence_after();
+  tmem_base = *c.tmem_slot;
+  return smem;
+}
+
+MACO_DEVICE void pair_cta_teardown(const GemmCtrl& c, uint32_t tmem_base, uint32_t* status) {
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();            // neither CTA frees TMEM or leaves while the other may still touch its memory
+  cluster_wait();
+  if ((threadIdx.x >> 5) == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *c.abort_word != 0 && status != nullptr) st_relaxed_sys_u32(status, MACO_STATUS_TIMEOUT);
+}
+
+constexpr int kPairStages = 6;
+
+// Stand-alone GEMM on two-CTA tiles: grid = 2 x (number of CTA pairs), launched as clusters of two.
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         GemmEpilogue epi, int K, uint32_t idesc, uint64_t budget_ns, uint32_t* status) {
+  extern __shared__ uint8_t dyn_smem[];
+  GemmCtrl c;
+  uint32_t tmem_base;
+  uint8_t* smem = pair_cta_setup<kPairStages>(dyn_smem, c, tmem_base);
+  const uint32_t rank = cluster_ctarank();
+  const int m_pairs = (epi.M + 2 * kBM - 1) / (2 * kBM), n_tiles = (epi.N + BN - 1) / BN;
+  const int num_tiles = m_pairs * n_tiles;
+  const int k_blocks = (K + kBK - 1) / kBK;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t tempty_leader = mapa_u32(smem_u32(&c.tmem_empty[0]), 0);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+        int mp, nb;
+        gemm_tile_coords(tile, m_pairs, n_tiles, mp, nb);
+        ok = pair_produce_tile<BN, kPairStages, A_MN, B_MN>(smem, c, rank, &tmA, &tmB, (mp * 2 + (int)rank) * kBM, nb * BN, 0,
+                                                            k_blocks, it, budget_ns);
+      }
+      if (!ok) gemm_drain_loads<kPairStages>(c, it);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      uint32_t it = 0, seq = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++seq)
+        ok = pair_mma_tile<BN, kPairStages, A_MN, B_MN>(smem, c, tmem_base, idesc, k_blocks, it, seq, budget_ns);
+    }
+    __syncwarp();
+  } else {
+    uint32_t seq = 0;
+    bool ok = true;
+    for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++seq) {
+      int mp, nb;
+      gemm_tile_coords(tile, m_pairs, n_tiles, mp, nb);
+      ok = gemm_epilogue_tile<BN, 256>(c, tmem_base, epi, epi.out, 0, (mp * 2 + (int)rank) * kBM, nb * BN, seq, budget_ns,
+                                       nullptr, nullptr, tempty_leader);
+    }
+  }
+  pair_cta_teardown(c, tmem_base, status);
 }
 
 // ---- stand-alone persistent GEMM kernel ---------------------------------------------------------

@@ -273,6 +273,45 @@ MACO_DEVICE void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 MACO_DEVICE void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- two-CTA forms (cta_group::2): a pair of CTAs in one cluster works on one 256-row tile -----------------
+// The MMA is issued by the pair's leader (cluster rank 0) and reads operand tiles at the same shared-memory
+// offset in both CTAs; each CTA's TMEM receives its 128 rows of the accumulator. Every tcgen05 instruction of
+// a kernel uses the same cta_group, so a kernel is built either from the forms above or from these.
+MACO_DEVICE uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+MACO_DEVICE void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+MACO_DEVICE void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// shared::cluster address of `smem_addr` (a shared::cta address of this CTA) in the CTA of cluster rank `rank`
+MACO_DEVICE uint32_t mapa_u32(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank)); return r;
+}
+MACO_DEVICE void mbar_arrive_cluster(uint32_t cluster_addr) {      // arrive on a barrier of any CTA of the cluster
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+}
+MACO_DEVICE void tmem_alloc2(uint32_t* smem_slot, uint32_t ncols) {   // one whole warp in EACH CTA of the pair
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(smem_slot)), "r"(ncols) : "memory");
+}
+MACO_DEVICE void tmem_relinquish2() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+MACO_DEVICE void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(ncols) : "memory");
+}
+// Arrive on the barrier at shared::cluster address `cluster_addr` once every MMA issued so far has finished.
+MACO_DEVICE void tc_commit2(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(cluster_addr) : "memory");
+}
+MACO_DEVICE void tc_mma2_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+      :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// TMA tile load into THIS CTA's shared memory whose byte count is credited to a barrier that may live in the
+// pair's other CTA (`bar_cluster_addr` is a shared::cluster address). No other CTA receives the data.
+MACO_DEVICE void tma_load_2d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      :: "r"(smem_u32(smem_dst)), "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
+
 // Shared-memory matrix descriptor for tcgen05.mma. Addresses and offsets are in 16-byte units.
 //   layout_type: 0 none, 2 = 128-byte swizzle, 4 = 64-byte, 6 = 32-byte.
 MACO_DEVICE uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {

@@ -52,6 +52,11 @@ static_assert(kMkSmemBytes <= 227 * 1024, "persistent kernel exceeds the shared 
 constexpr uint32_t kBulkBufBytes = 16384;                                  // staging buffers of bulk pushes
 constexpr uint32_t kBulkBuffers = MkLayout::kRingBytes / kBulkBufBytes;    // the whole operand ring
 static_assert(kBulkBuffers <= 16, "phase bits / barrier slots");
+// Two-CTA programs (cta_group::2) cut the same operand memory into six 32 KB stages; the control block sits at
+// the same offset, so everything behind it (task slots, bulk and attention barriers, scratch) is shared code.
+using MkPairLayout = PairSmemLayout<kPairStages>;
+static_assert(MkPairLayout::kRingBytes == MkLayout::kRingBytes && MkPairLayout::kCtrlBytes == MkLayout::kCtrlBytes,
+              "one-CTA and two-CTA programs share one shared-memory map");
 
 __device__ __forceinline__ void general_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -92,24 +97,26 @@ __device__ bool wait_deps(const MacoProgram& p, const MacoTaskDesc& d, uint32_t 
                           uint64_t* wait_ns) {
   const uint64_t t0 = wait_ns ? globaltimer_ns() : 0;
   {
-    // common case, both conditions already hold: read the two counters together (one round trip instead
-    // of two) and order everything that follows behind them with a single acquire fence
-    bool sat = true, any_sys = false;
-    uint32_t v[2] = {0u, 0u}, need[2] = {0u, 0u};
+    // Common case, every condition already holds. Counters bumped by this GPU only are read together with
+    // relaxed loads and ordered by ONE .gpu fence. Counters bumped by other GPUs are read with an acquire load
+    // at .sys scope instead of a relaxed load plus fence.acq_rel.sys: the full fence at system scope also waits
+    // for this GPU's outstanding writes to peers and to the host, and takes tens of microseconds while a
+    // host -> device copy is in flight (measured: +300 us per step of the tensor-parallel layer).
+    // A condition with count 0 always holds (a block that is already in place) and is not read at all.
+    bool sat = true, any_gpu = false;
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int e = d.wait_event[j];
-      if (e < 0) continue;
+      if (e < 0 || d.wait_count[j] == 0) continue;
       const bool sys = (d.flags & (j == 0 ? MACO_TF_WAIT0_SYS : MACO_TF_WAIT1_SYS)) != 0;
       const bool prev = (d.flags & (j == 0 ? MACO_TF_WAIT0_PREV : MACO_TF_WAIT1_PREV)) != 0;
-      need[j] = (p.epoch - (prev ? 1u : 0u)) * d.wait_count[j];
-      v[j] = sys ? ld_relaxed_sys_u32(&p.events[e]) : ld_relaxed_gpu_u32(&p.events[e]);
-      any_sys |= sys;
+      const uint32_t need = (p.epoch - (prev ? 1u : 0u)) * d.wait_count[j];
+      const uint32_t v = sys ? ld_acquire_sys_u32(&p.events[e]) : ld_relaxed_gpu_u32(&p.events[e]);
+      any_gpu |= !sys;
+      if ((int32_t)(v - need) < 0) sat = false;
     }
-#pragma unroll
-    for (int j = 0; j < 2; ++j) if (d.wait_event[j] >= 0 && (int32_t)(v[j] - need[j]) < 0) sat = false;
     if (sat) {
-      if (any_sys) fence_acq_rel_sys(); else fence_acq_rel_gpu();
+      if (any_gpu) fence_acq_rel_gpu();
       if (wait_ns) *wait_ns += globaltimer_ns() - t0;
       return true;
     }
@@ -117,7 +124,7 @@ __device__ bool wait_deps(const MacoProgram& p, const MacoTaskDesc& d, uint32_t 
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int e = d.wait_event[j];
-    if (e < 0) continue;
+    if (e < 0 || d.wait_count[j] == 0) continue;
     const bool sys = (d.flags & (j == 0 ? MACO_TF_WAIT0_SYS : MACO_TF_WAIT1_SYS)) != 0;
     const bool prev = (d.flags & (j == 0 ? MACO_TF_WAIT0_PREV : MACO_TF_WAIT1_PREV)) != 0;
     if (!mk_wait(p, &p.events[e], (p.epoch - (prev ? 1u : 0u)) * d.wait_count[j], sys)) {
@@ -181,6 +188,76 @@ __device__ __forceinline__ MacoTaskDesc load_desc(const MacoProgram& p, uint32_t
 #pragma unroll
   for (int i = 0; i < 8; ++i) dst[i] = src[i];
   return d;
+}
+
+// ---- producer warp (lane 0), two-CTA programs ----------------------------------------------------
+// Every GEMM task of such a program is one half (128 rows) of a 256 x BN tile; the two halves sit at the same
+// position of the GEMM sequences of workers 2j and 2j+1 (one cluster). Each CTA waits for ITS half's
+// conditions and loads its rows of A and its half of B; the leader's MMA warp starts when both have landed.
+__device__ void producer_role_pair(const MacoProgram& p, uint32_t w, uint32_t q_base, uint8_t* smem, const GemmCtrl& c) {
+  uint32_t it = 0;
+  bool ok = true;
+  const uint32_t rank = cluster_ctarank();
+  const CUtensorMap* tmaps = reinterpret_cast<const CUtensorMap*>(p.tmaps);
+  for (uint32_t i = 0; ok; ++i) {
+    uint32_t task;
+    if (!fetch_task(p, w, i, q_base, task, c.abort_word)) { ok = false; break; }
+    if (task == MACO_QUEUE_TERMINATE) break;
+    task &= MACO_QUEUE_INDEX_MASK;
+    const MacoTaskDesc& d = p.tasks[task];
+    if (!is_gemm(d.type)) continue;
+    if (!wait_deps(p, d, task, c.abort_word, nullptr)) { ok = false; break; }
+    const MacoGemmArgs& g = d.u.gemm;
+    fence_proxy_async_all();           // operands were written by generic-proxy stores of other CTAs
+    const CUtensorMap* ta = tmaps + g.tmap_a;
+    const CUtensorMap* tb = tmaps + g.tmap_b;
+    const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | (g.b_mn ? 1 : 0);
+    switch (sel) {
+      case 0: ok = pair_produce_tile<256, kPairStages, false, false>(smem, c, rank, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      case 1: ok = pair_produce_tile<256, kPairStages, false, true>(smem, c, rank, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      case 2: ok = pair_produce_tile<256, kPairStages, true, false>(smem, c, rank, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      case 3: ok = pair_produce_tile<256, kPairStages, true, true>(smem, c, rank, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      case 4: ok = pair_produce_tile<128, kPairStages, false, false>(smem, c, rank, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      case 5: ok = pair_produce_tile<128, kPairStages, false, true>(smem, c, rank, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      case 6: ok = pair_produce_tile<128, kPairStages, true, false>(smem, c, rank, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+      default: ok = pair_produce_tile<128, kPairStages, true, true>(smem, c, rank, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+    }
+    if (!ok) report_failure(p, MACO_STATUS_TIMEOUT, task, 0xffffffffu, c.abort_word);
+  }
+  if (!ok) {
+    // loads in flight land in this CTA's memory: the leader's barriers count both CTAs' bytes, the other CTA
+    // gives its own loads a fixed grace period
+    if (rank == 0) gemm_drain_loads<kPairStages>(c, it);
+    else { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000); }
+  }
+}
+
+// ---- MMA warp (lane 0) of the pair's leader ------------------------------------------------------
+__device__ void mma_role_pair(const MacoProgram& p, uint32_t w, uint32_t q_base, uint8_t* smem, const GemmCtrl& c,
+                              uint32_t tmem_base) {
+  uint32_t it = 0, seq = 0;
+  bool ok = true;
+  for (uint32_t i = 0; ok; ++i) {
+    uint32_t task;
+    if (!fetch_task(p, w, i, q_base, task, c.abort_word)) break;
+    if (task == MACO_QUEUE_TERMINATE) break;
+    task &= MACO_QUEUE_INDEX_MASK;
+    const MacoTaskDesc& d = p.tasks[task];
+    if (!is_gemm(d.type)) continue;
+    const MacoGemmArgs& g = d.u.gemm;
+    const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | (g.b_mn ? 1 : 0);
+    switch (sel) {
+      case 0: ok = pair_mma_tile<256, kPairStages, false, false>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      case 1: ok = pair_mma_tile<256, kPairStages, false, true>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      case 2: ok = pair_mma_tile<256, kPairStages, true, false>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      case 3: ok = pair_mma_tile<256, kPairStages, true, true>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      case 4: ok = pair_mma_tile<128, kPairStages, false, false>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      case 5: ok = pair_mma_tile<128, kPairStages, false, true>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      case 6: ok = pair_mma_tile<128, kPairStages, true, false>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+      default: ok = pair_mma_tile<128, kPairStages, true, true>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
+    }
+    ++seq;
+  }
 }
 
 // ---- producer warp (lane 0) ---------------------------------------------------------------------
@@ -301,10 +378,14 @@ __device__ __noinline__ void run_moe(const MacoProgram& p, uint32_t type, const 
 // ---- general warps (128 threads): GEMM epilogues and every non-GEMM task -------------------------
 // Control words shared by the 128 threads are double buffered by iteration parity, so the
 // leader can prepare iteration i+1 while slower threads still read the words of iteration i.
+template <int CG>
 __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, const GemmCtrl& c, uint32_t tmem_base,
                              volatile uint32_t* slots, uint8_t* scratch_smem, uint8_t* ring_smem, uint64_t* bulk_bars,
                              uint64_t* attn_bars) {
   const int tid = threadIdx.x - 64;          // 0..127
+  // two-CTA programs: the epilogue warps of both CTAs report "accumulator drained" to the leader's barrier
+  uint32_t pair_empty_bar = 0;
+  if constexpr (CG == 2) pair_empty_bar = mapa_u32(smem_u32(&c.tmem_empty[0]), 0);
   const bool leader = tid == 0;
   // Communication workers never get GEMM tasks, so their operand ring is free to stage bulk copies.
   const bool comm_worker = p.num_comm_workers > 0 && w >= p.num_workers - p.num_comm_workers;
@@ -354,8 +435,8 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
       const EpiBroadcast* bcp = g.peer == -2 ? &bc : nullptr;
       bool ok;
       uint8_t* stage = g.peer != -1 ? scratch_smem : nullptr;  // tiles that leave the GPU go through the bulk engine
-      if (g.bn == 128) ok = gemm_epilogue_tile<128, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns, bcp, stage);
-      else ok = gemm_epilogue_tile<256, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns, bcp, stage);
+      if (g.bn == 128) ok = gemm_epilogue_tile<128, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns, bcp, stage, pair_empty_bar);
+      else ok = gemm_epilogue_tile<256, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns, bcp, stage, pair_empty_bar);
       if (!ok) cur[2] = 1;
       ++seq;
       it += (uint32_t)g.k_blocks;
@@ -369,12 +450,19 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
             if (leader) report_failure(p, MACO_STATUS_BAD_TASK, task, d.u.comm.op, c.abort_word);
           }
         } else if (d.type == MACO_TASK_ATTENTION && attn_pipelined(d.u.elt)) {
-          const AttnPipe pipe{ring_smem, attn_bars + 4, attn_bars + 4 + kAttnStages, p.budget_ns, c.abort_word,
-                              nullptr, attn_bars, tmem_base};
-          if (!attn_consume(d.u.elt, tid, scratch_smem, pipe, ait, attn_chunks)) cur[2] = 1;
-          ait += attn_stage_uses(d.u.elt);
-          general_bar();
-          if (leader) slots[13] = slots[13] + 1;                 // lets the MMA warp move past this task
+          if constexpr (CG == 1) {
+            const AttnPipe pipe{ring_smem, attn_bars + 4, attn_bars + 4 + kAttnStages, p.budget_ns, c.abort_word,
+                                nullptr, attn_bars, tmem_base};
+            if (!attn_consume(d.u.elt, tid, scratch_smem, pipe, ait, attn_chunks)) cur[2] = 1;
+            ait += attn_stage_uses(d.u.elt);
+            general_bar();
+            if (leader) slots[13] = slots[13] + 1;                 // lets the MMA warp move past this task
+          } else {
+            // the tensor-core attention task issues one-CTA MMAs; a kernel has one cta_group (the builder
+            // keeps such tasks out of two-CTA programs)
+            cur[2] = 1;
+            if (leader) report_failure(p, MACO_STATUS_BAD_TASK, task, d.type, c.abort_word);
+          }
         } else if (d.type == MACO_TASK_ATTENTION || d.type == MACO_TASK_ATTN_MERGE) {
           run_attn(d.type, d.u.elt, tid, scratch_smem);
         } else if (d.type == MACO_TASK_TOPK || d.type == MACO_TASK_MOE_COUNTS || d.type == MACO_TASK_MOE_RETURN ||
@@ -494,13 +582,16 @@ __device__ void scheduler_role(const MacoProgram& p, uint32_t* heads_sm) {
   for (uint32_t w = lane; w < W; w += 32) sched_push(p, heads_sm, w, MACO_QUEUE_TERMINATE);
 }
 
-__global__ void __launch_bounds__(kGemmThreads, 1) maco_persistent_kernel(const __grid_constant__ MacoProgram p) {
+template <int CG>
+__device__ __forceinline__ void persistent_body(const MacoProgram& p) {
   extern __shared__ uint8_t dyn_smem[];
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool is_worker = blockIdx.x < p.num_workers;
   GemmCtrl c;
   uint32_t tmem_base;
-  uint8_t* smem = gemm_cta_setup<kMkBN, kMkStages>(dyn_smem, c, tmem_base, is_worker);
+  uint8_t* smem;
+  if constexpr (CG == 2) smem = pair_cta_setup<kPairStages>(dyn_smem, c, tmem_base);
+  else smem = gemm_cta_setup<kMkBN, kMkStages>(dyn_smem, c, tmem_base, is_worker);
   uint32_t* extra = reinterpret_cast<uint32_t*>(smem + MkLayout::kRingBytes + MkLayout::kCtrlBytes);
   if (is_worker) {
     const uint32_t w = blockIdx.x;
@@ -518,18 +609,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) maco_persistent_kernel(const 
     __syncthreads();
     const uint32_t q_base = extra[16];
     if (warp == 0) {
-      if (lane == 0) producer_role(p, w, q_base, smem, c, attn_bars + 4);
+      if (lane == 0) {
+        if constexpr (CG == 2) producer_role_pair(p, w, q_base, smem, c);
+        else producer_role(p, w, q_base, smem, c, attn_bars + 4);
+      }
       __syncwarp();
     } else if (warp == 1) {
-      if (lane == 0) mma_role(p, w, q_base, smem, c, tmem_base, extra + 13);
+      if (lane == 0) {
+        if constexpr (CG == 2) { if (cluster_ctarank() == 0) mma_role_pair(p, w, q_base, smem, c, tmem_base); }
+        else mma_role(p, w, q_base, smem, c, tmem_base, extra + 13);
+      }
       __syncwarp();
     } else {
-      general_role(p, w, q_base, c, tmem_base, extra, reinterpret_cast<uint8_t*>(extra) + kMkExtraSmem, smem, bulk_bars, attn_bars);
+      general_role<CG>(p, w, q_base, c, tmem_base, extra, reinterpret_cast<uint8_t*>(extra) + kMkExtraSmem, smem, bulk_bars, attn_bars);
     }
   } else {
-    if (warp == 0) scheduler_role(p, extra);
+    if constexpr (CG == 1) { if (warp == 0) scheduler_role(p, extra); }
   }
-  gemm_cta_teardown<kMkBN>(c, tmem_base, nullptr, is_worker);
+  if constexpr (CG == 2) pair_cta_teardown(c, tmem_base, nullptr);
+  else gemm_cta_teardown<kMkBN>(c, tmem_base, nullptr, is_worker);
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1) maco_persistent_kernel(const __grid_constant__ MacoProgram p) {
+  persistent_body<1>(p);
+}
+
+// The same kernel for programs whose GEMM tasks are halves of two-CTA tiles: launched as clusters of two
+// CTAs (workers 2j and 2j+1), every tcgen05 instruction in its cta_group::2 form, static queues only.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+maco_persistent_pair_kernel(const __grid_constant__ MacoProgram p) {
+  persistent_body<2>(p);
 }
 
 __global__ void maco_grid_barrier_demo_kernel(uint32_t* counter, uint32_t* order, float* data, int n_per_cta,
@@ -565,6 +674,20 @@ int maco_abi_sizes(int* task, int* group, int* program, int* epilogue, int* trac
 
 int maco_persistent_smem_bytes() { return kMkSmemBytes; }
 
+// Number of two-CTA clusters of the persistent kernel that can be resident at once on the current device
+// (0 = unknown before the first launch; the launcher refuses programs that need more).
+int maco_persistent_max_pairs() {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * 74, 1, 1); cfg.blockDim = dim3(kGemmThreads, 1, 1); cfg.dynamicSmemBytes = kMkSmemBytes;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  if (cudaFuncSetAttribute(maco_persistent_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMkSmemBytes) != cudaSuccess) return -1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, maco_persistent_pair_kernel, &cfg) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+  return n;
+}
+
 // Encodes one operand tensor map into `out` (128 bytes, host memory).
 int maco_encode_operand_tmap(void* out, const void* base, int rows_or_k, int cols, long long ld_elems, int mn_major,
                              int box_rows) {
@@ -577,10 +700,21 @@ int maco_encode_operand_tmap(void* out, const void* base, int rows_or_k, int col
 int maco_program_launch(const MacoProgram* prog, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   static bool attr_set[64] = {};
+  static int max_pairs[64] = {};
   int dev = 0;
   MACO_CHECK_CUDA(cudaGetDevice(&dev));
   if (!attr_set[dev]) {
     MACO_CHECK_CUDA(cudaFuncSetAttribute(maco_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMkSmemBytes));
+    MACO_CHECK_CUDA(cudaFuncSetAttribute(maco_persistent_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMkSmemBytes));
+    // how many two-CTA clusters can be resident at once (every CTA of a program must be)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 74, 1, 1); cfg.blockDim = dim3(kGemmThreads, 1, 1); cfg.dynamicSmemBytes = kMkSmemBytes;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, maco_persistent_pair_kernel, &cfg) != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
+    max_pairs[dev] = n;
     attr_set[dev] = true;
   }
   MacoProgram p = *prog;
@@ -593,6 +727,19 @@ int maco_program_launch(const MacoProgram* prog, void* stream_) {
     return -1;
   }
   if (p.num_workers == 0 || p.num_workers > MACO_MAX_WORKERS) { maco_host::set_error("bad worker count"); return -1; }
+  if (p.cta_group == 2) {
+    if (p.mode != MACO_MODE_STATIC || (p.num_workers & 1u)) {
+      maco_host::set_error("two-CTA programs need static queues and an even number of workers");
+      return -1;
+    }
+    if ((int)p.num_workers / 2 > max_pairs[dev]) {
+      maco_host::set_error("two-CTA program: more CTA pairs than can be resident at once");
+      return -1;
+    }
+    maco_persistent_pair_kernel<<<grid, kGemmThreads, kMkSmemBytes, stream>>>(p);
+    MACO_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
   maco_persistent_kernel<<<grid, kGemmThreads, kMkSmemBytes, stream>>>(p);
   MACO_CHECK_CUDA(cudaGetLastError());
   return 0;

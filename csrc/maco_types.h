@@ -218,6 +218,8 @@ struct MacoProgram {
   uint32_t num_tasks, num_groups, num_workers, num_comm_workers;
   uint32_t static_stride, mode, epoch;
   int32_t rank, world;
+  uint32_t cta_group;             /* 1: one-CTA GEMM tiles; 2: every GEMM task is half of a two-CTA tile (cluster launch) */
+  uint32_t _pad;
 };
 
 #ifdef __cplusplus

@@ -196,9 +196,13 @@ def all_to_all_single(output: Optional[torch.Tensor], input: torch.Tensor,
     return _AsyncHandle(work, output) if async_op else output
 
 
-def all_to_all_4D(tensor: torch.Tensor, scatter_dim: int = 2, gather_dim: int = 1, async_op: bool = False, group=None):
+def all_to_all_4D(tensor: torch.Tensor, scatter_dim: int = 2, gather_dim: int = 1, async_op: bool = False, group=None,
+                  out: Optional[torch.Tensor] = None):
     """Ulysses layout switch. (scatter 2, gather 1): [B, S/P, H, D] -> [B, S, H/P, D];
-    (scatter 1, gather 2): [B, S, H/P, D] -> [B, S/P, H, D]. One exchange of a single buffer."""
+    (scatter 1, gather 2): [B, S, H/P, D] -> [B, S/P, H, D]. One exchange of a single buffer.
+    With the peer backend and a tensor in the symmetric heap the exchange runs inside this package's
+    kernel; the result is written into ``out`` (a heap tensor) when given, and is otherwise a fresh tensor
+    (a copy out of the kernel's receive buffer), so successive calls never alias."""
     if tensor.dim() != 4:
         raise ValueError(f"all_to_all_4D expects a 4-D tensor, got {tensor.dim()}-D")
     world = get_world_size()
@@ -207,8 +211,11 @@ def all_to_all_4D(tensor: torch.Tensor, scatter_dim: int = 2, gather_dim: int = 
     heap = _peer_backend_for(tensor) if group is None else None
     if heap is not None and tensor.dtype in (torch.bfloat16, torch.float16, torch.float32):
         from ..parallel import collectives
-        out = collectives.all_to_all_4d(tensor, scatter_dim, gather_dim)
-        return _AsyncHandle(tensor=out) if async_op else out
+        if out is not None:
+            res = collectives.all_to_all_4d(tensor, scatter_dim, gather_dim, out=out)
+        else:
+            res = collectives.all_to_all_4d(tensor, scatter_dim, gather_dim).clone()
+        return _AsyncHandle(tensor=res) if async_op else res
     P = world
     if (scatter_dim, gather_dim) == (2, 1):
         B, s, H, D = tensor.shape

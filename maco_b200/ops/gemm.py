@@ -48,6 +48,7 @@ def gemm(
     max_ctas: int = 0,
     wait_budget_ms: float = 0.0,
     stream: Optional[torch.cuda.Stream] = None,
+    cta_pair: Optional[bool] = None,
 ) -> torch.Tensor:
     """``out = epilogue(alpha * A' @ B'^T)`` with ``A' = a.T if trans_a else a`` (shape [M, K]) and
     ``B' = b.T if trans_b else b`` (shape [N, K]).
@@ -55,6 +56,8 @@ def gemm(
     ``trans_*`` describe how the operand is *stored*: ``trans_a`` means ``a`` is [K, M] row-major,
     ``trans_b`` means ``b`` is [K, N] row-major (the plain ``a @ b`` case). No copy is made for
     either layout: the MMA reads MN-major operands directly from shared memory.
+    ``cta_pair``: True runs two-CTA tiles (``tcgen05.mma.cta_group::2``, 256 x bn per CTA pair), False one-CTA
+    tiles (128 x bn), None lets the launcher choose (pairs once the tiles cover every SM pair).
     """
     if not a.is_cuda:
         raise ValueError("maco_b200.ops.gemm needs CUDA tensors")
@@ -94,6 +97,7 @@ def gemm(
             a.data_ptr(), b.data_ptr(), out.data_ptr(), M, Nn, K, a.stride(0), b.stride(0), out.stride(0),
             int(trans_a), int(trans_b), N.DTYPE_CODE[a.dtype], N.DTYPE_CODE[out.dtype], mode, N.ptr(bias), bias_t,
             N.ptr(aux), ld_aux, aux_t, float(alpha), bn, max_ctas, float(wait_budget_ms), st,
+            0 if cta_pair is None else (2 if cta_pair else 1),
         )
         if rc == 0:
             return out

@@ -624,8 +624,9 @@ class Program:
         # events live in the symmetric heap when peers must reach them
         self.num_events = max(1, b.num_events)
         if b.heap is not None:
-            # Not cleared here: heap memory is zero from creation and never recycled for events, and a
-            # peer that built this program earlier may already have bumped these counters.
+            # Not cleared here: heap memory is zero from creation, a freed range is zeroed before it can be
+            # handed out again (SymmetricHeap.free), and a peer that built this program earlier may already
+            # have bumped these counters.
             self.d_events = b.heap.alloc((self.num_events + 64,), torch.int32)
         else:
             self.d_events = torch.zeros(self.num_events + 64, dtype=torch.int32, device=dev)
@@ -706,6 +707,14 @@ class Program:
         self._ps.epoch = self.epoch
         rc = self._lib.maco_program_launch(ctypes.byref(self._ps), N.current_stream_ptr(stream))
         N.check(rc, "maco_program_launch")
+
+    def free_heap(self) -> None:
+        """Gives the program's event counters back to the symmetric heap. The program must not run again.
+        Collective: see ``SymmetricHeap.free``."""
+        if self.heap is not None and self.d_events is not None and hasattr(self.heap, "free"):
+            self.heap.free(self.d_events)
+        self.d_events = None
+        self.num_tasks = 0
 
     def reset_after_failure(self) -> None:
         """Re-zeroes the control state after an aborted launch (events restart from epoch 0)."""

@@ -19,6 +19,55 @@ _current: Optional["SymmetricHeap"] = None
 _ALIGN = 1024
 
 
+class RangeAllocator:
+    """Offsets inside a fixed range: first fit over a sorted, coalesced free list, bump allocation behind it.
+    Deterministic, so ranks that issue the same calls get the same offsets. Pure Python (CPU-testable)."""
+
+    def __init__(self, nbytes: int, align: int = _ALIGN):
+        self.nbytes, self.align = int(nbytes), int(align)
+        self.cursor = 0
+        self.holes: List[tuple] = []        # sorted (start, size)
+        self.live = {}                      # start -> size
+
+    def alloc(self, nbytes: int) -> int:
+        need = max(self.align, (int(nbytes) + self.align - 1) // self.align * self.align)
+        for i, (fs, fsz) in enumerate(self.holes):
+            if fsz >= need:
+                if fsz == need:
+                    self.holes.pop(i)
+                else:
+                    self.holes[i] = (fs + need, fsz - need)
+                self.live[fs] = need
+                return fs
+        start = self.cursor
+        if start + need > self.nbytes:
+            raise MemoryError(f"symmetric heap exhausted: need {nbytes} bytes at {start}, heap has {self.nbytes}. "
+                              "Raise maco_b200.config.comm_buffer_size")
+        self.cursor = start + need
+        self.live[start] = need
+        return start
+
+    def free(self, start: int) -> tuple:
+        size = self.live.pop(start, None)
+        if size is None:
+            raise ValueError("free(): not the start of a live allocation")
+        holes = sorted(self.holes + [(start, size)])
+        merged: List[tuple] = []
+        for fs, fsz in holes:
+            if merged and merged[-1][0] + merged[-1][1] == fs:
+                merged[-1] = (merged[-1][0], merged[-1][1] + fsz)
+            else:
+                merged.append((fs, fsz))
+        if merged and merged[-1][0] + merged[-1][1] == self.cursor:       # the top hole rejoins the bump region
+            self.cursor = merged.pop()[0]
+        self.holes = merged
+        return start, size
+
+    @property
+    def free_bytes(self) -> int:
+        return self.nbytes - self.cursor + sum(sz for _, sz in self.holes)
+
+
 class _Span:
     """Exposes a raw device range through the CUDA array interface so torch can view it."""
 
@@ -58,39 +107,37 @@ class SymmetricHeap:
                 pb = P()
                 N.check(lib.maco_heap_open(h, ctypes.byref(pb)), f"maco_heap_open(rank {r})")
                 self._peer.append(pb.value)
-        self._cursor = 0
+        self._ranges = RangeAllocator(self.nbytes)
         self._whole = torch.as_tensor(_Span(self._base, self.nbytes, self), device=self.device)
         self._closed = False
         exchange(b"ready")          # nobody touches a peer's heap before every rank has mapped it
 
     # ------------------------------------------------------------------ allocation
     def alloc(self, shape, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
-        """Bump allocation; every rank must allocate the same sequence of sizes."""
+        """First fit in the free list, else bump allocation. Every rank must run the same sequence of
+        ``alloc`` / ``free`` calls with the same sizes, so a buffer has the same offset everywhere."""
         shape = tuple(int(s) for s in (shape if isinstance(shape, (tuple, list, torch.Size)) else (shape,)))
         numel = 1
         for s in shape:
             numel *= s
         nbytes = numel * torch.empty((), dtype=dtype).element_size()
-        start = (self._cursor + _ALIGN - 1) // _ALIGN * _ALIGN
-        if start + nbytes > self.nbytes:
-            raise MemoryError(f"symmetric heap exhausted: need {nbytes} bytes at {start}, heap has {self.nbytes}. "
-                              "Raise maco_b200.config.comm_buffer_size")
-        self._cursor = start + nbytes
+        start = self._ranges.alloc(nbytes)
         t = self._whole[start:start + nbytes].view(dtype).view(shape)
         if zero:
             t.zero_()
         return t
 
-    def mark(self) -> int:
-        return self._cursor
-
-    def release_to(self, mark: int) -> None:
-        """Frees everything allocated after ``mark`` (stack discipline, same on every rank)."""
-        self._cursor = mark
+    def free(self, t: torch.Tensor) -> None:
+        """Returns a buffer obtained from ``alloc`` to the heap and ZEROES it (event counters allocated later
+        from this range must start at zero). Collective in effect: every rank frees the same buffers in the
+        same order, after a device synchronisation and a host barrier (no kernel on any rank may still touch
+        the range); the callers in ``parallel.collectives`` do both."""
+        start, size = self._ranges.free(self.offset_of(t))
+        self._whole[start:start + size].zero_()
 
     @property
     def free_bytes(self) -> int:
-        return self.nbytes - self._cursor
+        return self._ranges.free_bytes
 
     # ------------------------------------------------------------------ addressing
     def owns(self, t: torch.Tensor) -> bool:
@@ -140,13 +187,13 @@ class LocalHeap:
         self.nbytes = (int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN
         self._whole = torch.zeros(self.nbytes, dtype=torch.uint8, device=self.device)
         self._base = self._whole.data_ptr()
-        self._cursor = 0
+        self._ranges = RangeAllocator(self.nbytes)
 
     alloc = SymmetricHeap.alloc
+    free = SymmetricHeap.free
+    free_bytes = SymmetricHeap.free_bytes
     owns = SymmetricHeap.owns
     offset_of = SymmetricHeap.offset_of
-    mark = SymmetricHeap.mark
-    release_to = SymmetricHeap.release_to
 
     def peer_base(self, r: int) -> int:
         return self._base

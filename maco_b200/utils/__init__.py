@@ -1,4 +1,5 @@
-"""Helpers around the core: the CPU model of the scheduling protocol and the input prefetcher."""
-from .prefetch import InputPrefetcher
+"""Helpers around the core: the CPU model of the scheduling protocol, the input prefetcher and the
+pipelined end-to-end step loop."""
+from .prefetch import InputPrefetcher, StepPipeline
 
-__all__ = ["InputPrefetcher"]
+__all__ = ["InputPrefetcher", "StepPipeline"]

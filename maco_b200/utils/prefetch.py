@@ -58,3 +58,55 @@ class InputPrefetcher:
             self._free[i].record(cur)
         self._used[i] = True
         return dst
+
+
+class StepPipeline:
+    """End-to-end step loop with the host one step behind the device.
+
+    ``step(host_input, launch, result)`` does, in stream order: deliver this step's input (its host -> device
+    copy was started during the previous step), ``launch()`` the layer, start the copy of the NEXT input,
+    copy ``result()`` (a small device tensor) into pinned host memory, and only then wait for the PREVIOUS
+    step's result. The host therefore never idles the GPU between steps: the launch of step i+1 is queued
+    while step i runs, and the device -> host read of step i completes under step i+1.
+    ``drain()`` returns the result of the last step. Every step's input crosses PCIe and every step's result
+    is read on the host, each exactly once.
+
+    The reference blocks on the stream after every step (maco/overlap/manager.py:207-208 synchronises both
+    events before returning); this keeps the same data movement and removes the bubble.
+    """
+
+    def __init__(self, input_buffer: torch.Tensor, result_like: torch.Tensor, depth: int = 2):
+        self.feed = InputPrefetcher(input_buffer, depth=depth)
+        self.input_buffer = input_buffer
+        self._host = [torch.empty(result_like.shape, dtype=result_like.dtype).pin_memory() for _ in range(depth)]
+        self._done = [torch.cuda.Event() for _ in range(depth)]
+        self._step = 0
+        self._pending: Deque[int] = deque()
+
+    def step(self, host_input: torch.Tensor, launch, result, next_host_input: Optional[torch.Tensor] = None):
+        """Runs one step; returns the host copy of the previous step's result (None on the first step)."""
+        if not self.feed.pending:
+            self.feed.submit(host_input)
+        self.feed.deliver(self.input_buffer)
+        launch()
+        self.feed.submit(next_host_input if next_host_input is not None else host_input)
+        slot = self._step % len(self._host)
+        self._host[slot].copy_(result(), non_blocking=True)
+        self._done[slot].record()
+        self._pending.append(slot)
+        self._step += 1
+        if len(self._pending) >= len(self._host):
+            return self._pop()
+        return None
+
+    def _pop(self) -> torch.Tensor:
+        slot = self._pending.popleft()
+        self._done[slot].synchronize()
+        return self._host[slot]
+
+    def drain(self) -> Optional[torch.Tensor]:
+        """Waits for every outstanding result; returns the newest."""
+        out = None
+        while self._pending:
+            out = self._pop()
+        return out

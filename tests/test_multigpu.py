@@ -1,4 +1,5 @@
-"""Peer-memory collectives and the fused tensor-parallel layer on 2 GPUs (one process per GPU)."""
+"""Peer-memory collectives and the fused multi-GPU layers, one process per GPU, on every world size in
+{2, 4, 8} that the machine has GPUs for."""
 import pytest
 import torch
 
@@ -7,6 +8,9 @@ from tests._dist import run_ranks
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 ENV = {"NCCL_NVLS_ENABLE": "0"}
+_NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
+worlds = pytest.mark.parametrize("world", [pytest.param(w, marks=pytest.mark.skipif(_NGPU < w, reason=f"needs {w} GPUs"))
+                                           for w in (2, 4, 8)])
 
 
 def _setup(rank, world, heap_mb=256):
@@ -67,6 +71,25 @@ def _collectives(rank, world):
     z = collectives.all_to_all_4d(y, 1, 2)
     torch.cuda.synchronize()
     assert torch.equal(z, mine)
+    # q, k, v back to back through the public call: three results, none overwritten by a later exchange
+    qkv = [heap.alloc((B, s, H, D), torch.float32) for _ in range(3)]
+    for i, t_ in enumerate(qkv):
+        t_.copy_(whole[:, rank * s:(rank + 1) * s] * (i + 1))
+    outs = [patterns.all_to_all_4D(t_, 2, 1) for t_ in qkv]
+    torch.cuda.synchronize()
+    for i, o_ in enumerate(outs):
+        assert torch.equal(o_, whole[:, :, rank * hp:(rank + 1) * hp] * (i + 1)), i
+    # the same input three times through the low-level call: a result survives the next call on that input
+    r1 = collectives.all_to_all_4d(qkv[0], 2, 1)
+    qkv[0].mul_(2)
+    r2 = collectives.all_to_all_4d(qkv[0], 2, 1)
+    torch.cuda.synchronize()
+    assert torch.equal(r1, whole[:, :, rank * hp:(rank + 1) * hp]) and torch.equal(r2, 2 * whole[:, :, rank * hp:(rank + 1) * hp])
+    # caller-provided destination
+    dest = heap.alloc((B, s * world, hp, D), torch.float32)
+    assert collectives.all_to_all_4d(qkv[1], 2, 1, out=dest) is dest
+    torch.cuda.synchronize()
+    assert torch.equal(dest, 2 * whole[:, :, rank * hp:(rank + 1) * hp])
     # broadcast from rank 1, repeated (the receive counter only grows)
     bt = heap.alloc((3 << 18,), torch.float32)
     for it in range(2):
@@ -119,8 +142,9 @@ def _collectives(rank, world):
     maco.cleanup()
 
 
-def test_peer_collectives():
-    run_ranks(_collectives, 2, env=ENV, timeout=100)
+@worlds
+def test_peer_collectives(world):
+    run_ranks(_collectives, world, env=ENV, timeout=150)
 
 
 def _tp_mlp(rank, world):
@@ -145,8 +169,9 @@ def _tp_mlp(rank, world):
     maco.cleanup()
 
 
-def test_fused_tp_mlp_matches_reference():
-    run_ranks(_tp_mlp, 2, env=ENV, timeout=100)
+@worlds
+def test_fused_tp_mlp_matches_reference(world):
+    run_ranks(_tp_mlp, world, env=ENV, timeout=150)
 
 
 def _dp_backward(rank, world):
@@ -169,8 +194,9 @@ def _dp_backward(rank, world):
     maco.cleanup()
 
 
-def test_dp_backward_with_tilewise_allreduce():
-    run_ranks(_dp_backward, 2, env=ENV, timeout=100)
+@worlds
+def test_dp_backward_with_tilewise_allreduce(world):
+    run_ranks(_dp_backward, world, env=ENV, timeout=150)
 
 
 def _qwen3(rank, world):
@@ -178,7 +204,7 @@ def _qwen3(rank, world):
     import torch.distributed as dist
     from maco_b200 import _native
     from maco_b200.models.qwen3_layer import Qwen3DecodeLayer
-    layer = Qwen3DecodeLayer(hidden=1024, q_heads=16, kv_heads=2, ffn=2048, batch=8, kv_len=300, rank=rank, world=world,
+    layer = Qwen3DecodeLayer(hidden=1024, q_heads=8 * max(2, world), kv_heads=max(2, world), ffn=2048, batch=8, kv_len=300, rank=rank, world=world,
                              heap=heap, seed=4, weight_std=0.05)
     torch.manual_seed(11)
     x = torch.randn(8, 1024, device="cuda", dtype=torch.bfloat16)        # replicated input
@@ -198,8 +224,9 @@ def _qwen3(rank, world):
     maco.cleanup()
 
 
-def test_qwen3_decode_layer_tensor_parallel():
-    run_ranks(_qwen3, 2, env=ENV, timeout=100)
+@worlds
+def test_qwen3_decode_layer_tensor_parallel(world):
+    run_ranks(_qwen3, world, env=ENV, timeout=150)
 
 
 def _moe(rank, world):
@@ -221,8 +248,9 @@ def _moe(rank, world):
     maco.cleanup()
 
 
-def test_moe_expert_parallel_dispatch_combine():
-    run_ranks(_moe, 2, env=ENV, timeout=100)
+@worlds
+def test_moe_expert_parallel_dispatch_combine(world):
+    run_ranks(_moe, world, env=ENV, timeout=150)
 
 
 def _peer_loss(rank, world):

@@ -31,6 +31,48 @@ def test_gemm_tcgen05_all_majors(dtype, shape, bn):
     assert _native.status() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (200, 328, 136), (1024, 512, 2048), (384, 1280, 512), (2304, 768, 320)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_two_cta_tiles_all_majors(dtype, shape, bn):
+    """Two-CTA tiles (tcgen05.mma.cta_group::2): every operand major, ragged edges, an odd number of row blocks
+    (the pair's second CTA then works on rows past the end and stores nothing)."""
+    ops = _ops()
+    M, N, K = shape
+    a = torch.randn(M, K, device="cuda", dtype=dtype)
+    b = torch.randn(N, K, device="cuda", dtype=dtype) * 0.1
+    ref = a.float() @ b.float().t()
+    scale = ref.abs().max().item()
+    for ta, tb in [(False, False), (False, True), (True, False), (True, True)]:
+        aa = a.t().contiguous() if ta else a
+        bb = b.t().contiguous() if tb else b
+        out = ops.gemm(aa, bb, trans_a=ta, trans_b=tb, bn=bn, cta_pair=True)
+        assert (out.float() - ref).abs().max().item() <= 1e-2 * scale, (ta, tb)
+    from maco_b200 import _native
+    assert _native.status() == 0
+
+
+def test_gemm_two_cta_tiles_swiglu_and_large():
+    ops = _ops()
+    dt = torch.bfloat16
+    F = torch.nn.functional
+    a = torch.randn(2048, 1024, device="cuda", dtype=dt)
+    wg = torch.randn(1536, 1024, device="cuda", dtype=dt) * 0.05
+    wu = torch.randn(1536, 1024, device="cuda", dtype=dt) * 0.05
+    fused = ops.interleave_gate_up(wg, wu)
+    ref = F.silu(a.float() @ wg.float().t()) * (a.float() @ wu.float().t())
+    assert_close(ops.gemm(a, fused, epilogue="swiglu", cta_pair=True), ref, dt)
+    # more tiles than CTA pairs: every pair walks several tiles (accumulator double buffer, ring wrap-around)
+    a = torch.randn(4096, 512, device="cuda", dtype=dt)
+    b = torch.randn(4096, 512, device="cuda", dtype=dt) * 0.05
+    one = ops.gemm(a, b, cta_pair=False)
+    two = ops.gemm(a, b, cta_pair=True)
+    assert_close(two, a.float() @ b.float().t(), dt)
+    assert torch.equal(one, two)          # same products, same accumulation order per output element
+    from maco_b200 import _native
+    assert _native.status() == 0
+
+
 def test_gemm_epilogues():
     ops = _ops()
     M, N, K = 512, 1024, 512

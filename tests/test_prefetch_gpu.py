@@ -20,3 +20,21 @@ def test_prefetcher_delivers_in_order():
     assert feed.pending == 0
     with pytest.raises(RuntimeError):
         feed.deliver(dst)
+
+
+def test_step_pipeline_results_lag_one_step():
+    from maco_b200.utils import StepPipeline
+    inp = torch.zeros(64, 32, device="cuda")
+    out = torch.zeros(2, device="cuda")
+    pipe = StepPipeline(inp, out)
+    hosts = [torch.full((64, 32), float(i)).pin_memory() for i in range(5)]
+    got = []
+    for i in range(5):
+        nxt = hosts[i + 1] if i + 1 < 5 else None
+        r = pipe.step(hosts[i], lambda: out.copy_(inp[0, :2] * 2), lambda: out, next_host_input=nxt)
+        got.append(None if r is None else r.clone())
+    last = pipe.drain()
+    assert got[0] is None
+    for i in range(1, 5):
+        assert torch.all(got[i] == 2.0 * (i - 1)), (i, got[i])
+    assert torch.all(last == 8.0)
