@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Small, self-ending single-GPU cases of the hot kernels, for profiler captures and quick timing.
 
-    python benchmarks/kernel_case.py gemm        # stand-alone tcgen05 GEMM, 8192 x 4096 x 4096 bf16
+    python benchmarks/kernel_case.py gemm        # stand-alone tcgen05 GEMM, 8192 x 4096 x 4096 bf16, one-CTA tiles
+    python benchmarks/kernel_case.py gemm_pair   # the same GEMM on two-CTA tiles (cta_group::2, clusters of two)
     python benchmarks/kernel_case.py mlp         # persistent kernel: fused SwiGLU MLP, 4096 tokens, 4096 -> 14336/4
     python benchmarks/kernel_case.py attention   # split-KV decode attention, batch 32, 4096 keys
     python benchmarks/kernel_case.py attention_tc  # persistent kernel: tensor-core decode attention, 512 tasks, 537 MB of KV
@@ -38,13 +39,13 @@ def timed(fn, iters=3, warm=2):
 def main():
     case = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     dt = torch.bfloat16
-    if case == "gemm":
+    if case in ("gemm", "gemm_pair"):
         M, N, K = 8192, 4096, 4096
         a = torch.randn(M, K, device="cuda", dtype=dt)
         b = torch.randn(N, K, device="cuda", dtype=dt) * 0.02
         out = torch.empty(M, N, device="cuda", dtype=dt)
-        us = timed(lambda: ops.gemm(a, b, out=out, bn=256))
-        print(f"gemm {M}x{N}x{K}: {us:.1f} us, {2 * M * N * K / us / 1e6:.0f} TFLOP/s")
+        us = timed(lambda: ops.gemm(a, b, out=out, bn=256, cta_pair=(case == "gemm_pair")))
+        print(f"{case} {M}x{N}x{K}: {us:.1f} us, {2 * M * N * K / us / 1e6:.0f} TFLOP/s")
     elif case == "mlp":
         from maco_b200.models.tp_mlp import TPSwiGLUMLP
         layer = TPSwiGLUMLP(4096, 4096, 3584)

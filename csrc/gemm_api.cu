@@ -12,6 +12,9 @@ using namespace maco;
 
 namespace {
 
+// Optional per-CTA cycle counters of the stand-alone GEMM kernels (8 x int64 per CTA), off unless set.
+long long* g_gemm_dbg = nullptr;
+
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmEpilogue& epi, int K, uint32_t idesc,
                 int max_ctas, uint64_t budget_ns, cudaStream_t stream) {
@@ -31,7 +34,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmEpilog
   if (grid > sms) grid = sms;
   if (grid <= 0) return 0;
   uint32_t* status = maco_host::status_device_ptr();
-  kern<<<grid, kGemmThreads, L::kTotalBytes, stream>>>(tmA, tmB, epi, K, idesc, budget_ns, status);
+  kern<<<grid, kGemmThreads, L::kTotalBytes, stream>>>(tmA, tmB, epi, K, idesc, budget_ns, status, g_gemm_dbg);
   MACO_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -65,7 +68,7 @@ int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmE
   if (pairs > sms / 2) pairs = sms / 2;
   if (pairs <= 0) return 0;
   uint32_t* status = maco_host::status_device_ptr();
-  kern<<<2 * pairs, kGemmThreads, L::kTotalBytes, stream>>>(tmA, tmB, epi, K, idesc, budget_ns, status);
+  kern<<<2 * pairs, kGemmThreads, L::kTotalBytes, stream>>>(tmA, tmB, epi, K, idesc, budget_ns, status, g_gemm_dbg);
   MACO_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -142,6 +145,13 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, long long sam
 }  // namespace
 
 extern "C" {
+
+// Cycle counters of the stand-alone GEMM kernels: `buf` (device memory, 8 x int64 per CTA, or null to switch
+// them off) receives per CTA [0] producer cycles waiting for a free stage, [1] MMA warp waiting for a free
+// accumulator, [2] MMA warp waiting for operands, [3] MMA warp total, [4] producer total. Word [7] of the buffer
+// is read as experiment switches (results are then meaningless): 1 = epilogue does the barrier handshake only,
+// 2 = the MMA warp does not wait for operands, 4 = no operand loads (use with 2).
+void maco_gemm_set_debug(long long* buf) { g_gemm_dbg = buf; }
 
 // Returns 0 on success; -2 means "operands are not TMA-addressable, use maco_gemm_simt".
 int maco_gemm(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,

@@ -87,15 +87,19 @@ MACO_DEVICE void gemm_tile_coords(int tile, int m_tiles, int n_tiles, int& m_blk
 template <int BN, int STAGES, bool A_MN, bool B_MN, int SBN = BN>
 MACO_DEVICE bool gemm_produce_tile(uint8_t* smem, const GemmCtrl& c, const CUtensorMap* tmA,
                                    const CUtensorMap* tmB, int m0, int n0, int k0, int k_blocks,
-                                   uint32_t& it, uint64_t budget_ns) {
+                                   uint32_t& it, uint64_t budget_ns, long long* prof = nullptr) {
   using L = GemmSmemLayout<BN, STAGES, SBN>;
-  for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-    if (!mbar_wait(&c.empty[s], ph ^ 1, budget_ns, c.abort_word)) return false;
-    uint8_t* sa = smem + s * L::kStageBytes;
+  // stage index and phase advance incrementally: the loop is one thread's instruction stream, and a division
+  // per k-block is a measurable part of it
+  uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+  uint8_t* sa = smem + s * L::kStageBytes;
+  int k = k0;
+  for (int kb = 0; kb < k_blocks; ++kb, k += kBK) {
+    const long long t0 = prof ? clock64() : 0;
+    if (!mbar_wait(&c.empty[s], ph ^ 1, budget_ns, c.abort_word)) { it += kb; return false; }
+    if (prof) prof[0] += clock64() - t0;
     uint8_t* sb = sa + L::kABytes;
     mbar_arrive_expect_tx(&c.full[s], L::kLoadBytes);
-    const int k = k0 + kb * kBK;
     if constexpr (!A_MN) {
       tma_load_2d(sa, tmA, &c.full[s], k, m0);
     } else {
@@ -108,7 +112,9 @@ MACO_DEVICE bool gemm_produce_tile(uint8_t* smem, const GemmCtrl& c, const CUten
 #pragma unroll
       for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, tmB, &c.full[s], n0 + j * 64, k);
     }
+    if (++s == STAGES) { s = 0; ph ^= 1; sa = smem; } else { sa += L::kStageBytes; }
   }
+  it += k_blocks;
   return true;
 }
 
@@ -128,31 +134,43 @@ MACO_DEVICE void gemm_drain_loads(const GemmCtrl& c, uint32_t issued) {
 // ---- MMA issuer ----------------------------------------------------------------------------
 template <int BN, int STAGES, bool A_MN, bool B_MN, int SBN = BN>
 MACO_DEVICE bool gemm_mma_tile(uint8_t* smem, const GemmCtrl& c, uint32_t tmem_base, uint32_t idesc,
-                               int k_blocks, uint32_t& it, uint32_t tile_seq, uint64_t budget_ns) {
+                               int k_blocks, uint32_t& it, uint32_t tile_seq, uint64_t budget_ns,
+                               long long* prof = nullptr) {
   using L = GemmSmemLayout<BN, STAGES, SBN>;
   const uint32_t acc = tile_seq & 1, acc_ph = (tile_seq >> 1) & 1;
+  long long t0 = prof ? clock64() : 0;
   if (!mbar_wait(&c.tmem_empty[acc], acc_ph ^ 1, budget_ns, c.abort_word)) return false;
+  if (prof) prof[1] += clock64() - t0;
   tc_fence_after();
   const uint32_t d_tmem = tmem_base + acc * SBN;
-  for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-    if (!mbar_wait(&c.full[s], ph, budget_ns, c.abort_word)) return false;
-    tc_fence_after();
-    const uint32_t a_base = smem_u32(smem + s * L::kStageBytes);
-    const uint32_t b_base = a_base + L::kABytes;
+  // K-major: 8-row groups are 1024 B apart (SBO); a K step of 16 elements is 32 B inside the swizzled row.
+  // MN-major: 64-row panels are 8192 B apart (LBO), 8-k groups 1024 B apart (SBO); a K step of 16 is two groups
+  // = 2048 B. The descriptors' high words are constant; the low word is the start address in 16-byte units.
+  const uint64_t da0 = A_MN ? make_smem_desc(0, 8192, 1024, 2) : make_smem_desc(0, 16, 1024, 2);
+  const uint64_t db0 = B_MN ? make_smem_desc(0, 8192, 1024, 2) : make_smem_desc(0, 16, 1024, 2);
+  const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+  const uint32_t a_lbo = (uint32_t)da0, b_lbo = (uint32_t)db0;          // leading-dimension offset field (bits 16-29)
+  constexpr uint32_t kStepA = (A_MN ? 2048 : 32) >> 4, kStepB = (B_MN ? 2048 : 32) >> 4;
+  constexpr uint32_t kStage16 = L::kStageBytes >> 4, kAB16 = L::kABytes >> 4;
+  const uint32_t base_lo = (smem_u32(smem) & 0x3FFFFu) >> 4;
+  uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+  uint32_t a_lo = base_lo + s * kStage16;
+  uint32_t accum = 0;
+  for (int kb = 0; kb < k_blocks; ++kb) {
+    if (prof) t0 = clock64();
+    if (!(prof && (prof[3] & 2)) && !mbar_wait(&c.full[s], ph, budget_ns, c.abort_word)) { it += kb; return false; }
+    if (prof) prof[2] += clock64() - t0;
+    const uint32_t b_lo = a_lo + kAB16;
 #pragma unroll
     for (int k = 0; k < kBK / kUmmaK; ++k) {
-      // K-major: 8-row groups are 1024 B apart (SBO); a K step of 16 elements is 32 B inside
-      // the swizzled row. MN-major: 64-row panels are 8192 B apart (LBO), 8-k groups 1024 B
-      // apart (SBO); a K step of 16 is two groups = 2048 B.
-      const uint64_t adesc = A_MN ? make_smem_desc(a_base + k * 2048, 8192, 1024, 2)
-                                  : make_smem_desc(a_base + k * 32, 16, 1024, 2);
-      const uint64_t bdesc = B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024, 2)
-                                  : make_smem_desc(b_base + k * 32, 16, 1024, 2);
-      tc_mma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+      // low descriptor words: start address (bits 0-13, never carries: shared memory is below 256 KB) | leading offset
+      tc_mma_f16_lo(d_tmem, (a_lo + k * kStepA) | a_lbo, a_hi, (b_lo + k * kStepB) | b_lbo, b_hi, idesc, accum);
+      accum = 1;
     }
     tc_commit(&c.empty[s]);          // frees the smem stage once these MMAs have read it
+    if (++s == STAGES) { s = 0; ph ^= 1; a_lo = base_lo; } else { a_lo += kStage16; }
   }
+  it += k_blocks;
   tc_commit(&c.tmem_full[acc]);      // accumulator complete -> epilogue
   return true;
 }
@@ -476,24 +494,29 @@ MACO_DEVICE GemmCtrl pair_ctrl(uint8_t* smem_base) {
 }
 
 // Producer of one CTA of the pair. `n0` is the tile's first column; this CTA loads B rows
-// [n0 + rank * BN/2, n0 + (rank + 1) * BN/2). All bytes of both CTAs are credited to the LEADER's full barrier.
+// [n0 + rank * BN/2, n0 + (rank + 1) * BN/2). All bytes of both CTAs are credited to the LEADER's full barrier
+// by the TMA units themselves. (Measured alternative: loads completing on each CTA's own barrier plus a thread
+// of the second CTA that forwards an arrival to the leader took twice as long per k-block.)
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 MACO_DEVICE bool pair_produce_tile(uint8_t* smem, const GemmCtrl& c, uint32_t rank, const CUtensorMap* tmA,
                                    const CUtensorMap* tmB, int m0, int n0, int k0, int k_blocks, uint32_t& it,
-                                   uint64_t budget_ns) {
+                                   uint64_t budget_ns, long long* prof = nullptr) {
   using L = PairSmemLayout<STAGES>;
   constexpr int kBHalf = BN / 2;
   constexpr uint32_t kPairBytes = 2u * (L::kABytes + kBHalf * kBK * 2);
   const uint32_t full0 = mapa_u32(smem_u32(&c.full[0]), 0);
   const int nb0 = n0 + (int)rank * kBHalf;
-  for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-    if (!mbar_wait(&c.empty[s], ph ^ 1, budget_ns, c.abort_word)) return false;
-    uint8_t* sa = smem + s * L::kStageBytes;
+  uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+  uint8_t* sa = smem + s * L::kStageBytes;
+  int k = k0;
+  for (int kb = 0; kb < k_blocks; ++kb, k += kBK) {
+    const long long t0 = prof ? clock64() : 0;
+    if (!mbar_wait(&c.empty[s], ph ^ 1, budget_ns, c.abort_word)) { it += kb; return false; }
+    if (prof) prof[0] += clock64() - t0;
+    if (prof && prof[4] && prof[5] < 512) reinterpret_cast<uint64_t*>(prof[4])[2 * prof[5]] = globaltimer_ns();
     uint8_t* sb = sa + L::kABytes;
     if (rank == 0) mbar_arrive_expect_tx(&c.full[s], kPairBytes);
     const uint32_t bar = full0 + s * 8;
-    const int k = k0 + kb * kBK;
     if constexpr (!A_MN) {
       tma_load_2d_pair(sa, tmA, bar, k, m0);
     } else {
@@ -506,40 +529,52 @@ MACO_DEVICE bool pair_produce_tile(uint8_t* smem, const GemmCtrl& c, uint32_t ra
 #pragma unroll
       for (int j = 0; j < kBHalf / 64; ++j) tma_load_2d_pair(sb + j * 8192, tmB, bar, nb0 + j * 64, k);
     }
+    if (prof && prof[4] && prof[5] < 512) { reinterpret_cast<uint64_t*>(prof[4])[2 * prof[5] + 1] = globaltimer_ns(); ++prof[5]; }
+    if (++s == STAGES) { s = 0; ph ^= 1; sa = smem; } else { sa += L::kStageBytes; }
   }
+  it += k_blocks;
   return true;
 }
 
 // MMA issuer: the pair's leader only. `peer_*` are the shared::cluster addresses of the other CTA's barriers.
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 MACO_DEVICE bool pair_mma_tile(uint8_t* smem, const GemmCtrl& c, uint32_t tmem_base, uint32_t idesc, int k_blocks,
-                               uint32_t& it, uint32_t tile_seq, uint64_t budget_ns) {
+                               uint32_t& it, uint32_t tile_seq, uint64_t budget_ns, long long* prof = nullptr) {
   using L = PairSmemLayout<STAGES>;
   const uint32_t acc = tile_seq & 1, acc_ph = (tile_seq >> 1) & 1;
-  const uint32_t empty_l = smem_u32(&c.empty[0]), empty_p = mapa_u32(empty_l, 1);
-  const uint32_t tfull_l = smem_u32(&c.tmem_full[0]), tfull_p = mapa_u32(tfull_l, 1);
+  const uint32_t empty0 = smem_u32(&c.empty[0]), tfull0 = smem_u32(&c.tmem_full[0]);
+  long long t0 = prof ? clock64() : 0;
   if (!mbar_wait(&c.tmem_empty[acc], acc_ph ^ 1, budget_ns, c.abort_word)) return false;
+  if (prof) prof[1] += clock64() - t0;
   tc_fence_after();
   const uint32_t d_tmem = tmem_base + acc * 256;
-  for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-    if (!mbar_wait(&c.full[s], ph, budget_ns, c.abort_word)) return false;
-    tc_fence_after();
-    const uint32_t a_base = smem_u32(smem + s * L::kStageBytes);
-    const uint32_t b_base = a_base + L::kABytes;
+  const uint64_t da0 = A_MN ? make_smem_desc(0, 8192, 1024, 2) : make_smem_desc(0, 16, 1024, 2);
+  const uint64_t db0 = B_MN ? make_smem_desc(0, 8192, 1024, 2) : make_smem_desc(0, 16, 1024, 2);
+  const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+  const uint32_t a_lbo = (uint32_t)da0, b_lbo = (uint32_t)db0;          // leading-dimension offset field (bits 16-29)
+  constexpr uint32_t kStepA = (A_MN ? 2048 : 32) >> 4, kStepB = (B_MN ? 2048 : 32) >> 4;
+  constexpr uint32_t kStage16 = L::kStageBytes >> 4, kAB16 = L::kABytes >> 4;
+  const uint32_t base_lo = (smem_u32(smem) & 0x3FFFFu) >> 4;
+  uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+  uint32_t a_lo = base_lo + s * kStage16;
+  uint32_t accum = 0;
+  for (int kb = 0; kb < k_blocks; ++kb) {
+    if (prof) t0 = clock64();
+    if (!(prof && (prof[3] & 2)) && !mbar_wait(&c.full[s], ph, budget_ns, c.abort_word)) { it += kb; return false; }
+    if (prof) prof[2] += clock64() - t0;
+    if (prof && prof[4] && prof[5] < 512) reinterpret_cast<uint64_t*>(prof[4])[2 * prof[5]] = globaltimer_ns();
+    const uint32_t b_lo = a_lo + kAB16;
 #pragma unroll
     for (int k = 0; k < kBK / kUmmaK; ++k) {
-      const uint64_t adesc = A_MN ? make_smem_desc(a_base + k * 2048, 8192, 1024, 2)
-                                  : make_smem_desc(a_base + k * 32, 16, 1024, 2);
-      const uint64_t bdesc = B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024, 2)
-                                  : make_smem_desc(b_base + k * 32, 16, 1024, 2);
-      tc_mma2_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+      tc_mma2_f16_lo(d_tmem, (a_lo + k * kStepA) | a_lbo, a_hi, (b_lo + k * kStepB) | b_lbo, b_hi, idesc, accum);
+      accum = 1;
     }
-    tc_commit2(empty_l + s * 8);     // both CTAs may refill the stage once these MMAs have read it
-    tc_commit2(empty_p + s * 8);
+    tc_commit2_both(empty0 + s * 8);   // both CTAs may refill the stage once these MMAs have read it
+    if (prof && prof[4] && prof[5] < 512) { reinterpret_cast<uint64_t*>(prof[4])[2 * prof[5] + 1] = globaltimer_ns(); ++prof[5]; }
+    if (++s == STAGES) { s = 0; ph ^= 1; a_lo = base_lo; } else { a_lo += kStage16; }
   }
-  tc_commit2(tfull_l + acc * 8);     // accumulator complete -> both CTAs' epilogues
-  tc_commit2(tfull_p + acc * 8);
+  it += k_blocks;
+  tc_commit2_both(tfull0 + acc * 8);   // accumulator complete -> both CTAs' epilogues
   return true;
 }
 
@@ -587,11 +622,21 @@ constexpr int kPairStages = 6;
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                         GemmEpilogue epi, int K, uint32_t idesc, uint64_t budget_ns, uint32_t* status) {
+                         GemmEpilogue epi, int K, uint32_t idesc, uint64_t budget_ns, uint32_t* status, long long* dbg) {
   extern __shared__ uint8_t dyn_smem[];
   GemmCtrl c;
   uint32_t tmem_base;
   uint8_t* smem = pair_cta_setup<kPairStages>(dyn_smem, c, tmem_base);
+  // optional cycle counters per CTA: [0] producer waiting for a free stage, [1] MMA waiting for a free
+  // accumulator, [2] MMA waiting for operands, [3] MMA warp total, [4] producer total
+  // [3]: experiment switches, see maco_gemm_set_debug; [4], [5]: optional time-line log (switch 8, first pair only):
+  // words 4096 + 2048 * cta + {0: producer, 1024: MMA warp} + 2 * i + {0: wait over, 1: issue done}, %globaltimer ns
+  long long prof[6] = {0, 0, 0, dbg != nullptr ? dbg[7] : 0, 0, 0};
+  long long* pp = dbg != nullptr ? prof : nullptr;
+  const int variant = (int)prof[3];
+  if (dbg != nullptr && (variant & 8) && blockIdx.x < 2)
+    prof[4] = reinterpret_cast<long long>(dbg + 4096 + 2048 * blockIdx.x + ((threadIdx.x >> 5) == 1 ? 1024 : 0));
+  const long long t_begin = clock64();
   const uint32_t rank = cluster_ctarank();
   const int m_pairs = (epi.M + 2 * kBM - 1) / (2 * kBM), n_tiles = (epi.N + BN - 1) / BN;
   const int num_tiles = m_pairs * n_tiles;
@@ -606,13 +651,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+      for (int tile = pair; ok && tile < num_tiles && !(variant & 4); tile += num_pairs) {
         int mp, nb;
         gemm_tile_coords(tile, m_pairs, n_tiles, mp, nb);
         ok = pair_produce_tile<BN, kPairStages, A_MN, B_MN>(smem, c, rank, &tmA, &tmB, (mp * 2 + (int)rank) * kBM, nb * BN, 0,
-                                                            k_blocks, it, budget_ns);
+                                                            k_blocks, it, budget_ns, pp);
       }
-      if (!ok) gemm_drain_loads<kPairStages>(c, it);
+      // after an abort the leader's barriers count both CTAs' bytes; the other CTA stays until the leader
+      // reaches the teardown (cluster barrier)
+      if (!ok && rank == 0) gemm_drain_loads<kPairStages>(c, it);
+      if (dbg != nullptr) { dbg[blockIdx.x * 8 + 0] = prof[0]; dbg[blockIdx.x * 8 + 4] = clock64() - t_begin; }
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -620,7 +668,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t it = 0, seq = 0;
       bool ok = true;
       for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++seq)
-        ok = pair_mma_tile<BN, kPairStages, A_MN, B_MN>(smem, c, tmem_base, idesc, k_blocks, it, seq, budget_ns);
+        ok = pair_mma_tile<BN, kPairStages, A_MN, B_MN>(smem, c, tmem_base, idesc, k_blocks, it, seq, budget_ns, pp);
+      if (dbg != nullptr) { dbg[blockIdx.x * 8 + 1] = prof[1]; dbg[blockIdx.x * 8 + 2] = prof[2]; dbg[blockIdx.x * 8 + 3] = clock64() - t_begin; }
     }
     __syncwarp();
   } else {
@@ -629,6 +678,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++seq) {
       int mp, nb;
       gemm_tile_coords(tile, m_pairs, n_tiles, mp, nb);
+      if (variant & 1) {           // experiment: barrier handshake only
+        if (lane == 0) ok = mbar_wait(&c.tmem_full[seq & 1], (seq >> 1) & 1, budget_ns, c.abort_word);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty_leader + (seq & 1) * 8);
+        continue;
+      }
       ok = gemm_epilogue_tile<BN, 256>(c, tmem_base, epi, epi.out, 0, (mp * 2 + (int)rank) * kBM, nb * BN, seq, budget_ns,
                                        nullptr, nullptr, tempty_leader);
     }
@@ -640,11 +696,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    GemmEpilogue epi, int K, uint32_t idesc, uint64_t budget_ns, uint32_t* status) {
+                    GemmEpilogue epi, int K, uint32_t idesc, uint64_t budget_ns, uint32_t* status, long long* dbg) {
   extern __shared__ uint8_t dyn_smem[];
   GemmCtrl c;
   uint32_t tmem_base;
   uint8_t* smem = gemm_cta_setup<BN, STAGES>(dyn_smem, c, tmem_base);
+  long long prof[4] = {0, 0, 0, dbg != nullptr ? dbg[7] : 0};   // see gemm_tcgen05_pair_kernel
+  long long* pp = dbg != nullptr ? prof : nullptr;
+  const int variant = (int)prof[3];
+  const long long t_begin = clock64();
 
   const int m_tiles = (epi.M + kBM - 1) / kBM, n_tiles = (epi.N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
@@ -657,12 +717,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      for (int tile = blockIdx.x; ok && tile < num_tiles && !(variant & 4); tile += gridDim.x) {
         int mb, nb;
         gemm_tile_coords(tile, m_tiles, n_tiles, mb, nb);
-        ok = gemm_produce_tile<BN, STAGES, A_MN, B_MN>(smem, c, &tmA, &tmB, mb * kBM, nb * BN, 0, k_blocks, it, budget_ns);
+        ok = gemm_produce_tile<BN, STAGES, A_MN, B_MN>(smem, c, &tmA, &tmB, mb * kBM, nb * BN, 0, k_blocks, it, budget_ns, pp);
       }
-      if (!ok) gemm_drain_loads<STAGES>(c, it);
+      if (!ok || (variant & 2)) gemm_drain_loads<STAGES>(c, it);      // experiment switch 2: see the two-CTA kernel
+      if (dbg != nullptr) { dbg[blockIdx.x * 8 + 0] = prof[0]; dbg[blockIdx.x * 8 + 4] = clock64() - t_begin; }
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -670,7 +731,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t it = 0, seq = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++seq)
-        ok = gemm_mma_tile<BN, STAGES, A_MN, B_MN>(smem, c, tmem_base, idesc, k_blocks, it, seq, budget_ns);
+        ok = gemm_mma_tile<BN, STAGES, A_MN, B_MN>(smem, c, tmem_base, idesc, k_blocks, it, seq, budget_ns, pp);
+      if (dbg != nullptr) { dbg[blockIdx.x * 8 + 1] = prof[1]; dbg[blockIdx.x * 8 + 2] = prof[2]; dbg[blockIdx.x * 8 + 3] = clock64() - t_begin; }
     }
     __syncwarp();
   } else {
@@ -679,6 +741,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++seq) {
       int mb, nb;
       gemm_tile_coords(tile, m_tiles, n_tiles, mb, nb);
+      if (variant & 1) {           // experiment: barrier handshake only
+        if (lane == 0) ok = mbar_wait(&c.tmem_full[seq & 1], (seq >> 1) & 1, budget_ns, c.abort_word);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        mbar_arrive(&c.tmem_empty[seq & 1]);
+        continue;
+      }
       ok = gemm_epilogue_tile<BN>(c, tmem_base, epi, epi.out, 0, mb * kBM, nb * BN, seq, budget_ns);
     }
   }

@@ -298,6 +298,11 @@ MACO_DEVICE void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
 MACO_DEVICE void tc_commit2(uint32_t cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(cluster_addr) : "memory");
 }
+// The same arrival on the barrier at this offset in BOTH CTAs of the pair (mask 0b11), one instruction.
+MACO_DEVICE void tc_commit2_both(uint32_t bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               :: "r"(bar_addr), "h"((uint16_t)3) : "memory");
+}
 MACO_DEVICE void tc_mma2_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
@@ -310,6 +315,23 @@ MACO_DEVICE void tma_load_2d_pair(void* smem_dst, const void* tmap, uint32_t bar
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       :: "r"(smem_u32(smem_dst)), "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
+
+// Lean issue forms for the main loops: the descriptor's high word (offsets, version, swizzle) is constant per
+// operand, only the low word (start address >> 4) moves, so the issuing thread spends one add per MMA.
+MACO_DEVICE void tc_mma_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                               uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
+      :: "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+MACO_DEVICE void tc_mma2_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}"
+      :: "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 // Shared-memory matrix descriptor for tcgen05.mma. Addresses and offsets are in 16-byte units.

@@ -31,7 +31,7 @@ class TPSwiGLUMLP:
     def __init__(self, tokens: int, hidden: int, ffn: int, *, rank: int = 0, world: int = 1, heap=None,
                  device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16, seed: int = 0,
                  mode: str = "static", trace: bool = False, weight_std: float = 0.02, num_workers: Optional[int] = None,
-                 comm_workers: Optional[int] = None):
+                 comm_workers: Optional[int] = None, cta_pair: bool = True):
         if tokens % (world * BM) or ffn % (world * 128):
             raise ValueError("tokens must be a multiple of world*128 and ffn of world*128")
         if world > 1 and heap is None:
@@ -52,8 +52,10 @@ class TPSwiGLUMLP:
             # they run out of local rows to work on
             # (8 GPUs, this layer: 12 workers 493 us, 16 workers 459-482 us, 24 workers 479 us)
             comm_workers = 6 if world <= 2 else 16
+        # two-CTA GEMM tiles: 256 x 256 per CTA pair (static queues only)
+        cta_pair = cta_pair and mode == "static"
         b = ProgramBuilder(dev, num_workers=num_workers, mode=mode, heap=heap, trace=trace,
-                           num_comm_workers=(comm_workers if world > 1 else 0))
+                           num_comm_workers=(comm_workers if world > 1 else 0), cta_pair=cta_pair)
         self.h = torch.empty(tokens, f_local, device=dev, dtype=dtype)
         if world == 1:
             self.x_shard = torch.empty(tokens, hidden, device=dev, dtype=dtype)

@@ -58,6 +58,7 @@ class _ProgramStruct(ctypes.Structure):
         ("num_tasks", ctypes.c_uint32), ("num_groups", ctypes.c_uint32), ("num_workers", ctypes.c_uint32),
         ("num_comm_workers", ctypes.c_uint32), ("static_stride", ctypes.c_uint32), ("mode", ctypes.c_uint32),
         ("epoch", ctypes.c_uint32), ("rank", ctypes.c_int32), ("world", ctypes.c_int32),
+        ("cta_group", ctypes.c_uint32), ("_pad", ctypes.c_uint32),
     ]
 
 
@@ -76,6 +77,7 @@ def _lib():
         lib.maco_program_launch.restype = I
         lib.maco_program_launch.argtypes = [ctypes.POINTER(_ProgramStruct), P]
         lib.maco_persistent_smem_bytes.restype = I
+        lib.maco_persistent_max_pairs.restype = I
         sizes = [I() for _ in range(6)]
         lib.maco_abi_sizes(*[ctypes.byref(s) for s in sizes])
         got = [s.value for s in sizes]
@@ -163,13 +165,29 @@ class ProgramBuilder:
     """Accumulates tasks, events, tensor maps and epilogues; ``build()`` uploads them."""
 
     def __init__(self, device: torch.device, num_workers: Optional[int] = None, mode: str = "static",
-                 num_comm_workers: int = 0, heap=None, trace: bool = False, wait_budget_ms: Optional[float] = None):
+                 num_comm_workers: int = 0, heap=None, trace: bool = False, wait_budget_ms: Optional[float] = None,
+                 cta_pair: bool = False):
+        """``cta_pair``: every GEMM tile of the program is computed by TWO CTAs (workers 2j and 2j+1, one
+        thread-block cluster) with ``tcgen05.mma.cta_group::2``: 256 x bn per pair, each CTA loading its own 128
+        rows of A and its own half of B. Static queues only; split-K, counted (MoE) and tensor-core attention
+        tasks stay in one-CTA programs (a kernel has one cta_group)."""
         self.device = torch.device(device)
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.mode = MODE_DYNAMIC if mode == "dynamic" else MODE_STATIC
+        self.cta_pair = bool(cta_pair)
+        if self.cta_pair and self.mode != MODE_STATIC:
+            raise ValueError("two-CTA programs run with static queues")
         limit = sms - (1 if self.mode == MODE_DYNAMIC else 0)
         self.num_workers = max(1, min(int(num_workers) if num_workers else limit, limit, 256))
         self.num_comm_workers = max(0, min(int(num_comm_workers), self.num_workers - 1))
+        if self.cta_pair:
+            max_pairs = _lib().maco_persistent_max_pairs()
+            if max_pairs > 0:
+                self.num_workers = min(self.num_workers, 2 * max_pairs)
+            self.num_workers -= self.num_workers & 1
+            self.num_comm_workers += self.num_comm_workers & 1          # compute workers come in pairs
+            if self.num_workers < 2 or self.num_workers - self.num_comm_workers < 2:
+                raise ValueError("two-CTA programs need at least one pair of compute workers")
         self.heap = heap
         self.trace = trace
         from ..config import config
@@ -196,7 +214,7 @@ class ProgramBuilder:
     def add_task(self, ttype: int, raw: bytes, waits: Sequence[Tuple[int, int, bool, bool]] = (),
                  signals: Sequence[int] = (), signal_peer: int = -1, signal_peer_event: int = -1, node_id: int = 0,
                  comm_worker: bool = False, signal_sys: bool = False, any_worker: bool = False,
-                 counted: bool = False, worker: Optional[int] = None) -> int:
+                 counted: bool = False, worker: Optional[int] = None, pair_half: Optional[int] = None) -> int:
         """``waits``: up to two (event, count, sys_scope, previous_epoch). ``worker`` pins the task to a compute
         worker's static queue (the dynamic scheduler ignores it)."""
         if len(waits) > 2 or len(signals) > 2:
@@ -219,7 +237,8 @@ class ProgramBuilder:
             flags |= TF_COUNTED
         se = list(signals) + [-1] * (2 - len(signals))
         self.tasks.append(dict(type=ttype, flags=flags, node_id=node_id, wait_event=we, wait_count=wc, signal_event=se,
-                               signal_peer=signal_peer, signal_peer_event=signal_peer_event, raw=raw, worker=worker))
+                               signal_peer=signal_peer, signal_peer_event=signal_peer_event, raw=raw, worker=worker,
+                               pair_half=pair_half))
         return len(self.tasks) - 1
 
     def join(self, waits: List[Tuple[int, int, bool, bool]], node_id: int = 0) -> List[Tuple[int, int, bool, bool]]:
@@ -282,9 +301,11 @@ class ProgramBuilder:
         if bn not in (128, 256):
             raise ValueError("bn must be 128 or 256")
         ab = 1 if a.dtype == torch.bfloat16 else 0
-        idesc = make_idesc(ab, BM, bn, int(trans_a), int(trans_b))
+        pair = self.cta_pair
+        # two-CTA tiles: the instruction spans 256 rows (two row blocks) and each CTA loads bn/2 rows of B
+        idesc = make_idesc(ab, 2 * BM if pair else BM, bn, int(trans_a), int(trans_b))
         ta = self._tmap(a, a.shape[0], a.shape[1], a.stride(0), trans_a, BM)
-        tb = self._tmap(b, b.shape[0], b.shape[1], b.stride(0), trans_b, bn)
+        tb = self._tmap(b, b.shape[0], b.shape[1], b.stride(0), trans_b, bn // 2 if pair else bn)
         out_ptr = out.data_ptr() if out is not None else 0
         ld_out = out.stride(0) if out is not None else 0
         out_type = N.DTYPE_CODE[out.dtype] if out is not None else N.DTYPE_CODE[a.dtype]
@@ -301,34 +322,58 @@ class ProgramBuilder:
         all_ev = self.new_event()
         row_events = {mb: self.new_event() for mb in mbs}
         base_waits = self.join(list(extra_waits), node_id)
+
+        def tile_waits(mb: int) -> list:
+            waits = list(base_waits)
+            if row_wait is not None:
+                w = row_wait(mb)
+                if w is not None:
+                    waits.append(w)
+            elif a_ready is not None:
+                ev, cnt = a_ready.for_rows(mb * BM, min(M, (mb + 1) * BM))
+                waits.append((ev, cnt, a_ready.sys, False))
+            waits = list(dict.fromkeys(waits))
+            if len(waits) > 2:
+                waits = self.join(waits, node_id)
+            return waits
+
+        def emit(mb: int, nb: int, half: Optional[int]) -> None:
+            waits = tile_waits(mb)
+            ov = per_tile(mb, nb) if per_tile is not None else {}
+            if ov.get("waits"):
+                waits = list(dict.fromkeys(waits + list(ov["waits"])))
+                if len(waits) > 2:
+                    waits = self.join(waits, node_id)
+            if pair and ov.get("count_ptr", 0):
+                raise ValueError("run-time counted tiles are not available in two-CTA programs")
+            raw = _pack_gemm(ta, tb, ov.get("epi", epi), int(trans_a), int(trans_b), mb * BM, nb * bn, 0, k_blocks, idesc,
+                             ov.get("peer", -1), ov.get("row_off", 0), ov.get("out_off", 0), bn,
+                             ov.get("count_base", 0), ov.get("count_ptr", 0))
+            self.add_task(int(TaskType.LINEAR), raw, waits=waits, signals=[row_events[mb], all_ev],
+                          signal_peer=ov.get("signal_peer", -1), signal_peer_event=ov.get("signal_peer_event", -1),
+                          node_id=node_id, signal_sys=signal_sys, counted=bool(ov.get("count_ptr", 0)), pair_half=half)
+
+        def emit_filler(nb: int) -> None:
+            # second half of a pair that has only one row block left: rows past the end of A (the loads return
+            # zeros, the epilogue stores nothing), no conditions, no signals; it keeps the pair's protocol whole
+            raw = _pack_gemm(ta, tb, epi, int(trans_a), int(trans_b), m_tiles * BM, nb * bn, 0, k_blocks, idesc, -1, 0, 0, bn)
+            self.add_task(int(TaskType.LINEAR), raw, node_id=node_id, pair_half=1)
+
         G = 8
         for g0 in range(0, len(mbs), G):
             grp = mbs[g0:g0 + G]
             # tiles of `G` row blocks sweep all column tiles: operands stay in L2, row blocks finish in order
             for nb in range(n_tiles):
-                for mb in grp:
-                    waits = list(base_waits)
-                    if row_wait is not None:
-                        w = row_wait(mb)
-                        if w is not None:
-                            waits.append(w)
-                    elif a_ready is not None:
-                        ev, cnt = a_ready.for_rows(mb * BM, min(M, (mb + 1) * BM))
-                        waits.append((ev, cnt, a_ready.sys, False))
-                    waits = list(dict.fromkeys(waits))
-                    if len(waits) > 2:
-                        waits = self.join(waits, node_id)
-                    ov = per_tile(mb, nb) if per_tile is not None else {}
-                    if ov.get("waits"):
-                        waits = list(dict.fromkeys(waits + list(ov["waits"])))
-                        if len(waits) > 2:
-                            waits = self.join(waits, node_id)
-                    raw = _pack_gemm(ta, tb, ov.get("epi", epi), int(trans_a), int(trans_b), mb * BM, nb * bn, 0, k_blocks, idesc,
-                                     ov.get("peer", -1), ov.get("row_off", 0), ov.get("out_off", 0), bn,
-                                     ov.get("count_base", 0), ov.get("count_ptr", 0))
-                    self.add_task(int(TaskType.LINEAR), raw, waits=waits, signals=[row_events[mb], all_ev],
-                                  signal_peer=ov.get("signal_peer", -1), signal_peer_event=ov.get("signal_peer_event", -1),
-                                  node_id=node_id, signal_sys=signal_sys, counted=bool(ov.get("count_ptr", 0)))
+                if not pair:
+                    for mb in grp:
+                        emit(mb, nb, None)
+                    continue
+                for j in range(0, len(grp), 2):
+                    emit(grp[j], nb, 0)
+                    if j + 1 < len(grp):
+                        emit(grp[j + 1], nb, 1)
+                    else:
+                        emit_filler(nb)
         total = len(mbs) * n_tiles
         return RowEvents(rows=M, block=BM, row_events=[(row_events.get(mb, all_ev), n_tiles) if mb in row_events
                                                        else (all_ev, total) for mb in range(m_tiles)],
@@ -370,6 +415,8 @@ class ProgramBuilder:
         one-shot all-reduce), bumping ``signal_peer_event`` on every rank.
         The reference runs such GEMMs as one torch.mm each (maco/task_graph/runtime.py:188-209).
         """
+        if self.cta_pair:
+            raise ValueError("split-K GEMMs are not available in two-CTA programs")
         M, K = a.shape
         Nn = w.shape[0]
         if M > BM or w.shape[1] != K or Nn % 256 or K % BK:
@@ -454,6 +501,8 @@ class ProgramBuilder:
         Returns (event, count) that is complete when every output row is final.
         The reference declares ATTENTION as a task type and never implements it (maco/csrc/maco_types.h:24-40).
         """
+        if self.cta_pair:
+            raise ValueError("attention tasks are not available in two-CTA programs")
         B, hq, D = q.shape
         _, hkv, S, _ = k_cache.shape
         G = hq // hkv
@@ -635,9 +684,18 @@ class Program:
         W, Wc = self.num_workers, self.num_comm_workers
         n_compute = W - Wc
         queues: List[List[int]] = [[] for _ in range(W)]
-        rr_c = rr_m = rr_a = 0
+        rr_c = rr_m = rr_a = rr_p = 0
+        n_pairs = n_compute // 2
+        pair_of_leader = 0
         for i, t in enumerate(b.tasks):
-            if (t["flags"] & TF_ANY_WORKER) and Wc > 0:
+            if t.get("pair_half") is not None:
+                # halves of a two-CTA tile: consecutive tasks, leader on worker 2j, the other half on 2j+1; both
+                # workers see their pair tiles in the same order (the MMA of one serves both)
+                if t["pair_half"] == 0:
+                    pair_of_leader = (rr_p + rr_p // n_pairs) % n_pairs
+                    rr_p += 1
+                queues[2 * pair_of_leader + t["pair_half"]].append(i)
+            elif (t["flags"] & TF_ANY_WORKER) and Wc > 0:
                 queues[(W - 1 - rr_a) % W].append(i)       # communication workers (highest indices) first
                 rr_a += 1
             elif (t["flags"] & TF_COMM_WORKER) and Wc > 0:
@@ -685,6 +743,8 @@ class Program:
         ps.num_tasks, ps.num_groups, ps.num_workers, ps.num_comm_workers = n, self.num_groups, W, Wc
         ps.static_stride, ps.mode, ps.epoch = stride, self.mode, 0
         ps.rank, ps.world = 0, 1
+        ps.cta_group = 2 if b.cta_pair else 1
+        self.cta_pair = b.cta_pair
         if b.heap is not None:
             ps.rank, ps.world = b.heap.rank, b.heap.world
             ev_off = b.heap.offset_of(self.d_events)
@@ -773,7 +833,8 @@ class Program:
     def describe(self) -> str:
         kind = "dynamic (scheduler CTA)" if self.mode == MODE_DYNAMIC else "static queues"
         return (f"Persistent kernel: {self.num_tasks} tile tasks, {self.num_groups} dispatch groups, "
-                f"{self.num_events} events, {self.num_workers} workers ({self.num_comm_workers} comm), {kind}")
+                f"{self.num_events} events, {self.num_workers} workers ({self.num_comm_workers} comm), {kind}"
+                + (", two-CTA GEMM tiles" if self.cta_pair else ""))
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -845,7 +906,19 @@ def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None)
     trace = config.profile if trace is None else trace
     sms = torch.cuda.get_device_properties(graph.device).multi_processor_count
     workers = min(graph.num_workers, sms - (1 if mode == "dynamic" else 0))
-    b = ProgramBuilder(graph.device, num_workers=workers, mode=mode, trace=trace)
+
+    def _few_rows(n: TaskNode) -> bool:
+        x2, w = _flat2d(n.inputs[0]), n.inputs[1]
+        return (n.task_type == TaskType.LINEAR and not n.attrs.get("has_bias") and n.attrs.get("activation") in (None, "none", "swiglu")
+                and x2.shape[0] <= BM and w.shape[0] % 256 == 0 and x2.shape[1] % BK == 0 and w.shape[0] * w.shape[1] >= (1 << 22))
+
+    gemm_nodes = [n for n in graph._nodes if n.task_type in (TaskType.LINEAR, TaskType.MATMUL) and n.outputs and n.outputs[0].numel()]
+    # two-CTA tiles pay once the 256-row tiles of every GEMM cover the worker pairs; decode-shaped (split-K)
+    # nodes keep the graph on one-CTA tiles
+    cta_pair = (mode == "static" and workers >= 4 and bool(gemm_nodes) and not any(_few_rows(n) for n in gemm_nodes)
+                and all(-(-_flat2d(n.inputs[0]).shape[0] // (2 * BM)) * -(-n.outputs[0].shape[-1] // 256) >= workers // 2
+                        for n in gemm_nodes))
+    b = ProgramBuilder(graph.device, num_workers=workers, mode=mode, trace=trace, cta_pair=cta_pair)
     produced: Dict[int, Tuple[TaskNode, RowEvents]] = {}       # node id -> events of its output
 
     def ready_of(node: TaskNode, t: torch.Tensor, rows: int) -> Tuple[Optional[RowEvents], List[tuple]]:

@@ -10,7 +10,7 @@ from tests.conftest import assert_close
 pytestmark = pytest.mark.gpu
 
 
-def _mlp_program(mode, tokens=1024, hidden=1024, ffn=2048, workers=None, trace=False):
+def _mlp_program(mode, tokens=1024, hidden=1024, ffn=2048, workers=None, trace=False, cta_pair=False):
     from maco_b200.ops import interleave_gate_up, megakernel as mk
     dt = torch.bfloat16
     x = torch.randn(tokens, hidden, device="cuda", dtype=dt)
@@ -22,7 +22,7 @@ def _mlp_program(mode, tokens=1024, hidden=1024, ffn=2048, workers=None, trace=F
     xn = torch.empty_like(x)
     h = torch.empty(tokens, ffn, device="cuda", dtype=dt)
     y = torch.empty(tokens, hidden, device="cuda", dtype=dt)
-    b = mk.ProgramBuilder(torch.device("cuda"), num_workers=workers, mode=mode, trace=trace)
+    b = mk.ProgramBuilder(torch.device("cuda"), num_workers=workers, mode=mode, trace=trace, cta_pair=cta_pair)
     e0 = b.elementwise(104, x, xn, in1=nw, rows=tokens, cols=hidden, f0=1e-6)
     e1 = b.gemm(xn, wgu, h, epilogue="swiglu", a_ready=e0)
     b.gemm(h, wd, y, epilogue="residual", aux=x, a_ready=e1)
@@ -46,6 +46,44 @@ def test_fused_mlp_program(mode, workers):
     assert_close(y, ref, torch.bfloat16)
     assert prog.tasks_completed() == 3 * prog.num_tasks
     assert "tile tasks" in prog.describe()
+
+
+@pytest.mark.parametrize("tokens", [1024, 640, 2304])
+@pytest.mark.parametrize("workers", [None, 6])
+def test_fused_mlp_program_two_cta_tiles(tokens, workers):
+    """The same program on two-CTA tiles (cluster launch, cta_group::2): whole pairs of row blocks, an odd block
+    count (one pair gets a filler half), a ragged last block, few and many worker pairs, re-execution."""
+    prog, y, ref = _mlp_program("static", tokens=tokens, workers=workers, cta_pair=True)
+    assert prog.cta_pair and prog.num_workers % 2 == 0
+    for _ in range(3):
+        y.zero_()
+        prog.run()
+    torch.cuda.synchronize()
+    assert _native.status() == 0
+    assert_close(y, ref, torch.bfloat16)
+    assert "two-CTA" in prog.describe()
+
+
+def test_two_cta_program_backward_majors():
+    """dgrad (plain a @ b: MN-major B) and wgrad (a^T @ b: both operands MN-major) as two-CTA tiles in one program."""
+    from maco_b200.ops import megakernel as mk
+    dt = torch.bfloat16
+    T, H = 1024, 768
+    dy = torch.randn(T, H, device="cuda", dtype=dt)
+    w = torch.randn(H, H, device="cuda", dtype=dt) * 0.05
+    xin = torch.randn(T, H, device="cuda", dtype=dt)
+    dx = torch.empty(T, H, device="cuda", dtype=dt)
+    dw = torch.empty(H, H, device="cuda", dtype=torch.float32)
+    b = mk.ProgramBuilder(torch.device("cuda"), cta_pair=True)
+    b.gemm(dy, w, dx, trans_b=True)                                   # dx = dy @ w
+    b.gemm(dy, xin, dw, trans_a=True, trans_b=True, epilogue="f32")   # dw = dy^T @ x
+    prog = b.build()
+    for _ in range(2):
+        prog.run()
+    torch.cuda.synchronize()
+    assert _native.status() == 0
+    assert_close(dx, dy.float() @ w.float(), dt)
+    torch.testing.assert_close(dw, dy.float().t() @ xin.float(), atol=0.3, rtol=2e-2)
 
 
 def test_trace_and_stats():

@@ -19,9 +19,11 @@ def test_dp_backward_single_gpu_matches_autograd():
     assert _native.status() == 0
 
 
-def test_tp_mlp_single_gpu():
+@pytest.mark.parametrize("cta_pair", [True, False])
+def test_tp_mlp_single_gpu(cta_pair):
     from maco_b200.models.tp_mlp import TPSwiGLUMLP
-    layer = TPSwiGLUMLP(512, 512, 1024, seed=1)
+    layer = TPSwiGLUMLP(512, 512, 1024, seed=1, cta_pair=cta_pair)
+    assert layer.program.cta_pair == cta_pair
     x = torch.randn(512, 512, device="cuda", dtype=torch.bfloat16)
     y = layer(x)
     torch.cuda.synchronize()
