@@ -431,24 +431,65 @@ MACO_DEVICE bool comm_run(const Program& p, const MacoTaskDesc& d, int tid, int 
 #undef MACO_REDUCE_DT
       return true;
     }
-    case MACO_COMM_ALLREDUCE_MC: {
+    case MACO_COMM_PUSH_MC: {
+      // Broadcast: every 16-byte vector is read once from this rank's heap and stored once to the multicast
+      // address; the switch delivers it to every rank (this one included), so the block leaves the GPU once
+      // whatever the number of peers.
       if (p.mc_heap == nullptr) return false;
-      for (uint32_t i = tid; i < total; i += nthreads) {
-        const uint8_t* src = p.mc_heap + a.src_off + blk_off(i, vpr, a.src_stride);
-        uint4 o;
-        if (a.dtype == MACO_DT_F32) {
-          float4 f = multimem_ld_reduce_f32x4(src);
-          o = make_uint4(__float_as_uint(f.x * a.scale), __float_as_uint(f.y * a.scale), __float_as_uint(f.z * a.scale),
-                         __float_as_uint(f.w * a.scale));
-        } else {
-          o = multimem_ld_reduce_bf16x8(src);
-          if (a.scale != 1.f) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            add8(acc, o, MACO_DT_BF16);
-            o = pack8(acc, a.scale, MACO_DT_BF16);
+      const uint8_t* src = mine + a.src_off;
+      uint8_t* dst = p.mc_heap + a.dst_off;
+      for (uint32_t base = tid; base < total; base += step) {
+        uint4 v[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const uint32_t i = base + (uint32_t)u * nthreads;
+          if (i < total) v[u] = ldv(src + blk_off(i, vpr, a.src_stride));
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const uint32_t i = base + (uint32_t)u * nthreads;
+          if (i < total) multimem_st_v4(dst + blk_off(i, vpr, a.dst_stride), v[u]);
+        }
+      }
+      return true;
+    }
+    case MACO_COMM_ALLREDUCE_MC: {
+      // One-shot all-reduce of a block through the switch: multimem.ld_reduce returns the sum over every rank's
+      // copy (accumulated in fp32 inside the switch for 16-bit types), multimem.st writes the result back to
+      // every copy. kU loads per thread are in flight together: one round trip through the switch is a few
+      // microseconds.
+      if (p.mc_heap == nullptr) return false;
+      const uint8_t* src = p.mc_heap + a.src_off;
+      uint8_t* dst = p.mc_heap + a.dst_off;
+      for (uint32_t base = tid; base < total; base += step) {
+        uint4 v[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const uint32_t i = base + (uint32_t)u * nthreads;
+          if (i >= total) continue;
+          const uint8_t* q = src + blk_off(i, vpr, a.src_stride);
+          if (a.dtype == MACO_DT_F32) {
+            const float4 f = multimem_ld_reduce_f32x4(q);
+            v[u] = make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z), __float_as_uint(f.w));
+          } else if (a.dtype == MACO_DT_F16) {
+            v[u] = multimem_ld_reduce_f16x8(q);
+          } else {
+            v[u] = multimem_ld_reduce_bf16x8(q);
           }
         }
-        multimem_st_v4(p.mc_heap + a.dst_off + blk_off(i, vpr, a.dst_stride), o);
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const uint32_t i = base + (uint32_t)u * nthreads;
+          if (i >= total) continue;
+          uint4 o = v[u];
+          if (a.scale != 1.f) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            add8(acc, o, a.dtype);
+            o = a.dtype == MACO_DT_F32 ? pack8(acc, a.scale, MACO_DT_F32)
+              : a.dtype == MACO_DT_F16 ? pack8(acc, a.scale, MACO_DT_F16) : pack8(acc, a.scale, MACO_DT_BF16);
+          }
+          multimem_st_v4(dst + blk_off(i, vpr, a.dst_stride), o);
+        }
       }
       return true;
     }

@@ -363,6 +363,12 @@ MACO_DEVICE uint4 multimem_ld_reduce_bf16x8(const void* mc_ptr) {
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_ptr) : "memory");
   return v;
 }
+MACO_DEVICE uint4 multimem_ld_reduce_f16x8(const void* mc_ptr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_ptr) : "memory");
+  return v;
+}
 MACO_DEVICE float4 multimem_ld_reduce_f32x4(const void* mc_ptr) {
   float4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"

@@ -140,6 +140,12 @@ __device__ void signal_done(const MacoProgram& p, const MacoTaskDesc& d) {
   // One release fence for the whole task, then relaxed counter bumps: a release per destination would
   // repeat the fence (a round trip over NVLink once a peer is involved) for every rank that is signalled.
   const bool sys = (d.flags & MACO_TF_SIGNAL_SYS) != 0 || d.signal_peer_event >= 0;
+  if (d.signal_peer == -4 && d.signal_peer_event >= 0 && d.signal_event[0] < 0 && d.signal_event[1] < 0 && p.mc_heap != nullptr) {
+    // one release-reduction through the NVSwitch bumps the counter in every rank's table (this rank's too)
+    uint32_t* mc_events = reinterpret_cast<uint32_t*>(p.mc_heap + (reinterpret_cast<uint8_t*>(p.events) - p.peer_heap[p.rank]));
+    multimem_red_add_u32(mc_events + d.signal_peer_event, 1);
+    return;
+  }
   if (sys) fence_acq_rel_sys(); else fence_acq_rel_gpu();
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
@@ -150,7 +156,7 @@ __device__ void signal_done(const MacoProgram& p, const MacoTaskDesc& d) {
   if (d.signal_peer_event >= 0) {
     if (d.signal_peer >= 0) {
       red_add_relaxed_sys_u32(&p.peer_events[d.signal_peer][d.signal_peer_event], 1);
-    } else if (d.signal_peer == -2) {
+    } else if (d.signal_peer == -2 || d.signal_peer == -4) {
       for (int r = 0; r < p.world; ++r) red_add_relaxed_sys_u32(&p.peer_events[r][d.signal_peer_event], 1);
     }
   }

@@ -149,7 +149,8 @@ enum MacoCommOp {
   MACO_COMM_ALLREDUCE = 3,        /* pull-reduce one block from every rank, store the result to every rank */
   MACO_COMM_ALLREDUCE_MC = 4,     /* same through the NVSwitch multicast address (multimem) */
   MACO_COMM_PULL = 5,             /* copy a block of peer `peer`'s heap into my heap */
-  MACO_COMM_REDUCE_LOCAL_BCAST = 6 /* sum `nslots` local slots (filled by the peers' stores) and write the result to dst_off on EVERY rank */
+  MACO_COMM_REDUCE_LOCAL_BCAST = 6,/* sum `nslots` local slots (filled by the peers' stores) and write the result to dst_off on EVERY rank */
+  MACO_COMM_PUSH_MC = 7           /* copy my block to dst_off of EVERY rank with multimem.st through the NVSwitch multicast address */
 };
 
 struct MacoTaskDesc {
@@ -159,7 +160,8 @@ struct MacoTaskDesc {
   int32_t wait_event[2];          /* -1: no condition; else wait until events[e] >= epoch * wait_count */
   uint32_t wait_count[2];
   int32_t signal_event[2];        /* local events bumped by 1 at completion, -1 none */
-  int32_t signal_peer;            /* rank whose event table is bumped, -1 none, -2 every rank */
+  int32_t signal_peer;            /* rank whose event table is bumped, -1 none, -2 every rank (one red per rank),
+                                     -4 every rank with ONE multimem.red on the multicast address of the table */
   int32_t signal_peer_event;
   union {
     MacoGemmArgs gemm;

@@ -3,7 +3,7 @@
 Same fields and methods as the reference's MacoConfig (maco/config.py:9-61), where nothing reads
 them. Here they are live: ``backend`` selects the collective implementation ("peer" = in-kernel
 collectives over NVLink peer memory, "nccl"/"gloo" = torch.distributed), ``comm_buffer_size`` sizes
-the symmetric heap, ``profile`` turns the device trace ring on, ``runtime`` picks the TaskGraph
+the symmetric heap, ``heap_mode`` how it is shared (with or without an NVSwitch multicast binding), ``profile`` turns the device trace ring on, ``runtime`` picks the TaskGraph
 executor. ``MACO_*`` environment variables override the defaults.
 """
 from __future__ import annotations
@@ -29,6 +29,7 @@ class MacoConfig:
     sm_policy: str = "auto"               # how SMs are split between compute / comm / scheduler roles
     overlap_strategy: str = "auto"        # "auto" | "wave" | "none"
     comm_buffer_size: str = "256MB"       # symmetric heap size per rank
+    heap_mode: str = "auto"               # "auto" | "nvls" (multicast-bound) | "vmm" (shared descriptors) | "ipc" (cudaMalloc + IPC)
     use_pinned_memory: bool = True
     runtime: str = "auto"                 # "auto" | "persistent" | "stream" | "reference"
     wait_budget_ms: float = 2000.0        # every device-side wait gives up after this long
@@ -41,6 +42,7 @@ class MacoConfig:
         self.backend = env.get("MACO_BACKEND", self.backend)
         self.runtime = env.get("MACO_RUNTIME", self.runtime)
         self.comm_buffer_size = env.get("MACO_COMM_BUFFER_SIZE", self.comm_buffer_size)
+        self.heap_mode = env.get("MACO_HEAP", self.heap_mode)
         if "MACO_WAIT_BUDGET_MS" in env:
             self.wait_budget_ms = float(env["MACO_WAIT_BUDGET_MS"])
         for flag in ("debug", "profile", "verbose"):

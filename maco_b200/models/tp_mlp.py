@@ -51,7 +51,11 @@ class TPSwiGLUMLP:
             # one SM pushes roughly 25-30 GB/s into a peer; the shard has to reach world-1 peers before
             # they run out of local rows to work on
             # (8 GPUs, this layer: 12 workers 493 us, 16 workers 459-482 us, 24 workers 479 us)
-            comm_workers = 6 if world <= 2 else 16
+            # a multicast-bound heap sends the shard once (multimem.st): fewer SMs do the same job
+            if heap is not None and heap.multicast_base():
+                comm_workers = 4 if world <= 2 else 8
+            else:
+                comm_workers = 6 if world <= 2 else 16
         # two-CTA GEMM tiles: 256 x 256 per CTA pair (static queues only)
         cta_pair = cta_pair and mode == "static"
         b = ProgramBuilder(dev, num_workers=num_workers, mode=mode, heap=heap, trace=trace,
@@ -70,7 +74,7 @@ class TPSwiGLUMLP:
             self.y_shard = torch.empty(self.rows_local, hidden, device=dev, dtype=dtype)
             fence = fused.epoch_fence_event(b)
             eg = fused.allgather_push(b, self.x_shard, self.x_full, fence=fence)
-            order = fused.rotated_blocks(rank, world, self.rows_local // BM)
+            order = fused.gathered_order(rank, world, self.rows_local // BM, bool(heap.multicast_base()))
             e1 = b.gemm(self.x_full, self.w_gate_up, self.h, epilogue="swiglu", a_ready=eg, m_blocks=order)
             _, eo = fused.gemm_reduce_scatter(b, self.h, self.w_down, self.staging, self.y_shard, a_ready=e1)
             fused.epoch_fence_signal(b, [(eo.all_event[0], eo.all_event[1], False, False),

@@ -28,7 +28,7 @@ MODE_STATIC, MODE_DYNAMIC = 0, 1
 TF_WAIT0_SYS, TF_WAIT1_SYS, TF_COMM_WORKER, TF_SIGNAL_SYS, TF_WAIT0_PREV, TF_WAIT1_PREV = 1, 2, 4, 8, 16, 32
 TF_ANY_WORKER = 64      # host-side placement hint: spread over compute AND communication workers
 TF_COUNTED = 128        # GEMM tile guarded by a run-time row count
-COMM_PUSH, COMM_REDUCE_LOCAL, COMM_REDUCE_PULL, COMM_ALLREDUCE, COMM_ALLREDUCE_MC, COMM_PULL, COMM_REDUCE_LOCAL_BCAST = range(7)
+COMM_PUSH, COMM_REDUCE_LOCAL, COMM_REDUCE_PULL, COMM_ALLREDUCE, COMM_ALLREDUCE_MC, COMM_PULL, COMM_REDUCE_LOCAL_BCAST, COMM_PUSH_MC = range(8)
 MAX_PEERS = 16
 WORKER_QUEUE_SIZE = 1024
 T_SPLITK_FIN = 118

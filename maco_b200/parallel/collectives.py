@@ -27,7 +27,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from .. import _native as N
-from ..ops.megakernel import COMM_PUSH, COMM_REDUCE_PULL, Program, ProgramBuilder, _pack_comm
+from ..ops.megakernel import COMM_ALLREDUCE_MC, COMM_PUSH, COMM_REDUCE_PULL, Program, ProgramBuilder, _pack_comm
 from ..task_graph.nodes import TaskType
 from . import fused
 from .symm_heap import current_heap
@@ -105,14 +105,43 @@ def _store(key: tuple, entry: _Entry) -> _Entry:
     return entry
 
 
-def all_reduce(t: torch.Tensor, avg: bool = False) -> torch.Tensor:
-    """In-place sum (or mean) of heap tensor ``t`` over all ranks. Chunk c belongs to rank c % world: every
-    rank stores its copy into the owner's staging slot, the owner sums the slots in fp32 and stores the
-    result into ``t`` on every rank (no remote reads). The owner's stores can only start after every rank's
-    kernel has contributed, so they never hit a buffer whose owner is still preparing it."""
+def all_reduce(t: torch.Tensor, avg: bool = False, multicast: Optional[bool] = None) -> torch.Tensor:
+    """In-place sum (or mean) of heap tensor ``t`` over all ranks.
+
+    With a multicast-bound heap (``multicast`` None = use it when there is one): chunk c belongs to rank
+    c % world, which loads the sum of every rank's copy with multimem.ld_reduce (the switch adds, in fp32
+    for 16-bit types) and stores the result to every copy with multimem.st: each byte crosses this GPU's
+    links about once in each direction. The kernels open with the handshake (every rank's buffer is ready)
+    and a rank's kernel ends when all chunks of its copy are final, which is also when nobody reads it any more.
+
+    Without: every rank stores its copy of a chunk into the owner's staging slot, the owner sums the slots in
+    fp32 and stores the result into ``t`` on every rank (no remote reads). The owner's stores can only start
+    after every rank's kernel has contributed, so they never hit a buffer whose owner is still preparing it."""
     heap = _heap()
-    key = ("ar", heap.offset_of(t), t.numel(), t.dtype, avg)
+    if multicast is None:
+        multicast = bool(heap.multicast_base())
+    key = ("ar", heap.offset_of(t), t.numel(), t.dtype, avg, multicast)
     e = _lookup(key)
+    if e is None and multicast:
+        nbytes = t.numel() * t.element_size()
+        if nbytes % 16:
+            raise ValueError("all-reduce buffers must be a multiple of 16 bytes")
+        chunk = 128 << 10
+        n_chunks = -(-nbytes // chunk)
+        b = _builder(heap, workers=max(1, min(32, -(-n_chunks // heap.world))))
+        ready = _open(b)
+        done = b.new_event()
+        off = heap.offset_of(t)
+        for c in range(n_chunks):
+            if c % heap.world != heap.rank:
+                continue
+            c0 = c * chunk
+            row, rows = _push_rows(min(chunk, nbytes - c0))
+            raw = _pack_comm(off + c0, off + c0, row, row, row, rows, N.DTYPE_CODE[t.dtype], -1, COMM_ALLREDUCE_MC,
+                             scale=(1.0 / heap.world if avg else 1.0))
+            b.add_task(int(TaskType.ALLREDUCE), raw, waits=[ready], signal_peer=-4, signal_peer_event=done)
+        _wait_local(b, [(done, n_chunks, True, False)])
+        e = _store(key, _Entry([b.build()], []))
     if e is None:
         nbytes = t.numel() * t.element_size()
         chunk = 256 << 10

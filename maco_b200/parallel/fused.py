@@ -27,8 +27,8 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 
 from .. import _native as N
-from ..ops.megakernel import (BM, COMM_ALLREDUCE, COMM_PUSH, COMM_REDUCE_LOCAL, COMM_REDUCE_LOCAL_BCAST, ProgramBuilder,
-                              RowEvents, _pack_comm)
+from ..ops.megakernel import (BM, COMM_ALLREDUCE, COMM_PUSH, COMM_PUSH_MC, COMM_REDUCE_LOCAL, COMM_REDUCE_LOCAL_BCAST,
+                              ProgramBuilder, RowEvents, _pack_comm)
 from ..task_graph.nodes import TaskType
 
 
@@ -48,13 +48,17 @@ def epoch_fence_signal(b: ProgramBuilder, waits: Sequence[Tuple[int, int, bool, 
 
 def allgather_push(b: ProgramBuilder, shard: torch.Tensor, gathered: torch.Tensor, *, chunk_rows: int = 128,
                    fence: Optional[Tuple[int, int, bool, bool]] = None,
-                   src_ready: Optional[RowEvents] = None) -> RowEvents:
+                   src_ready: Optional[RowEvents] = None, multicast: Optional[bool] = None) -> RowEvents:
     """Pushes this rank's ``shard`` [rows, cols] into rows ``[rank*rows, (rank+1)*rows)`` of every
     rank's ``gathered`` [world*rows, cols]. Returns row-block events of ``gathered``.
 
     ``shard`` may BE that slice of this rank's ``gathered`` (no local copy is made then, and the
-    local blocks carry an always-true condition). One task per (destination, chunk), ordered by when
-    the destination needs the rows: rank r-1 consumes this shard first, then r-2, ...
+    local blocks carry an always-true condition). With plain peer memory: one task per (destination,
+    chunk), ordered by when the destination needs the rows (rank r-1 consumes this shard first, then
+    r-2, ...). With a multicast-bound heap (``multicast`` None = use it when the heap has one): one task
+    per chunk stores the rows ONCE to the NVSwitch multicast address (multimem.st) and bumps the block's
+    counter on every rank with one multimem.red; the shard leaves the GPU once instead of world-1 times,
+    and every rank receives block j of every shard at about the same time (see ``gathered_order``).
     """
     heap = b.heap
     rank, world = heap.rank, heap.world
@@ -70,6 +74,29 @@ def allgather_push(b: ProgramBuilder, shard: torch.Tensor, gathered: torch.Tenso
     events = [b.new_event() for _ in range(blocks)]
     all_ev = b.new_event()
     per_block = BM // chunk_rows
+    if multicast is None:
+        multicast = bool(heap.multicast_base())
+    if multicast and not heap.multicast_base():
+        raise ValueError("the symmetric heap has no multicast binding")
+    if multicast:
+        for c0 in range(0, rows, chunk_rows):
+            waits = []
+            if fence is not None:
+                waits.append(fence)
+            if src_ready is not None:
+                ev, cnt = src_ready.for_rows(c0, c0 + chunk_rows)
+                waits.append((ev, cnt, src_ready.sys, False))
+            grow = rank * rows + c0
+            raw = _pack_comm(s_off + c0 * row_bytes, g_off + grow * row_bytes, row_bytes, row_bytes, row_bytes,
+                             chunk_rows, N.DTYPE_CODE[shard.dtype], -1, COMM_PUSH_MC)
+            b.add_task(int(TaskType.ALLGATHER), raw, waits=waits, signal_peer=-4, signal_peer_event=events[grow // BM],
+                       comm_worker=True)
+        b.keepalive += [shard, gathered]
+        own = range(rank * rows // BM, (rank + 1) * rows // BM)
+        # the multicast store also lands in this rank's own copy: its blocks are counted like everybody's unless
+        # they are already in place
+        row_events = [(e, 0 if (in_place and i in own) else per_block) for i, e in enumerate(events)]
+        return RowEvents(rows=world * rows, block=BM, row_events=row_events, all_event=(all_ev, 0), sys=True)
     dests = [(rank - k) % world for k in range(1, world)]
     if not in_place:
         dests = [rank] + dests
@@ -90,6 +117,18 @@ def allgather_push(b: ProgramBuilder, shard: torch.Tensor, gathered: torch.Tenso
     own = range(rank * rows // BM, (rank + 1) * rows // BM)
     row_events = [(e, 0 if (in_place and i in own) else per_block) for i, e in enumerate(events)]
     return RowEvents(rows=world * rows, block=BM, row_events=row_events, all_event=(all_ev, 0), sys=True)
+
+
+def gathered_order(rank: int, world: int, blocks_per_rank: int, multicast: bool) -> List[int]:
+    """Order in which a rank consumes the row blocks of an all-gathered buffer. Peer pushes deliver shard
+    rank+1 first, then rank+2, ... (``rotated_blocks``). Multicast stores deliver block j of EVERY shard at
+    about the same time: own shard first, then block 0 of all other shards, block 1 of all, ..."""
+    if not multicast:
+        return rotated_blocks(rank, world, blocks_per_rank)
+    out = list(range(rank * blocks_per_rank, (rank + 1) * blocks_per_rank))
+    for j in range(blocks_per_rank):
+        out += [((rank + k) % world) * blocks_per_rank + j for k in range(1, world)]
+    return out
 
 
 def rotated_blocks(rank: int, world: int, blocks_per_rank: int, own_last: bool = False) -> List[int]:

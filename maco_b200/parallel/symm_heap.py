@@ -77,11 +77,62 @@ class _Span:
         self._owner = owner
 
 
+def _exchange_fds(serve_fd: Optional[int], fetch_from: List[int], rank: int, world: int, exchange, tag: str) -> dict:
+    """Passes file descriptors between the ranks of one node over Unix-domain sockets (SCM_RIGHTS): every rank
+    that has a descriptor serves it to whoever connects, and fetches one from each rank in ``fetch_from``.
+    ``exchange`` publishes the socket names. Returns {source rank: received descriptor}."""
+    import os
+    import socket
+    import threading
+    name = f"\0maco_b200_{tag}_{os.getpid()}_{rank}"           # abstract namespace: nothing to unlink
+    server = None
+    n_clients = 0
+    if serve_fd is not None:
+        server = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        server.bind(name)
+        server.listen(world)
+    names = exchange((name if serve_fd is not None else None, list(fetch_from)))
+    if serve_fd is not None:
+        n_clients = sum(1 for r, (_, wants) in enumerate(names) if r != rank and rank in wants)
+
+    def serve():
+        for _ in range(n_clients):
+            conn, _ = server.accept()
+            with conn:
+                conn.recv(4)
+                socket.send_fds(conn, [b"fd"], [serve_fd])
+
+    th = None
+    if server is not None and n_clients:
+        th = threading.Thread(target=serve, daemon=True)
+        th.start()
+    got = {}
+    for src in fetch_from:
+        with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as c:
+            c.settimeout(60.0)
+            c.connect(names[src][0])
+            c.sendall(rank.to_bytes(4, "little"))
+            _, fds, _, _ = socket.recv_fds(c, 16, 1)
+            got[src] = fds[0]
+    if th is not None:
+        th.join(60.0)
+    if server is not None:
+        server.close()
+    return got
+
+
 class SymmetricHeap:
-    def __init__(self, nbytes: int, rank: int, world: int, device: torch.device, exchange):
-        """``exchange(obj) -> list`` gathers one Python object from every rank (rank order)."""
+    def __init__(self, nbytes: int, rank: int, world: int, device: torch.device, exchange, mode: Optional[str] = None):
+        """``exchange(obj) -> list`` gathers one Python object from every rank (rank order).
+
+        ``mode``: "ipc" = cudaMalloc + CUDA IPC (plain peer loads / stores only); "vmm" = CUDA virtual-memory
+        allocations shared through file descriptors; "nvls" = "vmm" plus one NVSwitch multicast object over
+        all ranks' heaps (``multicast_base()`` is then non-zero and kernels may use multimem instructions);
+        None = the environment variable MACO_HEAP if set, else "nvls" where the devices support it (and
+        MACO_NVLS is not 0), falling back to "vmm" and then "ipc". All ranks take the same decision."""
+        import os
         lib = N.lib()
-        P, U64 = ctypes.c_void_p, ctypes.c_ulonglong
+        P, U64, I = ctypes.c_void_p, ctypes.c_ulonglong, ctypes.c_int
         lib.maco_heap_create.restype = ctypes.c_int
         lib.maco_heap_create.argtypes = [U64, ctypes.POINTER(P), ctypes.c_char_p]
         lib.maco_heap_open.restype = ctypes.c_int
@@ -90,10 +141,44 @@ class SymmetricHeap:
         lib.maco_heap_close.argtypes = [P]
         lib.maco_heap_destroy.restype = ctypes.c_int
         lib.maco_heap_destroy.argtypes = [P]
+        lib.maco_vheap_supported.argtypes = [ctypes.POINTER(I)]
+        lib.maco_vheap_create.argtypes = [ctypes.POINTER(U64), I, I, I, ctypes.POINTER(P), ctypes.POINTER(I)]
+        lib.maco_vheap_import.argtypes = [I, I, ctypes.POINTER(P)]
+        lib.maco_vheap_mc_create.argtypes = [ctypes.POINTER(I)]
+        lib.maco_vheap_mc_import.argtypes = [I]
+        lib.maco_vheap_mc_map.argtypes = [ctypes.POINTER(P)]
         self._lib = lib
         self.rank, self.world, self.device = rank, world, torch.device(device)
         self.nbytes = (int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN
         torch.cuda.set_device(self.device)
+        self._mc_base = 0
+        mode = mode or os.environ.get("MACO_HEAP") or None
+        mc_flag = I(0)
+        fd_ok = bool(lib.maco_vheap_supported(ctypes.byref(mc_flag)))
+        nvls_ok = bool(mc_flag.value) and os.environ.get("MACO_NVLS", "1") != "0" and world > 1
+        if mode is None:
+            mode = "nvls" if (fd_ok and nvls_ok) else ("vmm" if fd_ok else "ipc")
+        if mode not in ("ipc", "vmm", "nvls"):
+            raise ValueError(f"unknown heap mode {mode!r}")
+        if mode != "ipc" and not fd_ok:
+            mode = "ipc"
+        if mode == "nvls" and not nvls_ok:
+            mode = "vmm"
+        # the ranks agree on the weakest mode any of them can offer
+        order = {"ipc": 0, "vmm": 1, "nvls": 2}
+        mode = min(exchange(mode), key=order.get)
+        self.mode = mode
+        if mode == "ipc":
+            self._init_ipc(exchange)
+        else:
+            self._init_vmm(exchange, want_multicast=(mode == "nvls"))
+        self._ranges = RangeAllocator(self.nbytes)
+        self._whole = torch.as_tensor(_Span(self._base, self.nbytes, self), device=self.device)
+        self._closed = False
+        exchange(b"ready")          # nobody touches a peer's heap before every rank has mapped it
+
+    def _init_ipc(self, exchange) -> None:
+        lib, P = self._lib, ctypes.c_void_p
         base = P()
         handle = ctypes.create_string_buffer(64)
         N.check(lib.maco_heap_create(self.nbytes, ctypes.byref(base), handle), "maco_heap_create")
@@ -101,16 +186,60 @@ class SymmetricHeap:
         handles = exchange(handle.raw)
         self._peer: List[int] = []
         for r, h in enumerate(handles):
-            if r == rank:
+            if r == self.rank:
                 self._peer.append(self._base)
             else:
                 pb = P()
                 N.check(lib.maco_heap_open(h, ctypes.byref(pb)), f"maco_heap_open(rank {r})")
                 self._peer.append(pb.value)
-        self._ranges = RangeAllocator(self.nbytes)
-        self._whole = torch.as_tensor(_Span(self._base, self.nbytes, self), device=self.device)
-        self._closed = False
-        exchange(b"ready")          # nobody touches a peer's heap before every rank has mapped it
+
+    def _init_vmm(self, exchange, want_multicast: bool) -> None:
+        import os
+        lib, P, I = self._lib, ctypes.c_void_p, ctypes.c_int
+        size = ctypes.c_ulonglong(self.nbytes)
+        base, fd = P(), I(-1)
+        N.check(lib.maco_vheap_create(ctypes.byref(size), self.rank, self.world, int(want_multicast), ctypes.byref(base),
+                                      ctypes.byref(fd)), "maco_vheap_create")
+        self.nbytes = int(size.value)
+        self._base = base.value
+        others = [r for r in range(self.world) if r != self.rank]
+        got = _exchange_fds(fd.value, others, self.rank, self.world, exchange, "heap")
+        self._peer = [0] * self.world
+        self._peer[self.rank] = self._base
+        for r in others:
+            pb = P()
+            N.check(lib.maco_vheap_import(r, got[r], ctypes.byref(pb)), f"maco_vheap_import(rank {r})")
+            self._peer[r] = pb.value
+            os.close(got[r])
+        exchange(b"imported")
+        os.close(fd.value)
+        if not want_multicast:
+            return
+        # multicast object: created by rank 0, joined by every device, then every rank binds its own allocation.
+        # A step that fails anywhere leaves the whole job on plain peer access (the ranks vote after each step).
+        def all_ok(rc: int) -> bool:
+            return all(v == 0 for v in exchange(int(rc)))
+        mc_fd = I(-1)
+        rc = lib.maco_vheap_mc_create(ctypes.byref(mc_fd)) if self.rank == 0 else 0
+        if not all_ok(rc):
+            return
+        got = _exchange_fds(mc_fd.value if self.rank == 0 else None, [0] if self.rank != 0 else [], self.rank, self.world,
+                            exchange, "mc")
+        rc = 0
+        if self.rank != 0:
+            rc = lib.maco_vheap_mc_import(got[0])
+            os.close(got[0])
+        ok = all_ok(rc)
+        if self.rank == 0:
+            os.close(mc_fd.value)
+        if not ok or not all_ok(lib.maco_vheap_mc_add_device()):
+            return
+        if not all_ok(lib.maco_vheap_mc_bind()):
+            return
+        mc = P()
+        if not all_ok(lib.maco_vheap_mc_map(ctypes.byref(mc))):
+            return
+        self._mc_base = mc.value
 
     # ------------------------------------------------------------------ allocation
     def alloc(self, shape, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
@@ -156,7 +285,7 @@ class SymmetricHeap:
 
     def multicast_base(self) -> int:
         """Multicast (NVLS) address of the heap; 0 = not bound (plain peer loads/stores are used)."""
-        return 0
+        return self._mc_base
 
     def peer_view(self, t: torch.Tensor, r: int) -> torch.Tensor:
         """The tensor at the same offset in rank ``r``'s heap (for tests and debugging)."""
@@ -169,11 +298,15 @@ class SymmetricHeap:
         if self._closed:
             return
         torch.cuda.synchronize(self.device)
-        for r, p in enumerate(self._peer):
-            if r != self.rank:
-                self._lib.maco_heap_close(p)
         self._whole = None
-        self._lib.maco_heap_destroy(self._base)
+        if self.mode == "ipc":
+            for r, p in enumerate(self._peer):
+                if r != self.rank:
+                    self._lib.maco_heap_close(p)
+            self._lib.maco_heap_destroy(self._base)
+        else:
+            self._lib.maco_vheap_destroy()
+        self._mc_base = 0
         self._closed = True
 
 
@@ -221,7 +354,7 @@ def init_heap(nbytes: Optional[int] = None) -> SymmetricHeap:
     if pgm.device.type != "cuda":
         raise RuntimeError("the symmetric heap needs CUDA devices")
     _current = SymmetricHeap(nbytes or config.comm_buffer_bytes, pgm.rank, pgm.world_size, pgm.device,
-                             pgm.all_gather_object)
+                             pgm.all_gather_object, mode=None if config.heap_mode == "auto" else config.heap_mode)
     return _current
 
 

@@ -8,6 +8,13 @@ from tests._dist import run_ranks
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 ENV = {"NCCL_NVLS_ENABLE": "0"}
+# the symmetric heap with and without the NVSwitch multicast binding (multimem tasks on / off); a box whose
+# GPUs cannot join a multicast object runs "nvls" as plain peer memory too
+heaps = pytest.mark.parametrize("heap_mode", ["nvls", "ipc"])
+
+
+def _env(heap_mode):
+    return dict(ENV, MACO_HEAP=heap_mode)
 _NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
 worlds = pytest.mark.parametrize("world", [pytest.param(w, marks=pytest.mark.skipif(_NGPU < w, reason=f"needs {w} GPUs"))
                                            for w in (2, 4, 8)])
@@ -26,6 +33,8 @@ def _collectives(rank, world):
     from maco_b200 import _native
     from maco_b200.parallel import collectives
     assert heap is not None and heap.world == world and maco.is_nvshmem_available()
+    import os
+    assert heap.mode in ("nvls", "vmm", "ipc") and (os.environ["MACO_HEAP"] != "ipc" or heap.mode == "ipc")
     # all-reduce, closed form P(P+1)/2; repeated to exercise the epoch logic
     for dtype, n in ((torch.float32, 1 << 20), (torch.bfloat16, 3 << 16)):
         t = heap.alloc((n,), dtype)
@@ -51,6 +60,34 @@ def _collectives(rank, world):
     torch.cuda.synchronize()
     assert torch.all(v == world * (world + 1) / 2)
     maco.nvshmem_barrier()
+    # the multimem forms against the peer-memory forms on the same data (only on a multicast-bound heap)
+    if heap.multicast_base():
+        g = torch.Generator(device="cuda").manual_seed(5 + rank)
+        data = torch.randn(1 << 18, device="cuda", generator=g)
+        for dtype in (torch.float32, torch.bfloat16, torch.float16):
+            a_mc, a_p2p = heap.alloc((1 << 18,), dtype), heap.alloc((1 << 18,), dtype)
+            a_mc.copy_(data)
+            a_p2p.copy_(data)
+            collectives.all_reduce(a_mc, multicast=True)
+            collectives.all_reduce(a_p2p, multicast=False)
+            torch.cuda.synchronize()
+            tol = 1e-5 if dtype == torch.float32 else 2e-2
+            assert torch.allclose(a_mc.float(), a_p2p.float(), atol=tol * world, rtol=tol), dtype
+        sh = heap.alloc((256, 512), torch.bfloat16)
+        sh.copy_(data[: 256 * 512].view(256, 512))
+        f_mc, f_p2p = heap.alloc((256 * world, 512), torch.bfloat16), heap.alloc((256 * world, 512), torch.bfloat16)
+        from maco_b200.parallel import fused
+        from maco_b200.ops.megakernel import ProgramBuilder
+        for full, mc in ((f_mc, True), (f_p2p, False)):
+            b = ProgramBuilder(heap.device, num_workers=8, heap=heap)
+            ready = collectives._open(b)
+            ev = fused.allgather_push(b, sh, full, fence=ready, multicast=mc)
+            collectives._wait_local(b, [(e_, c_, True, False) for e_, c_ in ev.row_events if c_])
+            prog = b.build()
+            for _ in range(2):
+                prog.run()
+            torch.cuda.synchronize()
+        assert torch.equal(f_mc, f_p2p)
     # all-gather
     shard = heap.alloc((256, 512), torch.bfloat16)
     full = heap.alloc((256 * world, 512), torch.bfloat16)
@@ -142,9 +179,10 @@ def _collectives(rank, world):
     maco.cleanup()
 
 
+@heaps
 @worlds
-def test_peer_collectives(world):
-    run_ranks(_collectives, world, env=ENV, timeout=150)
+def test_peer_collectives(world, heap_mode):
+    run_ranks(_collectives, world, env=_env(heap_mode), timeout=150)
 
 
 def _tp_mlp(rank, world):
@@ -169,9 +207,10 @@ def _tp_mlp(rank, world):
     maco.cleanup()
 
 
+@heaps
 @worlds
-def test_fused_tp_mlp_matches_reference(world):
-    run_ranks(_tp_mlp, world, env=ENV, timeout=150)
+def test_fused_tp_mlp_matches_reference(world, heap_mode):
+    run_ranks(_tp_mlp, world, env=_env(heap_mode), timeout=150)
 
 
 def _dp_backward(rank, world):
@@ -286,4 +325,5 @@ def _peer_loss(rank, world):
 
 
 def test_peer_loss_detected_before_the_next_launch():
-    run_ranks(_peer_loss, 2, env=ENV, timeout=100)
+    # plain peer memory: a rank must not leave while its heap is bound to a multicast object
+    run_ranks(_peer_loss, 2, env=_env("ipc"), timeout=100)
