@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--mode", default=os.environ.get("MACO_PERSISTENT_MODE", "static"), choices=["static", "dynamic"])
     ap.add_argument("--cta-pair", type=int, default=1, choices=[0, 1],
                     help="1: two-CTA GEMM tiles (tcgen05.mma.cta_group::2, the default); 0: one-CTA tiles")
+    ap.add_argument("--nvls-allgather", type=int, default=0, choices=[0, 1],
+                    help="1: push the all-gather with multimem.st through the NVSwitch multicast address")
     ap.add_argument("--tokens", type=int, default=TOKENS)
     ap.add_argument("--hidden", type=int, default=HIDDEN)
     ap.add_argument("--ffn", type=int, default=FFN)
@@ -162,7 +164,7 @@ def run_ours(args):
         maco.init(backend="nccl")
         heap = symm_heap.current_heap()
     layer = TPSwiGLUMLP(args.tokens, args.hidden, args.ffn, rank=rank, world=world, heap=heap, seed=0, mode=args.mode,
-                        cta_pair=bool(args.cta_pair))
+                        cta_pair=bool(args.cta_pair), nvls_allgather=bool(args.nvls_allgather))
     rows = args.tokens // world
     g = torch.Generator(device="cpu").manual_seed(1234 + rank)
     x_host = torch.randn(rows, args.hidden, generator=g).to(torch.bfloat16).pin_memory()
@@ -201,7 +203,9 @@ def run_ours(args):
             "config": {"model": "TP SwiGLU MLP forward (all-gather->GEMM, GEMM->reduce-scatter)", "global_batch": args.tokens,
                        "seq_len": args.tokens, "hidden": args.hidden, "ffn": args.ffn, "parallelism": f"tp{world}",
                        "l2": "per-GPU working set (activations + weights) exceeds the 126 MB L2; no flush",
-                       "scheduler": args.mode, "gemm_tiles": "two-CTA 256x256" if layer.program.cta_pair else "one-CTA 128x256"},
+                       "scheduler": args.mode, "gemm_tiles": "two-CTA 256x256" if layer.program.cta_pair else "one-CTA 128x256",
+                       "heap": (heap.mode + ("+multicast" if heap.multicast_base() else "")) if heap is not None else "none",
+                       "comm_workers": layer.program.num_comm_workers},
             "tflops_per_gpu": round(flops / world / (us * 1e-6) / 1e12, 1),
             "clocks": clocks,
             "e2e": {"value": round(us_e2e, 2), "unit": "us", "h2d_bytes_per_step": x_host.numel() * 2,

@@ -448,7 +448,10 @@ MACO_DEVICE bool comm_run(const Program& p, const MacoTaskDesc& d, int tid, int 
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
           const uint32_t i = base + (uint32_t)u * nthreads;
-          if (i < total) multimem_st_v4(dst + blk_off(i, vpr, a.dst_stride), v[u]);
+          if (i < total) {
+            if (a.nslots == 1) multimem_st_v4_weak(dst + blk_off(i, vpr, a.dst_stride), v[u]);
+            else multimem_st_v4(dst + blk_off(i, vpr, a.dst_stride), v[u]);
+          }
         }
       }
       return true;

@@ -379,6 +379,10 @@ MACO_DEVICE void multimem_st_v4(void* mc_ptr, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
                :: "l"(mc_ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+MACO_DEVICE void multimem_st_v4_weak(void* mc_ptr, uint4 v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               :: "l"(mc_ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 MACO_DEVICE void multimem_red_add_u32(uint32_t* mc_ptr, uint32_t v) {
   asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" :: "l"(mc_ptr), "r"(v) : "memory");
 }

@@ -31,7 +31,7 @@ class TPSwiGLUMLP:
     def __init__(self, tokens: int, hidden: int, ffn: int, *, rank: int = 0, world: int = 1, heap=None,
                  device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16, seed: int = 0,
                  mode: str = "static", trace: bool = False, weight_std: float = 0.02, num_workers: Optional[int] = None,
-                 comm_workers: Optional[int] = None, cta_pair: bool = True):
+                 comm_workers: Optional[int] = None, cta_pair: bool = True, nvls_allgather: bool = False):
         if tokens % (world * BM) or ffn % (world * 128):
             raise ValueError("tokens must be a multiple of world*128 and ffn of world*128")
         if world > 1 and heap is None:
@@ -51,11 +51,7 @@ class TPSwiGLUMLP:
             # one SM pushes roughly 25-30 GB/s into a peer; the shard has to reach world-1 peers before
             # they run out of local rows to work on
             # (8 GPUs, this layer: 12 workers 493 us, 16 workers 459-482 us, 24 workers 479 us)
-            # a multicast-bound heap sends the shard once (multimem.st): fewer SMs do the same job
-            if heap is not None and heap.multicast_base():
-                comm_workers = 4 if world <= 2 else 8
-            else:
-                comm_workers = 6 if world <= 2 else 16
+            comm_workers = 6 if world <= 2 else 16
         # two-CTA GEMM tiles: 256 x 256 per CTA pair (static queues only)
         cta_pair = cta_pair and mode == "static"
         b = ProgramBuilder(dev, num_workers=num_workers, mode=mode, heap=heap, trace=trace,
@@ -73,8 +69,9 @@ class TPSwiGLUMLP:
             self.staging = heap.alloc((world, self.rows_local, hidden), dtype)
             self.y_shard = torch.empty(self.rows_local, hidden, device=dev, dtype=dtype)
             fence = fused.epoch_fence_event(b)
-            eg = fused.allgather_push(b, self.x_shard, self.x_full, fence=fence)
-            order = fused.gathered_order(rank, world, self.rows_local // BM, bool(heap.multicast_base()))
+            nvls_allgather = nvls_allgather and bool(heap.multicast_base())
+            eg = fused.allgather_push(b, self.x_shard, self.x_full, fence=fence, multicast=nvls_allgather)
+            order = fused.gathered_order(rank, world, self.rows_local // BM, nvls_allgather)
             e1 = b.gemm(self.x_full, self.w_gate_up, self.h, epilogue="swiglu", a_ready=eg, m_blocks=order)
             _, eo = fused.gemm_reduce_scatter(b, self.h, self.w_down, self.staging, self.y_shard, a_ready=e1)
             fused.epoch_fence_signal(b, [(eo.all_event[0], eo.all_event[1], False, False),

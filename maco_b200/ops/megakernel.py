@@ -773,6 +773,9 @@ class Program:
         Collective: see ``SymmetricHeap.free``."""
         if self.heap is not None and self.d_events is not None and hasattr(self.heap, "free"):
             self.heap.free(self.d_events)
+            for buf in getattr(self, "heap_buffers", []):
+                self.heap.free(buf)
+            self.heap_buffers = []
         self.d_events = None
         self.num_tasks = 0
 
@@ -871,8 +874,9 @@ def _gemm_ok(node: TaskNode) -> bool:
 
 
 def can_lower(graph) -> bool:
-    """True when every node has a task form. Custom host callables and collectives over more than
-    one rank (outside the symmetric heap) are run by the stream runtime instead."""
+    """True when every node has a task form. Custom host callables, and collectives over more than one rank
+    when there is no symmetric heap (or for shapes the communication tasks cannot express), are run by the
+    stream runtime instead."""
     from ..comm.process_group import get_world_size
     if not graph._nodes:
         return False
@@ -887,12 +891,17 @@ def can_lower(graph) -> bool:
                 return False
             if any(x.dtype != n.inputs[0].dtype for x in n.inputs):
                 return False
-        elif t in (TaskType.ALLREDUCE, TaskType.BROADCAST, TaskType.NOP):
+        elif t == TaskType.NOP:
+            pass
+        elif t in (TaskType.ALLREDUCE, TaskType.BROADCAST, TaskType.ALL_TO_ALL, TaskType.ALLGATHER, TaskType.REDUCE_SCATTER):
+            if any(not x.is_contiguous() for x in n.inputs + n.outputs):
+                return False
             if world > 1:
-                return False
-        elif t in (TaskType.ALL_TO_ALL, TaskType.ALLGATHER, TaskType.REDUCE_SCATTER):
-            if world > 1 or any(not x.is_contiguous() for x in n.inputs + n.outputs):
-                return False
+                # more than one rank: the collective becomes communication tasks over the symmetric heap
+                from ..parallel.graph_collectives import can_lower_collective
+                from ..parallel.symm_heap import current_heap
+                if not can_lower_collective(n, current_heap()):
+                    return False
         else:
             return False
     return True
@@ -918,7 +927,32 @@ def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None)
     cta_pair = (mode == "static" and workers >= 4 and bool(gemm_nodes) and not any(_few_rows(n) for n in gemm_nodes)
                 and all(-(-_flat2d(n.inputs[0]).shape[0] // (2 * BM)) * -(-n.outputs[0].shape[-1] // 256) >= workers // 2
                         for n in gemm_nodes))
-    b = ProgramBuilder(graph.device, num_workers=workers, mode=mode, trace=trace, cta_pair=cta_pair)
+    from ..comm.process_group import get_world_size
+    _COLL = (TaskType.ALLREDUCE, TaskType.BROADCAST, TaskType.ALL_TO_ALL, TaskType.ALLGATHER, TaskType.REDUCE_SCATTER)
+    dist = get_world_size() > 1 and any(n.task_type in _COLL for n in graph._nodes)
+    heap, comm_workers = None, 0
+    if dist:
+        from ..parallel.symm_heap import current_heap
+        heap = current_heap()
+        comm_workers = graph_comm_workers(graph, workers)
+        mode = "static"
+    b = ProgramBuilder(graph.device, num_workers=workers, mode=mode, trace=trace, cta_pair=cta_pair and mode == "static",
+                       heap=heap, num_comm_workers=comm_workers)
+    ctx = None
+    fused_rs: Dict[int, TaskNode] = {}                         # linear node id -> the reduce_scatter it feeds
+    skip: Dict[int, bool] = {}
+    if dist:
+        from ..parallel import graph_collectives as gc
+        ctx = gc.DistContext(b)
+        consumers: Dict[int, List[TaskNode]] = {}
+        for n in graph._nodes:
+            for d in n.depends_on:
+                consumers.setdefault(d._node_id, []).append(n)
+        for n in graph._nodes:
+            cs = consumers.get(n._node_id, [])
+            if (len(cs) == 1 and cs[0].task_type == TaskType.REDUCE_SCATTER and len(cs[0].depends_on) == 1
+                    and gc.fusable_linear_reduce_scatter(n, cs[0], heap.world) and not _few_rows(n)):
+                fused_rs[n._node_id] = cs[0]
     produced: Dict[int, Tuple[TaskNode, RowEvents]] = {}       # node id -> events of its output
 
     def ready_of(node: TaskNode, t: torch.Tensor, rows: int) -> Tuple[Optional[RowEvents], List[tuple]]:
@@ -950,6 +984,15 @@ def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None)
             act = node.attrs.get("activation")
             bias = node.inputs[2] if node.attrs.get("has_bias") else None
             out2 = out.view(-1, out.shape[-1])
+            if node._node_id in fused_rs:
+                # linear -> reduce_scatter: partial tiles leave through the GEMM epilogue; the product itself is
+                # never written on this rank
+                rs = fused_rs[node._node_id]
+                gemm_ev, out_ev = gc.lower_linear_reduce_scatter(ctx, node, rs, aligned, extra)
+                produced[node._node_id] = (node, gemm_ev)
+                produced[rs._node_id] = (rs, out_ev)
+                skip[rs._node_id] = True
+                continue
             few_rows = (t == TaskType.LINEAR and bias is None and act in (None, "none", "swiglu") and x2.shape[0] <= BM
                         and w.shape[0] % 256 == 0 and x2.shape[1] % BK == 0 and w.shape[0] * w.shape[1] >= (1 << 22))
             if few_rows:
@@ -987,6 +1030,16 @@ def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None)
             ev = b.elementwise(int(t), x, out, in1=in1, in2=in2, rows=rows, cols=cols, in_ready=readies,
                                extra_waits=extra, **kw)
             produced[node._node_id] = (node, ev)
+        elif dist and t in _COLL:
+            if skip.get(node._node_id):
+                continue
+            x = node.inputs[0]
+            rows = x.numel() // max(1, x.shape[-1] if x.dim() else 1)
+            aligned, extra = ready_of(node, x, rows)
+            fn = {TaskType.ALLGATHER: gc.lower_allgather, TaskType.REDUCE_SCATTER: gc.lower_reduce_scatter,
+                  TaskType.ALLREDUCE: gc.lower_allreduce, TaskType.BROADCAST: gc.lower_broadcast,
+                  TaskType.ALL_TO_ALL: gc.lower_all_to_all}[t]
+            produced[node._node_id] = (node, fn(ctx, node, aligned, extra))
         elif t in (TaskType.ALL_TO_ALL, TaskType.ALLGATHER, TaskType.REDUCE_SCATTER):
             # world size 1: the collective degenerates to a copy
             x = node.inputs[0]
@@ -1004,4 +1057,28 @@ def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None)
             produced[node._node_id] = (node, RowEvents(rows=-1, block=BM, row_events=[], all_event=(e, 1)))
         else:
             raise NotImplementedError(f"no task form for {t.name}")
-    return b.build()
+    if ctx is not None:
+        ctx.finish()
+    prog = b.build()
+    if ctx is not None:
+        prog.heap_buffers = ctx.heap_buffers
+    return prog
+
+
+def graph_comm_workers(graph, workers: int) -> int:
+    """Communication workers of a multi-rank graph program: the REMOTE_SCHEDULER share of the graph's SM
+    configuration (``graph.sm_config``, an ``SMConfig``) when the user set one, else ``config.sm_policy``
+    ("auto": the SMManager's automatic split; "compute": none; a number: that many)."""
+    from ..config import config
+    from ..core.sm_manager import SMManager
+    smc = getattr(graph, "sm_config", None)
+    policy = str(config.sm_policy).lower()
+    if smc is not None:
+        n = SMManager(smc, device=graph.device).get_worker_config()["num_remote_schedulers"]
+    elif policy.isdigit():
+        n = int(policy)
+    elif policy in ("compute", "none"):
+        n = 0
+    else:
+        n = SMManager(device=graph.device).get_worker_config()["num_remote_schedulers"]
+    return max(0, min(n, workers - 2))

@@ -128,7 +128,8 @@ def all_reduce(t: torch.Tensor, avg: bool = False, multicast: Optional[bool] = N
             raise ValueError("all-reduce buffers must be a multiple of 16 bytes")
         chunk = 128 << 10
         n_chunks = -(-nbytes // chunk)
-        b = _builder(heap, workers=max(1, min(32, -(-n_chunks // heap.world))))
+        # nothing else runs beside a stand-alone collective: one chunk per worker, every SM if there are enough chunks
+        b = _builder(heap, workers=max(1, min(N.lib().maco_sm_count(), -(-n_chunks // heap.world))))
         ready = _open(b)
         done = b.new_event()
         off = heap.offset_of(t)
@@ -150,7 +151,7 @@ def all_reduce(t: torch.Tensor, avg: bool = False, multicast: Optional[bool] = N
         # staging of its own per program: a faster rank's next call (another program) may already be storing
         # into the owner's slots while the owner still sums this call's
         staging = heap.alloc((heap.world * per_owner * chunk,), torch.uint8)
-        b = _builder(heap, workers=max(1, min(32, nbytes >> 18)))
+        b = _builder(heap, workers=max(1, min(N.lib().maco_sm_count(), 2 * n_chunks)))
         fence = fused.epoch_fence_event(b)
         done, n = fused.allreduce_push_tasks(b, t.view(-1), staging, avg=avg, chunk_bytes=chunk, fence=fence)
         fused.epoch_fence_signal(b, [(done, n, True, False)])

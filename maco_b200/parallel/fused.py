@@ -55,10 +55,12 @@ def allgather_push(b: ProgramBuilder, shard: torch.Tensor, gathered: torch.Tenso
     ``shard`` may BE that slice of this rank's ``gathered`` (no local copy is made then, and the
     local blocks carry an always-true condition). With plain peer memory: one task per (destination,
     chunk), ordered by when the destination needs the rows (rank r-1 consumes this shard first, then
-    r-2, ...). With a multicast-bound heap (``multicast`` None = use it when the heap has one): one task
-    per chunk stores the rows ONCE to the NVSwitch multicast address (multimem.st) and bumps the block's
-    counter on every rank with one multimem.red; the shard leaves the GPU once instead of world-1 times,
-    and every rank receives block j of every shard at about the same time (see ``gathered_order``).
+    r-2, ...). ``multicast=True`` (needs a multicast-bound heap): one task per chunk stores the rows ONCE to
+    the NVSwitch multicast address (multimem.st) and bumps the block's counter on every rank with one
+    multimem.red; the shard leaves the GPU once instead of world-1 times, and every rank receives block j of
+    every shard at about the same time (see ``gathered_order``). It is opt-in: the 128 general threads of a
+    worker reach about 3 GB/s with 16-byte multimem.st (2 GPUs, measured), against 11-17 GB/s per worker for
+    the bulk-copy engine's peer stores, so the multicast form only pays with many destinations.
     """
     heap = b.heap
     rank, world = heap.rank, heap.world
@@ -68,14 +70,15 @@ def allgather_push(b: ProgramBuilder, shard: torch.Tensor, gathered: torch.Tenso
     if BM % chunk_rows:
         raise ValueError("chunk_rows must divide 128")
     row_bytes = cols * shard.element_size()
-    s_off, g_off = heap.offset_of(shard), heap.offset_of(gathered)
-    in_place = s_off == g_off + rank * rows * row_bytes
+    # the source is read by this rank only: it may live outside the heap (its offset from the heap base then wraps)
+    g_off = heap.offset_of(gathered)
+    s_off = heap.offset_of(shard) if heap.owns(shard) else (shard.data_ptr() - heap.peer_base(rank)) % (1 << 64)
+    in_place = heap.owns(shard) and s_off == g_off + rank * rows * row_bytes
     blocks = world * rows // BM
     events = [b.new_event() for _ in range(blocks)]
     all_ev = b.new_event()
     per_block = BM // chunk_rows
-    if multicast is None:
-        multicast = bool(heap.multicast_base())
+    multicast = bool(multicast)
     if multicast and not heap.multicast_base():
         raise ValueError("the symmetric heap has no multicast binding")
     if multicast:
@@ -146,7 +149,8 @@ def rotated_blocks(rank: int, world: int, blocks_per_rank: int, own_last: bool =
 
 def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, staging: torch.Tensor,
                         out: torch.Tensor, *, a_ready: Optional[RowEvents] = None, bn: int = 256,
-                        reduce_rows: Optional[int] = None, scale: float = 1.0) -> Tuple[RowEvents, RowEvents]:
+                        reduce_rows: Optional[int] = None, scale: float = 1.0,
+                        extra_waits: Sequence[Tuple[int, int, bool, bool]] = ()) -> Tuple[RowEvents, RowEvents]:
     """``out[rows_local, N] = reduce_scatter(a @ w.T)`` with the partial tiles leaving through the
     GEMM epilogue. ``staging`` is a heap tensor [world, rows_local, N] (slot = source rank).
 
@@ -187,7 +191,7 @@ def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, sta
             return dict(peer=owner, out_off=st_off + rank * slot_bytes, row_off=-(owner * rows_local), signal_peer=owner,
                         signal_peer_event=part_events[mb % blocks_per_rank])
 
-        gemm_ev = b.gemm(a, w, staging[0], a_ready=a_ready, bn=bn, per_tile=per_tile2, m_blocks=order)
+        gemm_ev = b.gemm(a, w, staging[0], a_ready=a_ready, bn=bn, per_tile=per_tile2, m_blocks=order, extra_waits=extra_waits)
         b.keepalive += [staging, out]
         own = gemm_ev.row_events[own_first: own_first + blocks_per_rank]
         return gemm_ev, RowEvents(rows=rows_local, block=BM, row_events=list(own), all_event=gemm_ev.all_event)
@@ -203,7 +207,7 @@ def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, sta
         return dict(peer=owner, out_off=st_off + rank * slot_bytes, row_off=-(owner * rows_local), signal_peer=owner,
                     signal_peer_event=part_events[mb % blocks_per_rank])
 
-    gemm_ev = b.gemm(a, w, staging[0], a_ready=a_ready, bn=bn, per_tile=per_tile, m_blocks=order)
+    gemm_ev = b.gemm(a, w, staging[0], a_ready=a_ready, bn=bn, per_tile=per_tile, m_blocks=order, extra_waits=extra_waits)
     # owner-side reduction of the `world` slots, fp32 accumulation
     out_events = [b.new_event() for _ in range(blocks_per_rank)]
     all_ev = b.new_event()

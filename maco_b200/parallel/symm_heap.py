@@ -153,6 +153,8 @@ class SymmetricHeap:
         torch.cuda.set_device(self.device)
         self._mc_base = 0
         mode = mode or os.environ.get("MACO_HEAP") or None
+        if mode == "auto":
+            mode = None
         mc_flag = I(0)
         fd_ok = bool(lib.maco_vheap_supported(ctypes.byref(mc_flag)))
         nvls_ok = bool(mc_flag.value) and os.environ.get("MACO_NVLS", "1") != "0" and world > 1

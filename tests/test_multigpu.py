@@ -327,3 +327,83 @@ def _peer_loss(rank, world):
 def test_peer_loss_detected_before_the_next_launch():
     # plain peer memory: a rank must not leave while its heap is bound to a multicast object
     run_ranks(_peer_loss, 2, env=_env("ipc"), timeout=100)
+
+
+def _graph_collectives(rank, world):
+    """Multi-rank TaskGraphs run inside ONE launch of the persistent kernel: all-gather -> GEMM, GEMM ->
+    reduce-scatter, all-reduce, all-to-all and broadcast nodes, with tensors inside and outside the heap."""
+    maco, heap = _setup(rank, world, heap_mb=256)
+    import torch.distributed as dist
+    from maco_b200 import _native, ops
+    dt = torch.bfloat16
+    F = torch.nn.functional
+    tokens, hidden, ffn = 128 * world * 2, 512, 1024
+    rows = tokens // world
+    torch.manual_seed(3)
+    x_full = torch.randn(tokens, hidden, device="cuda", dtype=dt)                  # same on every rank
+    g = torch.Generator(device="cuda").manual_seed(10 + rank)
+    wg = torch.randn(ffn // world, hidden, device="cuda", dtype=dt, generator=g) * 0.05
+    wu = torch.randn(ffn // world, hidden, device="cuda", dtype=dt, generator=g) * 0.05
+    wd = torch.randn(hidden, ffn // world, device="cuda", dtype=dt, generator=g) * 0.05
+    for in_heap in (True, False):
+        x_shard = heap.alloc((rows, hidden), dt) if in_heap else torch.empty(rows, hidden, device="cuda", dtype=dt)
+        x_shard.copy_(x_full[rank * rows:(rank + 1) * rows])
+        gr = maco.TaskGraph()
+        ag = gr.allgather(x_shard)
+        h = gr.linear(ag.output, ops.interleave_gate_up(wg, wu), activation="swiglu")
+        y = gr.linear(h.output, wd)
+        rs = gr.reduce_scatter(y.output)
+        gr.compile()
+        assert gr.runtime_kind == "persistent", gr.runtime_kind
+        hf = (F.silu(x_full.float() @ wg.float().t()) * (x_full.float() @ wu.float().t())).to(dt).float()
+        part = hf @ wd.float().t()
+        dist.all_reduce(part)
+        ref = part[rank * rows:(rank + 1) * rows]
+        for it in range(3):
+            gr.execute()
+            torch.cuda.synchronize()
+            assert torch.equal(ag.output, x_full), (in_heap, it)
+            err = (rs.output.float() - ref).abs().max().item()
+            assert err < 3e-2 * max(1.0, ref.abs().max().item()), (in_heap, it, err)
+    # all-reduce (sum and avg, inside and outside the heap), broadcast, flat and 4-D all-to-all in one graph
+    gr = maco.TaskGraph()
+    a_h = heap.alloc((1 << 16,), torch.float32)
+    a_o = torch.empty(3000, device="cuda", dtype=torch.float32)                    # 12000 bytes: a multiple of 16
+    bc = heap.alloc((4096,), torch.float32)
+    flat = torch.empty(world * 64, 32, device="cuda", dtype=torch.float32)
+    B, s, H, D = 2, 8, 4 * world, 64
+    whole = torch.arange(B * s * world * H * D, dtype=torch.float32, device="cuda").reshape(B, s * world, H, D)
+    q4 = torch.empty(B, s, H, D, device="cuda", dtype=torch.float32)
+    n1 = gr.allreduce(a_h)
+    n2 = gr.allreduce(a_o, op="avg")
+    n3 = gr.broadcast(bc, src=world - 1)
+    n4 = gr.all_to_all(flat, scatter_dim=0, gather_dim=0)
+    n5 = gr.all_to_all(q4, scatter_dim=2, gather_dim=1)
+    n6 = gr.all_to_all(n5.output, scatter_dim=1, gather_dim=2)
+    gr.compile()
+    assert gr.runtime_kind == "persistent", gr.runtime_kind
+    hp = H // world
+    for it in range(3):
+        a_h.fill_(float(rank + 1 + it))
+        a_o.fill_(float(rank + it))
+        bc.fill_(float(10 * rank + it))
+        for d in range(world):
+            flat[d * 64:(d + 1) * 64].fill_(float(100 * rank + d + it))
+        q4.copy_(whole[:, rank * s:(rank + 1) * s] + it)
+        gr.execute()
+        torch.cuda.synchronize()
+        assert torch.all(a_h == sum(r + 1 + it for r in range(world))), it
+        assert torch.allclose(a_o, torch.full_like(a_o, sum(r + it for r in range(world)) / world)), it
+        assert torch.all(bc == 10 * (world - 1) + it), it
+        for s_ in range(world):
+            assert torch.all(n4.output[s_ * 64:(s_ + 1) * 64] == 100 * s_ + rank + it), (it, s_)
+        assert torch.equal(n5.output, whole[:, :, rank * hp:(rank + 1) * hp] + it), it
+        assert torch.equal(n6.output, q4), it
+    assert _native.status() == 0
+    maco.cleanup()
+
+
+@heaps
+@worlds
+def test_multirank_taskgraph_runs_in_the_persistent_kernel(world, heap_mode):
+    run_ranks(_graph_collectives, world, env=_env(heap_mode), timeout=150)
