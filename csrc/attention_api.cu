@@ -62,6 +62,17 @@ int check_and_fill(AttnParams& p, const void* q, const void* k, const void* v, v
   if (Hkv <= 0 || Hq % Hkv != 0 || Hq / Hkv > kAttnMaxG) { maco_host::set_error("attention_decode: need 1..8 query heads per KV head"); return -1; }
   if (dtype != MACO_DT_BF16 && dtype != MACO_DT_F16) { maco_host::set_error("attention_decode: bf16 or fp16 only"); return -1; }
   if (splits < 1 || S < 1 || B < 1) { maco_host::set_error("attention_decode: empty problem"); return -1; }
+  // the kernels read K / V rows and q with 16-byte vector loads and launch B * Hkv * splits CTAs
+  if (((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(q) |
+        reinterpret_cast<uintptr_t>(out)) & 15) != 0) {
+    maco_host::set_error("attention_decode: q, k, v and out must be 16-byte aligned");
+    return -1;
+  }
+  if (kv_batch_stride % 8 != 0 || kv_head_stride % 8 != 0) {
+    maco_host::set_error("attention_decode: KV batch and head strides must be multiples of 8 elements (16 bytes)");
+    return -1;
+  }
+  if ((long long)B * Hkv * splits > 2147483647LL) { maco_host::set_error("attention_decode: B * Hkv * splits exceeds the grid limit"); return -1; }
   p.q = q; p.k = k; p.v = v; p.out = out; p.scratch = scratch; p.B = B; p.Hkv = Hkv; p.G = Hq / Hkv; p.S = S;
   p.splits = splits; p.dtype = dtype; p.kv_batch_stride = kv_batch_stride; p.kv_head_stride = kv_head_stride;
   p.scale = scale;

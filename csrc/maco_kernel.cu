@@ -60,19 +60,24 @@ static_assert(MkPairLayout::kRingBytes == MkLayout::kRingBytes && MkPairLayout::
 
 __device__ __forceinline__ void general_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+__device__ __forceinline__ bool is_gemm_type(uint32_t type) { return type == MACO_TASK_MATMUL || type == MACO_TASK_LINEAR; }
+
 __device__ __forceinline__ bool aborted(const MacoProgram& p) { return ld_relaxed_gpu_u32(p.abort_word) == p.epoch; }
 
 __device__ void report_failure(const MacoProgram& p, uint32_t status, uint32_t task, uint32_t event,
                                volatile uint32_t* cta_abort) {
   if (cta_abort != nullptr) *cta_abort = 1;
-  if (ld_relaxed_gpu_u32(p.abort_word) != p.epoch) {
-    st_relaxed_gpu_u32(p.abort_word, p.epoch);
-    if (p.status != nullptr) {
-      volatile MacoStatusBlock* s = p.status;
-      s->task = task; s->event = event; s->cta = blockIdx.x; s->rank = (uint32_t)p.rank;
-      __threadfence_system();
-      s->status = s->status | status;
-    }
+  // The first CTA to fail claims the abort word with one compare-and-swap (it holds the epoch of an aborted
+  // launch, anything else otherwise) and is the only one to fill the status block, so {task, event, cta}
+  // always describe the same failure.
+  const uint32_t seen = ld_relaxed_gpu_u32(p.abort_word);
+  if (seen == p.epoch) return;
+  if (atomicCAS(p.abort_word, seen, p.epoch) != seen) return;
+  if (p.status != nullptr) {
+    volatile MacoStatusBlock* s = p.status;
+    s->task = task; s->event = event; s->cta = blockIdx.x; s->rank = (uint32_t)p.rank;
+    __threadfence_system();
+    s->status = s->status | status;
   }
 }
 
@@ -162,6 +167,36 @@ __device__ void signal_done(const MacoProgram& p, const MacoTaskDesc& d) {
   }
 }
 
+// Debug re-check of a descriptor on the device (MacoProgram.debug): the same conditions the host checks when the
+// program is built. A descriptor that fails is not run; the launch reports BAD_TASK.
+__device__ bool desc_ok(const MacoProgram& p, const MacoTaskDesc& d) {
+  for (int j = 0; j < 2; ++j) {
+    if (d.wait_event[j] >= (int)p.num_events || d.signal_event[j] >= (int)p.num_events) return false;
+  }
+  if (d.signal_peer_event >= (int)p.num_events) return false;
+  if (d.signal_peer >= p.world || d.signal_peer < -4) return false;
+  if (is_gemm_type(d.type)) {
+    const MacoGemmArgs& g = d.u.gemm;
+    if (g.tmap_a >= p.num_tmaps || g.tmap_b >= p.num_tmaps || g.epi >= p.num_epis) return false;
+    if (g.peer >= p.world || g.peer < -2) return false;
+    if (g.peer != -1 && (p.heap_bytes == 0 || g.out_off >= p.heap_bytes)) return false;
+    return g.k_blocks >= 0 && (g.bn == 128 || g.bn == 256);
+  }
+  if (d.type >= 200 && d.type < 300 && d.u.comm.rows != 0) {
+    const MacoCommArgs& a = d.u.comm;
+    if (a.row_bytes % 16 != 0 || a.peer >= p.world || a.peer < -3) return false;
+    const uint64_t ext = (uint64_t)(a.rows - 1) * a.dst_stride + a.row_bytes;
+    const bool writes_heap = a.local_ptr == nullptr && a.op != MACO_COMM_REDUCE_LOCAL;
+    if (writes_heap && (p.heap_bytes == 0 || a.dst_off + ext > p.heap_bytes)) return false;
+    const uint64_t sext = (uint64_t)(a.rows - 1) * a.src_stride + a.row_bytes;
+    const bool reads_peer = a.op == MACO_COMM_REDUCE_PULL || a.op == MACO_COMM_ALLREDUCE || a.op == MACO_COMM_PULL ||
+                            a.op == MACO_COMM_ALLREDUCE_MC;
+    if (reads_peer && (p.heap_bytes == 0 || a.src_off + sext > p.heap_bytes)) return false;
+    if ((a.op == MACO_COMM_PUSH_MC || a.op == MACO_COMM_ALLREDUCE_MC) && p.mc_heap == nullptr) return false;
+  }
+  return true;
+}
+
 // Next entry of this worker's queue. false = aborted / timed out.
 __device__ bool fetch_task(const MacoProgram& p, uint32_t w, uint32_t i, uint32_t q_base, uint32_t& task,
                            volatile uint32_t* cta_abort) {
@@ -212,6 +247,7 @@ __device__ void producer_role_pair(const MacoProgram& p, uint32_t w, uint32_t q_
     task &= MACO_QUEUE_INDEX_MASK;
     const MacoTaskDesc& d = p.tasks[task];
     if (!is_gemm(d.type)) continue;
+    if (p.debug != 0 && !desc_ok(p, d)) { report_failure(p, MACO_STATUS_BAD_TASK, task, d.type, c.abort_word); ok = false; break; }
     if (!wait_deps(p, d, task, c.abort_word, nullptr)) { ok = false; break; }
     const MacoGemmArgs& g = d.u.gemm;
     fence_proxy_async_all();           // operands were written by generic-proxy stores of other CTAs
@@ -294,6 +330,7 @@ __device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base,
       continue;
     }
     if (!is_gemm(d.type)) continue;
+    if (p.debug != 0 && !desc_ok(p, d)) { report_failure(p, MACO_STATUS_BAD_TASK, task, d.type, c.abort_word); ok = false; break; }
     if (!wait_deps(p, d, task, c.abort_word, nullptr)) { ok = false; break; }
     const MacoGemmArgs& g = d.u.gemm;
     // run-time guarded tile: every role reads the same (final) count after the task's conditions hold
@@ -420,6 +457,10 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
     const MacoTaskDesc& d = p.tasks[task];   // read in place (L1/L2 resident): a register copy would cost 32 registers
     uint64_t t_start = 0, wait_ns = 0;
     if (leader && p.trace != nullptr) t_start = globaltimer_ns();
+    if (p.debug != 0 && !desc_ok(p, d)) {            // uniform over the 128 threads (same descriptor)
+      if (leader) report_failure(p, MACO_STATUS_BAD_TASK, task, d.type, c.abort_word);
+      break;
+    }
     bool skip_tile = false;
     if (is_gemm(d.type) && (d.flags & MACO_TF_COUNTED)) {
       if (leader) {

@@ -221,7 +221,9 @@ struct MacoProgram {
   uint32_t static_stride, mode, epoch;
   int32_t rank, world;
   uint32_t cta_group;             /* 1: one-CTA GEMM tiles; 2: every GEMM task is half of a two-CTA tile (cluster launch) */
-  uint32_t _pad;
+  uint32_t debug;                 /* non-zero: workers re-check every descriptor (events, peers, heap extents) before running it */
+  uint64_t heap_bytes;            /* size of each rank's symmetric heap (0: no heap) */
+  uint32_t num_events, num_tmaps, num_epis, _pad;
 };
 
 #ifdef __cplusplus

@@ -26,14 +26,14 @@ def _parse_size(text) -> int:
 @dataclass
 class MacoConfig:
     backend: str = "peer"                 # "peer" | "nccl" | "gloo"
-    sm_policy: str = "auto"               # how SMs are split between compute / comm / scheduler roles
-    overlap_strategy: str = "auto"        # "auto" | "wave" | "none"
+    sm_policy: str = "auto"               # communication workers of multi-rank graphs: "auto" (SMManager) | "compute" (none) | "<n>"
+    overlap_strategy: str = "auto"        # "auto" | "wave" | "pipeline" | "none": stream-level overlap of comm nodes / OverlapRuntime default
     comm_buffer_size: str = "256MB"       # symmetric heap size per rank
     heap_mode: str = "auto"               # "auto" | "nvls" (multicast-bound) | "vmm" (shared descriptors) | "ipc" (cudaMalloc + IPC)
-    use_pinned_memory: bool = True
+    use_pinned_memory: bool = True        # host staging of the input feed / result read-back goes through pinned memory
     runtime: str = "auto"                 # "auto" | "persistent" | "stream" | "reference"
     wait_budget_ms: float = 2000.0        # every device-side wait gives up after this long
-    debug: bool = False
+    debug: bool = False                   # kernels re-check every task descriptor before running it (BAD_TASK on failure)
     profile: bool = False
     verbose: bool = False
 

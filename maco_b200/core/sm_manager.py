@@ -1,9 +1,11 @@
 """SM role assignment: which SMs compute, which schedule, which serve communication.
 
 API of the reference's maco/core/sm_manager.py:14-227 (``Role``, ``SMAssignment``, ``SMConfig``,
-``SMManager``, ``auto_config``). In the reference the numbers are stored and never enforced; here
-``SMManager.get_worker_config()`` is what the persistent kernel is launched with: one CTA per SM,
-CTA index ranges mapped to the worker / scheduler / communication roles.
+``SMManager``, ``auto_config``). In the reference the numbers are stored and never enforced. Here a multi-rank
+``TaskGraph`` lowered to the persistent kernel takes its number of communication workers from
+``SMManager.get_worker_config()["num_remote_schedulers"]`` (the graph's ``sm_config`` attribute when set, else the
+automatic split, see ``ops.megakernel.graph_comm_workers``), and ``PersistentContext`` its worker count; the
+hand-assembled model programs (``maco_b200.models``) pass their own measured counts.
 
 B200 sizing (148 SMs): the scheduler needs one CTA; NVLink 5 copies saturate with roughly 8-16
 CTAs issuing 16-byte peer stores, so the communication share is far smaller than the

@@ -58,7 +58,8 @@ class _ProgramStruct(ctypes.Structure):
         ("num_tasks", ctypes.c_uint32), ("num_groups", ctypes.c_uint32), ("num_workers", ctypes.c_uint32),
         ("num_comm_workers", ctypes.c_uint32), ("static_stride", ctypes.c_uint32), ("mode", ctypes.c_uint32),
         ("epoch", ctypes.c_uint32), ("rank", ctypes.c_int32), ("world", ctypes.c_int32),
-        ("cta_group", ctypes.c_uint32), ("_pad", ctypes.c_uint32),
+        ("cta_group", ctypes.c_uint32), ("debug", ctypes.c_uint32), ("heap_bytes", ctypes.c_uint64),
+        ("num_events", ctypes.c_uint32), ("num_tmaps", ctypes.c_uint32), ("num_epis", ctypes.c_uint32), ("_pad", ctypes.c_uint32),
     ]
 
 
@@ -632,11 +633,59 @@ class ProgramBuilder:
         return Program(self)
 
 
+class DescriptorError(ValueError):
+    """A task descriptor points outside the tables or the heap it may touch (found when the program is built)."""
+
+
+def validate_tasks(b: "ProgramBuilder") -> None:
+    """Host-side check of every descriptor: event, tensor-map and epilogue indices inside their tables, peer ranks
+    inside the world, and every block a communication task or a GEMM tile writes into (or reads from) a PEER's
+    heap inside the heap. The kernel repeats the same checks per task when ``config.debug`` is set."""
+    n_ev, n_tm, n_ep = max(1, b.num_events), len(b.tmaps), len(b.epis)
+    world = b.heap.world if b.heap is not None else 1
+    heap_bytes = b.heap.nbytes if b.heap is not None else 0
+    for i, t in enumerate(b.tasks):
+        def bad(msg):
+            raise DescriptorError(f"task {i} (type {t['type']}): {msg}")
+        for e in list(t["wait_event"]) + list(t["signal_event"]) + [t["signal_peer_event"]]:
+            if e >= n_ev:
+                bad(f"event {e} outside the table of {n_ev}")
+        if t["signal_peer"] >= world or t["signal_peer"] < -4:
+            bad(f"signal_peer {t['signal_peer']} outside the world of {world}")
+        raw = t["raw"]
+        if t["type"] in (100, 101) and len(raw) >= 60:
+            tm_a, tm_b, epi, _, _, _, _, _, k_blocks, _, peer, _, out_off, bn = struct.unpack_from("<HHHBBiiiiIiqQI", raw)
+            if tm_a >= n_tm or tm_b >= n_tm or epi >= n_ep:
+                bad("tensor-map or epilogue index outside its table")
+            if peer >= world or peer < -2:
+                bad(f"destination rank {peer} outside the world of {world}")
+            if peer != -1 and out_off >= heap_bytes:
+                bad(f"tile destination offset {out_off} outside the heap of {heap_bytes} bytes")
+            if bn not in (128, 256) or k_blocks < 0:
+                bad("bad tile width or k-block count")
+        elif 200 <= t["type"] < 300 and len(raw) >= 72:
+            src_off, dst_off, s_str, d_str, row_bytes, rows, _, peer, op, _, _, local_ptr = struct.unpack_from("<QQQQIIiiiiQQ", raw)
+            if rows == 0:
+                continue
+            if row_bytes % 16:
+                bad("rows must be whole 16-byte vectors")
+            if peer >= world or peer < -3:
+                bad(f"peer {peer} outside the world of {world}")
+            ext = (rows - 1) * d_str + row_bytes
+            if local_ptr == 0 and op != COMM_REDUCE_LOCAL and dst_off + ext > heap_bytes:
+                bad(f"destination block [{dst_off}, {dst_off + ext}) outside the heap of {heap_bytes} bytes")
+            if op in (COMM_REDUCE_PULL, COMM_ALLREDUCE, COMM_PULL, COMM_ALLREDUCE_MC) and src_off + (rows - 1) * s_str + row_bytes > heap_bytes:
+                bad("source block read from peers lies outside the heap")
+            if op in (COMM_PUSH_MC, COMM_ALLREDUCE_MC) and not (b.heap is not None and b.heap.multicast_base()):
+                bad("multimem task without a multicast-bound heap")
+
+
 class Program:
     """Device tables of a built program plus the launch call."""
 
     def __init__(self, b: ProgramBuilder):
         lib = _lib()
+        validate_tasks(b)
         self.device = b.device
         self.mode = b.mode
         self.num_workers = b.num_workers
@@ -744,6 +793,10 @@ class Program:
         ps.static_stride, ps.mode, ps.epoch = stride, self.mode, 0
         ps.rank, ps.world = 0, 1
         ps.cta_group = 2 if b.cta_pair else 1
+        from ..config import config as _cfg
+        ps.debug = 1 if _cfg.debug else 0
+        ps.heap_bytes = b.heap.nbytes if b.heap is not None else 0
+        ps.num_events, ps.num_tmaps, ps.num_epis = self.num_events + 64, max(1, len(b.tmaps)), max(1, len(b.epis))
         self.cta_pair = b.cta_pair
         if b.heap is not None:
             ps.rank, ps.world = b.heap.rank, b.heap.world
@@ -788,6 +841,15 @@ class Program:
             self.d_heads.zero_(); self.d_tails.zero_()
         self.epoch = 0
         N.status(clear=True)
+
+    def event_signal(self, event: int):
+        """The counter behind one of the program's events as a ``DeviceSignal``: tasks bump it with release
+        semantics when they finish; after launch number E it holds E times the event's per-launch count. Lets
+        host code (tests, debugging, a polling thread) observe progress inside a running launch."""
+        from ..sync.signal_wait import DeviceSignal
+        if not 0 <= event < self.num_events:
+            raise IndexError(f"event {event} outside the table of {self.num_events}")
+        return DeviceSignal(self.d_events[event:event + 1])
 
     def tasks_completed(self) -> int:
         return int(self.d_ctrl[1].item())

@@ -153,8 +153,9 @@ class DeviceSignal:
     """A monotonically increasing 32-bit counter in device memory used as a signal by kernels.
 
     ``tensor`` is a 1-element int32 CUDA tensor (inside the symmetric heap when peers must see
-    it). Kernels of this package add to it with release semantics and wait on it with acquire
-    semantics and a time budget; the host can read it for tests and debugging.
+    it). ``Program.event_signal(e)`` hands out the counters of a persistent-kernel program's events in this
+    form: tasks add to them with release semantics and wait on them with acquire semantics and a time
+    budget; the host can read them, or wait on them with a bound, while a launch is running.
     """
 
     def __init__(self, tensor: Optional[torch.Tensor] = None, device=None):
@@ -173,3 +174,23 @@ class DeviceSignal:
 
     def reset(self) -> None:
         self.tensor.zero_()
+
+    def wait_value(self, value: int, timeout_s: float = 10.0, poll_s: float = 1e-4) -> bool:
+        """Host-side bounded wait until the counter reaches ``value`` (wrap-safe). Reads go through a side stream,
+        so a kernel that is still running on the current stream does not block them. Returns False on timeout."""
+        import time
+        if not self.tensor.is_cuda:
+            return ((int(self.tensor.item()) - value) & 0xFFFFFFFF) < 0x80000000
+        if not hasattr(self, "_side"):
+            self._side = torch.cuda.Stream(device=self.tensor.device)
+            self._host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        t0 = time.monotonic()
+        while True:
+            with torch.cuda.stream(self._side):
+                self._host.copy_(self.tensor, non_blocking=True)
+            self._side.synchronize()
+            if ((int(self._host.item()) - value) & 0xFFFFFFFF) < 0x80000000:
+                return True
+            if time.monotonic() - t0 > timeout_s:
+                return False
+            time.sleep(poll_s)

@@ -119,8 +119,14 @@ class OverlapRuntime:
         self.scheduler = OverlapScheduler(device)
 
     def execute_overlap(self, compute_tasks: list, comm_tasks: list, compute_executor: Callable,
-                        comm_executor: Callable, mode: OverlapMode = OverlapMode.WAVE,
+                        comm_executor: Callable, mode: Optional[OverlapMode] = None,
                         num_waves: Optional[int] = None) -> None:
+        """``mode`` None takes ``config.overlap_strategy``: "auto" / "wave" -> WAVE, "pipeline" -> PIPELINE,
+        "none" -> NONE (compute, then communication, on one stream)."""
+        if mode is None:
+            from ..config import config
+            mode = {"none": OverlapMode.NONE, "pipeline": OverlapMode.PIPELINE}.get(str(config.overlap_strategy).lower(),
+                                                                                    OverlapMode.WAVE)
         plan = self.scheduler.create_plan(compute_tasks, comm_tasks, mode=mode, num_waves=num_waves)
         self.scheduler.execute_plan(plan, compute_executor, comm_executor)
 

@@ -193,9 +193,11 @@ class StreamRuntime(_RuntimeBase):
         comm_stream = self._sm.comm_stream
         done: Dict[int, torch.cuda.Event] = {}      # node id -> completion event of an off-stream node
         forked = False
+        from ..config import config
+        overlap_on = str(config.overlap_strategy).lower() != "none"      # "none": everything on the main stream
         for wave in schedule.waves:
             for node in wave:
-                off = node.is_comm and node._overlap_role == "comm" and _world() > 1
+                off = overlap_on and node.is_comm and node._overlap_role == "comm" and _world() > 1
                 target = comm_stream if off else main
                 for dep in node.depends_on:
                     ev = done.get(dep._node_id)

@@ -37,6 +37,13 @@ class InputPrefetcher:
         """Starts copying ``host`` (pinned) into the next staging buffer on the copy stream."""
         if len(self._queue) == len(self._bufs):
             raise RuntimeError("every staging buffer holds an undelivered input")
+        from ..config import config
+        if config.use_pinned_memory and not host.is_pinned():
+            # pageable memory would make the copy synchronous with the host: go through a pinned bounce buffer
+            if not hasattr(self, "_bounce") or self._bounce.shape != host.shape or self._bounce.dtype != host.dtype:
+                self._bounce = [torch.empty(host.shape, dtype=host.dtype).pin_memory() for _ in self._bufs]
+            self._bounce[self._next].copy_(host)
+            host = self._bounce[self._next]
         i = self._next
         self._next = (i + 1) % len(self._bufs)
         with torch.cuda.stream(self.stream):
@@ -78,7 +85,10 @@ class StepPipeline:
     def __init__(self, input_buffer: torch.Tensor, result_like: torch.Tensor, depth: int = 2):
         self.feed = InputPrefetcher(input_buffer, depth=depth)
         self.input_buffer = input_buffer
-        self._host = [torch.empty(result_like.shape, dtype=result_like.dtype).pin_memory() for _ in range(depth)]
+        from ..config import config
+        self._host = [torch.empty(result_like.shape, dtype=result_like.dtype) for _ in range(depth)]
+        if config.use_pinned_memory:
+            self._host = [h.pin_memory() for h in self._host]
         self._done = [torch.cuda.Event() for _ in range(depth)]
         self._step = 0
         self._pending: Deque[int] = deque()
