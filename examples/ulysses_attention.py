@@ -1,6 +1,7 @@
 #!/usr/bin/env python
-"""Ulysses sequence parallelism: [B, S/P, H, D] -> all-to-all -> attention over the full sequence on
-H/P heads -> inverse all-to-all, with the exchange overlapped against independent compute.
+"""Ulysses sequence parallelism on this package's kernels: projections, the three head <-> sequence exchanges and
+the inverse exchange + output projection run as two launches of the persistent kernel per rank; the tensors live in
+the symmetric heap, so the exchanges are in-kernel peer pushes, not NCCL calls.
 
     torchrun --standalone --local-addr 127.0.0.1 --nproc-per-node 2 examples/ulysses_attention.py
 (counterpart of the reference's examples/test_overlap_attention.py)"""
@@ -9,29 +10,30 @@ import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import torch
+import torch.distributed as dist
 
 import maco_b200 as maco
-from maco_b200.comm import patterns
+from maco_b200.models.ulysses_attention import UlyssesAttention
+from maco_b200.parallel import symm_heap
 
 
 def main():
-    cuda = torch.cuda.is_available()
-    maco.init(backend="nccl" if cuda else "gloo")
+    maco.config.set(comm_buffer_size="256MB", backend="peer")
+    maco.init(backend="nccl")
     rank, world = maco.get_rank(), maco.get_world_size()
-    dev = maco.ProcessGroupManager().device
-    B, S, H, D = 2, 512, 8, 64
+    B, S, H, D, hidden = 2, 1024, 8 * world, 64, 1024
+    layer = UlyssesAttention(B, S, H, D, hidden, rank=rank, world=world, heap=symm_heap.current_heap())
+    torch.manual_seed(0)
+    x_full = torch.randn(B, S, hidden, device="cuda", dtype=torch.bfloat16)
     s = S // world
-    torch.manual_seed(rank)
-    q, k, v = (torch.randn(B, s, H, D, device=dev) for _ in range(3))
-    w = torch.randn(1024, 1024, device=dev)
-
-    def exchange():
-        return [patterns.all_to_all_4D(t, 2, 1) for t in (q, k, v)]      # -> [B, S, H/P, D]
-
-    (qf, kf, vf), side = maco.overlap_all_to_all_with_compute(exchange, lambda: w @ w)
-    att = torch.nn.functional.scaled_dot_product_attention(qf.transpose(1, 2), kf.transpose(1, 2), vf.transpose(1, 2))
-    out = patterns.all_to_all_4D(att.transpose(1, 2).contiguous(), 1, 2)  # back to [B, S/P, H, D]
-    print(f"[rank {rank}] output {tuple(out.shape)}, side compute {tuple(side.shape)}")
+    out = layer(x_full[:, rank * s:(rank + 1) * s])
+    torch.cuda.synchronize()
+    ref = layer.reference(x_full)
+    err = (out.float() - ref).abs().max().item()
+    print(f"[rank {rank}] runtimes {layer.graph_in.runtime_kind}/{layer.graph_out.runtime_kind}, output {tuple(out.shape)}, "
+          f"max abs error vs fp32 {err:.3e}")
+    if world > 1:
+        dist.barrier()
     maco.cleanup()
 
 

@@ -128,6 +128,43 @@ def cleanup(abort: bool = False) -> None:
     _initialized = False
 
 
+def recover(lost_ranks, port: Optional[int] = None, backend: Optional[str] = None,
+            timeout_s: Optional[float] = None):
+    """Elastic recovery after ``PeerLostError``: tears this rank's state down without any collective (heap, cached
+    programs, process group), then rendezvouses again with the SURVIVORS only. Ranks are renumbered in their old
+    order (the lowest surviving rank becomes rank 0 and hosts the new rendezvous store, on ``port`` or the old
+    master port + 1 + number of recoveries so far). Graphs and programs must be rebuilt afterwards: their task
+    tables name the old world. Returns (new_rank, new_world_size).
+
+    Every survivor calls it with the same ``lost_ranks`` (they learn them from the same heartbeats). The reference
+    has no failure path at all (maco/__init__.py:262-273 only destroys the group)."""
+    global _recoveries
+    import os
+    pgm = ProcessGroupManager._instance
+    old_rank, old_world = (pgm.rank, pgm.world_size) if pgm is not None else (_rank, _world_size)
+    be = backend or (pgm.backend if pgm is not None else None) or "gloo"
+    lost = sorted(set(int(r) for r in lost_ranks))
+    if old_rank in lost:
+        raise ValueError("a rank that is counted as lost cannot take part in the recovery")
+    survivors = [r for r in range(old_world) if r not in lost]
+    cleanup(abort=True)
+    try:
+        import torch.distributed as _dist
+        if _dist.is_initialized():
+            _dist.destroy_process_group()
+    except Exception:
+        pass
+    _recoveries += 1
+    new_rank, new_world = survivors.index(old_rank), len(survivors)
+    new_port = int(port) if port is not None else int(os.environ.get("MASTER_PORT", "29500")) + _recoveries
+    os.environ.update({"RANK": str(new_rank), "WORLD_SIZE": str(new_world), "MASTER_PORT": str(new_port)})
+    init(backend=be, rank=new_rank, world_size=new_world, timeout_s=timeout_s)
+    return new_rank, new_world
+
+
+_recoveries = 0
+
+
 def get_rank() -> int:
     return comm.get_rank()
 
@@ -173,7 +210,7 @@ def sync_streams() -> None:
 
 
 __all__ = [
-    "init", "cleanup", "get_rank", "get_world_size", "is_initialized", "config", "MacoConfig",
+    "init", "cleanup", "recover", "get_rank", "get_world_size", "is_initialized", "config", "MacoConfig",
     "get_overlap_manager", "overlap_compute_and_comm", "overlap_all_to_all_with_compute", "overlap_region",
     "get_comm_stream", "get_compute_stream", "sync_streams",
     "TaskGraph", "TaskNode", "TaskType", "OverlapGroup", "TaskSchedule", "OverlapScheduler", "OverlapPlan",

@@ -119,3 +119,50 @@ def _heartbeat(rank, world):
 
 def test_peer_loss_is_detected_on_the_host():
     run_ranks(_heartbeat, 2)
+
+
+def _recover(rank, world):
+    """Three ranks run two steps; rank 1 leaves between steps with nothing in flight. The two survivors learn of
+    it from the heartbeats, tear down without collectives, rendezvous again as a world of two, rebuild their
+    graph and all-reduce correctly."""
+    import os
+    import maco_b200 as maco
+    from maco_b200.comm.process_group import ProcessGroupManager, ensure_peers
+    maco.init(backend="gloo", timeout_s=30.0)
+
+    def step_graph(value):
+        t = torch.full((1024,), float(value))
+        g = maco.TaskGraph(num_workers=4)
+        ar = g.allreduce(t)
+        g.compile()
+        g.execute()
+        return ar.output
+
+    for step in (1, 2):
+        ensure_peers(step, timeout_s=20.0)
+        out = step_graph(rank + 1)
+        assert torch.all(out == 6.0), (step, out[0])
+    pgm = ProcessGroupManager()
+    if rank == 1:
+        pgm.heartbeat(2)
+        pgm.announce_exit()
+        os._exit(0)                          # gone: no collective of this rank is in flight
+    lost = None
+    try:
+        ensure_peers(3, timeout_s=5.0)
+    except maco.PeerLostError as exc:
+        lost = exc.rank
+    assert lost == 1
+    new_rank, new_world = maco.recover([1], timeout_s=30.0)
+    assert new_world == 2 and new_rank == {0: 0, 2: 1}[rank]
+    assert maco.get_world_size() == 2 and maco.get_rank() == new_rank
+    for step in (1, 2):                      # the recompiled graph runs in the smaller world
+        ensure_peers(step, timeout_s=20.0)
+        out = step_graph(rank + 1)           # old ranks 0 and 2 contribute 1 + 3
+        assert torch.all(out == 4.0), (step, out[0])
+    maco.cleanup()
+    os._exit(0)
+
+
+def test_survivors_rerendezvous_and_recompile_after_peer_loss():
+    run_ranks(_recover, 3, timeout=120)
