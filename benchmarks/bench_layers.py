@@ -30,7 +30,9 @@ def peaks():
         p["source"] = "measured"
     except Exception:
         pass
+    # per direction per GPU: the peer-copy rate measured on this pool (the rooflines use it); 900 GB/s is nominal
     p["nvlink_gbs"] = 770.0
+    p["nvlink_gbs_nominal"] = 900.0
     return p
 
 
@@ -232,9 +234,17 @@ def main():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--mode", default="static", choices=["static", "dynamic"])
     ap.add_argument("--arms", default="library,ours")
+    ap.add_argument("--impl", default="", choices=["", "reference"],
+                    help="reference: run the unmodified reference package through its own API instead "
+                         "(benchmarks/bench_layers_reference.py; tp_mlp: bench.py --impl reference)")
     ap.add_argument("--trace-file", default="", help="with --trace: write the Chrome-trace JSON of rank 0 here")
     ap.add_argument("--trace", action="store_true", help="record the device task trace of one step and print per-type statistics")
     args = ap.parse_args()
+    if args.impl == "reference":
+        script = os.path.join(REPO, "bench.py") if args.config == "tp_mlp" else os.path.join(REPO, "benchmarks", "bench_layers_reference.py")
+        extra = ["--impl", "reference"] if args.config == "tp_mlp" else ["--config", args.config, "--layers", str(args.layers)]
+        sys.exit(subprocess.call([sys.executable, script, "--gpus", str(args.gpus), "--steps", str(args.steps),
+                                  "--warmup", str(args.warmup)] + extra))
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 2000), os.path.abspath(__file__)] + sys.argv[1:]
@@ -265,7 +275,9 @@ def main():
         if rank == 0:
             line = {"config": args.config, "impl": arm, "n_gpus": world, "latency_us": round(us, 2), "steps": args.steps,
                     "warmup": args.warmup, "roofline_us": {k: round(v, 1) for k, v in roof.items()},
-                    "fraction_of_roofline": round(bound / us, 3), "peaks": p["source"], "kernel_status": _native.status(clear=False)}
+                    "fraction_of_roofline": round(bound / us, 3), "peaks": p["source"],
+                    "nvlink_gbs": {"measured_used": p["nvlink_gbs"], "nominal": p["nvlink_gbs_nominal"]},
+                    "kernel_status": _native.status(clear=False)}
             os.write(real_stdout, (json.dumps(line) + "\n").encode())
             if arm == "ours" and args.trace:
                 os.write(real_stdout, (json.dumps({"config": args.config, "trace": args.program.stats()}) + "\n").encode())
