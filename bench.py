@@ -105,6 +105,59 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+class NvmlSampler:
+    """The same record through NVML from a thread of this process (read-only queries every 5 ms): the timed region
+    lasts tens of milliseconds, too short for more than one or two nvidia-smi samples."""
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.reasons, self._stop, self._thread, self.ok = index, [], set(), False, None, False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def _loop(self):
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self._stop:
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                mask = int(get_reasons(self.h))
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def start(self):
+        import threading
+        self._thread = threading.Thread(target=self._loop, daemon=True)
+        self._thread.start()
+
+    def stop(self) -> dict:
+        self._stop = True
+        if self._thread is not None:
+            self._thread.join(1.0)
+        sm = self.samples
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz, "samples": len(sm),
+                "reasons": sorted(self.reasons), "source": "nvml"}
+
+
+def make_sampler(index: int):
+    s = NvmlSampler(index)
+    return s if s.ok else ClockSampler(index)
+
+
 def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
@@ -184,7 +237,7 @@ def run_ours(args):
 
     for _ in range(args.warmup):
         step()
-    ms, clocks = timed_region(torch, dist, world, args.steps, step, ClockSampler(local_rank) if rank == 0 else None)
+    ms, clocks = timed_region(torch, dist, world, args.steps, step, make_sampler(local_rank) if rank == 0 else None)
     for _ in range(max(3, args.warmup // 2)):
         step_e2e()
     pipe.drain()
@@ -338,7 +391,7 @@ def run_reference(args):
     with contextlib.redirect_stdout(sys.stderr):
         for _ in range(args.warmup):
             step()
-        ms, clocks = timed_region(torch, dist, world, args.steps, step, ClockSampler(local_rank) if rank == 0 else None)
+        ms, clocks = timed_region(torch, dist, world, args.steps, step, make_sampler(local_rank) if rank == 0 else None)
         for _ in range(max(3, args.warmup // 2)):
             step_e2e()
         drain()

@@ -88,7 +88,8 @@ def cfg_tp_mlp(torch, dist, rank, world, heap, args):
 def cfg_dp_backward(torch, dist, rank, world, heap, args):
     from maco_b200.models.dp_mlp_stack import DPMLPStackBackward
     L, H, T = args.layers, 4096, 8192
-    m = DPMLPStackBackward(L, H, T, rank=rank, world=world, heap=heap, mode=args.mode, trace=args.trace)
+    m = DPMLPStackBackward(L, H, T, rank=rank, world=world, heap=heap, mode=args.mode, trace=args.trace,
+                           cta_pair=bool(args.cta_pair))
     args.program = m.program
     m.forward()
     grads = [torch.empty(H, H, device="cuda", dtype=torch.float32) for _ in range(L)]
@@ -234,6 +235,7 @@ def main():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--mode", default="static", choices=["static", "dynamic"])
     ap.add_argument("--arms", default="library,ours")
+    ap.add_argument("--cta-pair", type=int, default=1, choices=[0, 1], help="two-CTA GEMM tiles where the model offers them")
     ap.add_argument("--impl", default="", choices=["", "reference"],
                     help="reference: run the unmodified reference package through its own API instead "
                          "(benchmarks/bench_layers_reference.py; tp_mlp: bench.py --impl reference)")

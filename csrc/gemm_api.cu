@@ -48,6 +48,28 @@ int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorM
   return launch_gemm<BN, STAGES, true, true>(tmA, tmB, epi, K, idesc, max_ctas, budget_ns, stream);
 }
 
+// fp32 operands on the tensor cores (kind::tf32): K-major operands only, 128 x 256 tiles.
+int launch_gemm_tf32(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmEpilogue& epi, int K, uint32_t idesc,
+                     int max_ctas, uint64_t budget_ns, cudaStream_t stream) {
+  using L = GemmSmemLayout<256, 4>;
+  auto kern = gemm_tcgen05_kernel<256, 4, false, false, true>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  MACO_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev]) {
+    MACO_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes));
+    attr_set[dev] = true;
+  }
+  int grid = ((epi.M + kBM - 1) / kBM) * ((epi.N + 255) / 256);
+  int sms = maco_host::sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  if (grid > sms) grid = sms;
+  if (grid <= 0) return 0;
+  kern<<<grid, kGemmThreads, L::kTotalBytes, stream>>>(tmA, tmB, epi, K, idesc, budget_ns, maco_host::status_device_ptr(), g_gemm_dbg);
+  MACO_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 // Two-CTA tiles: clusters of two CTAs, 256 x BN per pair.
 template <int BN, bool A_MN, bool B_MN>
 int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmEpilogue& epi, int K, uint32_t idesc,
@@ -201,6 +223,32 @@ int maco_gemm(const void* A, const void* B, void* D, int M, int N, int K, long l
   const uint32_t idesc = make_idesc(ab_type == MACO_DT_BF16 ? 1u : 0u, kBM, bn, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
   if (bn == 256) return dispatch_major<256, 4>(a_mn, b_mn, tmA, tmB, e, K, idesc, max_ctas, budget_ns, stream);
   return dispatch_major<128, 6>(a_mn, b_mn, tmA, tmB, e, K, idesc, max_ctas, budget_ns, stream);
+}
+
+// fp32 inputs on the tensor cores as TF32 (10-bit mantissa: an opt-in, the default fp32 path is maco_gemm_simt).
+// A [M, K] and B [N, K] row-major fp32 with 16-byte aligned rows; same epilogues as maco_gemm.
+// Returns -2 when the operands are not TMA-addressable.
+int maco_gemm_tf32(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb, long long ldd,
+                   int out_type, int mode, const void* bias, int bias_type, const void* aux, long long ld_aux,
+                   int aux_type, float alpha, int max_ctas, double wait_budget_ms, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || mode == MACO_EPI_SWIGLU) { maco_host::set_error("maco_gemm_tf32: K must be positive; no SwiGLU epilogue"); return -2; }
+  const int out_vec = out_type == MACO_DT_F32 ? 4 : 8;
+  if ((reinterpret_cast<uintptr_t>(D) & 15) != 0 || (ldd % out_vec) != 0) {
+    maco_host::set_error("maco_gemm_tf32: output base and row stride must be 16-byte aligned");
+    return -2;
+  }
+  CUtensorMap tmA, tmB;
+  int r = maco_host::encode_tmap_2d(&tmA, A, 4, M, K, lda * 4, kBK / 2, kBM);
+  if (r != 0) return r == -2 ? -2 : -1;
+  r = maco_host::encode_tmap_2d(&tmB, B, 4, N, K, ldb * 4, kBK / 2, 256);
+  if (r != 0) return r == -2 ? -2 : -1;
+  GemmEpilogue e;
+  e.out = D; e.bias = bias; e.aux = aux; e.ld_out = ldd; e.ld_aux = ld_aux; e.mode = mode; e.out_type = out_type;
+  e.bias_type = bias_type; e.aux_type = aux_type; e.M = M; e.N = N; e.alpha = alpha; e._pad = 0;
+  const uint64_t budget_ns = (uint64_t)((wait_budget_ms > 0 ? wait_budget_ms : 2000.0) * 1e6);
+  return launch_gemm_tf32(tmA, tmB, e, K, make_idesc(2u, kBM, 256, 0u, 0u), max_ctas, budget_ns, stream);
 }
 
 // Element strides: A(m,k) = A[m*sam + k*sak], B(n,k) = B[n*sbn + k*sbk].

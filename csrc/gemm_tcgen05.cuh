@@ -87,14 +87,15 @@ MACO_DEVICE void gemm_tile_coords(int tile, int m_tiles, int n_tiles, int& m_blk
 template <int BN, int STAGES, bool A_MN, bool B_MN, int SBN = BN>
 MACO_DEVICE bool gemm_produce_tile(uint8_t* smem, const GemmCtrl& c, const CUtensorMap* tmA,
                                    const CUtensorMap* tmB, int m0, int n0, int k0, int k_blocks,
-                                   uint32_t& it, uint64_t budget_ns, long long* prof = nullptr) {
+                                   uint32_t& it, uint64_t budget_ns, long long* prof = nullptr, int k_step = kBK) {
+  // k_step: elements per 128-byte k-block (64 for 16-bit operands, 32 for fp32 operands run as TF32)
   using L = GemmSmemLayout<BN, STAGES, SBN>;
   // stage index and phase advance incrementally: the loop is one thread's instruction stream, and a division
   // per k-block is a measurable part of it
   uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
   uint8_t* sa = smem + s * L::kStageBytes;
   int k = k0;
-  for (int kb = 0; kb < k_blocks; ++kb, k += kBK) {
+  for (int kb = 0; kb < k_blocks; ++kb, k += k_step) {
     const long long t0 = prof ? clock64() : 0;
     if (!mbar_wait(&c.empty[s], ph ^ 1, budget_ns, c.abort_word)) { it += kb; return false; }
     if (prof) prof[0] += clock64() - t0;
@@ -132,7 +133,7 @@ MACO_DEVICE void gemm_drain_loads(const GemmCtrl& c, uint32_t issued) {
 }
 
 // ---- MMA issuer ----------------------------------------------------------------------------
-template <int BN, int STAGES, bool A_MN, bool B_MN, int SBN = BN>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int SBN = BN, bool TF32 = false>
 MACO_DEVICE bool gemm_mma_tile(uint8_t* smem, const GemmCtrl& c, uint32_t tmem_base, uint32_t idesc,
                                int k_blocks, uint32_t& it, uint32_t tile_seq, uint64_t budget_ns,
                                long long* prof = nullptr) {
@@ -164,7 +165,9 @@ MACO_DEVICE bool gemm_mma_tile(uint8_t* smem, const GemmCtrl& c, uint32_t tmem_b
 #pragma unroll
     for (int k = 0; k < kBK / kUmmaK; ++k) {
       // low descriptor words: start address (bits 0-13, never carries: shared memory is below 256 KB) | leading offset
-      tc_mma_f16_lo(d_tmem, (a_lo + k * kStepA) | a_lbo, a_hi, (b_lo + k * kStepB) | b_lbo, b_hi, idesc, accum);
+      // fp32 operands (TF32): 8 elements of 4 bytes per MMA, the same 32-byte step inside the swizzled row
+      if constexpr (TF32) tc_mma_tf32_lo(d_tmem, (a_lo + k * kStepA) | a_lbo, a_hi, (b_lo + k * kStepB) | b_lbo, b_hi, idesc, accum);
+      else tc_mma_f16_lo(d_tmem, (a_lo + k * kStepA) | a_lbo, a_hi, (b_lo + k * kStepB) | b_lbo, b_hi, idesc, accum);
       accum = 1;
     }
     tc_commit(&c.empty[s]);          // frees the smem stage once these MMAs have read it
@@ -693,7 +696,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 }
 
 // ---- stand-alone persistent GEMM kernel ---------------------------------------------------------
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool TF32 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     GemmEpilogue epi, int K, uint32_t idesc, uint64_t budget_ns, uint32_t* status, long long* dbg) {
@@ -708,7 +711,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   const int m_tiles = (epi.M + kBM - 1) / kBM, n_tiles = (epi.N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
-  const int k_blocks = (K + kBK - 1) / kBK;
+  constexpr int kStepElems = TF32 ? kBK / 2 : kBK;
+  const int k_blocks = (K + kStepElems - 1) / kStepElems;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (warp == 0) {
@@ -720,7 +724,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int tile = blockIdx.x; ok && tile < num_tiles && !(variant & 4); tile += gridDim.x) {
         int mb, nb;
         gemm_tile_coords(tile, m_tiles, n_tiles, mb, nb);
-        ok = gemm_produce_tile<BN, STAGES, A_MN, B_MN>(smem, c, &tmA, &tmB, mb * kBM, nb * BN, 0, k_blocks, it, budget_ns, pp);
+        ok = gemm_produce_tile<BN, STAGES, A_MN, B_MN>(smem, c, &tmA, &tmB, mb * kBM, nb * BN, 0, k_blocks, it, budget_ns, pp, kStepElems);
       }
       if (!ok || (variant & 2)) gemm_drain_loads<STAGES>(c, it);      // experiment switch 2: see the two-CTA kernel
       if (dbg != nullptr) { dbg[blockIdx.x * 8 + 0] = prof[0]; dbg[blockIdx.x * 8 + 4] = clock64() - t_begin; }
@@ -731,7 +735,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t it = 0, seq = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++seq)
-        ok = gemm_mma_tile<BN, STAGES, A_MN, B_MN>(smem, c, tmem_base, idesc, k_blocks, it, seq, budget_ns, pp);
+        ok = gemm_mma_tile<BN, STAGES, A_MN, B_MN, BN, TF32>(smem, c, tmem_base, idesc, k_blocks, it, seq, budget_ns, pp);
       if (dbg != nullptr) { dbg[blockIdx.x * 8 + 1] = prof[1]; dbg[blockIdx.x * 8 + 2] = prof[2]; dbg[blockIdx.x * 8 + 3] = clock64() - t_begin; }
     }
     __syncwarp();

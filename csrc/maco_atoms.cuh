@@ -326,6 +326,13 @@ MACO_DEVICE void tc_mma_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, ui
       " tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
       :: "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
+MACO_DEVICE void tc_mma_tf32_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n"
+      " tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n}"
+      :: "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
 MACO_DEVICE void tc_mma2_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
                                 uint32_t accumulate) {
   asm volatile(

@@ -40,6 +40,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "maco_status": (c_uint, [I]),
         "maco_sm_count": (I, []),
         "maco_gemm": (I, [P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, P, I, P, LL, I, F, I, I, D, P, I]),
+        "maco_gemm_tf32": (I, [P, P, P, I, I, I, LL, LL, LL, I, I, P, I, P, LL, I, F, I, D, P]),
         "maco_gemm_simt": (I, [P, P, P, I, I, I, LL, LL, LL, LL, LL, I, I, I, P, I, P, LL, I, F, P]),
     }
     for name, (res, args) in sigs.items():

@@ -32,6 +32,7 @@ class MacoConfig:
     heap_mode: str = "auto"               # "auto" | "nvls" (multicast-bound) | "vmm" (shared descriptors) | "ipc" (cudaMalloc + IPC)
     use_pinned_memory: bool = True        # host staging of the input feed / result read-back goes through pinned memory
     runtime: str = "auto"                 # "auto" | "persistent" | "stream" | "reference"
+    allow_tf32: bool = False              # fp32 GEMMs on the tensor cores as TF32 (10-bit mantissa) instead of CUDA-core fp32
     wait_budget_ms: float = 2000.0        # every device-side wait gives up after this long
     debug: bool = False                   # kernels re-check every task descriptor before running it (BAD_TASK on failure)
     profile: bool = False
@@ -45,7 +46,7 @@ class MacoConfig:
         self.heap_mode = env.get("MACO_HEAP", self.heap_mode)
         if "MACO_WAIT_BUDGET_MS" in env:
             self.wait_budget_ms = float(env["MACO_WAIT_BUDGET_MS"])
-        for flag in ("debug", "profile", "verbose"):
+        for flag in ("debug", "profile", "verbose", "allow_tf32"):
             key = f"MACO_{flag.upper()}"
             if key in env:
                 setattr(self, flag, env[key] not in ("0", "", "false", "False"))

@@ -32,7 +32,11 @@ from ..task_graph.nodes import TaskType
 class DPMLPStackBackward:
     def __init__(self, layers: int = 16, hidden: int = 4096, tokens: int = 8192, *, rank: int = 0, world: int = 1,
                  heap=None, device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16, seed: int = 0,
-                 mode: str = "static", trace: bool = False, comm_workers: Optional[int] = None, weight_std: float = 0.02):
+                 mode: str = "static", trace: bool = False, comm_workers: Optional[int] = None, weight_std: float = 0.02,
+                 cta_pair: bool = False):
+        # two-CTA tiles measured slower here (8.5 ms against 8.0 ms on one GPU: both operands of the wgrad tiles are
+        # MN-major, 64-column TMA boxes), so the one-CTA form is the default
+        self.cta_pair = cta_pair and mode == "static"
         if tokens % BM or hidden % 256:
             raise ValueError("tokens must be a multiple of 128 and hidden of 256")
         if world > 1 and heap is None:
@@ -75,7 +79,8 @@ class DPMLPStackBackward:
     # ------------------------------------------------------------------ backward program
     def _build(self, mode: str, trace: bool, comm_workers: int) -> None:
         L, H, T, world, rank = self.layers, self.hidden, self.tokens, self.world, self.rank
-        b = ProgramBuilder(self.device, mode=mode, heap=self.heap, trace=trace, num_comm_workers=comm_workers)
+        b = ProgramBuilder(self.device, mode=mode, heap=self.heap, trace=trace, num_comm_workers=comm_workers,
+                           cta_pair=self.cta_pair)
         numel = float(T * H)
         e_da = b.elementwise(int(TaskType.AXPBY), self.a[L - 1], self.da, in1=self.target, rows=T, cols=H,
                              f0=2.0 / numel, f1=-2.0 / numel)

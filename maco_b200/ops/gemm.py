@@ -103,6 +103,17 @@ def gemm(
             return out
         if rc != -2:
             N.check(rc, "maco_gemm")
+    from ..config import config
+    if (config.allow_tf32 and a.dtype == torch.float32 and not trans_a and not trans_b and mode != EPI_SWIGLU
+            and _tma_ok(a) and _tma_ok(b) and out.data_ptr() % 16 == 0 and (out.stride(0) * out.element_size()) % 16 == 0):
+        # opt-in: fp32 operands through tcgen05.mma.kind::tf32 (inputs rounded to 10 mantissa bits, fp32 accumulation)
+        rc = lib.maco_gemm_tf32(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, Nn, K, a.stride(0), b.stride(0), out.stride(0),
+                                N.DTYPE_CODE[out.dtype], mode, N.ptr(bias), bias_t, N.ptr(aux), ld_aux, aux_t, float(alpha),
+                                max_ctas, float(wait_budget_ms), st)
+        if rc == 0:
+            return out
+        if rc != -2:
+            N.check(rc, "maco_gemm_tf32")
     if mode == EPI_SWIGLU:
         raise ValueError("the swiglu epilogue needs 16-bit, 16-byte aligned operands")
     sam, sak = (1, a.stride(0)) if trans_a else (a.stride(0), 1)

@@ -200,6 +200,7 @@ class ProgramBuilder:
         self.epis: List[bytes] = []
         self.num_events = 0
         self.keepalive: List[torch.Tensor] = []
+        self.launch_state: List[torch.Tensor] = []     # buffers that must be zero when the FIRST launch starts
         self._node_counter = 0
 
     # ------------------------------------------------------------------ primitives
@@ -428,6 +429,7 @@ class ProgramBuilder:
             split_k = pick_split_k(n_tiles, k_blocks, self.num_workers)
         split_k = max(1, min(split_k, k_blocks))
         ws = torch.zeros(M, Nn, device=a.device, dtype=torch.float32)      # SPLITK_FIN leaves it zeroed again
+        self.launch_state.append(ws)
         out_dtype = out.dtype if out is not None else a.dtype
         ab = 1 if a.dtype == torch.bfloat16 else 0
         idesc = make_idesc(ab, BM, 256, 0, 0)
@@ -545,6 +547,7 @@ class ProgramBuilder:
             partials = torch.empty(len(pieces) * rec, device=q.device, dtype=torch.float32)
             counters = torch.zeros(B * hkv, device=q.device, dtype=torch.int32)   # only ever grow: one per piece and launch
             self.keepalive += [partials, counters]
+            self.launch_state.append(counters)
             idx_in_group = [0] * (B * hkv)
             for pi, (bh, s0, keys, wk) in enumerate(pieces):
                 bi, j = divmod(bh, hkv)
@@ -691,6 +694,7 @@ class Program:
         self.num_workers = b.num_workers
         self.num_comm_workers = b.num_comm_workers
         self.keepalive = b.keepalive
+        self.launch_state = list(getattr(b, "launch_state", []))
         self.heap = b.heap
         n = len(b.tasks)
         self.num_tasks = n
@@ -833,8 +837,14 @@ class Program:
         self.num_tasks = 0
 
     def reset_after_failure(self) -> None:
-        """Re-zeroes the control state after an aborted launch (events restart from epoch 0)."""
+        """Re-zeroes the control state after an aborted launch (events restart from epoch 0), together with the
+        buffers a launch expects in their start-of-launch state (split-K workspaces, the arrival counters of the
+        tensor-core attention tasks), which an aborted launch may have left half advanced. For a program over a
+        symmetric heap every rank calls this between two host barriers (the callers' job): peers bump these
+        counters too."""
         torch.cuda.synchronize(self.device)
+        for t in getattr(self, "launch_state", []):
+            t.zero_()
         self.d_events.zero_()
         self.d_ctrl.zero_()
         if self.mode == MODE_DYNAMIC:
@@ -1113,6 +1123,8 @@ def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None)
         elif t in (TaskType.ALLREDUCE, TaskType.BROADCAST, TaskType.NOP):
             # in place and a no-op at world size 1: consumers inherit the producers of the tensor
             aligned, extra = ready_of(node, node.inputs[0] if node.inputs else None, -1)
+            if aligned is not None:      # another in-place node on the same tensor (its events carry rows = -1 too)
+                extra = extra + [(aligned.all_event[0], aligned.all_event[1], aligned.sys, False)]
             waits = b.join(extra, 0)
             e = b.new_event()
             b.add_task(int(TaskType.NOP), b"", waits=waits, signals=[e])

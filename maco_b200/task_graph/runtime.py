@@ -254,13 +254,66 @@ class StreamRuntime(_RuntimeBase):
             raise NotImplementedError(f"StreamRuntime has no implementation for {t.name}")
 
 
+def _schedule_key(graph) -> tuple:
+    """Identity of a compiled schedule: node types and attributes, the address / shape / strides / dtype of every
+    tensor (task descriptors carry absolute addresses), the dependency structure, and everything else the lowering
+    reads (world, rank, device architecture, worker count, scheduling mode, debug / trace switches)."""
+    import os
+    from ..comm.process_group import get_rank, get_world_size
+    from ..config import config
+
+    def tkey(t):
+        return (t.data_ptr(), tuple(t.shape), tuple(t.stride()), str(t.dtype))
+
+    nodes = []
+    for n in graph._nodes:
+        attrs = tuple(sorted((k, v if isinstance(v, (int, float, str, bool, type(None))) else repr(v)) for k, v in n.attrs.items()))
+        nodes.append((int(n.task_type), attrs, tuple(tkey(t) for t in n.inputs), tuple(tkey(t) for t in n.outputs),
+                      tuple(d._node_id for d in n.depends_on), n._wave_id, n._overlap_role))
+    cap = torch.cuda.get_device_capability(graph.device)
+    smc = getattr(graph, "sm_config", None)
+    return (tuple(nodes), get_world_size(), get_rank(), str(graph.device), cap, graph.num_workers,
+            os.environ.get("MACO_PERSISTENT_MODE", "static"), bool(config.debug), bool(config.profile), str(config.sm_policy),
+            repr(smc.to_dict()) if smc is not None else None)
+
+
 class PersistentRuntime(_RuntimeBase):
-    """Runs the graph as tile tasks inside one launch of the persistent task kernel."""
+    """Runs the graph as tile tasks inside one launch of the persistent task kernel.
+
+    Compiled programs are cached per process (least recently used first out, ``SCHEDULE_CACHE_SIZE`` entries) under
+    ``_schedule_key``: code that rebuilds the same graph over the same tensors every step (the reference's examples
+    do) pays the lowering, thousands of descriptors for a large layer, once. A cached program keeps its tensors
+    alive, so the addresses in its descriptors stay valid. Programs over the symmetric heap are not cached: their
+    stand-in buffers and event tables come from a collective allocation sequence."""
+
+    SCHEDULE_CACHE_SIZE = 32
+    _cache: "OrderedDict[tuple, object]" = None
+    cache_hits = 0
 
     def __init__(self, graph):
         super().__init__(graph.device, graph)
+        from collections import OrderedDict
         from ..ops import megakernel
-        self._program = megakernel.lower_graph(graph)
+        cls = PersistentRuntime
+        if cls._cache is None:
+            cls._cache = OrderedDict()
+        key = _schedule_key(graph)
+        prog = cls._cache.get(key)
+        if prog is not None:
+            cls._cache.move_to_end(key)
+            cls.cache_hits += 1
+        else:
+            prog = megakernel.lower_graph(graph)
+            if prog.heap is None:
+                cls._cache[key] = prog
+                while len(cls._cache) > cls.SCHEDULE_CACHE_SIZE:
+                    cls._cache.popitem(last=False)
+        self._program = prog
+
+    @classmethod
+    def clear_schedule_cache(cls) -> None:
+        if cls._cache is not None:
+            cls._cache.clear()
 
     @staticmethod
     def can_run(graph) -> bool:

@@ -144,3 +144,32 @@ def test_decode_shaped_linear_takes_the_split_k_path():
     hf = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()).to(dt).float()
     ref = (hf @ w1.float().t()).to(dt).float() @ w2.float().t()
     assert_close(t2.output, ref, dt)
+
+
+def test_compiled_schedule_is_cached_for_identical_graphs():
+    """Rebuilding the same graph over the same tensors reuses the compiled program; a different shape does not."""
+    import maco_b200 as maco
+    from maco_b200.task_graph.runtime import PersistentRuntime
+    PersistentRuntime.clear_schedule_cache()
+    x = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(512, 512, device="cuda", dtype=torch.bfloat16) * 0.05
+    out = torch.empty(256, 512, device="cuda", dtype=torch.bfloat16)
+
+    def build(xx):
+        g = maco.TaskGraph()
+        g.linear(xx, w, output=out if xx is x else None)
+        g.compile()
+        return g
+
+    g1 = build(x)
+    hits = PersistentRuntime.cache_hits
+    g2 = build(x)
+    assert g1.runtime_kind == g2.runtime_kind == "persistent"
+    assert PersistentRuntime.cache_hits == hits + 1 and g2._runtime._program is g1._runtime._program
+    g3 = build(torch.randn(384, 512, device="cuda", dtype=torch.bfloat16))
+    assert PersistentRuntime.cache_hits == hits + 1 and g3._runtime._program is not g1._runtime._program
+    for g in (g1, g2):
+        out.zero_()
+        g.execute()
+        torch.cuda.synchronize()
+        torch.testing.assert_close(out.float(), x.float() @ w.float().t(), atol=1e-1, rtol=5e-2)

@@ -100,6 +100,27 @@ def test_gemm_epilogues():
     assert_close(ops.gemm(a, fused, epilogue="swiglu"), ref, dt)
 
 
+def test_gemm_fp32_on_tensor_cores_as_tf32_is_opt_in():
+    """fp32 operands: CUDA-core fp32 by default (1e-4), tcgen05 kind::tf32 with config.allow_tf32 (TF32 accuracy)."""
+    import maco_b200 as maco
+    ops = _ops()
+    a = torch.randn(300, 520, device="cuda")
+    w = torch.randn(264, 520, device="cuda") * 0.1
+    bias = torch.randn(264, device="cuda")
+    ref = torch.nn.functional.linear(a.double(), w.double(), bias.double()).float()
+    torch.testing.assert_close(ops.linear(a, w, bias), ref, atol=1e-4, rtol=1e-4)
+    maco.config.set(allow_tf32=True)
+    try:
+        out = ops.linear(a, w, bias)
+        big = ops.gemm(torch.randn(1024, 2048, device="cuda"), torch.randn(1536, 2048, device="cuda"))
+    finally:
+        maco.config.set(allow_tf32=False)
+    err = (out - ref).abs().max().item()
+    assert 1e-6 < err < 3e-2, err          # TF32 rounding is visible, and bounded
+    from maco_b200 import _native
+    assert _native.status() == 0 and torch.isfinite(big).all()
+
+
 def test_gemm_fp32_simt_and_odd_shapes():
     ops = _ops()
     a = torch.randn(33, 70, device="cuda")
