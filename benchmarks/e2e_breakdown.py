@@ -34,7 +34,8 @@ def main():
     layer = TPSwiGLUMLP(T, H, F, rank=rank, world=world, heap=heap, seed=0)
     rows = T // world
     x_host = torch.randn(rows, H).to(torch.bfloat16).pin_memory()
-    dbuf = torch.empty(rows, H, device="cuda", dtype=torch.bfloat16)
+    dbuf = x_host.cuda()
+    layer.x_shard.copy_(x_host)          # the same N(0,1) data as the benchmark in every variant
     res_host = torch.zeros(2, dtype=torch.bfloat16).pin_memory()
     side = torch.cuda.Stream()
 

@@ -4,6 +4,9 @@
     python benchmarks/kernel_case.py gemm        # stand-alone tcgen05 GEMM, 8192 x 4096 x 4096 bf16, one-CTA tiles
     python benchmarks/kernel_case.py gemm_pair   # the same GEMM on two-CTA tiles (cta_group::2, clusters of two)
     python benchmarks/kernel_case.py mlp         # persistent kernel: fused SwiGLU MLP, 4096 tokens, 4096 -> 14336/4
+    python benchmarks/kernel_case.py gemm_gate_up / gemm_down  # the layer's two GEMMs as stand-alone two-CTA kernels
+    python benchmarks/kernel_case.py mlp_full    # the benchmark's layer on one GPU: 8192 tokens, 4096 -> 14336 (two-CTA tiles)
+    python benchmarks/kernel_case.py mlp_full_1cta  # the same with one-CTA tiles
     python benchmarks/kernel_case.py attention   # split-KV decode attention, batch 32, 4096 keys
     python benchmarks/kernel_case.py attention_tc  # persistent kernel: tensor-core decode attention, 512 tasks, 537 MB of KV
     python benchmarks/kernel_case.py decode_gemm # persistent kernel: split-K 64 x 5120 x 25600 gate/up projection with SwiGLU
@@ -52,6 +55,35 @@ def main():
         layer.x_shard.normal_()
         us = timed(lambda: layer.forward(None))
         print(f"persistent fused MLP 4096 tok 4096->3584: {us:.1f} us, {layer.flops() / us / 1e6:.0f} TFLOP/s")
+    elif case in ("gemm_gate_up", "gemm_down"):
+        # the two GEMMs of the benchmark's layer as stand-alone two-CTA kernels (DRAM traffic per GEMM)
+        M, N, K = (8192, 28672, 4096) if case == "gemm_gate_up" else (8192, 4096, 14336)
+        a = torch.randn(M, K, device="cuda", dtype=dt)
+        b = torch.randn(N, K, device="cuda", dtype=dt) * 0.02
+        epi = "swiglu" if case == "gemm_gate_up" else None
+        out = torch.empty(M, N // 2 if epi else N, device="cuda", dtype=dt)
+        us = timed(lambda: ops.gemm(a, b, out=out, bn=256, epilogue=epi, cta_pair=True))
+        print(f"{case} {M}x{N}x{K}: {us:.1f} us, {2 * M * N * K / us / 1e6:.0f} TFLOP/s")
+    elif case in ("prog_gate_up", "prog_down"):
+        # the same two GEMMs, each as a one-node program of the persistent kernel (two-CTA tiles)
+        from maco_b200.ops.megakernel import ProgramBuilder
+        M, N, K = (8192, 28672, 4096) if case == "prog_gate_up" else (8192, 4096, 14336)
+        a = torch.randn(M, K, device="cuda", dtype=dt)
+        b = torch.randn(N, K, device="cuda", dtype=dt) * 0.02
+        epi = "swiglu" if case == "prog_gate_up" else None
+        out = torch.empty(M, N // 2 if epi else N, device="cuda", dtype=dt)
+        pb = ProgramBuilder(torch.device("cuda"), cta_pair=True)
+        pb.gemm(a, b, out, epilogue=epi)
+        prog = pb.build()
+        us = timed(prog.run)
+        print(f"{case} {M}x{N}x{K}: {us:.1f} us, {2 * M * N * K / us / 1e6:.0f} TFLOP/s")
+    elif case in ("mlp_full", "mlp_full_1cta"):
+        from maco_b200.models.tp_mlp import TPSwiGLUMLP
+        layer = TPSwiGLUMLP(8192, 4096, 14336, cta_pair=(case == "mlp_full"))
+        layer.x_shard.normal_()
+        us = timed(lambda: layer.forward(None))
+        print(f"persistent fused MLP 8192 tok 4096->14336 ({'two' if layer.program.cta_pair else 'one'}-CTA tiles): {us:.1f} us, "
+              f"{layer.flops() / us / 1e6:.0f} TFLOP/s")
     elif case == "attention":
         B, Hq, Hkv, S = 32, 8, 1, 4096
         q = torch.randn(B, Hq, 128, device="cuda", dtype=dt)

@@ -31,7 +31,8 @@ class TPSwiGLUMLP:
     def __init__(self, tokens: int, hidden: int, ffn: int, *, rank: int = 0, world: int = 1, heap=None,
                  device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16, seed: int = 0,
                  mode: str = "static", trace: bool = False, weight_std: float = 0.02, num_workers: Optional[int] = None,
-                 comm_workers: Optional[int] = None, cta_pair: bool = True, nvls_allgather: bool = False):
+                 comm_workers: Optional[int] = None, cta_pair: bool = True, nvls_allgather: bool = False,
+                 input_slots: int = 1):
         if tokens % (world * BM) or ffn % (world * 128):
             raise ValueError("tokens must be a multiple of world*128 and ffn of world*128")
         if world > 1 and heap is None:
@@ -54,36 +55,44 @@ class TPSwiGLUMLP:
             comm_workers = 6 if world <= 2 else 16
         # two-CTA GEMM tiles: 256 x 256 per CTA pair (static queues only)
         cta_pair = cta_pair and mode == "static"
-        b = ProgramBuilder(dev, num_workers=num_workers, mode=mode, heap=heap, trace=trace,
-                           num_comm_workers=(comm_workers if world > 1 else 0), cta_pair=cta_pair)
         self.h = torch.empty(tokens, f_local, device=dev, dtype=dtype)
-        if world == 1:
-            self.x_shard = torch.empty(tokens, hidden, device=dev, dtype=dtype)
-            self.y_shard = torch.empty(tokens, hidden, device=dev, dtype=dtype)
-            e1 = b.gemm(self.x_shard, self.w_gate_up, self.h, epilogue="swiglu")
-            b.gemm(self.h, self.w_down, self.y_shard, a_ready=e1)
-        else:
-            self.x_full = heap.alloc((tokens, hidden), dtype)
-            # the input shard IS this rank's slice of the gathered buffer: nothing to copy locally
-            self.x_shard = self.x_full[rank * self.rows_local:(rank + 1) * self.rows_local]
-            self.staging = heap.alloc((world, self.rows_local, hidden), dtype)
-            self.y_shard = torch.empty(self.rows_local, hidden, device=dev, dtype=dtype)
-            fence = fused.epoch_fence_event(b)
-            nvls_allgather = nvls_allgather and bool(heap.multicast_base())
-            eg = fused.allgather_push(b, self.x_shard, self.x_full, fence=fence, multicast=nvls_allgather)
-            order = fused.gathered_order(rank, world, self.rows_local // BM, nvls_allgather)
-            e1 = b.gemm(self.x_full, self.w_gate_up, self.h, epilogue="swiglu", a_ready=eg, m_blocks=order)
-            _, eo = fused.gemm_reduce_scatter(b, self.h, self.w_down, self.staging, self.y_shard, a_ready=e1)
-            fused.epoch_fence_signal(b, [(eo.all_event[0], eo.all_event[1], False, False),
-                                         (e1.all_event[0], e1.all_event[1], False, False)])
-        self.program = b.build()
+        self.y_shard = torch.empty(self.rows_local if world > 1 else tokens, hidden, device=dev, dtype=dtype)
+        # ``input_slots`` = 2 builds the program twice over two input buffers (weights, h and the output are shared):
+        # an end-to-end loop copies the next input from the host straight into the slot the running launch does not read
+        self.programs, self.x_shards = [], []
+        for _ in range(max(1, int(input_slots))):
+            b = ProgramBuilder(dev, num_workers=num_workers, mode=mode, heap=heap, trace=trace,
+                               num_comm_workers=(comm_workers if world > 1 else 0), cta_pair=cta_pair)
+            if world == 1:
+                x_shard = torch.empty(tokens, hidden, device=dev, dtype=dtype)
+                e1 = b.gemm(x_shard, self.w_gate_up, self.h, epilogue="swiglu")
+                b.gemm(self.h, self.w_down, self.y_shard, a_ready=e1)
+            else:
+                # every slot has its own gathered buffer and staging slots: what a peer's launch on one slot writes
+                # is never touched by a launch on the other slot, so each program's own fence is all the ordering needed
+                x_full = heap.alloc((tokens, hidden), dtype)
+                # the input shard IS this rank's slice of the gathered buffer: nothing to copy locally
+                x_shard = x_full[rank * self.rows_local:(rank + 1) * self.rows_local]
+                staging = heap.alloc((world, self.rows_local, hidden), dtype)
+                self.x_full, self.staging = x_full, staging
+                fence = fused.epoch_fence_event(b)
+                use_mc = nvls_allgather and bool(heap.multicast_base())
+                eg = fused.allgather_push(b, x_shard, x_full, fence=fence, multicast=use_mc)
+                order = fused.gathered_order(rank, world, self.rows_local // BM, use_mc)
+                e1 = b.gemm(x_full, self.w_gate_up, self.h, epilogue="swiglu", a_ready=eg, m_blocks=order)
+                _, eo = fused.gemm_reduce_scatter(b, self.h, self.w_down, staging, self.y_shard, a_ready=e1)
+                fused.epoch_fence_signal(b, [(eo.all_event[0], eo.all_event[1], False, False),
+                                             (e1.all_event[0], e1.all_event[1], False, False)])
+            self.programs.append(b.build())
+            self.x_shards.append(x_shard)
+        self.program, self.x_shard = self.programs[0], self.x_shards[0]
 
-    def forward(self, x_shard: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    def forward(self, x_shard: Optional[torch.Tensor] = None, stream=None, slot: int = 0) -> torch.Tensor:
         """Runs the layer on ``x_shard`` [T/P, H] (copied into the layer's input buffer; pass None
-        when the caller already wrote ``self.x_shard``). Returns this rank's output rows."""
+        when the caller already wrote ``self.x_shards[slot]``). Returns this rank's output rows."""
         if x_shard is not None:
-            self.x_shard.copy_(x_shard, non_blocking=True)
-        self.program.run(stream=stream)
+            self.x_shards[slot].copy_(x_shard, non_blocking=True)
+        self.programs[slot].run(stream=stream)
         return self.y_shard
 
     __call__ = forward

@@ -277,7 +277,7 @@ class ProgramBuilder:
              aux: Optional[torch.Tensor] = None, alpha: float = 1.0, bn: int = 0,
              a_ready: Optional[RowEvents] = None, extra_waits: Sequence[Tuple[int, int, bool, bool]] = (),
              per_tile=None, m_blocks: Optional[Sequence[int]] = None, signal_sys: bool = False,
-             row_wait=None) -> RowEvents:
+             row_wait=None, group_blocks: Optional[int] = None) -> RowEvents:
         """Adds the tiles of ``out = epilogue(alpha * A · B^T)`` (A logically [M,K], B logically [N,K]).
 
         ``a_ready`` gives row-block events of A (a tile waits only for its 128 rows); ``extra_waits``
@@ -285,6 +285,10 @@ class ProgramBuilder:
         ``row_off``, ``signal_peer``, ``signal_peer_event``, ``epi`` (index from ``add_epilogue``) and add
         ``waits`` per tile (fused GEMM -> reduce-scatter).
         ``row_wait(mb) -> wait`` supplies a per-row-block wait instead of ``a_ready``.
+        ``group_blocks``: tiles are emitted as groups of that many row blocks sweeping all column tiles. While a
+        group runs, its A panel (group_blocks x 128 x K) stays in L2 and B streams through once, so DRAM reads
+        B once per GROUP: large groups cut the re-reads of a B that does not fit the 126 MB L2. Default: as many
+        blocks as keep the A panel near 32 MB (MACO_GEMM_PANEL_MB; at least 8) when the caller did not fix the block order, else 8.
         """
         for t in (a, b):
             if t.dim() != 2 or t.stride(1) != 1 or t.dtype not in (torch.bfloat16, torch.float16):
@@ -361,7 +365,15 @@ class ProgramBuilder:
             raw = _pack_gemm(ta, tb, epi, int(trans_a), int(trans_b), m_tiles * BM, nb * bn, 0, k_blocks, idesc, -1, 0, 0, bn)
             self.add_task(int(TaskType.LINEAR), raw, node_id=node_id, pair_half=1)
 
-        G = 8
+        if group_blocks is None:
+            G = 8
+            if m_blocks is None:
+                import os
+                panel_mb = float(os.environ.get("MACO_GEMM_PANEL_MB", "32"))
+                G = max(8, min(len(mbs), int(panel_mb * (1 << 20)) // max(1, BM * K * a.element_size())))
+        else:
+            G = max(1, int(group_blocks))
+        G += G & 1 if self.cta_pair else 0           # whole pairs of row blocks per group
         for g0 in range(0, len(mbs), G):
             grp = mbs[g0:g0 + G]
             # tiles of `G` row blocks sweep all column tiles: operands stay in L2, row blocks finish in order

@@ -82,8 +82,25 @@ class StepPipeline:
     events before returning); this keeps the same data movement and removes the bubble.
     """
 
-    def __init__(self, input_buffer: torch.Tensor, result_like: torch.Tensor, depth: int = 2):
-        self.feed = InputPrefetcher(input_buffer, depth=depth)
+    def __init__(self, input_buffer, result_like: torch.Tensor, depth: int = 2):
+        """``input_buffer``: the layer's input tensor, or a list of TWO alternating input tensors (a layer built
+        with two input slots). With two slots the host -> device copy of step i+1 goes straight into the slot that
+        step i does not read, and ``launch`` / ``result`` are called with the slot index; with one, inputs are staged
+        in side buffers and moved in with a device-to-device copy before each launch."""
+        self.slots = list(input_buffer) if isinstance(input_buffer, (list, tuple)) else None
+        if self.slots is not None:
+            if len(self.slots) != 2:
+                raise ValueError("direct input delivery alternates between exactly two input buffers")
+            dev = self.slots[0].device
+            self._copy_stream = torch.cuda.Stream(device=dev)
+            self._ready = [torch.cuda.Event() for _ in range(2)]
+            self._free = [torch.cuda.Event() for _ in range(2)]
+            self._loaded = [False, False]
+            self._consumed = [False, False]
+            input_buffer = self.slots[0]
+            self.feed = None
+        else:
+            self.feed = InputPrefetcher(input_buffer, depth=depth)
         self.input_buffer = input_buffer
         from ..config import config
         self._host = [torch.empty(result_like.shape, dtype=result_like.dtype) for _ in range(depth)]
@@ -95,6 +112,8 @@ class StepPipeline:
 
     def step(self, host_input: torch.Tensor, launch, result, next_host_input: Optional[torch.Tensor] = None):
         """Runs one step; returns the host copy of the previous step's result (None on the first step)."""
+        if self.slots is not None:
+            return self._step_direct(host_input, launch, result, next_host_input)
         if not self.feed.pending:
             self.feed.submit(host_input)
         self.feed.deliver(self.input_buffer)
@@ -104,6 +123,34 @@ class StepPipeline:
         self._host[slot].copy_(result(), non_blocking=True)
         self._done[slot].record()
         self._pending.append(slot)
+        self._step += 1
+        if len(self._pending) >= len(self._host):
+            return self._pop()
+        return None
+
+    def _h2d(self, slot: int, host: torch.Tensor) -> None:
+        cs = self._copy_stream
+        with torch.cuda.stream(cs):
+            if self._consumed[slot]:
+                cs.wait_event(self._free[slot])          # the launch that read this slot last has finished
+            self.slots[slot].copy_(host, non_blocking=True)
+            self._ready[slot].record(cs)
+        self._loaded[slot] = True
+
+    def _step_direct(self, host_input, launch, result, next_host_input):
+        slot = self._step & 1
+        cur = torch.cuda.current_stream(self.slots[0].device)
+        if not self._loaded[slot]:
+            self._h2d(slot, host_input)
+        cur.wait_event(self._ready[slot])
+        launch(slot)
+        self._free[slot].record(cur)
+        self._consumed[slot], self._loaded[slot] = True, False
+        self._h2d(slot ^ 1, next_host_input if next_host_input is not None else host_input)
+        hs = self._step % len(self._host)
+        self._host[hs].copy_(result(slot), non_blocking=True)
+        self._done[hs].record()
+        self._pending.append(hs)
         self._step += 1
         if len(self._pending) >= len(self._host):
             return self._pop()

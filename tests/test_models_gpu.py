@@ -31,6 +31,17 @@ def test_tp_mlp_single_gpu(cta_pair):
     assert (y.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
 
 
+def test_tp_mlp_two_input_slots():
+    from maco_b200.models.tp_mlp import TPSwiGLUMLP
+    layer = TPSwiGLUMLP(512, 512, 1024, seed=1, input_slots=2)
+    xs = [torch.randn(512, 512, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    for it in range(4):
+        y = layer(xs[it & 1], slot=it & 1)
+        torch.cuda.synchronize()
+        ref = layer.reference(xs[it & 1])
+        assert (y.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item()), it
+
+
 @pytest.mark.parametrize("mode", ["static", "dynamic"])
 def test_qwen3_decode_layer_single_gpu(mode):
     from maco_b200 import _native

@@ -202,7 +202,7 @@ def _tp_mlp(rank, world):
     from maco_b200 import _native
     from maco_b200.models.tp_mlp import TPSwiGLUMLP
     tokens, hidden, ffn = 1024, 1024, 2048
-    layer = TPSwiGLUMLP(tokens, hidden, ffn, rank=rank, world=world, heap=heap, seed=3)
+    layer = TPSwiGLUMLP(tokens, hidden, ffn, rank=rank, world=world, heap=heap, seed=3, input_slots=2)
     torch.manual_seed(7)
     x_full = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)      # same on every rank
     rows = tokens // world
@@ -211,7 +211,7 @@ def _tp_mlp(rank, world):
     ref = partial[rank * rows:(rank + 1) * rows]
     outs = []
     for it in range(5):
-        y = layer(x_full[rank * rows:(rank + 1) * rows])
+        y = layer(x_full[rank * rows:(rank + 1) * rows], slot=it & 1)       # alternating input slots
         torch.cuda.synchronize()
         err = (y.float() - ref).abs().max().item()
         assert err < 3e-2 * max(1.0, ref.abs().max().item()), (it, err)
