@@ -78,6 +78,28 @@ def cfg_tp_mlp(torch, dist, rank, world, heap, args):
         if world > 1:
             dist.reduce_scatter_tensor(y_shard, y)
 
+    # the same layer written against the public TaskGraph API (arm "graph"): allgather -> linear(swiglu) -> linear ->
+    # reduce_scatter, lowered to one persistent launch
+    import maco_b200 as maco
+    from maco_b200 import ops
+    gr = maco.TaskGraph()
+    if world > 1:
+        xs_g = heap.alloc((rows, H), torch.bfloat16)
+        xs_g.copy_(x_shard)
+        ag = gr.allgather(xs_g)
+        hh = gr.linear(ag.output, layer.w_gate_up, activation="swiglu")
+        yy = gr.linear(hh.output, layer.w_down)
+        gr.reduce_scatter(yy.output)
+    else:
+        hh = gr.linear(x_shard, layer.w_gate_up, activation="swiglu")
+        gr.linear(hh.output, layer.w_down)
+    from maco_b200.config import config as _cfg
+    _cfg.set(profile=bool(args.trace))
+    gr.compile()
+    _cfg.set(profile=False)
+    args.graph_program = getattr(gr._runtime, "_program", None)
+    args.graph_step = gr.execute
+    args.graph_kind = gr.runtime_kind
     p = peaks()
     flops = 2.0 * T * H * F * 3 / world
     link = (T * H * 2) * (world - 1) / world                       # bytes in (all-gather) = bytes out (partials)
@@ -223,7 +245,7 @@ def cfg_moe(torch, dist, rank, world, heap, args):
 
 
 CONFIGS = {"tp_mlp": cfg_tp_mlp, "dp_backward": cfg_dp_backward, "qwen3_decode": cfg_qwen3_decode, "moe": cfg_moe}
-HEAP_MB = {"tp_mlp": 256, "dp_backward": 2500, "qwen3_decode": 64, "moe": 700}
+HEAP_MB = {"tp_mlp": 512, "dp_backward": 2500, "qwen3_decode": 64, "moe": 700}
 
 
 def main():
@@ -268,7 +290,10 @@ def main():
     ours, library, roof = CONFIGS[args.config](torch, dist, rank, world, heap, args)
     p = peaks()
     bound = max(roof.values())
-    for arm, fn in (("library", library), ("ours", ours)):
+    arms = [("library", library), ("ours", ours)]
+    if getattr(args, "graph_step", None) is not None:
+        arms.append(("graph", args.graph_step))
+    for arm, fn in arms:
         if arm not in args.arms.split(","):
             continue
         for _ in range(args.warmup):
@@ -280,7 +305,11 @@ def main():
                     "fraction_of_roofline": round(bound / us, 3), "peaks": p["source"],
                     "nvlink_gbs": {"measured_used": p["nvlink_gbs"], "nominal": p["nvlink_gbs_nominal"]},
                     "kernel_status": _native.status(clear=False)}
+            if arm == "graph":
+                line["runtime"] = args.graph_kind
             os.write(real_stdout, (json.dumps(line) + "\n").encode())
+            if arm == "graph" and args.trace and getattr(args, "graph_program", None) is not None:
+                os.write(real_stdout, (json.dumps({"config": args.config, "graph_trace": args.graph_program.stats()}) + "\n").encode())
             if arm == "ours" and args.trace:
                 os.write(real_stdout, (json.dumps({"config": args.config, "trace": args.program.stats()}) + "\n").encode())
                 if args.trace_file:

@@ -343,7 +343,9 @@ class ProgramBuilder:
                 waits = self.join(waits, node_id)
             return waits
 
-        def emit(mb: int, nb: int, half: Optional[int]) -> None:
+        def prepare(mb: int, nb: int):
+            """The tile's wait conditions (reduced to two, which may add join tasks) and per-tile overrides."""
+            first_join = len(self.tasks)
             waits = tile_waits(mb)
             ov = per_tile(mb, nb) if per_tile is not None else {}
             if ov.get("waits"):
@@ -352,6 +354,15 @@ class ProgramBuilder:
                     waits = self.join(waits, node_id)
             if pair and ov.get("count_ptr", 0):
                 raise ValueError("run-time counted tiles are not available in two-CTA programs")
+            return waits, ov, range(first_join, len(self.tasks))
+
+        def emit(mb: int, nb: int, half: Optional[int], prepared=None) -> None:
+            waits, ov, joins = prepared if prepared is not None else prepare(mb, nb)
+            # The tile's own join tasks run on the tile's worker, directly in front of it: a join blocks the worker
+            # that holds it, and on any other worker it would stall that worker's tiles (and, in two-CTA
+            # programs, its partner) for a condition only this tile cares about.
+            for j in joins:
+                self.tasks[j]["attach_to"] = len(self.tasks)
             raw = _pack_gemm(ta, tb, ov.get("epi", epi), int(trans_a), int(trans_b), mb * BM, nb * bn, 0, k_blocks, idesc,
                              ov.get("peer", -1), ov.get("row_off", 0), ov.get("out_off", 0), bn,
                              ov.get("count_base", 0), ov.get("count_ptr", 0))
@@ -383,9 +394,14 @@ class ProgramBuilder:
                         emit(mb, nb, None)
                     continue
                 for j in range(0, len(grp), 2):
-                    emit(grp[j], nb, 0)
-                    if j + 1 < len(grp):
-                        emit(grp[j + 1], nb, 1)
+                    # Join tasks of BOTH halves go in front of both halves: the leader half cannot finish before
+                    # the other half's operands are loaded, so nothing the other half waits for may sit behind the
+                    # leader half in any queue (static queues follow emission order).
+                    p0 = prepare(grp[j], nb)
+                    p1 = prepare(grp[j + 1], nb) if j + 1 < len(grp) else None
+                    emit(grp[j], nb, 0, p0)
+                    if p1 is not None:
+                        emit(grp[j + 1], nb, 1, p1)
                     else:
                         emit_filler(nb)
         total = len(mbs) * n_tiles
@@ -752,28 +768,37 @@ class Program:
         rr_c = rr_m = rr_a = rr_p = 0
         n_pairs = n_compute // 2
         pair_of_leader = 0
+        attached: Dict[int, List[int]] = {}             # task -> join tasks that run right in front of it
         for i, t in enumerate(b.tasks):
+            if t.get("attach_to") is not None:
+                # Still a topological order: a join's only consumer is the task it is attached to.
+                attached.setdefault(t["attach_to"], []).append(i)
+                continue
             if t.get("pair_half") is not None:
                 # halves of a two-CTA tile: consecutive tasks, leader on worker 2j, the other half on 2j+1; both
                 # workers see their pair tiles in the same order (the MMA of one serves both)
                 if t["pair_half"] == 0:
                     pair_of_leader = (rr_p + rr_p // n_pairs) % n_pairs
                     rr_p += 1
-                queues[2 * pair_of_leader + t["pair_half"]].append(i)
+                q = 2 * pair_of_leader + t["pair_half"]
             elif (t["flags"] & TF_ANY_WORKER) and Wc > 0:
-                queues[(W - 1 - rr_a) % W].append(i)       # communication workers (highest indices) first
+                q = (W - 1 - rr_a) % W                     # communication workers (highest indices) first
                 rr_a += 1
             elif (t["flags"] & TF_COMM_WORKER) and Wc > 0:
-                queues[n_compute + rr_m % Wc].append(i)
+                q = n_compute + rr_m % Wc
                 rr_m += 1
             elif t.get("worker") is not None:
-                queues[t["worker"] % n_compute].append(i)
+                q = t["worker"] % n_compute
             else:
                 # rotate by one worker per wave: with a plain modulo a worker would see the same position of
                 # every periodic task pattern (the same row block of every expert slab, say) and the load
                 # would follow that pattern instead of averaging out
-                queues[(rr_c + rr_c // n_compute) % n_compute].append(i)
+                q = (rr_c + rr_c // n_compute) % n_compute
                 rr_c += 1
+            queues[q] += attached.pop(i, [])
+            queues[q].append(i)
+        if attached:
+            raise RuntimeError("join tasks attached to a task that was never emitted")
         stride = max(1, max(len(q) for q in queues))
         sq = np.full((W, stride), QUEUE_TERMINATE, dtype=np.uint32)
         for w, q in enumerate(queues):
@@ -1038,6 +1063,7 @@ def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None)
                     and gc.fusable_linear_reduce_scatter(n, cs[0], heap.world) and not _few_rows(n)):
                 fused_rs[n._node_id] = cs[0]
     produced: Dict[int, Tuple[TaskNode, RowEvents]] = {}       # node id -> events of its output
+    behind_collective: set = set()                             # nodes that (transitively) depend on a collective
 
     def ready_of(node: TaskNode, t: torch.Tensor, rows: int) -> Tuple[Optional[RowEvents], List[tuple]]:
         """Row-aligned events for tensor ``t`` if one dependency produced exactly this view; every other
@@ -1061,6 +1087,9 @@ def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None)
         out = node.outputs[0] if node.outputs else None
         if out is None or out.numel() == 0:
             continue
+        after_coll = any(d._node_id in behind_collective for d in node.depends_on)
+        if dist and (t in _COLL or after_coll):
+            behind_collective.add(node._node_id)
         if t in (TaskType.LINEAR, TaskType.MATMUL):
             x2 = _flat2d(node.inputs[0])
             w = node.inputs[1]
@@ -1072,7 +1101,8 @@ def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None)
                 # linear -> reduce_scatter: partial tiles leave through the GEMM epilogue; the product itself is
                 # never written on this rank
                 rs = fused_rs[node._node_id]
-                gemm_ev, out_ev = gc.lower_linear_reduce_scatter(ctx, node, rs, aligned, extra)
+                gemm_ev, out_ev = gc.lower_linear_reduce_scatter(ctx, node, rs, aligned, extra, need_opening=not after_coll)
+                behind_collective.add(rs._node_id)
                 produced[node._node_id] = (node, gemm_ev)
                 produced[rs._node_id] = (rs, out_ev)
                 skip[rs._node_id] = True
@@ -1083,8 +1113,16 @@ def lower_graph(graph, mode: Optional[str] = None, trace: Optional[bool] = None)
                 # decode-shaped linear: a weight stream, cut along K over every SM (csrc/splitk_tasks.cuh)
                 ev = b.gemm_splitk(x2, w, out2, epilogue=act if act == "swiglu" else None, a_ready=aligned, extra_waits=extra)
             else:
+                order = None
+                if dist and aligned is not None and aligned.sys and x2.shape[0] % (heap.world * BM) == 0:
+                    # rows that arrive from other ranks (an all-gathered input): own shard first, then in arrival order
+                    from ..parallel import fused as _fused
+                    src = next((d for d in node.depends_on if d.task_type == TaskType.ALLGATHER
+                                and d.outputs[0].data_ptr() == node.inputs[0].data_ptr()), None)
+                    if src is not None:
+                        order = _fused.gathered_order(heap.rank, heap.world, x2.shape[0] // heap.world // BM, False)
                 ev = b.gemm(x2, w, out2, trans_b=(t == TaskType.MATMUL), epilogue=act, bias=bias,
-                            a_ready=aligned, extra_waits=extra)
+                            a_ready=aligned, extra_waits=extra, m_blocks=order)
             produced[node._node_id] = (node, ev)
         elif t in _ELT_TYPES:
             x = node.inputs[0]

@@ -235,7 +235,10 @@ def fusable_linear_reduce_scatter(lin: TaskNode, rs: TaskNode, world: int) -> bo
 
 
 def lower_linear_reduce_scatter(ctx: DistContext, lin: TaskNode, rs: TaskNode, a_ready: Optional[RowEvents],
-                                extra: Sequence[Wait]) -> Tuple[RowEvents, RowEvents]:
+                                extra: Sequence[Wait], need_opening: bool = True) -> Tuple[RowEvents, RowEvents]:
+    """``need_opening`` False: the input already hangs on a collective of this launch. Whatever arrived from a peer
+    left it after that peer saw every rank's opening signal, so the tiles need no opening wait of their own (a
+    third condition would cost every own-block tile a join task)."""
     b, heap, world = ctx.b, ctx.heap, ctx.world
     x, w = lin.inputs[0], lin.inputs[1]
     out = rs.outputs[0]
@@ -244,7 +247,7 @@ def lower_linear_reduce_scatter(ctx: DistContext, lin: TaskNode, rs: TaskNode, a
     ctx.heap_buffers.append(staging)
     scale = 1.0 / world if rs.attrs.get("op", "sum") in ("avg", "mean") else 1.0
     gemm_ev, out_ev = fused.gemm_reduce_scatter(b, x, w, staging, out.view(rows_local, Nn), a_ready=a_ready, scale=scale,
-                                                extra_waits=list(extra) + [ctx.opening()])
+                                                extra_waits=list(extra) + ([ctx.opening()] if need_opening else []))
     return gemm_ev, out_ev
 
 

@@ -69,6 +69,7 @@ class TaskGraph:
         self._next_node_id = 0
         self._weights: Dict[str, torch.Tensor] = {}
         self.runtime_kind: Optional[str] = None
+        self._heap_outputs: List[torch.Tensor] = []      # outputs this graph took from the symmetric heap
 
     # ------------------------------------------------------------------ construction helpers
     @staticmethod
@@ -80,7 +81,7 @@ class TaskGraph:
     def _auto_detect_workers(self) -> int:
         if self.device.type == "cuda" and torch.cuda.is_available():
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-            return max(1, sms - 8)
+            return max(1, sms)          # every SM runs a worker CTA; static programs need no scheduler CTA
         return max(1, min(8, os.cpu_count() or 1))
 
     def _check_not_compiled(self) -> None:
@@ -110,9 +111,25 @@ class TaskGraph:
         return self._add_node(TaskNode(name=name or "", task_type=ttype, inputs=list(inputs),
                                        outputs=list(outputs), dims=list(dims), attrs=dict(attrs)))
 
-    def _out_like(self, ref: torch.Tensor, shape, output: Optional[torch.Tensor], method: str) -> torch.Tensor:
+    def _out_like(self, ref: torch.Tensor, shape, output: Optional[torch.Tensor], method: str,
+                  peer_written: bool = False) -> torch.Tensor:
         shape = tuple(shape)
         if output is None:
+            if peer_written and ref.is_cuda:
+                # A buffer other ranks write into (all-gather, all-to-all) comes out of the symmetric heap when one
+                # exists: peers then push straight into it, where a private tensor would need a heap stand-in
+                # of the same size plus a copy inside the launch. Every rank builds the same graph, so the offsets
+                # agree.
+                from ..comm.process_group import get_world_size
+                from ..parallel.symm_heap import current_heap
+                heap = current_heap() if get_world_size() > 1 else None
+                if heap is not None:
+                    try:
+                        out = heap.alloc(shape, ref.dtype)
+                        self._heap_outputs.append(out)
+                        return out
+                    except MemoryError:
+                        pass
             return torch.empty(shape, dtype=ref.dtype, device=ref.device)
         self._validate(output, "output", method)
         if tuple(output.shape) != shape:
@@ -261,7 +278,8 @@ class TaskGraph:
         self._validate(tensor, "tensor", "allgather", min_ndim=1)
         from ..comm.process_group import get_world_size
         world = get_world_size()
-        out = self._out_like(tensor, (tensor.shape[0] * world,) + tuple(tensor.shape[1:]), output, "allgather")
+        out = self._out_like(tensor, (tensor.shape[0] * world,) + tuple(tensor.shape[1:]), output, "allgather",
+                             peer_written=True)
         return self._new(TaskType.ALLGATHER, name, [tensor], [out], [tensor.numel()])
 
     def reduce_scatter(self, tensor, name: Optional[str] = None, output=None, op: str = "sum") -> TaskNode:
@@ -299,7 +317,7 @@ class TaskGraph:
             if sd != gd:
                 shape[sd] //= world
                 shape[gd] *= world
-        out = self._out_like(input, shape, output, "all_to_all")
+        out = self._out_like(input, shape, output, "all_to_all", peer_written=True)
         return self._new(TaskType.ALL_TO_ALL, name, [input], [out], list(input.shape), scatter_dim=sd, gather_dim=gd)
 
     # ------------------------------------------------------------------ overlap
@@ -328,6 +346,26 @@ class TaskGraph:
         if not self._compiled:
             self.compile()
         self._runtime.execute(self._schedule, stream=stream)
+
+    def release(self) -> None:
+        """Returns what this graph holds in the symmetric heap (peer-written outputs it allocated itself, and the
+        event counters and staging buffers of its persistent program). Collective: every rank calls it at the
+        same point; the graph must not run again."""
+        from ..parallel.symm_heap import current_heap
+        heap = current_heap()
+        prog = getattr(self._runtime, "_program", None)
+        if heap is None or (not self._heap_outputs and getattr(prog, "heap", None) is None):
+            return
+        from ..comm.process_group import barrier
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        barrier()
+        if prog is not None and getattr(prog, "heap", None) is not None and prog.d_events is not None:
+            prog.free_heap()
+        for t in self._heap_outputs:
+            heap.free(t)
+        self._heap_outputs = []
+        self._compiled, self._runtime = False, None
 
     def _infer_dependencies(self) -> None:
         """RAW, WAW and WAR edges from the byte ranges nodes read and write."""

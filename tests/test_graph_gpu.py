@@ -173,3 +173,29 @@ def test_compiled_schedule_is_cached_for_identical_graphs():
         g.execute()
         torch.cuda.synchronize()
         torch.testing.assert_close(out.float(), x.float() @ w.float().t(), atol=1e-1, rtol=5e-2)
+
+
+def test_persistent_context_compiles_a_sequential_module():
+    """PersistentContext turns a chain of supported layers into one persistent-kernel launch per forward."""
+    import torch.nn as nn
+    from maco_b200.core import PersistentContext, SMConfig, Role
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(512, 1024), nn.GELU(approximate="tanh"), nn.LayerNorm(1024), nn.Linear(1024, 256, bias=False),
+                          nn.SiLU()).cuda().to(torch.bfloat16).eval()
+    x = torch.randn(384, 512, device="cuda", dtype=torch.bfloat16)
+    cfg = SMConfig(total_sms=148)
+    cfg.assign_role((0, 96), Role.COMPUTE)
+    cfg.assign_role((96, 97), Role.LOCAL_SCHEDULER)
+    with torch.no_grad(), PersistentContext(model, cfg) as ctx:
+        for _ in range(2):
+            y = ctx(x)
+            torch.cuda.synchronize()
+            assert ctx.last_runtime == "persistent" and ctx.worker_config["num_workers"] == 96
+            import copy
+            ref = copy.deepcopy(model).float()(x.float())
+            torch.testing.assert_close(y.float(), ref, atol=1e-1, rtol=5e-2)
+        assert "layer0.weight" in ctx.registry.weights
+        # a module the kernel has no tasks for runs as it is
+        other = PersistentContext(nn.Sequential(nn.Linear(512, 64), nn.Tanh()).cuda().to(torch.bfloat16))
+        other(x)
+        assert other.last_runtime == "module"

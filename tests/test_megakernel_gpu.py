@@ -64,6 +64,31 @@ def test_fused_mlp_program_two_cta_tiles(tokens, workers):
     assert "two-CTA" in prog.describe()
 
 
+def test_two_cta_tiles_with_joined_wait_conditions():
+    """Tiles with three wait conditions get join tasks; in a two-CTA program the joins of both halves must precede
+    both halves in the queues (few workers, so every queue holds joins and halves of many tiles)."""
+    from maco_b200.ops import megakernel as mk
+    dt = torch.bfloat16
+    x = torch.randn(1024, 512, device="cuda", dtype=dt)
+    s1, s2 = torch.randn(256, 512, device="cuda", dtype=dt), torch.randn(256, 512, device="cuda", dtype=dt)
+    w = torch.randn(768, 512, device="cuda", dtype=dt) * 0.05
+    xn, o1, o2 = torch.empty_like(x), torch.empty_like(s1), torch.empty_like(s2)
+    y = torch.empty(1024, 768, device="cuda", dtype=dt)
+    b = mk.ProgramBuilder(torch.device("cuda"), num_workers=6, cta_pair=True)
+    e0 = b.elementwise(112, x, xn, rows=1024, cols=512, f0=2.0)                     # scale: row-block events
+    ea = b.elementwise(105, s1, o1, rows=256, cols=512)
+    eb = b.elementwise(106, s2, o2, rows=256, cols=512)
+    b.gemm(xn, w, y, a_ready=e0, extra_waits=[(ea.all_event[0], ea.all_event[1], False, False),
+                                               (eb.all_event[0], eb.all_event[1], False, False)])
+    prog = b.build()
+    for _ in range(3):
+        y.zero_()
+        prog.run()
+    torch.cuda.synchronize()
+    assert _native.status() == 0
+    assert_close(y, (2.0 * x.float()).to(dt).float() @ w.float().t(), dt)
+
+
 def test_two_cta_program_backward_majors():
     """dgrad (plain a @ b: MN-major B) and wgrad (a^T @ b: both operands MN-major) as two-CTA tiles in one program."""
     from maco_b200.ops import megakernel as mk
