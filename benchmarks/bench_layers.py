@@ -84,9 +84,11 @@ def cfg_tp_mlp(torch, dist, rank, world, heap, args):
     from maco_b200 import ops
     gr = maco.TaskGraph()
     if world > 1:
-        xs_g = heap.alloc((rows, H), torch.bfloat16)
+        # the shard is this rank's slice of the gathered buffer (both in the symmetric heap): no local copy
+        x_all = heap.alloc((T, H), torch.bfloat16)
+        xs_g = x_all[rank * rows:(rank + 1) * rows]
         xs_g.copy_(x_shard)
-        ag = gr.allgather(xs_g)
+        ag = gr.allgather(xs_g, output=x_all)
         hh = gr.linear(ag.output, layer.w_gate_up, activation="swiglu")
         yy = gr.linear(hh.output, layer.w_down)
         gr.reduce_scatter(yy.output)

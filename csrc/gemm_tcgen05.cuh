@@ -199,7 +199,7 @@ MACO_DEVICE void epi_store_row32(const GemmEpilogue& e, void* out_base, long lon
                                  int ncols_valid, const float (&v)[32]) {
   if (e.out_type == MACO_DT_F32) {
     float* p = reinterpret_cast<float*>(out_base) + row * e.ld_out + col0;
-    if (e.mode == MACO_EPI_F32_ATOMIC) {
+    if (e.mode == MACO_EPI_F32_ATOMIC || e.mode == MACO_EPI_SPLITK_FUSED) {
       // split-K: several tiles add into the same fp32 block; vector reductions at the L2
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
@@ -386,7 +386,7 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
       float v[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * e.alpha;
-      if (e.bias != nullptr) {
+      if (e.bias != nullptr && e.mode != MACO_EPI_SPLITK_FUSED) {     // (that mode keeps its arrival counters there)
 #pragma unroll
         for (int j = 0; j < 32; ++j) if (j < valid) v[j] += epi_bias(e, col0 + j);
       }

@@ -487,6 +487,30 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
       if (!ok) cur[2] = 1;
       ++seq;
       it += (uint32_t)g.k_blocks;
+      if (e.mode == MACO_EPI_SPLITK_FUSED) {
+        // Split-K with the finishing pass folded in: every tile adds its partial sums to the workspace and then
+        // arrives at its column tile's counter; whoever arrives last finds all K slices summed and finishes the
+        // columns here, while this worker's TMA and MMA warps already stream the next tile. (No separate
+        // finishing task, no dependency hop between the two.) The counter only grows: `bias_type` arrivals per launch.
+        __threadfence();                               // this thread's reductions are performed before the arrival
+        general_bar();
+        if (leader) {
+          uint32_t* ctr = reinterpret_cast<uint32_t*>(const_cast<void*>(e.bias)) + g.n0 / 256;
+          cur[3] = ((atomicAdd(ctr, 1u) + 1u) % (uint32_t)e.bias_type) == 0u ? 1u : 0u;
+        }
+        general_bar();
+        if (cur[3] != 0) {
+          __threadfence();
+          MacoEltArgs fa = *reinterpret_cast<const MacoEltArgs*>(e.aux);
+          const int c0 = fa.i0 == 1 ? g.n0 / 2 : g.n0;    // SwiGLU folds 256 workspace columns into 128 outputs
+          fa.in0 = reinterpret_cast<const float*>(fa.in0) + g.n0;
+          if (fa.in1 != nullptr) fa.in1 = reinterpret_cast<const uint16_t*>(fa.in1) + c0;
+          fa.in2 = reinterpret_cast<const void*>(reinterpret_cast<unsigned long long>(fa.in2) + (unsigned long long)c0 * 2ull);
+          if (fa.out != nullptr) fa.out = reinterpret_cast<uint16_t*>(fa.out) + c0;
+          fa.cols = fa.i0 == 1 ? 128 : 256;
+          splitk_finalize(p, fa, tid);
+        }
+      }
     } else {
       if (leader) cur[1] = wait_deps(p, d, task, c.abort_word, p.trace ? &wait_ns : nullptr) ? 1u : 0u;
       general_bar();

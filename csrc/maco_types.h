@@ -62,7 +62,13 @@ enum MacoEpilogueMode {
   MACO_EPI_GELU_BWD = 5,   /* out = alpha * acc * gelu'(aux) */
   MACO_EPI_SILU = 6,
   MACO_EPI_RESIDUAL = 7,   /* out = alpha * acc + bias + aux */
-  MACO_EPI_F32_ATOMIC = 8  /* fp32 out += alpha * acc with atomic adds: split-K partial tiles share one buffer */
+  MACO_EPI_F32_ATOMIC = 8, /* fp32 out += alpha * acc with atomic adds: split-K partial tiles share one buffer */
+  /* As F32_ATOMIC, and the tile that arrives LAST for its 256 columns finishes them (sum -> operator -> 16-bit
+     output, workspace zeroed again). The record's other fields change meaning: `bias` = uint32 arrival counters,
+     one per 256-column tile, never reset; `bias_type` = arrivals per column tile (the K slices); `aux` = a
+     MacoEltArgs in device memory written as for a SPLITK_FIN task over ALL columns (the kernel offsets it to the
+     tile's columns). */
+  MACO_EPI_SPLITK_FUSED = 9
 };
 
 struct GemmEpilogue {

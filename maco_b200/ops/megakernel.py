@@ -33,7 +33,8 @@ MAX_PEERS = 16
 WORKER_QUEUE_SIZE = 1024
 T_SPLITK_FIN = 118
 
-EPI = {None: 0, "none": 0, "gelu": 1, "swiglu": 2, "f32": 3, "f32_acc": 4, "gelu_bwd": 5, "silu": 6, "residual": 7, "f32_atomic": 8}
+EPI = {None: 0, "none": 0, "gelu": 1, "swiglu": 2, "f32": 3, "f32_acc": 4, "gelu_bwd": 5, "silu": 6, "residual": 7, "f32_atomic": 8,
+       "splitk_fused": 9}
 
 TASK_DTYPE = np.dtype([
     ("type", "<u2"), ("flags", "<u2"), ("node_id", "<u4"), ("wait_event", "<i4", 2), ("wait_count", "<u4", 2),
@@ -244,12 +245,18 @@ class ProgramBuilder:
         return len(self.tasks) - 1
 
     def join(self, waits: List[Tuple[int, int, bool, bool]], node_id: int = 0) -> List[Tuple[int, int, bool, bool]]:
-        """Reduces a list of wait conditions to at most two by chaining NOP tasks."""
+        """Reduces a list of wait conditions to at most two with a balanced tree of NOP tasks (depth log2 n: a
+        chain of n would add one dependency hop of a few microseconds per condition)."""
         waits = list(dict.fromkeys(waits))
         while len(waits) > 2:
-            ev = self.new_event()
-            self.add_task(int(TaskType.NOP), b"", waits=waits[:2], signals=[ev], node_id=node_id)
-            waits = [(ev, 1, False, False)] + waits[2:]
+            nxt = []
+            for i in range(0, len(waits) - 1, 2):
+                ev = self.new_event()
+                self.add_task(int(TaskType.NOP), b"", waits=waits[i:i + 2], signals=[ev], node_id=node_id)
+                nxt.append((ev, 1, False, False))
+            if len(waits) % 2:
+                nxt.append(waits[-1])
+            waits = nxt
         return waits
 
     def _tmap(self, t: torch.Tensor, rows: int, cols: int, ld: int, mn_major: bool, box_rows: int) -> int:
@@ -434,15 +441,19 @@ class ProgramBuilder:
                     epilogue: Optional[str] = None, aux: Optional[torch.Tensor] = None,
                     a_ready: Optional[RowEvents] = None, extra_waits: Sequence[Tuple[int, int, bool, bool]] = (),
                     heap_out_off: Optional[int] = None, ld_out: Optional[int] = None,
-                    signal_peer_event: int = -1, rows_per_task: int = 0) -> RowEvents:
+                    signal_peer_event: int = -1, rows_per_task: int = 0, fused_finish: Optional[bool] = None) -> RowEvents:
         """``out = op(a @ w.T)`` for at most 128 rows, bound by streaming ``w`` out of HBM.
 
         The K dimension is cut into ``split_k`` slices (0: enough slices for every worker to hold a tile),
         256-column tcgen05 tiles add their fp32 partial sums into one workspace with vector reductions,
-        and SPLITK_FIN tasks (csrc/splitk_tasks.cuh) apply ``epilogue`` (None, "swiglu" over the
-        interleaved gate/up layout, "residual" with ``aux``) and write the 16-bit result: into ``out``, or,
+        and a finishing pass (csrc/splitk_tasks.cuh) applies ``epilogue`` (None, "swiglu" over the
+        interleaved gate/up layout, "residual" with ``aux``) and writes the 16-bit result: into ``out``, or,
         with ``heap_out_off``, at that byte offset of EVERY rank's symmetric heap (the exchange step of a
         one-shot all-reduce), bumping ``signal_peer_event`` on every rank.
+        ``fused_finish`` (default on; env ``MACO_SPLITK_FUSED=0`` turns it off): the tile that arrives last at
+        its column tile's counter runs the finishing pass for those columns in its own epilogue warps, while the
+        worker's TMA and MMA warps stream the next tile. Off: SPLITK_FIN tasks behind an event that counts all
+        tiles (one more dependency hop and a tail of short tasks).
         The reference runs such GEMMs as one torch.mm each (maco/task_graph/runtime.py:188-209).
         """
         if self.cta_pair:
@@ -463,8 +474,30 @@ class ProgramBuilder:
         idesc = make_idesc(ab, BM, 256, 0, 0)
         ta = self._tmap(a, a.shape[0], a.shape[1], a.stride(0), False, BM)
         tb = self._tmap(w, w.shape[0], w.shape[1], w.stride(0), False, 256)
-        self.epis.append(_pack_epilogue(ws.data_ptr(), None, None, Nn, 0, EPI["f32_atomic"], N.DTYPE_CODE[torch.float32], 0, 0,
-                                        M, Nn, 1.0))
+        out_cols = Nn // 2 if mode == 1 else Nn
+        ld_o = ld_out if ld_out is not None else (out.stride(0) if out is not None else out_cols)
+        if aux is not None and aux.stride(0) != ld_o:
+            raise ValueError("gemm_splitk: aux must have the output's row stride")
+        dt = N.DTYPE_CODE[out_dtype]
+        es = 2
+        if fused_finish is None:
+            import os
+            fused_finish = os.environ.get("MACO_SPLITK_FUSED", "1") != "0"
+        if fused_finish:
+            # the tile that arrives last at its column tile's counter finishes those columns itself
+            # (MACO_EPI_SPLITK_FUSED in csrc/maco_types.h): no finishing tasks, no hop between the two halves
+            counters = torch.zeros(n_tiles, device=a.device, dtype=torch.int32)
+            self.launch_state.append(counters)
+            fin = _pack_elt(ws.data_ptr(), aux.data_ptr() if aux is not None else 0, heap_out_off or 0,
+                            out.data_ptr() if out is not None else 0, 0, M, out_cols, dt, Nn, ld_o, i0=mode,
+                            i1=-2 if heap_out_off is not None else -1)
+            fin_dev = torch.frombuffer(bytearray(fin), dtype=torch.uint8).to(a.device)
+            self.keepalive += [counters, fin_dev]
+            self.epis.append(_pack_epilogue(ws.data_ptr(), counters.data_ptr(), fin_dev.data_ptr(), Nn, 0, EPI["splitk_fused"],
+                                            N.DTYPE_CODE[torch.float32], split_k, 0, M, Nn, 1.0))
+        else:
+            self.epis.append(_pack_epilogue(ws.data_ptr(), None, None, Nn, 0, EPI["f32_atomic"], N.DTYPE_CODE[torch.float32], 0, 0,
+                                            M, Nn, 1.0))
         epi = len(self.epis) - 1
         self.keepalive += [t for t in (a, w, out, aux, ws) if t is not None]
         node_id = self.new_node_id()
@@ -478,17 +511,17 @@ class ProgramBuilder:
         for sp in range(split_k):
             kb0 = sp * k_blocks // split_k
             kb1 = (sp + 1) * k_blocks // split_k
-            if kb1 <= kb0:
-                continue
             for nb in range(n_tiles):
                 raw = _pack_gemm(ta, tb, epi, 0, 0, 0, nb * 256, kb0 * BK, kb1 - kb0, idesc, -1, 0, 0, 256)
-                self.add_task(int(TaskType.LINEAR), raw, waits=waits, signals=[e_ws], node_id=node_id)
+                if fused_finish:
+                    self.add_task(int(TaskType.LINEAR), raw, waits=waits, signals=[e_ws], node_id=node_id,
+                                  signal_peer=-2 if signal_peer_event >= 0 else -1, signal_peer_event=signal_peer_event)
+                else:
+                    self.add_task(int(TaskType.LINEAR), raw, waits=waits, signals=[e_ws], node_id=node_id)
                 n_parts += 1
+        if fused_finish:
+            return RowEvents(rows=M, block=BM, row_events=[(e_ws, n_parts)], all_event=(e_ws, n_parts))
         # second half: one task per few rows, spread over the workers
-        out_cols = Nn // 2 if mode == 1 else Nn
-        ld_o = ld_out if ld_out is not None else (out.stride(0) if out is not None else out_cols)
-        if aux is not None and aux.stride(0) != ld_o:
-            raise ValueError("gemm_splitk: aux must have the output's row stride")
         if rows_per_task <= 0:
             rows_per_task = max(1, M // self.num_workers)
         # one task per (row group, column chunk): about one per worker (a task costs several us of fixed
@@ -500,8 +533,6 @@ class ProgramBuilder:
         nc = out_cols // chunks
         done = self.new_event()
         n_fin = 0
-        dt = N.DTYPE_CODE[out_dtype]
-        es = 2
         for r0 in range(0, M, rows_per_task):
             rr = min(rows_per_task, M - r0)
             for ch in range(chunks):

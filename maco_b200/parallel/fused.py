@@ -102,6 +102,9 @@ def allgather_push(b: ProgramBuilder, shard: torch.Tensor, gathered: torch.Tenso
         return RowEvents(rows=world * rows, block=BM, row_events=row_events, all_event=(all_ev, 0), sys=True)
     dests = [(rank - k) % world for k in range(1, world)]
     if not in_place:
+        # The local copy goes first and through the communication workers' bulk copies. (On the compute workers,
+        # whose operand rings are busy, it would run as plain vector loads and stores: measured 500 us slower
+        # for the 2-GPU TP MLP.)
         dests = [rank] + dests
     for dst in dests:
         for c0 in range(0, rows, chunk_rows):

@@ -206,9 +206,11 @@ def test_sm_scheduling_demo_barrier():
 
 @pytest.mark.parametrize("mode", ["static", "dynamic"])
 @pytest.mark.parametrize("epilogue", [None, "swiglu", "residual"])
-def test_splitk_decode_gemm(mode, epilogue):
-    """Few-row GEMM as split-K tiles with fp32 vector reductions plus finishing tasks, run three times:
-    the finishing tasks must leave the workspace zeroed for the next launch."""
+@pytest.mark.parametrize("fused", [True, False])
+def test_splitk_decode_gemm(mode, epilogue, fused):
+    """Few-row GEMM as split-K tiles with fp32 vector reductions, finished by the tile that arrives last for its
+    columns (fused) or by separate finishing tasks, run three times: the finishing pass must leave the workspace
+    zeroed (and the arrival counters consistent) for the next launch."""
     from maco_b200.ops import interleave_gate_up, megakernel as mk
     dt = torch.bfloat16
     M, K, Nn = 48, 1536, 1024
@@ -227,7 +229,7 @@ def test_splitk_decode_gemm(mode, epilogue):
         ref = xf @ w.float().t() + (aux.float() if aux is not None else 0)
         out = torch.empty(M, Nn, device="cuda", dtype=dt)
     b = mk.ProgramBuilder(torch.device("cuda"), mode=mode)
-    b.gemm_splitk(x, wk, out, split_k=5, epilogue=epilogue, aux=aux)
+    b.gemm_splitk(x, wk, out, split_k=5, epilogue=epilogue, aux=aux, fused_finish=fused)
     prog = b.build()
     for _ in range(3):
         out.zero_()
