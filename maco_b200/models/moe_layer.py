@@ -15,7 +15,8 @@ Per rank, inside the persistent kernel:
 6. the source sums the k rows of every token.
 
 Receive slabs have a fixed capacity per (source rank, expert); routed pairs that do not fit are
-dropped for that expert (zero contribution) and counted in ``dropped()``.
+dropped for that expert (zero contribution) and counted: the count of every step reaches the host without a
+blocking read, and the next ``forward()`` warns or raises (``on_drop``) when it is not zero; ``dropped()`` returns it.
 
 The reference simulates expert parallelism with equal splits on one GPU and a dummy all_to_all node
 (examples/benchmark_all_to_all.py:31-127): no router, no top-k, no permute, no variable splits.
@@ -48,7 +49,7 @@ class MoEEPLayer:
     def __init__(self, hidden: int = 2048, experts: int = 128, top_k: int = 8, inter: int = 768, tokens: int = 4096, *,
                  rank: int = 0, world: int = 1, heap=None, device: Optional[torch.device] = None,
                  dtype: torch.dtype = torch.bfloat16, capacity_factor: float = 2.0, seed: int = 0, mode: str = "static",
-                 trace: bool = False, weight_std: float = 0.02, router_std: float = 0.02):
+                 trace: bool = False, weight_std: float = 0.02, router_std: float = 0.02, on_drop: str = "warn"):
         if experts % world or tokens % BM or inter % 128 or hidden % 256:
             raise ValueError("experts % world, tokens % 128, inter % 128 and hidden % 256 must be 0")
         if top_k > 8 or experts > 256 or hidden * 2 * 4 > 20480:
@@ -93,6 +94,14 @@ class MoEEPLayer:
                              heap.offset_of(self.cnt), heap.offset_of(self.comb), self.y.data_ptr(), H, experts, K, EL, C, T,
                              N.DTYPE_CODE[dtype], 0)
         self.d_params = torch.from_numpy(np.frombuffer(params, dtype=np.uint8).copy()).to(dev)
+        # Dropped-pair count of the last step, delivered without a blocking read: every forward() copies the counter
+        # into pinned host memory behind the launch, and the NEXT forward() (or dropped()) looks at it. A step that
+        # dropped pairs therefore never goes unnoticed, and nothing waits for the GPU on the way.
+        self._drop_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._drop_event = torch.cuda.Event()
+        self._drop_pending = False
+        self.total_dropped = 0
+        self.on_drop = on_drop
         self._build(mode, trace)
 
     def expert_weights(self, e: int):
@@ -169,16 +178,45 @@ class MoEEPLayer:
         self.program = b.build()
 
     def forward(self, x: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """One step. ``on_drop`` ("warn", "raise", "ignore") says what happens when an EARLIER step turns out to have
+        dropped routed pairs (a slab's capacity was exceeded, ``capacity_factor`` too small for the routing skew)."""
+        self._poll_drops(wait=False)
         if x is not None:
             self.x.copy_(x, non_blocking=True)
         self.program.run(stream=stream)
+        st = stream if stream is not None else torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(st):
+            self._drop_host.copy_(self.counts[self.experts:self.experts + 1], non_blocking=True)
+            self._drop_event.record(st)
+        self._drop_pending = True
         return self.out
 
     __call__ = forward
 
+    def _poll_drops(self, wait: bool) -> int:
+        if not self._drop_pending:
+            return int(self._drop_host[0])
+        if wait:
+            self._drop_event.synchronize()
+        elif not self._drop_event.query():
+            return -1
+        self._drop_pending = False
+        n = int(self._drop_host[0])
+        if n > 0:
+            self.total_dropped += n
+            msg = (f"MoE layer dropped {n} routed (token, expert) pairs in its last step: a receive slab holds "
+                   f"{self.capacity} rows per (source rank, expert); raise capacity_factor")
+            if self.on_drop == "raise":
+                raise RuntimeError(msg)
+            if self.on_drop == "warn":
+                import warnings
+                warnings.warn(msg, RuntimeWarning, stacklevel=3)
+        return n
+
     def dropped(self) -> int:
-        """(token, expert) pairs of the last step that exceeded a slab's capacity."""
-        return int(self.counts[self.experts].item())
+        """(token, expert) pairs of the last step that exceeded a slab's capacity. Waits only for that step's
+        copy of the counter (an event), not for the device."""
+        return self._poll_drops(wait=True)
 
     # ------------------------------------------------------------------ oracle
     def reference(self, x: torch.Tensor) -> torch.Tensor:

@@ -92,3 +92,30 @@ def test_moe_layer_single_gpu(mode):
         err = (out.float() - ref).abs().max().item()
         assert err < 4e-2 * max(1.0, ref.abs().max().item()), err
     assert _native.status() == 0
+
+
+def test_moe_layer_reports_dropped_pairs_without_a_blocking_read():
+    """Slabs too small for the routing skew: the step's dropped-pair count reaches the host behind the launch, the
+    next forward() warns (or raises with on_drop="raise"), and dropped() agrees with a recount from the logits."""
+    from maco_b200 import _native
+    from maco_b200.models.moe_layer import MoEEPLayer
+    layer = MoEEPLayer(hidden=256, experts=8, top_k=2, inter=128, tokens=1024, capacity_factor=0.5, seed=11,
+                       weight_std=0.05, router_std=2.0)
+    assert layer.capacity == 128                                   # mean load is 256 rows per expert
+    x = torch.randn(1024, 256, device="cuda", dtype=torch.bfloat16)
+    layer(x)
+    n = layer.dropped()                                            # waits for the counter's copy only
+    logits = layer.logits.float()                                  # the router GEMM's own output
+    idx = torch.sort(logits, dim=-1, descending=True, stable=True)[1][:, :2]
+    load = torch.bincount(idx.flatten(), minlength=8)
+    assert n == int((load - layer.capacity).clamp(min=0).sum())
+    assert n > 0 and layer.total_dropped == n
+    layer(x)
+    torch.cuda.synchronize()
+    with pytest.warns(RuntimeWarning, match="dropped"):
+        layer(x)                                                   # learns about the previous step's drops
+    torch.cuda.synchronize()
+    layer.on_drop = "raise"
+    with pytest.raises(RuntimeError, match="capacity_factor"):
+        layer(x)
+    assert _native.status() == 0
