@@ -196,6 +196,9 @@ struct AttnPipe {
   const CUtensorMap* tmaps;
   uint64_t* mma_bars;     // [4]: scores ready (two buffers), P.V issued from P buffer 0 / 1 finished
   uint32_t tmem_base;
+  uint64_t* p_ready;      // [3]: P buffer 0 / 1 staged by the softmax warps; [2]: Q tile staged (once per task)
+  volatile uint32_t* pv_flags;   // [2]: 1 = the P.V product of this buffer adds to the accumulator, 0 = it starts a new sum
+  uint32_t task_idx;      // pipelined attention tasks this worker has run before this one (parity of p_ready[2])
 };
 
 constexpr int kAttnStages = 6;
@@ -210,32 +213,42 @@ MACO_DEVICE bool attn_pipelined(const MacoEltArgs& a) { return a.ld_in == kAttnD
 MACO_DEVICE uint32_t attn_stage_uses(const MacoEltArgs& a) { return 2u * (uint32_t)((a.rows + 127) / 128); }
 
 // Producer side: called by one thread. `ait` counts the stage uses of the attention ring on this worker.
-MACO_DEVICE bool attn_produce(const MacoEltArgs& ar, const AttnPipe& pp, uint32_t& ait) {
+// Called by all 32 lanes of the producer warp, converged. Lane 0 waits for the two stages of a chunk (K, then V)
+// to be free and arms their barriers; lanes 0-5 then issue the chunk's six boxes with one warp instruction: lanes
+// 0, 1 the two 64-dim halves of the 128 keys of K, lanes 2-5 the (64-key block, 64-dim half) boxes of V. One thread
+// alone issues only a few TMA operations per microsecond, which capped this stream at about 4 TB/s over the GPU.
+// `ait` advances identically in every lane.
+MACO_DEVICE bool attn_produce(const MacoEltArgs& ar, const AttnPipe& pp, uint32_t& ait, uint32_t lane) {
   const MacoEltArgs a = ar;
   const CUtensorMap* tmK = pp.tmaps + ((a.ld_out & 0xffff) - 1);
   const CUtensorMap* tmV = pp.tmaps + (((uint32_t)a.ld_out >> 16) - 1);
+  const bool is_k = lane < 2;
+  const uint32_t vb = lane - 2;                                       // V box: bit 0 dim half, bit 1 key block
+  const CUtensorMap* tm = is_k ? tmK : tmV;
+  const int x = is_k ? (int)lane * 64 : (int)(vb & 1u) * 64;
+  const int y_off = is_k ? 0 : (int)(vb >> 1) * 64;
+  const uint32_t s_off = is_k ? lane * 16384u : (vb >> 1) * 16384u + (vb & 1u) * 8192u;
   for (int base = 0; base < a.rows; base += 128) {
     const int y = a.row0 + base;
-    {
-      const uint32_t s = ait % kAttnStages, ph = (ait / kAttnStages) & 1;
-      if (!mbar_wait(&pp.empty[s], ph ^ 1, pp.budget_ns, pp.abort_word)) return false;
-      uint8_t* st = pp.ring + (size_t)s * kAttnStageBytes;
-      mbar_arrive_expect_tx(&pp.full[s], kAttnStageBytes);
-      tma_load_2d(st, tmK, &pp.full[s], 0, y);               // dims 0..63 of 128 keys
-      tma_load_2d(st + 16384, tmK, &pp.full[s], 64, y);      // dims 64..127
-      ++ait;
+    const uint32_t sk = ait % kAttnStages, phk = (ait / kAttnStages) & 1;
+    const uint32_t sv = (ait + 1) % kAttnStages, phv = ((ait + 1) / kAttnStages) & 1;
+    uint32_t good = 1;
+    if (lane == 0) {
+      good = (mbar_wait(&pp.empty[sk], phk ^ 1, pp.budget_ns, pp.abort_word) &&
+              mbar_wait(&pp.empty[sv], phv ^ 1, pp.budget_ns, pp.abort_word)) ? 1u : 0u;
+      if (good) {
+        mbar_arrive_expect_tx(&pp.full[sk], kAttnStageBytes);
+        mbar_arrive_expect_tx(&pp.full[sv], kAttnStageBytes);
+      }
     }
-    {
-      const uint32_t s = ait % kAttnStages, ph = (ait / kAttnStages) & 1;
-      if (!mbar_wait(&pp.empty[s], ph ^ 1, pp.budget_ns, pp.abort_word)) return false;
-      uint8_t* st = pp.ring + (size_t)s * kAttnStageBytes;
-      mbar_arrive_expect_tx(&pp.full[s], kAttnStageBytes);
-#pragma unroll
-      for (int kb = 0; kb < 2; ++kb)                         // 64 keys per k-block, two 64-dim panels each
-#pragma unroll
-        for (int j = 0; j < 2; ++j) tma_load_2d(st + kb * 16384 + j * 8192, tmV, &pp.full[s], j * 64, y + kb * 64);
-      ++ait;
+    good = __shfl_sync(0xffffffffu, good, 0);
+    if (!good) return false;
+    if (lane < 6) {
+      const uint32_t s = is_k ? sk : sv;
+      tma_load_2d(pp.ring + (size_t)s * kAttnStageBytes + s_off, tm, &pp.full[s], x, y + y_off);
     }
+    __syncwarp();
+    ait += 2;
   }
   return true;
 }
@@ -309,35 +322,13 @@ __device__ __noinline__ bool attn_consume_t(const MacoEltArgs& ar, int tid, uint
 #pragma unroll
   for (int g = 0; g < kAttnMaxG; ++g) { m_ref[g] = -INFINITY; l_thr[g] = 0.f; o[g] = 0.f; }
   attn_bar();
+  if (tid == 0) mbar_arrive(&pp.p_ready[2]);             // Q and the zeroed P buffers are in place: the MMA warp may start
   bool ok = true;
   bool acc_live = false;                                 // TMEM holds P.V sums not yet drained (same in every thread)
-  const uint32_t fmt = DTT == MACO_DT_BF16 ? 1u : 0u;
-  const uint32_t idesc_s = make_idesc(fmt, 128, 16, 0, 0);
-  const uint32_t idesc_o = make_idesc(fmt, 128, 16, 1, 0);
-  const uint32_t q_addr = smem_u32(q_t), p_addr = smem_u32(p_t);
   const uint32_t t_lane = (uint32_t)(quarter * 32) << 16;
   const uint32_t t_o = pp.tmem_base + 32;
   const int chunks = (a.rows + 127) / 128;
 
-  // thread 0: scores of chunk `c` (ring use ait + 2c) into S buffer (seq & 1)
-  auto issue_scores = [&](int c, uint32_t seq) {
-    const uint32_t u = ait + 2u * (uint32_t)c, sk = u % kAttnStages, phk = (u / kAttnStages) & 1;
-    if (ok && mbar_wait(&pp.full[sk], phk, pp.budget_ns, pp.abort_word)) {
-      tc_fence_after();
-      const uint32_t k_addr = smem_u32(pp.ring + (size_t)sk * kAttnStageBytes);
-      const uint32_t t_s = pp.tmem_base + (seq & 1) * 16;
-#pragma unroll
-      for (int k = 0; k < kAttnD / 16; ++k) {
-        const uint64_t adesc = make_smem_desc(k_addr + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024, 2);
-        const uint64_t bdesc = make_smem_desc(q_addr + (k >> 2) * 2048 + (k & 3) * 32, 16, 1024, 2);
-        tc_mma_f16(t_s, adesc, bdesc, idesc_s, k != 0 ? 1u : 0u);
-      }
-      tc_commit(&pp.empty[sk]);
-      tc_commit(&pp.mma_bars[seq & 1]);
-    } else {
-      ok = false;
-    }
-  };
   // every thread: waits for the P.V of chunk `seq` (and all before it), then o += accumulator
   auto drain_output = [&](uint32_t seq) {
     if (!mbar_wait(&pp.mma_bars[2 + (seq & 1)], (seq >> 1) & 1, pp.budget_ns, pp.abort_word)) ok = false;
@@ -370,12 +361,10 @@ __device__ __noinline__ bool attn_consume_t(const MacoEltArgs& ar, int tid, uint
     fence_proxy_async_smem();
   };
 
-  if (tid == 0) issue_scores(0, chunk_seq);
   for (int c = 0; c < chunks; ++c, ++chunk_seq) {
     const int nk = min(128, a.rows - c * 128);
     const bool valid = row < nk;
     const uint32_t seq = chunk_seq, buf = seq & 1, par = (seq >> 1) & 1;
-    if (tid == 0 && c + 1 < chunks) issue_scores(c + 1, seq + 1);
     if (!mbar_wait(&pp.mma_bars[buf], par, pp.budget_ns, pp.abort_word)) ok = false;
     tc_fence_after();
     float s[kAttnMaxG], pr[kAttnMaxG];
@@ -416,23 +405,11 @@ __device__ __noinline__ bool attn_consume_t(const MacoEltArgs& ar, int tid, uint
     }
 #pragma unroll
     for (int g = 0; g < kAttnMaxG; ++g) l_thr[g] += pr[g];
+    // P of this chunk is staged (the barrier above ordered every thread's stores and proxy fence): hand it to
+    // the MMA warp, which issues the P.V product as soon as the chunk's V rows have landed
     if (tid == 0) {
-      const uint32_t u = ait + 2u * (uint32_t)c + 1u, sv = u % kAttnStages, phv = (u / kAttnStages) & 1;
-      if (ok && mbar_wait(&pp.full[sv], phv, pp.budget_ns, pp.abort_word)) {
-        tc_fence_after();
-        const uint32_t v_addr = smem_u32(pp.ring + (size_t)sv * kAttnStageBytes);
-        const uint32_t pb = p_addr + buf * kAttnTileBytes;
-#pragma unroll
-        for (int k = 0; k < 128 / 16; ++k) {
-          const uint64_t adesc = make_smem_desc(v_addr + (k >> 2) * 16384 + (k & 3) * 2048, 8192, 1024, 2);
-          const uint64_t bdesc = make_smem_desc(pb + (k >> 2) * 2048 + (k & 3) * 32, 16, 1024, 2);
-          tc_mma_f16(t_o, adesc, bdesc, idesc_o, (k != 0 || acc_live) ? 1u : 0u);
-        }
-        tc_commit(&pp.empty[sv]);
-        tc_commit(&pp.mma_bars[2 + buf]);
-      } else {
-        ok = false;
-      }
+      pp.pv_flags[buf] = acc_live ? 1u : 0u;
+      mbar_arrive(&pp.p_ready[buf]);
     }
     acc_live = true;
   }
@@ -508,6 +485,62 @@ __device__ __noinline__ bool attn_consume_t(const MacoEltArgs& ar, int tid, uint
   }
   attn_bar();                                     // red_m is free again
   return ok;
+}
+
+// MMA side of the task: one thread (the worker's MMA warp, idle during an attention task otherwise) issues every
+// tensor-core product, so the softmax warps never issue one. Per chunk c: scores S(c+1) = K(c+1) Q^T as soon as the
+// chunk's K rows have landed (into the score buffer the softmax warps left two chunks ago), then, when the softmax
+// warps have staged P(c), O (+)= V(c)^T P(c). With the issue inside the softmax loop, one thread's instruction stream
+// (two waits, 16 descriptor pairs, 16 MMAs, 4 commits per chunk) sat on the critical path of all 128 threads and
+// held a worker at about 23 GB/s of K/V.
+// `ait`, `chunk_seq`: this worker's ring uses and chunks before this task (same counts as the consumer's).
+MACO_DEVICE bool attn_mma(const MacoEltArgs& ar, uint8_t* scratch, const AttnPipe& pp, uint32_t ait, uint32_t chunk_seq) {
+  const MacoEltArgs a = ar;
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(scratch) + 1023) & ~uintptr_t(1023));
+  const uint32_t q_addr = smem_u32(tiles), p_addr = smem_u32(tiles + kAttnTileBytes);
+  const uint32_t fmt = a.dtype == MACO_DT_BF16 ? 1u : 0u;
+  const uint32_t idesc_s = make_idesc(fmt, 128, 16, 0, 0);
+  const uint32_t idesc_o = make_idesc(fmt, 128, 16, 1, 0);
+  const uint32_t t_o = pp.tmem_base + 32;
+  const int chunks = (a.rows + 127) / 128;
+  if (!mbar_wait(&pp.p_ready[2], pp.task_idx & 1u, pp.budget_ns, pp.abort_word)) return false;
+  auto issue_scores = [&](int c, uint32_t seq) -> bool {
+    const uint32_t u = ait + 2u * (uint32_t)c, sk = u % kAttnStages, phk = (u / kAttnStages) & 1;
+    if (!mbar_wait(&pp.full[sk], phk, pp.budget_ns, pp.abort_word)) return false;
+    tc_fence_after();
+    const uint32_t k_addr = smem_u32(pp.ring + (size_t)sk * kAttnStageBytes);
+    const uint32_t t_s = pp.tmem_base + (seq & 1) * 16;
+#pragma unroll
+    for (int k = 0; k < kAttnD / 16; ++k) {
+      const uint64_t adesc = make_smem_desc(k_addr + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024, 2);
+      const uint64_t bdesc = make_smem_desc(q_addr + (k >> 2) * 2048 + (k & 3) * 32, 16, 1024, 2);
+      tc_mma_f16(t_s, adesc, bdesc, idesc_s, k != 0 ? 1u : 0u);
+    }
+    tc_commit(&pp.empty[sk]);
+    tc_commit(&pp.mma_bars[seq & 1]);
+    return true;
+  };
+  if (!issue_scores(0, chunk_seq)) return false;
+  for (int c = 0; c < chunks; ++c) {
+    const uint32_t seq = chunk_seq + (uint32_t)c, buf = seq & 1, par = (seq >> 1) & 1;
+    if (c + 1 < chunks && !issue_scores(c + 1, seq + 1)) return false;
+    if (!mbar_wait(&pp.p_ready[buf], par, pp.budget_ns, pp.abort_word)) return false;
+    const uint32_t accum = pp.pv_flags[buf];
+    const uint32_t u = ait + 2u * (uint32_t)c + 1u, sv = u % kAttnStages, phv = (u / kAttnStages) & 1;
+    if (!mbar_wait(&pp.full[sv], phv, pp.budget_ns, pp.abort_word)) return false;
+    tc_fence_after();
+    const uint32_t v_addr = smem_u32(pp.ring + (size_t)sv * kAttnStageBytes);
+    const uint32_t pb = p_addr + buf * kAttnTileBytes;
+#pragma unroll
+    for (int k = 0; k < 128 / 16; ++k) {
+      const uint64_t adesc = make_smem_desc(v_addr + (k >> 2) * 16384 + (k & 3) * 2048, 8192, 1024, 2);
+      const uint64_t bdesc = make_smem_desc(pb + (k >> 2) * 2048 + (k & 3) * 32, 16, 1024, 2);
+      tc_mma_f16(t_o, adesc, bdesc, idesc_o, (k != 0 || accum != 0) ? 1u : 0u);
+    }
+    tc_commit(&pp.empty[sv]);
+    tc_commit(&pp.mma_bars[2 + buf]);
+  }
+  return true;
 }
 
 MACO_DEVICE bool attn_consume(const MacoEltArgs& a, int tid, uint8_t* scratch, const AttnPipe& pp, uint32_t it, uint32_t& chunk_seq) {

@@ -213,7 +213,7 @@ int maco_gemm(const void* A, const void* B, void* D, int M, int N, int K, long l
   if (r != 0) return r == -2 ? -2 : -1;
   GemmEpilogue e;
   e.out = D; e.bias = bias; e.aux = aux; e.ld_out = ldd; e.ld_aux = ld_aux; e.mode = mode; e.out_type = out_type;
-  e.bias_type = bias_type; e.aux_type = aux_type; e.M = M; e.N = N; e.alpha = alpha; e._pad = 0;
+  e.bias_type = bias_type; e.aux_type = aux_type; e.M = M; e.N = N; e.alpha = alpha; e.aux_pack = 0;
   const uint64_t budget_ns = (uint64_t)((wait_budget_ms > 0 ? wait_budget_ms : 2000.0) * 1e6);
   if (pair) {
     const uint32_t idesc2 = make_idesc(ab_type == MACO_DT_BF16 ? 1u : 0u, 2 * kBM, bn, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
@@ -246,7 +246,7 @@ int maco_gemm_tf32(const void* A, const void* B, void* D, int M, int N, int K, l
   if (r != 0) return r == -2 ? -2 : -1;
   GemmEpilogue e;
   e.out = D; e.bias = bias; e.aux = aux; e.ld_out = ldd; e.ld_aux = ld_aux; e.mode = mode; e.out_type = out_type;
-  e.bias_type = bias_type; e.aux_type = aux_type; e.M = M; e.N = N; e.alpha = alpha; e._pad = 0;
+  e.bias_type = bias_type; e.aux_type = aux_type; e.M = M; e.N = N; e.alpha = alpha; e.aux_pack = 0;
   const uint64_t budget_ns = (uint64_t)((wait_budget_ms > 0 ? wait_budget_ms : 2000.0) * 1e6);
   return launch_gemm_tf32(tmA, tmB, e, K, make_idesc(2u, kBM, 256, 0u, 0u), max_ctas, budget_ns, stream);
 }
@@ -259,7 +259,7 @@ int maco_gemm_simt(const void* A, const void* B, void* D, int M, int N, int K, l
   if (M <= 0 || N <= 0) return 0;
   GemmEpilogue e;
   e.out = D; e.bias = bias; e.aux = aux; e.ld_out = ldd; e.ld_aux = ld_aux; e.mode = mode; e.out_type = out_type;
-  e.bias_type = bias_type; e.aux_type = aux_type; e.M = M; e.N = N; e.alpha = alpha; e._pad = 0;
+  e.bias_type = bias_type; e.aux_type = aux_type; e.M = M; e.N = N; e.alpha = alpha; e.aux_pack = 0;
   dim3 grid((N + 63) / 64, (M + 63) / 64);
   if (ab_type == MACO_DT_F32)
     gemm_simt_kernel<float><<<grid, 256, 0, stream>>>((const float*)A, (const float*)B, sam, sak, sbn, sbk, e, K);

@@ -87,7 +87,12 @@ MACO_DEVICE void gemm_tile_coords(int tile, int m_tiles, int n_tiles, int& m_blk
 template <int BN, int STAGES, bool A_MN, bool B_MN, int SBN = BN>
 MACO_DEVICE bool gemm_produce_tile(uint8_t* smem, const GemmCtrl& c, const CUtensorMap* tmA,
                                    const CUtensorMap* tmB, int m0, int n0, int k0, int k_blocks,
-                                   uint32_t& it, uint64_t budget_ns, long long* prof = nullptr, int k_step = kBK) {
+                                   uint32_t& it, uint64_t budget_ns, long long* prof = nullptr, int k_step = kBK,
+                                   int b_blocked_row0 = -1) {
+  // b_blocked_row0 >= 0: B is stored tile by tile ([N / BN][K / 64][BN][64], see ops.block_weight) and its tensor map
+  // is the 2-D view [rows, 64]; k-block kb of this tile is the contiguous BN x 64 block at row b_blocked_row0 + kb * BN.
+  // (A K-major [N, K] weight read once from HBM comes in as BN separate 128-byte pieces per box, one per DRAM
+  // page; the blocked form streams at the rate of a plain copy.)
   // k_step: elements per 128-byte k-block (64 for 16-bit operands, 32 for fp32 operands run as TF32)
   using L = GemmSmemLayout<BN, STAGES, SBN>;
   // stage index and phase advance incrementally: the loop is one thread's instruction stream, and a division
@@ -108,7 +113,8 @@ MACO_DEVICE bool gemm_produce_tile(uint8_t* smem, const GemmCtrl& c, const CUten
       for (int j = 0; j < kBM / 64; ++j) tma_load_2d(sa + j * 8192, tmA, &c.full[s], m0 + j * 64, k);
     }
     if constexpr (!B_MN) {
-      tma_load_2d(sb, tmB, &c.full[s], k, n0);
+      if (b_blocked_row0 >= 0) tma_load_2d(sb, tmB, &c.full[s], 0, b_blocked_row0 + kb * BN);
+      else tma_load_2d(sb, tmB, &c.full[s], k, n0);
     } else {
 #pragma unroll
       for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, tmB, &c.full[s], n0 + j * 64, k);
@@ -302,6 +308,13 @@ MACO_DEVICE void epi_stage_chunk(uint8_t* srow, int half, int out_type, const fl
   }
 }
 
+MACO_DEVICE void epi_stage_chunk_f32(uint8_t* srow, const float (&v)[32]) {
+  uint4* dst = reinterpret_cast<uint4*>(srow);
+#pragma unroll
+  for (int j = 0; j < 32; j += 4)
+    dst[j >> 2] = make_uint4(__float_as_uint(v[j]), __float_as_uint(v[j + 1]), __float_as_uint(v[j + 2]), __float_as_uint(v[j + 3]));
+}
+
 // Extra destinations of a tile: the same values are also stored at bases[k] + off for k < n
 // (used to broadcast a partial result into every rank's staging slot).
 struct EpiBroadcast {
@@ -332,14 +345,16 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
   const int out_cols = e.mode == MACO_EPI_SWIGLU ? e.N / 2 : e.N;
   const int tile_col0 = e.mode == MACO_EPI_SWIGLU ? n0 / 2 : n0;
   const int tile_cols = e.mode == MACO_EPI_SWIGLU ? BN / 2 : BN;
-  const bool staged = stage != nullptr && e.out_type != MACO_DT_F32 && tile_col0 + tile_cols <= out_cols &&
+  // (fp32 tiles that are plain stores take the same path: 32 columns are one 128-byte row chunk)
+  const bool f32_out = e.out_type == MACO_DT_F32;
+  const bool staged = stage != nullptr && (!f32_out || e.mode == MACO_EPI_F32_STORE) && tile_col0 + tile_cols <= out_cols &&
                       e.mode != MACO_EPI_F32_ACC;
   uint8_t* srow = stage != nullptr ? stage + q * kEpiStageWarpBytes + lane * kEpiStageRowBytes : nullptr;
   auto flush_group = [&](int gcol) {
     fence_proxy_async_smem();
     __syncwarp();
     if (row_ok) {
-      const long long eoff = ((long long)(row + row_off) * e.ld_out + gcol) * 2;
+      const long long eoff = ((long long)(row + row_off) * e.ld_out + gcol) * (f32_out ? 4 : 2);
       if (bc == nullptr) {
         bulk_store(reinterpret_cast<uint8_t*>(out_base) + eoff, srow, 128);
       } else {
@@ -402,17 +417,35 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = silu(v[j]);
       } else if (e.mode == MACO_EPI_RESIDUAL) {
-        float ax[32];
-        epi_load_aux32(e, row, col0, valid, ax);
+        const int n_aux = e.aux_pack & 15;
+        if (n_aux <= 1) {
+          float ax[32];
+          epi_load_aux32(e, row, col0, valid, ax);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] += ax[j];
+          for (int j = 0; j < 32; ++j) v[j] += ax[j];
+        } else {
+          // several blocks (a reduce-scatter's staging slots): the tile sums them all into its accumulator
+          const int skip = (e.aux_pack >> 4) & 15;
+          const long long slot_rows = e.aux_pack >> 8;
+          for (int sl = 0; sl < n_aux; ++sl) {
+            if (sl == skip) continue;
+            float ax[32];
+            epi_load_aux32(e, row + sl * slot_rows, col0, valid, ax);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += ax[j];
+          }
+        }
       }
       if (staged) {
-        if (row_ok) epi_stage_chunk(srow, ch & 1, e.out_type, v);
+        if (row_ok) {
+          if (f32_out) epi_stage_chunk_f32(srow, v);
+          else epi_stage_chunk(srow, ch & 1, e.out_type, v);
+        }
       } else if (bc == nullptr) epi_store_row32(e, out_base, row + row_off, col0, valid, v);
       else for (int k = 0; k < bc->n; ++k) epi_store_row32(e, bc->bases[k] + bc->off, row + row_off, col0, valid, v);
       }
-      if (staged && (ch & 1)) flush_group(col0 - 32);
+      if (staged && f32_out) flush_group(col0);
+      else if (staged && (ch & 1)) flush_group(col0 - 32);
       __syncwarp();
     }
   }

@@ -253,7 +253,7 @@ __device__ void producer_role_pair(const MacoProgram& p, uint32_t w, uint32_t q_
     fence_proxy_async_all();           // operands were written by generic-proxy stores of other CTAs
     const CUtensorMap* ta = tmaps + g.tmap_a;
     const CUtensorMap* tb = tmaps + g.tmap_b;
-    const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | (g.b_mn ? 1 : 0);
+    const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | ((g.b_mn & 1) ? 1 : 0);
     switch (sel) {
       case 0: ok = pair_produce_tile<256, kPairStages, false, false>(smem, c, rank, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
       case 1: ok = pair_produce_tile<256, kPairStages, false, true>(smem, c, rank, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
@@ -287,7 +287,7 @@ __device__ void mma_role_pair(const MacoProgram& p, uint32_t w, uint32_t q_base,
     const MacoTaskDesc& d = p.tasks[task];
     if (!is_gemm(d.type)) continue;
     const MacoGemmArgs& g = d.u.gemm;
-    const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | (g.b_mn ? 1 : 0);
+    const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | ((g.b_mn & 1) ? 1 : 0);
     switch (sel) {
       case 0: ok = pair_mma_tile<256, kPairStages, false, false>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
       case 1: ok = pair_mma_tile<256, kPairStages, false, true>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
@@ -302,64 +302,105 @@ __device__ void mma_role_pair(const MacoProgram& p, uint32_t w, uint32_t q_base,
   }
 }
 
-// ---- producer warp (lane 0) ---------------------------------------------------------------------
+// ---- producer warp ------------------------------------------------------------------------------
+// All 32 lanes walk the task sequence together. Lane 0 owns every decision and every side effect (queue reads,
+// dependency waits, GEMM loads); its verdicts are broadcast with shuffles. The other lanes exist for one thing:
+// the K / V stream of a decode-attention task is six TMA boxes per 64 KB chunk, and one thread issues a few TMA
+// operations per microsecond only; lanes 0-5 issue the six boxes with ONE warp instruction.
+
+// One GEMM task on lane 0: 1 = carry on, 0 = stop (failure already reported where it has a reporter).
+__device__ int producer_gemm_task(const MacoProgram& p, const MacoTaskDesc& d, uint32_t task, uint8_t* smem, const GemmCtrl& c,
+                                  const CUtensorMap* tmaps, const AttnPipe& apipe, uint32_t ait, uint32_t& it, int& owner) {
+  if (p.debug != 0 && !desc_ok(p, d)) { report_failure(p, MACO_STATUS_BAD_TASK, task, d.type, c.abort_word); return 0; }
+  if (!wait_deps(p, d, task, c.abort_word, nullptr)) return 0;
+  const MacoGemmArgs& g = d.u.gemm;
+  // run-time guarded tile: every role reads the same (final) count after the task's conditions hold
+  if ((d.flags & MACO_TF_COUNTED) && ld_relaxed_gpu_u32(g.count_ptr) <= g.count_base) return 1;
+  fence_proxy_async_all();           // operands were written by generic-proxy stores of other CTAs
+  if (owner == 2 && !attn_ring_drained(apipe, ait)) return 0;
+  owner = 1;
+  const CUtensorMap* ta = tmaps + g.tmap_a;
+  const CUtensorMap* tb = tmaps + g.tmap_b;
+  const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | ((g.b_mn & 1) ? 1 : 0);
+  bool ok;
+  // b_mn bit 1: blocked B (256-column tiles only); count_base then holds the weight's total number of k-blocks
+  const int b_row0 = (g.b_mn & 2) ? (int)(((uint32_t)g.n0 / 256u * g.count_base + (uint32_t)g.k0 / (uint32_t)kBK) * 256u) : -1;
+  switch (sel) {
+    case 0: ok = gemm_produce_tile<256, kMkStages, false, false, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns, nullptr, kBK, b_row0); break;
+    case 1: ok = gemm_produce_tile<256, kMkStages, false, true, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+    case 2: ok = gemm_produce_tile<256, kMkStages, true, false, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+    case 3: ok = gemm_produce_tile<256, kMkStages, true, true, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+    case 4: ok = gemm_produce_tile<128, kMkStages, false, false, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+    case 5: ok = gemm_produce_tile<128, kMkStages, false, true, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+    case 6: ok = gemm_produce_tile<128, kMkStages, true, false, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+    default: ok = gemm_produce_tile<128, kMkStages, true, true, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
+  }
+  if (!ok) report_failure(p, MACO_STATUS_TIMEOUT, task, 0xffffffffu, c.abort_word);
+  return ok ? 1 : 0;
+}
+
 __device__ void producer_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint8_t* smem, const GemmCtrl& c,
                               uint64_t* attn_ring_bars) {
-  uint32_t it = 0, ait = 0;          // stage uses of the GEMM ring / of the attention ring (same memory)
-  int owner = 0;                     // which pipeline used the operand memory last: 1 GEMM, 2 attention
-  bool ok = true;
+  const uint32_t lane = threadIdx.x & 31;
+  uint32_t it = 0;                   // stage uses of the GEMM ring (lane 0)
+  uint32_t ait = 0;                  // stage uses of the attention ring (same memory); every lane keeps the same count
+  int owner = 0;                     // lane 0: which pipeline used the operand memory last: 1 GEMM, 2 attention
+  bool ok = true;                    // uniform over the warp
   const CUtensorMap* tmaps = reinterpret_cast<const CUtensorMap*>(p.tmaps);
-  const AttnPipe apipe{smem, attn_ring_bars, attn_ring_bars + kAttnStages, p.budget_ns, c.abort_word, tmaps, nullptr, 0};
+  const AttnPipe apipe{smem, attn_ring_bars, attn_ring_bars + kAttnStages, p.budget_ns, c.abort_word, tmaps, nullptr, 0,
+                       nullptr, nullptr, 0};
   for (uint32_t i = 0; ok; ++i) {
-    uint32_t task;
-    if (!fetch_task(p, w, i, q_base, task, c.abort_word)) { ok = false; break; }
-    if (task == MACO_QUEUE_TERMINATE) break;
+    uint32_t task = 0, verdict = 0;  // 0 run, 1 end of queue, 2 failure
+    if (lane == 0) {
+      if (!fetch_task(p, w, i, q_base, task, c.abort_word)) verdict = 2;
+      else if (task == MACO_QUEUE_TERMINATE) verdict = 1;
+    }
+    verdict = __shfl_sync(0xffffffffu, verdict, 0);
+    task = __shfl_sync(0xffffffffu, task, 0);
+    if (verdict == 2) { ok = false; break; }
+    if (verdict == 1) break;
     task &= MACO_QUEUE_INDEX_MASK;
     const MacoTaskDesc& d = p.tasks[task];   // read in place (L1/L2 resident): a register copy would cost 32 registers
     if (d.type == MACO_TASK_ATTENTION && attn_pipelined(d.u.elt)) {
       // K / V rows of the split stream through the operand ring; the general warps consume them
-      if (!wait_deps(p, d, task, c.abort_word, nullptr)) { ok = false; break; }
-      fence_proxy_async_all();
-      if (owner == 1) {            // the MMA warp may still be reading the last GEMM stages out of this memory
-        for (uint32_t u = it > (uint32_t)kMkStages ? it - kMkStages : 0; u < it && ok; ++u)
-          ok = mbar_wait(&c.empty[u % kMkStages], (u / kMkStages) & 1, p.budget_ns, c.abort_word);
+      uint32_t go = 1;               // 1 produce, 0 stop silently (the wait reported), 2 stop and report
+      if (lane == 0) {
+        if (!wait_deps(p, d, task, c.abort_word, nullptr)) {
+          go = 0;
+        } else {
+          fence_proxy_async_all();
+          if (owner == 1) {          // the MMA warp may still be reading the last GEMM stages out of this memory
+            bool free_ok = true;
+            for (uint32_t u = it > (uint32_t)kMkStages ? it - kMkStages : 0; u < it && free_ok; ++u)
+              free_ok = mbar_wait(&c.empty[u % kMkStages], (u / kMkStages) & 1, p.budget_ns, c.abort_word);
+            if (!free_ok) go = 2;
+          }
+          owner = 2;
+        }
       }
-      owner = 2;
-      ok = ok && attn_produce(d.u.elt, apipe, ait);
-      if (!ok) report_failure(p, MACO_STATUS_TIMEOUT, task, 0xffffffffu, c.abort_word);
+      go = __shfl_sync(0xffffffffu, go, 0);
+      if (go == 1 && !attn_produce(d.u.elt, apipe, ait, lane)) go = 2;
+      if (go != 1) {
+        if (go == 2 && lane == 0) report_failure(p, MACO_STATUS_TIMEOUT, task, 0xffffffffu, c.abort_word);
+        ok = false;
+      }
       continue;
     }
     if (!is_gemm(d.type)) continue;
-    if (p.debug != 0 && !desc_ok(p, d)) { report_failure(p, MACO_STATUS_BAD_TASK, task, d.type, c.abort_word); ok = false; break; }
-    if (!wait_deps(p, d, task, c.abort_word, nullptr)) { ok = false; break; }
-    const MacoGemmArgs& g = d.u.gemm;
-    // run-time guarded tile: every role reads the same (final) count after the task's conditions hold
-    if ((d.flags & MACO_TF_COUNTED) && ld_relaxed_gpu_u32(g.count_ptr) <= g.count_base) continue;
-    fence_proxy_async_all();           // operands were written by generic-proxy stores of other CTAs
-    if (owner == 2 && !attn_ring_drained(apipe, ait)) { ok = false; break; }
-    owner = 1;
-    const CUtensorMap* ta = tmaps + g.tmap_a;
-    const CUtensorMap* tb = tmaps + g.tmap_b;
-    const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | (g.b_mn ? 1 : 0);
-    switch (sel) {
-      case 0: ok = gemm_produce_tile<256, kMkStages, false, false, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
-      case 1: ok = gemm_produce_tile<256, kMkStages, false, true, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
-      case 2: ok = gemm_produce_tile<256, kMkStages, true, false, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
-      case 3: ok = gemm_produce_tile<256, kMkStages, true, true, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
-      case 4: ok = gemm_produce_tile<128, kMkStages, false, false, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
-      case 5: ok = gemm_produce_tile<128, kMkStages, false, true, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
-      case 6: ok = gemm_produce_tile<128, kMkStages, true, false, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
-      default: ok = gemm_produce_tile<128, kMkStages, true, true, kMkBN>(smem, c, ta, tb, g.m0, g.n0, g.k0, g.k_blocks, it, p.budget_ns); break;
-    }
-    if (!ok) report_failure(p, MACO_STATUS_TIMEOUT, task, 0xffffffffu, c.abort_word);
+    uint32_t carry_on = 1;
+    if (lane == 0) carry_on = (uint32_t)producer_gemm_task(p, d, task, smem, c, tmaps, apipe, ait, it, owner);
+    carry_on = __shfl_sync(0xffffffffu, carry_on, 0);
+    if (carry_on == 0) ok = false;
   }
-  if (!ok) { gemm_drain_loads<kMkStages>(c, it); attn_drain_loads(apipe, ait); }
+  if (!ok && lane == 0) { gemm_drain_loads<kMkStages>(c, it); attn_drain_loads(apipe, ait); }
 }
 
 // ---- MMA warp (lane 0) --------------------------------------------------------------------------
 __device__ void mma_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint8_t* smem, const GemmCtrl& c,
-                         uint32_t tmem_base, volatile uint32_t* attn_done) {
+                         uint32_t tmem_base, volatile uint32_t* attn_done, uint64_t* attn_bars, uint64_t* p_ready,
+                         volatile uint32_t* pv_flags, uint8_t* scratch_smem) {
   uint32_t it = 0, seq = 0, attn_seen = 0;
+  uint32_t ait = 0, attn_chunks = 0;   // attention ring uses / chunks so far: the same counts the general warps keep
   bool ok = true;
   for (uint32_t i = 0; ok; ++i) {
     uint32_t task;
@@ -371,6 +412,18 @@ __device__ void mma_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint
       // The attention task issues its own tensor-core products into the low TMEM columns: this warp must
       // not start the next GEMM tile's accumulator there before the general warps have finished the task
       // (CTA-local counter).
+      {
+        // this warp issues the task's tensor-core products (scores and P.V), the general warps do the softmax
+        const AttnPipe pipe{smem, attn_bars + 4, attn_bars + 4 + kAttnStages, p.budget_ns, c.abort_word, nullptr, attn_bars,
+                            tmem_base, p_ready, pv_flags, attn_seen};
+        if (!attn_mma(d.u.elt, scratch_smem, pipe, ait, attn_chunks)) {
+          report_failure(p, MACO_STATUS_TIMEOUT, task, 0xfffffffeu, c.abort_word);
+          ok = false;
+          break;
+        }
+        ait += attn_stage_uses(d.u.elt);
+        attn_chunks += (uint32_t)((d.u.elt.rows + 127) / 128);
+      }
       ++attn_seen;
       const uint64_t t0 = globaltimer_ns();
       while ((int32_t)(*attn_done - attn_seen) < 0) {
@@ -385,7 +438,7 @@ __device__ void mma_role(const MacoProgram& p, uint32_t w, uint32_t q_base, uint
       if (!wait_deps(p, d, task, c.abort_word, nullptr)) break;
       if (ld_relaxed_gpu_u32(g.count_ptr) <= g.count_base) continue;
     }
-    const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | (g.b_mn ? 1 : 0);
+    const int sel = (g.bn == 128 ? 4 : 0) | (g.a_mn ? 2 : 0) | ((g.b_mn & 1) ? 1 : 0);
     switch (sel) {
       case 0: ok = gemm_mma_tile<256, kMkStages, false, false, kMkBN>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
       case 1: ok = gemm_mma_tile<256, kMkStages, false, true, kMkBN>(smem, c, tmem_base, g.idesc, g.k_blocks, it, seq, p.budget_ns); break;
@@ -424,7 +477,7 @@ __device__ __noinline__ void run_moe(const MacoProgram& p, uint32_t type, const 
 template <int CG>
 __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, const GemmCtrl& c, uint32_t tmem_base,
                              volatile uint32_t* slots, uint8_t* scratch_smem, uint8_t* ring_smem, uint64_t* bulk_bars,
-                             uint64_t* attn_bars) {
+                             uint64_t* attn_bars, uint64_t* attn_p_ready) {
   const int tid = threadIdx.x - 64;          // 0..127
   // two-CTA programs: the epilogue warps of both CTAs report "accumulator drained" to the leader's barrier
   uint32_t pair_empty_bar = 0;
@@ -435,6 +488,7 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
   BulkCtx bulk{ring_smem, bulk_bars, kBulkBuffers, kBulkBufBytes, slots + 12};   // phase word: zeroed at kernel start
   uint32_t seq = 0, done = 0, it = 0;      // it: ring stages consumed so far (kept in step with the TMA and MMA warps)
   uint32_t attn_chunks = 0, ait = 0;       // attention chunks done (parity of its MMA barriers), uses of its ring
+  uint32_t attn_tasks = 0;                 // pipelined attention tasks done (parity of the "Q staged" barrier)
   for (uint32_t i = 0;; ++i) {
     volatile uint32_t* cur = slots + (i & 1u) * 4;     // [0] task, [1] dependencies satisfied, [2] failure
     if (leader) {
@@ -523,9 +577,10 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
         } else if (d.type == MACO_TASK_ATTENTION && attn_pipelined(d.u.elt)) {
           if constexpr (CG == 1) {
             const AttnPipe pipe{ring_smem, attn_bars + 4, attn_bars + 4 + kAttnStages, p.budget_ns, c.abort_word,
-                                nullptr, attn_bars, tmem_base};
+                                nullptr, attn_bars, tmem_base, attn_p_ready, slots + 20, attn_tasks};
             if (!attn_consume(d.u.elt, tid, scratch_smem, pipe, ait, attn_chunks)) cur[2] = 1;
             ait += attn_stage_uses(d.u.elt);
+            ++attn_tasks;
             general_bar();
             if (leader) slots[13] = slots[13] + 1;                 // lets the MMA warp move past this task
           } else {
@@ -669,30 +724,36 @@ __device__ __forceinline__ void persistent_body(const MacoProgram& p) {
     // All roles must start from the same ring position: one thread reads it before anyone can move it.
     uint64_t* bulk_bars = reinterpret_cast<uint64_t*>(extra + 32);          // bytes 128.. of the extra block
     uint64_t* attn_bars = reinterpret_cast<uint64_t*>(extra + 64);          // bytes 256..383: 4 MMA barriers, then full[6], empty[6] of the K/V ring
+    uint64_t* attn_p_ready = reinterpret_cast<uint64_t*>(extra + 96);       // bytes 384..407: P staged (two buffers), Q staged; words 20, 21: P.V accumulate flags
     if (threadIdx.x == 0) {
       extra[16] = p.mode == MACO_MODE_DYNAMIC ? ld_relaxed_gpu_u32(&p.tails[w]) : 0;
       extra[12] = 0;                                                     // parity bits of the bulk barriers
       extra[13] = 0;                                                     // pipelined attention tasks finished
       for (uint32_t b = 0; b < kBulkBuffers; ++b) mbar_init(&bulk_bars[b], 1);
       for (int b = 0; b < 4 + 2 * kAttnStages; ++b) mbar_init(&attn_bars[b], 1);   // attention: 4 MMA barriers, ring full / empty
+      for (int b = 0; b < 3; ++b) mbar_init(&attn_p_ready[b], 1);
+      extra[20] = 0; extra[21] = 0;
       fence_mbar_init();
     }
     __syncthreads();
     const uint32_t q_base = extra[16];
     if (warp == 0) {
-      if (lane == 0) {
-        if constexpr (CG == 2) producer_role_pair(p, w, q_base, smem, c);
-        else producer_role(p, w, q_base, smem, c, attn_bars + 4);
+      if constexpr (CG == 2) {
+        if (lane == 0) producer_role_pair(p, w, q_base, smem, c);
+      } else {
+        producer_role(p, w, q_base, smem, c, attn_bars + 4);          // all 32 lanes (see the role)
       }
       __syncwarp();
     } else if (warp == 1) {
       if (lane == 0) {
         if constexpr (CG == 2) { if (cluster_ctarank() == 0) mma_role_pair(p, w, q_base, smem, c, tmem_base); }
-        else mma_role(p, w, q_base, smem, c, tmem_base, extra + 13);
+        else mma_role(p, w, q_base, smem, c, tmem_base, extra + 13, attn_bars, attn_p_ready, extra + 20,
+                      reinterpret_cast<uint8_t*>(extra) + kMkExtraSmem);
       }
       __syncwarp();
     } else {
-      general_role<CG>(p, w, q_base, c, tmem_base, extra, reinterpret_cast<uint8_t*>(extra) + kMkExtraSmem, smem, bulk_bars, attn_bars);
+      general_role<CG>(p, w, q_base, c, tmem_base, extra, reinterpret_cast<uint8_t*>(extra) + kMkExtraSmem, smem, bulk_bars, attn_bars,
+                       attn_p_ready);
     }
   } else {
     if constexpr (CG == 1) { if (warp == 0) scheduler_role(p, extra); }

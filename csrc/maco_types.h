@@ -83,7 +83,10 @@ struct GemmEpilogue {
   int aux_type;
   int M, N;             /* logical extent of the accumulator grid (rows, columns before any fold) */
   float alpha;
-  int _pad;
+  /* MACO_EPI_RESIDUAL with several aux blocks of the same shape (the staging slots of a reduce-scatter): bits 0-3
+     number of blocks (0 or 1: the single `aux`), bits 4-7 index of a block to leave out (15: none), bits 8-31
+     rows between consecutive blocks (block s starts `s * rows` rows, of ld_aux elements, behind `aux`). */
+  int aux_pack;
 };
 
 /* ---- status words written by kernels, read by the host --------------------------------------- */
@@ -109,7 +112,7 @@ struct MacoStatusBlock {          /* lives in host-mapped pinned memory */
 struct MacoGemmArgs {             /* one output tile */
   uint16_t tmap_a, tmap_b;        /* indices into the tensor-map table */
   uint16_t epi;                   /* index into the epilogue table */
-  uint8_t a_mn, b_mn;             /* operand majors */
+  uint8_t a_mn, b_mn;             /* operand majors (bit 0: MN-major). b_mn bit 1: B is stored tile by tile ([N/256][K/64][256][64]); count_base = its total k-blocks */
   int32_t m0, n0, k0, k_blocks;
   uint32_t idesc;
   int32_t peer;                   /* -1: store to the epilogue's out; >= 0: into that rank's heap at out_off; -2: into every rank's heap at out_off */

@@ -22,7 +22,7 @@ from typing import Optional
 import torch
 
 from .. import _native as N
-from ..ops import interleave_gate_up
+from ..ops import block_weight, interleave_gate_up
 from ..ops.megakernel import BM, COMM_REDUCE_LOCAL, ProgramBuilder, RowEvents, _pack_comm, _pack_elt
 from ..parallel import fused
 from ..task_graph.nodes import TaskType
@@ -42,7 +42,7 @@ class Qwen3DecodeLayer:
                  batch: int = 64, kv_len: int = 4096, *, rank: int = 0, world: int = 1, heap=None,
                  device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16, theta: float = 1e6,
                  eps: float = 1e-6, seed: int = 0, mode: str = "static", trace: bool = False,
-                 splits: Optional[int] = None, weight_std: float = 0.02):
+                 splits: Optional[int] = None, weight_std: float = 0.02, blocked_weights: bool = True):
         if head_dim != 128:
             raise ValueError("head_dim must be 128")
         if q_heads % world or kv_heads % world or ffn % (world * 64):
@@ -69,6 +69,12 @@ class Qwen3DecodeLayer:
         self.w_o = mk(g, H, hq * D)
         self.w_gate, self.w_up, self.w_down = mk(g, self.f_local, H), mk(g, self.f_local, H), mk(g, H, self.f_local)
         self.w_gate_up = interleave_gate_up(self.w_gate, self.w_up, block=128)   # 256-column tiles: gate 128 | up 128
+        # The four projections stream their weights exactly once per step: tile-by-tile copies so that every TMA box
+        # is one contiguous 32 KB block (the plain [N, K] tensors stay for the fp32 oracle).
+        self.blocked = blocked_weights and all(t.shape[0] % 256 == 0 and t.shape[1] % 64 == 0
+                                               for t in (self.w_qkv, self.w_o, self.w_gate_up, self.w_down)) and batch <= BM
+        blk = (lambda t: block_weight(t)) if self.blocked else (lambda t: None)
+        self.wb_qkv, self.wb_o, self.wb_gate_up, self.wb_down = blk(self.w_qkv), blk(self.w_o), blk(self.w_gate_up), blk(self.w_down)
         self.S = kv_len + 1                                        # cache rows incl. the new token
         self.k_cache = mk(g, B, hkv, self.S, D, std=1.0)
         self.v_cache = mk(g, B, hkv, self.S, D, std=1.0)
@@ -94,7 +100,7 @@ class Qwen3DecodeLayer:
         e_h1 = b.elementwise(int(TaskType.RMSNORM), self.x, self.h1, in1=self.w_in, rows=B, cols=H, f0=self.eps,
                              extra_waits=fence)
         # the four projections are weight-streaming GEMMs with 64 rows: split-K tiles over every SM
-        e_qkv = b.gemm_splitk(self.h1, self.w_qkv, self.qkv, a_ready=e_h1)
+        e_qkv = b.gemm_splitk(self.h1, self.w_qkv, self.qkv, a_ready=e_h1, w_blocked=self.wb_qkv)
         qkv_done = (e_qkv.all_event[0], e_qkv.all_event[1], False, False)
         # QK-norm + RoPE: q into its own buffer, k straight into the cache row of the new token, v copied
         # beside it. All of it bumps one event, so the attention tasks carry a single wait condition; task
@@ -121,11 +127,13 @@ class Qwen3DecodeLayer:
         e_attn = RowEvents(rows=B, block=BM, row_events=[(merged, n_merged)], all_event=(merged, n_merged))
         slots1 = self.slots1 if self.world > 1 else None
         slots2 = self.slots2 if self.world > 1 else None
-        e_y1 = fused.gemm_allreduce(b, self.attn, self.w_o, slots1, self.y1, residual=self.x, a_ready=e_attn)
+        e_y1 = fused.gemm_allreduce(b, self.attn, self.w_o, slots1, self.y1, residual=self.x, a_ready=e_attn,
+                                    w_blocked=self.wb_o)
         e_h2 = b.elementwise(int(TaskType.RMSNORM), self.y1, self.h2, in1=self.w_post, rows=B, cols=H, f0=self.eps,
                              in_ready=[e_y1])
-        e_act = b.gemm_splitk(self.h2, self.w_gate_up, self.act, epilogue="swiglu", a_ready=e_h2)
-        e_out = fused.gemm_allreduce(b, self.act, self.w_down, slots2, self.out, residual=self.y1, a_ready=e_act)
+        e_act = b.gemm_splitk(self.h2, self.w_gate_up, self.act, epilogue="swiglu", a_ready=e_h2, w_blocked=self.wb_gate_up)
+        e_out = fused.gemm_allreduce(b, self.act, self.w_down, slots2, self.out, residual=self.y1, a_ready=e_act,
+                                     w_blocked=self.wb_down)
         if self.world > 1:
             fused.epoch_fence_signal(b, [(e_out.all_event[0], e_out.all_event[1], False, False)])
         self.program = b.build()

@@ -107,9 +107,9 @@ def _pack_comm(src_off, dst_off, src_stride, dst_stride, row_bytes, rows, dtype,
                        nslots, slot_stride, local_ptr or 0, scale, 0, aux_ptr or 0)
 
 
-def _pack_epilogue(out, bias, aux, ld_out, ld_aux, mode, out_type, bias_type, aux_type, M, Nn, alpha) -> bytes:
+def _pack_epilogue(out, bias, aux, ld_out, ld_aux, mode, out_type, bias_type, aux_type, M, Nn, alpha, aux_pack=0) -> bytes:
     return struct.pack("<QQQqqiiiiiifi", out or 0, bias or 0, aux or 0, ld_out, ld_aux, mode, out_type, bias_type,
-                       aux_type, M, Nn, alpha, 0)
+                       aux_type, M, Nn, alpha, aux_pack)
 
 
 def make_idesc(ab_format: int, m: int, n: int, a_mn: int, b_mn: int) -> int:
@@ -273,10 +273,19 @@ class ProgramBuilder:
 
     # ------------------------------------------------------------------ GEMM node
     def add_epilogue(self, out_ptr: int, ld_out: int, out_dtype: torch.dtype, M: int, Nn: int, *, mode: str = None,
-                     aux_ptr: int = 0, ld_aux: int = 0, aux_dtype: Optional[torch.dtype] = None, alpha: float = 1.0) -> int:
-        """Registers an extra epilogue record (raw pointers) and returns its index for ``per_tile``'s ``epi``."""
+                     aux_ptr: int = 0, ld_aux: int = 0, aux_dtype: Optional[torch.dtype] = None, alpha: float = 1.0,
+                     aux_slots: Optional[Tuple[int, int, int]] = None) -> int:
+        """Registers an extra epilogue record (raw pointers) and returns its index for ``per_tile``'s ``epi``.
+        ``aux_slots`` = (count, index to leave out or 15, rows between slots): mode "residual" adds every slot
+        ``aux_ptr + s * rows * ld_aux`` instead of the single ``aux`` block."""
+        pack = 0
+        if aux_slots is not None:
+            cnt, skip, rows = aux_slots
+            if not (2 <= cnt <= 15 and 0 <= skip <= 15 and 0 <= rows < (1 << 23)):
+                raise ValueError("aux_slots: 2..15 slots, skip index 0..15, fewer than 2^23 rows between slots")
+            pack = cnt | (skip << 4) | (rows << 8)
         self.epis.append(_pack_epilogue(out_ptr, 0, aux_ptr, ld_out, ld_aux, EPI[mode], N.DTYPE_CODE[out_dtype], 0,
-                                        N.DTYPE_CODE[aux_dtype] if aux_dtype is not None else 0, M, Nn, float(alpha)))
+                                        N.DTYPE_CODE[aux_dtype] if aux_dtype is not None else 0, M, Nn, float(alpha), pack))
         return len(self.epis) - 1
 
     def gemm(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor], *, trans_a: bool = False,
@@ -441,7 +450,8 @@ class ProgramBuilder:
                     epilogue: Optional[str] = None, aux: Optional[torch.Tensor] = None,
                     a_ready: Optional[RowEvents] = None, extra_waits: Sequence[Tuple[int, int, bool, bool]] = (),
                     heap_out_off: Optional[int] = None, ld_out: Optional[int] = None,
-                    signal_peer_event: int = -1, rows_per_task: int = 0, fused_finish: Optional[bool] = None) -> RowEvents:
+                    signal_peer_event: int = -1, rows_per_task: int = 0, fused_finish: Optional[bool] = None,
+                    w_blocked: Optional[torch.Tensor] = None) -> RowEvents:
         """``out = op(a @ w.T)`` for at most 128 rows, bound by streaming ``w`` out of HBM.
 
         The K dimension is cut into ``split_k`` slices (0: enough slices for every worker to hold a tile),
@@ -450,6 +460,8 @@ class ProgramBuilder:
         interleaved gate/up layout, "residual" with ``aux``) and writes the 16-bit result: into ``out``, or,
         with ``heap_out_off``, at that byte offset of EVERY rank's symmetric heap (the exchange step of a
         one-shot all-reduce), bumping ``signal_peer_event`` on every rank.
+        ``w_blocked``: the same weight laid out tile by tile (``ops.block_weight(w)``, [N/256, K/64, 256, 64]); the
+        tiles then load contiguous 32 KB blocks (``w`` itself is not read).
         ``fused_finish`` (default on; env ``MACO_SPLITK_FUSED=0`` turns it off): the tile that arrives last at
         its column tile's counter runs the finishing pass for those columns in its own epilogue warps, while the
         worker's TMA and MMA warps stream the next tile. Off: SPLITK_FIN tasks behind an event that counts all
@@ -473,7 +485,13 @@ class ProgramBuilder:
         ab = 1 if a.dtype == torch.bfloat16 else 0
         idesc = make_idesc(ab, BM, 256, 0, 0)
         ta = self._tmap(a, a.shape[0], a.shape[1], a.stride(0), False, BM)
-        tb = self._tmap(w, w.shape[0], w.shape[1], w.stride(0), False, 256)
+        if w_blocked is not None:
+            if tuple(w_blocked.shape) != (n_tiles, k_blocks, 256, BK) or not w_blocked.is_contiguous() or w_blocked.dtype != w.dtype:
+                raise ValueError("gemm_splitk: w_blocked must be ops.block_weight(w) ([N/256, K/64, 256, 64], contiguous)")
+            tb = self._tmap(w_blocked.view(-1, BK), n_tiles * k_blocks * 256, BK, BK, False, 256)
+            self.keepalive.append(w_blocked)
+        else:
+            tb = self._tmap(w, w.shape[0], w.shape[1], w.stride(0), False, 256)
         out_cols = Nn // 2 if mode == 1 else Nn
         ld_o = ld_out if ld_out is not None else (out.stride(0) if out is not None else out_cols)
         if aux is not None and aux.stride(0) != ld_o:
@@ -512,7 +530,9 @@ class ProgramBuilder:
             kb0 = sp * k_blocks // split_k
             kb1 = (sp + 1) * k_blocks // split_k
             for nb in range(n_tiles):
-                raw = _pack_gemm(ta, tb, epi, 0, 0, 0, nb * 256, kb0 * BK, kb1 - kb0, idesc, -1, 0, 0, 256)
+                # b_mn bit 1 + count_base: blocked B and its total number of k-blocks (csrc/maco_types.h)
+                raw = _pack_gemm(ta, tb, epi, 0, 2 if w_blocked is not None else 0, 0, nb * 256, kb0 * BK, kb1 - kb0, idesc,
+                                 -1, 0, 0, 256, count_base=k_blocks if w_blocked is not None else 0)
                 if fused_finish:
                     self.add_task(int(TaskType.LINEAR), raw, waits=waits, signals=[e_ws], node_id=node_id,
                                   signal_peer=-2 if signal_peer_event >= 0 else -1, signal_peer_event=signal_peer_event)

@@ -46,3 +46,15 @@ def test_split_k_fills_the_machine_without_extra_waves():
         assert waves * (-(-k_blocks // sp) + 8) <= -(-n_tiles // W) * (k_blocks + 8)
     assert pick_split_k(20, 80, W) * 20 <= W            # one wave when the tiles fit
     assert pick_split_k(400, 16, W) == 1 or pick_split_k(400, 16, W) <= 8
+
+
+def test_block_weight_round_trip_and_tile_contiguity():
+    import torch
+    from maco_b200.ops.gemm import block_weight, unblock_weight
+    w = torch.arange(512 * 192, dtype=torch.float32).view(512, 192).to(torch.bfloat16)
+    wb = block_weight(w)
+    assert wb.shape == (2, 3, 256, 64) and wb.is_contiguous()
+    assert torch.equal(wb[1, 2], w[256:512, 128:192])           # one tile's k-block is one contiguous 32 KB block
+    assert torch.equal(unblock_weight(wb), w)
+    with pytest.raises(ValueError):
+        block_weight(w[:100])

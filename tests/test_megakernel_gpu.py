@@ -206,8 +206,8 @@ def test_sm_scheduling_demo_barrier():
 
 @pytest.mark.parametrize("mode", ["static", "dynamic"])
 @pytest.mark.parametrize("epilogue", [None, "swiglu", "residual"])
-@pytest.mark.parametrize("fused", [True, False])
-def test_splitk_decode_gemm(mode, epilogue, fused):
+@pytest.mark.parametrize("fused,blocked", [(True, False), (False, False), (True, True)])
+def test_splitk_decode_gemm(mode, epilogue, fused, blocked):
     """Few-row GEMM as split-K tiles with fp32 vector reductions, finished by the tile that arrives last for its
     columns (fused) or by separate finishing tasks, run three times: the finishing pass must leave the workspace
     zeroed (and the arrival counters consistent) for the next launch."""
@@ -229,7 +229,9 @@ def test_splitk_decode_gemm(mode, epilogue, fused):
         ref = xf @ w.float().t() + (aux.float() if aux is not None else 0)
         out = torch.empty(M, Nn, device="cuda", dtype=dt)
     b = mk.ProgramBuilder(torch.device("cuda"), mode=mode)
-    b.gemm_splitk(x, wk, out, split_k=5, epilogue=epilogue, aux=aux, fused_finish=fused)
+    from maco_b200.ops import block_weight
+    b.gemm_splitk(x, wk, out, split_k=5, epilogue=epilogue, aux=aux, fused_finish=fused,
+                  w_blocked=block_weight(wk) if blocked else None)      # tile-by-tile copy of the weight: contiguous boxes
     prog = b.build()
     for _ in range(3):
         out.zero_()
