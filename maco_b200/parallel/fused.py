@@ -151,9 +151,12 @@ def rotated_blocks(rank: int, world: int, blocks_per_rank: int, own_last: bool =
 
 
 # Up to this many ranks the own tiles of a fused GEMM -> reduce-scatter sum the peers' slots in their epilogue; beyond
-# it (7 slots of 64 KB per tile at 8 ranks) the loads would outlast a tile's main loop, and reduction tasks spread
-# over every worker do the sums instead.
-EPILOGUE_REDUCE_MAX_WORLD = 4
+# it reduction tasks spread over every worker do the sums. Two ranks: one slot, always there in time. The several-slot
+# form (``aux_slots`` of the residual epilogue) works and is tested at four ranks, but measured slower there for the
+# 8192 x 4096 x 14336 layer (651 us against 618-628 us with reduction tasks): the own tiles wait for the slowest
+# peer's partial and their epilogues read three 64 KB slots with plain loads, which stretches the tiles of the
+# last phase by more than the 40 us tail of reduction tasks it removes.
+EPILOGUE_REDUCE_MAX_WORLD = 2
 
 
 def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, staging: torch.Tensor,
@@ -210,7 +213,7 @@ def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, sta
         # its own blocks last, so the last peer's partial for block j of this rank left one phase before this rank
         # reaches block j; the own tile's epilogue adds the world-1 peer slots to its accumulator (a few microseconds
         # of loads per tile, hidden under the next tile's main loop) and no reduction tasks follow the last tile.
-        # (Measured before, 4 GPUs: 256 reduction tasks queued behind the tiles ran as two rounds of 18 us.)
+        # (With reduction tasks, 4 GPUs: 256 tasks queued behind the tiles run as two rounds of 18 us.)
         own_first = rank * blocks_per_rank
         shift = rank * rows_local
         epi_own = b.add_epilogue(out.data_ptr() - shift * out.stride(0) * out.element_size(), out.stride(0), out.dtype, M, Nn,
