@@ -156,7 +156,7 @@ def rotated_blocks(rank: int, world: int, blocks_per_rank: int, own_last: bool =
 # 8192 x 4096 x 14336 layer (651 us against 618-628 us with reduction tasks): the own tiles wait for the slowest
 # peer's partial and their epilogues read three 64 KB slots with plain loads, which stretches the tiles of the
 # last phase by more than the 40 us tail of reduction tasks it removes.
-EPILOGUE_REDUCE_MAX_WORLD = 2
+EPILOGUE_REDUCE_MAX_WORLD = 2           # the environment variable MACO_EPILOGUE_REDUCE_MAX_WORLD (2..4) overrides it
 
 
 def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, staging: torch.Tensor,
@@ -208,7 +208,8 @@ def gemm_reduce_scatter(b: ProgramBuilder, a: torch.Tensor, w: torch.Tensor, sta
         own = gemm_ev.row_events[own_first: own_first + blocks_per_rank]
         return gemm_ev, RowEvents(rows=rows_local, block=BM, row_events=list(own), all_event=gemm_ev.all_event)
 
-    if world <= EPILOGUE_REDUCE_MAX_WORLD and scale == 1.0:
+    import os
+    if world <= int(os.environ.get("MACO_EPILOGUE_REDUCE_MAX_WORLD", EPILOGUE_REDUCE_MAX_WORLD)) and scale == 1.0:
         # Three or four ranks: the same idea with several slots. Rank r serves the owners r+1, r+2, ... in turn and
         # its own blocks last, so the last peer's partial for block j of this rank left one phase before this rank
         # reaches block j; the own tile's epilogue adds the world-1 peer slots to its accumulator (a few microseconds

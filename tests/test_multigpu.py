@@ -228,6 +228,15 @@ def test_fused_tp_mlp_matches_reference(world, heap_mode):
     run_ranks(_tp_mlp, world, env=_env(heap_mode), timeout=150)
 
 
+@pytest.mark.skipif(_NGPU < 4, reason="needs 4 GPUs")
+def test_fused_tp_mlp_with_the_reduction_in_the_own_tiles_epilogue_at_four_ranks():
+    """Four ranks, own tiles of the GEMM -> reduce-scatter add the three peer slots in their epilogue (the several-slot
+    residual epilogue; the default above two ranks is reduction tasks)."""
+    env = _env("nvls")
+    env["MACO_EPILOGUE_REDUCE_MAX_WORLD"] = "4"
+    run_ranks(_tp_mlp, 4, env=env, timeout=150)
+
+
 def _dp_backward(rank, world):
     maco, heap = _setup(rank, world, heap_mb=192)
     import torch.distributed as dist
