@@ -327,7 +327,7 @@ template <int BN, int SBN = BN>
 MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const GemmEpilogue& e_in,
                                     void* out_base, long long row_off, int m0, int n0,
                                     uint32_t tile_seq, uint64_t budget_ns, const EpiBroadcast* bc = nullptr,
-                                    uint8_t* stage = nullptr, uint32_t pair_empty_bar = 0) {
+                                    uint8_t* stage = nullptr, uint32_t pair_empty_bar = 0, int row_limit = 0x7fffffff) {
   // private copy: the record lives in global memory; read in place, its fields would be loaded again after
   // every store of the tile (the stores could alias it)
   const GemmEpilogue e = e_in;
@@ -340,7 +340,16 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
   if (!ok) return false;
   tc_fence_after();
   const int row = m0 + q * 32 + lane;
-  const bool row_ok = row < e.M;
+  const bool scatter = e.mode == MACO_EPI_SCATTER_ROWS;
+  const bool row_ok = row < e.M && (!scatter || row < row_limit);
+  // scatter: this thread's row has its own destination row and weight (one 16-byte record per row)
+  long long out_row = row + row_off;
+  float row_weight = 1.f;
+  if (scatter && row_ok) {
+    const int4 rec = reinterpret_cast<const int4*>(e.aux)[row];
+    out_row = (long long)rec.x * e.bias_type + rec.y;
+    row_weight = __int_as_float(rec.z);
+  }
   // staged path: 16-bit output, tile completely inside the output columns (uniform over the CTA)
   const int out_cols = e.mode == MACO_EPI_SWIGLU ? e.N / 2 : e.N;
   const int tile_col0 = e.mode == MACO_EPI_SWIGLU ? n0 / 2 : n0;
@@ -354,7 +363,7 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
     fence_proxy_async_smem();
     __syncwarp();
     if (row_ok) {
-      const long long eoff = ((long long)(row + row_off) * e.ld_out + gcol) * (f32_out ? 4 : 2);
+      const long long eoff = (out_row * e.ld_out + gcol) * (f32_out ? 4 : 2);
       if (bc == nullptr) {
         bulk_store(reinterpret_cast<uint8_t*>(out_base) + eoff, srow, 128);
       } else {
@@ -384,8 +393,8 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
         if (row_ok) epi_stage_chunk(srow, ch & 1, e.out_type, v);
         if (ch & 1) flush_group(col0 - 32);
       } else if (row_ok && valid > 0) {
-        if (bc == nullptr) epi_store_row32(e, out_base, row + row_off, col0, valid, v);
-        else for (int k = 0; k < bc->n; ++k) epi_store_row32(e, bc->bases[k] + bc->off, row + row_off, col0, valid, v);
+        if (bc == nullptr) epi_store_row32(e, out_base, out_row, col0, valid, v);
+        else for (int k = 0; k < bc->n; ++k) epi_store_row32(e, bc->bases[k] + bc->off, out_row, col0, valid, v);
       }
       __syncwarp();
     }
@@ -401,6 +410,15 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
       float v[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * e.alpha;
+      if (scatter) {
+        // the expert's output row is rounded to the output type first (what a separate return pass would read)
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const uint32_t pk = epi_pack(e.out_type, v[j], v[j + 1]);
+          const float2 f = e.out_type == MACO_DT_F16 ? __half22float2(*reinterpret_cast<const __half2*>(&pk)) : unpack_bf16x2(pk);
+          v[j] = f.x * row_weight; v[j + 1] = f.y * row_weight;
+        }
+      }
       if (e.bias != nullptr && e.mode != MACO_EPI_SPLITK_FUSED) {     // (that mode keeps its arrival counters there)
 #pragma unroll
         for (int j = 0; j < 32; ++j) if (j < valid) v[j] += epi_bias(e, col0 + j);
@@ -441,8 +459,8 @@ MACO_DEVICE bool gemm_epilogue_tile(const GemmCtrl& c, uint32_t tmem_base, const
           if (f32_out) epi_stage_chunk_f32(srow, v);
           else epi_stage_chunk(srow, ch & 1, e.out_type, v);
         }
-      } else if (bc == nullptr) epi_store_row32(e, out_base, row + row_off, col0, valid, v);
-      else for (int k = 0; k < bc->n; ++k) epi_store_row32(e, bc->bases[k] + bc->off, row + row_off, col0, valid, v);
+      } else if (bc == nullptr) epi_store_row32(e, out_base, out_row, col0, valid, v);
+      else for (int k = 0; k < bc->n; ++k) epi_store_row32(e, bc->bases[k] + bc->off, out_row, col0, valid, v);
       }
       if (staged && f32_out) flush_group(col0);
       else if (staged && (ch & 1)) flush_group(col0 - 32);

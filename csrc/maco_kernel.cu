@@ -536,8 +536,10 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
       const EpiBroadcast* bcp = g.peer == -2 ? &bc : nullptr;
       bool ok;
       uint8_t* stage = g.peer != -1 ? scratch_smem : nullptr;  // tiles that leave the GPU go through the bulk engine
-      if (g.bn == 128) ok = gemm_epilogue_tile<128, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns, bcp, stage, pair_empty_bar);
-      else ok = gemm_epilogue_tile<256, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns, bcp, stage, pair_empty_bar);
+      // run-time row count of a counted tile's operand block (rows at or beyond it hold no tokens)
+      const int row_limit = (d.flags & MACO_TF_COUNTED) ? (int)ld_relaxed_gpu_u32(g.count_ptr) : 0x7fffffff;
+      if (g.bn == 128) ok = gemm_epilogue_tile<128, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns, bcp, stage, pair_empty_bar, row_limit);
+      else ok = gemm_epilogue_tile<256, kMkBN>(c, tmem_base, e, out_base, g.row_off, g.m0, g.n0, seq, p.budget_ns, bcp, stage, pair_empty_bar, row_limit);
       if (!ok) cur[2] = 1;
       ++seq;
       it += (uint32_t)g.k_blocks;

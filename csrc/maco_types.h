@@ -68,7 +68,12 @@ enum MacoEpilogueMode {
      one per 256-column tile, never reset; `bias_type` = arrivals per column tile (the K slices); `aux` = a
      MacoEltArgs in device memory written as for a SPLITK_FIN task over ALL columns (the kernel offsets it to the
      tile's columns). */
-  MACO_EPI_SPLITK_FUSED = 9
+  MACO_EPI_SPLITK_FUSED = 9,
+  /* Row scatter with a per-row weight (the MoE combine all-to-all fused into the down projection): row r of the
+     tile's operand block has a 16-byte record {int32 token, int32 k, float weight, pad} at `aux`[r]; the 16-bit
+     output row goes to row token * bias_type + k of the destination (ld_out elements per row), scaled by the weight
+     after rounding the product to the output type. Rows at or beyond the task's run-time count are not written. */
+  MACO_EPI_SCATTER_ROWS = 10
 };
 
 struct GemmEpilogue {

@@ -10,8 +10,9 @@ Per rank, inside the persistent kernel:
 3. the per-expert counts are published to the expert owners
 4. grouped expert GEMMs over the slabs: gate/up with SwiGLU in the epilogue, then down; tiles whose
    128-row block holds no tokens are skipped by all roles of the worker (run-time counted tiles)
-5. MOE_RETURN tasks scale every valid output row by its routing weight and send it back into the
-   source rank's combine buffer at [token, k] (combine all-to-all)
+5. the down projection's epilogue scales every valid output row by its routing weight and sends it back into the
+   source rank's combine buffer at [token, k] (combine all-to-all fused into the GEMM; ``fused_return=False``: separate
+   MOE_RETURN tasks do it from a slab of outputs)
 6. the source sums the k rows of every token.
 
 Receive slabs have a fixed capacity per (source rank, expert); routed pairs that do not fit are
@@ -49,7 +50,13 @@ class MoEEPLayer:
     def __init__(self, hidden: int = 2048, experts: int = 128, top_k: int = 8, inter: int = 768, tokens: int = 4096, *,
                  rank: int = 0, world: int = 1, heap=None, device: Optional[torch.device] = None,
                  dtype: torch.dtype = torch.bfloat16, capacity_factor: float = 2.0, seed: int = 0, mode: str = "static",
-                 trace: bool = False, weight_std: float = 0.02, router_std: float = 0.02, on_drop: str = "warn"):
+                 trace: bool = False, weight_std: float = 0.02, router_std: float = 0.02, on_drop: str = "warn",
+                 fused_return: Optional[bool] = None):
+        import os
+        # The weighted return of the expert outputs (the combine all-to-all) happens in the epilogue of the down
+        # projection: every output row goes, scaled, straight into its source rank's combine buffer. Off: separate
+        # MOE_RETURN tasks read the slab of outputs back and send the rows (they queue behind all expert tiles).
+        self.fused_return = (os.environ.get("MACO_MOE_FUSED_RETURN", "1") != "0") if fused_return is None else bool(fused_return)
         if experts % world or tokens % BM or inter % 128 or hidden % 256:
             raise ValueError("experts % world, tokens % 128, inter % 128 and hidden % 256 must be 0")
         if top_k > 8 or experts > 256 or hidden * 2 * 4 > 20480:
@@ -160,12 +167,28 @@ class MoEEPLayer:
         # down-projection tiles was tried, to send rows back under the remaining GEMM work: with static queues
         # a return that waits even briefly holds up the epilogues of its worker, and the layer got 28 % slower.
         # (Also tried without gain: pulling the next tile's expert weights into L2 with TMA prefetches.)
-        for el, s in pairs:
-            ys[el, s] = b.gemm(self.act[el, s], self.w2[el], self.y[el, s], bn=256, a_ready=acts[el, s],
-                               per_tile=guards[el, s])
-        for el, s in pairs:
-            emit_return(el, s)
-        n_ret = W * EL * (C // BM)
+        if self.fused_return:
+            comb_off = self.heap.offset_of(self.comb)
+            meta_base = self.meta.data_ptr()
+            n_tiles_down = H // 256
+            for el, s in pairs:
+                cptr = cnt_base + (s * EL + el) * 4
+                epi = b.add_epilogue(0, H, self.dtype, C, H, mode="scatter_rows", aux_ptr=meta_base + ((el * W + s) * C) * 16,
+                                     bias_type=K)
+
+                def scatter(mb, nb, cptr=cptr, epi=epi, s=s):
+                    return dict(count_ptr=cptr, count_base=mb * BM, epi=epi, peer=s, out_off=comb_off, signal_peer=s,
+                                signal_peer_event=e_ret)
+
+                ys[el, s] = b.gemm(self.act[el, s], self.w2[el], self.y[el, s], bn=256, a_ready=acts[el, s], per_tile=scatter)
+            n_ret = W * EL * (C // BM) * n_tiles_down
+        else:
+            for el, s in pairs:
+                ys[el, s] = b.gemm(self.act[el, s], self.w2[el], self.y[el, s], bn=256, a_ready=acts[el, s],
+                                   per_tile=guards[el, s])
+            for el, s in pairs:
+                emit_return(el, s)
+            n_ret = W * EL * (C // BM)
         # 6. combine: sum the k rows of every token (token blocks streamed through the idle operand ring)
         e_out = b.new_event()
         n_out = 0

@@ -34,7 +34,7 @@ WORKER_QUEUE_SIZE = 1024
 T_SPLITK_FIN = 118
 
 EPI = {None: 0, "none": 0, "gelu": 1, "swiglu": 2, "f32": 3, "f32_acc": 4, "gelu_bwd": 5, "silu": 6, "residual": 7, "f32_atomic": 8,
-       "splitk_fused": 9}
+       "splitk_fused": 9, "scatter_rows": 10}
 
 TASK_DTYPE = np.dtype([
     ("type", "<u2"), ("flags", "<u2"), ("node_id", "<u4"), ("wait_event", "<i4", 2), ("wait_count", "<u4", 2),
@@ -274,17 +274,19 @@ class ProgramBuilder:
     # ------------------------------------------------------------------ GEMM node
     def add_epilogue(self, out_ptr: int, ld_out: int, out_dtype: torch.dtype, M: int, Nn: int, *, mode: str = None,
                      aux_ptr: int = 0, ld_aux: int = 0, aux_dtype: Optional[torch.dtype] = None, alpha: float = 1.0,
-                     aux_slots: Optional[Tuple[int, int, int]] = None) -> int:
+                     aux_slots: Optional[Tuple[int, int, int]] = None, bias_type: int = 0) -> int:
         """Registers an extra epilogue record (raw pointers) and returns its index for ``per_tile``'s ``epi``.
         ``aux_slots`` = (count, index to leave out or 15, rows between slots): mode "residual" adds every slot
-        ``aux_ptr + s * rows * ld_aux`` instead of the single ``aux`` block."""
+        ``aux_ptr + s * rows * ld_aux`` instead of the single ``aux`` block. Mode "scatter_rows": ``aux_ptr`` is the
+        table of 16-byte {token, k, weight} row records and ``bias_type`` the number of k slots per token
+        (MACO_EPI_SCATTER_ROWS in csrc/maco_types.h)."""
         pack = 0
         if aux_slots is not None:
             cnt, skip, rows = aux_slots
             if not (2 <= cnt <= 15 and 0 <= skip <= 15 and 0 <= rows < (1 << 23)):
                 raise ValueError("aux_slots: 2..15 slots, skip index 0..15, fewer than 2^23 rows between slots")
             pack = cnt | (skip << 4) | (rows << 8)
-        self.epis.append(_pack_epilogue(out_ptr, 0, aux_ptr, ld_out, ld_aux, EPI[mode], N.DTYPE_CODE[out_dtype], 0,
+        self.epis.append(_pack_epilogue(out_ptr, 0, aux_ptr, ld_out, ld_aux, EPI[mode], N.DTYPE_CODE[out_dtype], int(bias_type),
                                         N.DTYPE_CODE[aux_dtype] if aux_dtype is not None else 0, M, Nn, float(alpha), pack))
         return len(self.epis) - 1
 
@@ -462,7 +464,8 @@ class ProgramBuilder:
         one-shot all-reduce), bumping ``signal_peer_event`` on every rank.
         ``w_blocked``: the same weight laid out tile by tile (``ops.block_weight(w)``, [N/256, K/64, 256, 64]); the
         tiles then load contiguous 32 KB blocks (``w`` itself is not read).
-        ``fused_finish`` (default on; env ``MACO_SPLITK_FUSED=0`` turns it off): the tile that arrives last at
+        ``fused_finish`` (default: on for a local ``out``, off with ``heap_out_off``; env ``MACO_SPLITK_FUSED=0``
+        turns it off): the tile that arrives last at
         its column tile's counter runs the finishing pass for those columns in its own epilogue warps, while the
         worker's TMA and MMA warps stream the next tile. Off: SPLITK_FIN tasks behind an event that counts all
         tiles (one more dependency hop and a tail of short tasks).
@@ -500,7 +503,10 @@ class ProgramBuilder:
         es = 2
         if fused_finish is None:
             import os
-            fused_finish = os.environ.get("MACO_SPLITK_FUSED", "1") != "0"
+            # A result that goes into every rank's heap is finished by tasks spread over all workers: with the
+            # fused form only the last arrival of each 256-column tile (20 CTAs for 5120 columns) would push all
+            # rows to every peer (measured: the 4-GPU decode layer's o-proj ended 35 us later).
+            fused_finish = os.environ.get("MACO_SPLITK_FUSED", "1") != "0" and heap_out_off is None
         if fused_finish:
             # the tile that arrives last at its column tile's counter finishes those columns itself
             # (MACO_EPI_SPLITK_FUSED in csrc/maco_types.h): no finishing tasks, no hop between the two halves

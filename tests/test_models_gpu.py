@@ -42,13 +42,15 @@ def test_tp_mlp_two_input_slots():
         assert (y.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item()), it
 
 
-@pytest.mark.parametrize("mode", ["static", "dynamic"])
-def test_qwen3_decode_layer_single_gpu(mode):
+@pytest.mark.parametrize("mode,blocked", [("static", False), ("dynamic", False), ("static", True)])
+def test_qwen3_decode_layer_single_gpu(mode, blocked):
     from maco_b200 import _native
     from maco_b200.models.qwen3_layer import Qwen3DecodeLayer
     # 1400 cached keys in 2 splits: 6 chunks of 128 keys per task, so the K/V ring wraps several times
+    # (blocked: the four projections read tile-by-tile copies of their weights)
     layer = Qwen3DecodeLayer(hidden=1024, q_heads=16, kv_heads=2, ffn=2048, batch=8, kv_len=1400, seed=4, mode=mode, splits=2,
-                             weight_std=0.05)
+                             weight_std=0.05, blocked_weights=blocked)
+    assert layer.blocked == blocked
     x = torch.randn(8, 1024, device="cuda", dtype=torch.bfloat16)
     ref = layer.reference(x)
     for _ in range(2):

@@ -242,8 +242,9 @@ def _dp_backward(rank, world):
     import torch.distributed as dist
     from maco_b200 import _native
     from maco_b200.models.dp_mlp_stack import DPMLPStackBackward
-    m = DPMLPStackBackward(layers=3, hidden=512, tokens=1024, rank=rank, world=world, heap=heap, seed=5, weight_std=0.05,
-                           comm_workers=4)
+    # a 128-row block of every gradient is owned by one rank: hidden / 128 has to be a multiple of the world size
+    m = DPMLPStackBackward(layers=3, hidden=max(512, 128 * world), tokens=1024, rank=rank, world=world, heap=heap, seed=5,
+                           weight_std=0.05, comm_workers=4)
     ref = m.reference_grads()
     dist.all_reduce(ref)
     ref /= world
