@@ -102,7 +102,7 @@ def test_moe_layer_reports_dropped_pairs_without_a_blocking_read():
     from maco_b200 import _native
     from maco_b200.models.moe_layer import MoEEPLayer
     layer = MoEEPLayer(hidden=256, experts=8, top_k=2, inter=128, tokens=1024, capacity_factor=0.5, seed=11,
-                       weight_std=0.05, router_std=2.0)
+                       weight_std=0.05, router_std=2.0, on_drop="ignore")
     assert layer.capacity == 128                                   # mean load is 256 rows per expert
     x = torch.randn(1024, 256, device="cuda", dtype=torch.bfloat16)
     layer(x)
@@ -114,6 +114,7 @@ def test_moe_layer_reports_dropped_pairs_without_a_blocking_read():
     assert n > 0 and layer.total_dropped == n
     layer(x)
     torch.cuda.synchronize()
+    layer.on_drop = "warn"
     with pytest.warns(RuntimeWarning, match="dropped"):
         layer(x)                                                   # learns about the previous step's drops
     torch.cuda.synchronize()
