@@ -11,6 +11,7 @@ one launch.
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 import struct
 from dataclasses import dataclass, field
@@ -163,6 +164,124 @@ class RowEvents:
         return self.all_event
 
 
+def assign_static_queues(tasks: Sequence[dict], num_workers: int, num_comm_workers: int) -> List[List[int]]:
+    """Static per-worker queues of a program: the tasks in emission (= a topological) order, round-robin over the
+    worker class each task prefers. Pure host code (no device needed), so schedules can be checked on a CPU
+    (``simulate_static_queues``)."""
+    W, Wc = num_workers, num_comm_workers
+    n_compute = W - Wc
+    queues: List[List[int]] = [[] for _ in range(W)]
+    rr_c = rr_m = rr_a = rr_p = 0
+    n_pairs = max(1, n_compute // 2)
+    pair_of_leader = 0
+    attached: Dict[int, List[int]] = {}             # task -> join tasks that run right in front of it
+    for i, t in enumerate(tasks):
+        if t.get("attach_to") is not None:
+            # Still a topological order: a join's only consumer is the task it is attached to.
+            attached.setdefault(t["attach_to"], []).append(i)
+            continue
+        if t.get("pair_half") is not None:
+            # halves of a two-CTA tile: consecutive tasks, leader on worker 2j, the other half on 2j+1; both
+            # workers see their pair tiles in the same order (the MMA of one serves both)
+            if t["pair_half"] == 0:
+                pair_of_leader = (rr_p + rr_p // n_pairs) % n_pairs
+                rr_p += 1
+            q = 2 * pair_of_leader + t["pair_half"]
+        elif (t["flags"] & TF_ANY_WORKER) and Wc > 0:
+            q = (W - 1 - rr_a) % W                     # communication workers (highest indices) first
+            rr_a += 1
+        elif (t["flags"] & TF_COMM_WORKER) and Wc > 0:
+            q = n_compute + rr_m % Wc
+            rr_m += 1
+        elif t.get("worker") is not None:
+            q = t["worker"] % n_compute
+        else:
+            # rotate by one worker per wave: with a plain modulo a worker would see the same position of
+            # every periodic task pattern (the same row block of every expert slab, say) and the load
+            # would follow that pattern instead of averaging out
+            q = (rr_c + rr_c // n_compute) % n_compute
+            rr_c += 1
+        queues[q] += attached.pop(i, [])
+        queues[q].append(i)
+    if attached:
+        raise RuntimeError("join tasks attached to a task that was never emitted")
+    return queues
+
+
+def simulate_static_queues(programs: Sequence[Tuple[Sequence[dict], List[List[int]]]], max_rounds: int = 1 << 22) -> int:
+    """Runs the static schedules of one program per rank on the host, with the rules of the kernel: a worker runs the
+    head of its queue once both wait conditions hold (event counter >= count; "previous launch" conditions hold at
+    once in a first launch), the two halves of a two-CTA tile only run together, a finished task bumps its local
+    events and the events it signals on a peer (-2 / -4: on every rank). Returns the number of rounds; raises
+    RuntimeError with the stuck queue heads if no task can run (a deadlock of the schedule). Counted (run-time
+    skipped) tiles and time are not modelled: this checks the ORDER of the queues, on any machine."""
+    world = len(programs)
+    events = [collections.defaultdict(int) for _ in range(world)]
+    heads = [[0] * len(q) for _, q in programs]
+    left = sum(len(t) for t, _ in programs)
+
+    def ready(r: int, t: dict) -> bool:
+        for k in range(2):
+            ev, cnt = t["wait_event"][k], t["wait_count"][k]
+            prev = t["flags"] & (TF_WAIT0_PREV if k == 0 else TF_WAIT1_PREV)
+            if ev >= 0 and cnt > 0 and not prev and events[r][ev] < cnt:
+                return False
+        return True
+
+    def finish(r: int, t: dict) -> None:
+        for ev in t["signal_event"]:
+            if ev >= 0:
+                events[r][ev] += 1
+        sp, spe = t["signal_peer"], t["signal_peer_event"]
+        if spe >= 0 and sp != -1:
+            for d in (range(world) if sp in (-2, -4) else [sp]):
+                events[d][spe] += 1
+
+    rounds = 0
+    while left:
+        rounds += 1
+        if rounds > max_rounds:
+            raise RuntimeError("simulate_static_queues: round limit reached")
+        progressed = False
+        for r, (tasks, queues) in enumerate(programs):
+            for w, q in enumerate(queues):
+                h = heads[r][w]
+                if h >= len(q):
+                    continue
+                t = tasks[q[h]]
+                if not ready(r, t):
+                    continue
+                half = t.get("pair_half")
+                if half is None:
+                    finish(r, t)
+                    heads[r][w] += 1
+                    left -= 1
+                    progressed = True
+                elif half == 0:
+                    # leader half: its partner (worker w + 1) must be at the other half of the same tile, ready
+                    hp = heads[r][w + 1]
+                    qp = queues[w + 1]
+                    if hp < len(qp) and qp[hp] == q[h] + 1 and ready(r, tasks[qp[hp]]):
+                        finish(r, t)
+                        finish(r, tasks[qp[hp]])
+                        heads[r][w] += 1
+                        heads[r][w + 1] += 1
+                        left -= 2
+                        progressed = True
+                # half == 1 runs with its leader
+        if not progressed:
+            stuck = []
+            for r, (tasks, queues) in enumerate(programs):
+                for w, q in enumerate(queues):
+                    if heads[r][w] < len(q):
+                        t = tasks[q[heads[r][w]]]
+                        stuck.append((r, w, q[heads[r][w]], t["type"], t["wait_event"], t["wait_count"],
+                                      [events[r][e] for e in t["wait_event"] if e >= 0]))
+            raise RuntimeError(f"static schedule deadlocks; stuck queue heads (rank, worker, task, type, waits, counts, "
+                               f"values): {stuck[:8]}")
+    return rounds
+
+
 class ProgramBuilder:
     """Accumulates tasks, events, tensor maps and epilogues; ``build()`` uploads them."""
 
@@ -174,7 +293,8 @@ class ProgramBuilder:
         rows of A and its own half of B. Static queues only; split-K, counted (MoE) and tensor-core attention
         tasks stay in one-CTA programs (a kernel has one cta_group)."""
         self.device = torch.device(device)
-        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        # (a CPU device gives a planning-only builder: tasks and queues can be produced and checked, not built)
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 148
         self.mode = MODE_DYNAMIC if mode == "dynamic" else MODE_STATIC
         self.cta_pair = bool(cta_pair)
         if self.cta_pair and self.mode != MODE_STATIC:
@@ -183,7 +303,7 @@ class ProgramBuilder:
         self.num_workers = max(1, min(int(num_workers) if num_workers else limit, limit, 256))
         self.num_comm_workers = max(0, min(int(num_comm_workers), self.num_workers - 1))
         if self.cta_pair:
-            max_pairs = _lib().maco_persistent_max_pairs()
+            max_pairs = _lib().maco_persistent_max_pairs() if self.device.type == "cuda" else 0
             if max_pairs > 0:
                 self.num_workers = min(self.num_workers, 2 * max_pairs)
             self.num_workers -= self.num_workers & 1
@@ -818,44 +938,8 @@ class Program:
         else:
             self.d_events = torch.zeros(self.num_events + 64, dtype=torch.int32, device=dev)
         self.d_ctrl = torch.zeros(8, dtype=torch.int32, device=dev)        # [0] abort word, [1] task counter
-        # static queues: global order, round-robin over the worker class the task prefers
-        W, Wc = self.num_workers, self.num_comm_workers
-        n_compute = W - Wc
-        queues: List[List[int]] = [[] for _ in range(W)]
-        rr_c = rr_m = rr_a = rr_p = 0
-        n_pairs = n_compute // 2
-        pair_of_leader = 0
-        attached: Dict[int, List[int]] = {}             # task -> join tasks that run right in front of it
-        for i, t in enumerate(b.tasks):
-            if t.get("attach_to") is not None:
-                # Still a topological order: a join's only consumer is the task it is attached to.
-                attached.setdefault(t["attach_to"], []).append(i)
-                continue
-            if t.get("pair_half") is not None:
-                # halves of a two-CTA tile: consecutive tasks, leader on worker 2j, the other half on 2j+1; both
-                # workers see their pair tiles in the same order (the MMA of one serves both)
-                if t["pair_half"] == 0:
-                    pair_of_leader = (rr_p + rr_p // n_pairs) % n_pairs
-                    rr_p += 1
-                q = 2 * pair_of_leader + t["pair_half"]
-            elif (t["flags"] & TF_ANY_WORKER) and Wc > 0:
-                q = (W - 1 - rr_a) % W                     # communication workers (highest indices) first
-                rr_a += 1
-            elif (t["flags"] & TF_COMM_WORKER) and Wc > 0:
-                q = n_compute + rr_m % Wc
-                rr_m += 1
-            elif t.get("worker") is not None:
-                q = t["worker"] % n_compute
-            else:
-                # rotate by one worker per wave: with a plain modulo a worker would see the same position of
-                # every periodic task pattern (the same row block of every expert slab, say) and the load
-                # would follow that pattern instead of averaging out
-                q = (rr_c + rr_c // n_compute) % n_compute
-                rr_c += 1
-            queues[q] += attached.pop(i, [])
-            queues[q].append(i)
-        if attached:
-            raise RuntimeError("join tasks attached to a task that was never emitted")
+        W = self.num_workers
+        queues = assign_static_queues(b.tasks, self.num_workers, self.num_comm_workers)
         stride = max(1, max(len(q) for q in queues))
         sq = np.full((W, stride), QUEUE_TERMINATE, dtype=np.uint32)
         for w, q in enumerate(queues):
@@ -887,7 +971,7 @@ class Program:
         ps.status = None
         ps.trace = self.d_trace.data_ptr() if self.d_trace is not None else None
         ps.budget_ns = int(b.wait_budget_ms * 1e6)
-        ps.num_tasks, ps.num_groups, ps.num_workers, ps.num_comm_workers = n, self.num_groups, W, Wc
+        ps.num_tasks, ps.num_groups, ps.num_workers, ps.num_comm_workers = n, self.num_groups, W, self.num_comm_workers
         ps.static_stride, ps.mode, ps.epoch = stride, self.mode, 0
         ps.rank, ps.world = 0, 1
         ps.cta_group = 2 if b.cta_pair else 1

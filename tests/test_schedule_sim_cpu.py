@@ -1,0 +1,149 @@
+"""Static schedules checked on the host: the program builder runs in planning mode (CPU tensors, no tensor maps),
+the queues come from the same assignment the kernel gets, and ``simulate_static_queues`` runs them under the
+kernel's rules (head of the queue only, both wait conditions, two-CTA halves together, peer signals). A schedule
+whose order can deadlock fails here, on any machine, instead of running into a device-side wait budget."""
+import pytest
+import torch
+
+from maco_b200.ops import megakernel as mk
+
+
+@pytest.fixture
+def planning(monkeypatch):
+    """Builder without tensor maps: planning needs the tasks and their order only."""
+    counter = {"n": 0}
+
+    def fake_tmap(self, *a, **k):
+        counter["n"] += 1
+        self.tmaps.append(b"\0" * 128)
+        return len(self.tmaps) - 1
+
+    monkeypatch.setattr(mk.ProgramBuilder, "_tmap", fake_tmap)
+    return counter
+
+
+def _bf(*shape):
+    return torch.empty(*shape, dtype=torch.bfloat16)
+
+
+@pytest.mark.parametrize("pair", [False, True])
+def test_chain_of_gemms_with_row_events_and_joins_runs_to_completion(planning, pair):
+    """Two dependent GEMMs whose second one carries an extra condition: every pair tile has three wait conditions, so
+    join tasks appear; they must sit on their consumer's worker, directly in front of it."""
+    b = mk.ProgramBuilder(torch.device("cpu"), num_workers=20, cta_pair=pair)
+    x, w1, h, w2, y = _bf(1024, 512), _bf(768, 512), _bf(1024, 768), _bf(512, 768), _bf(1024, 512)
+    gate = b.new_event()
+    b.add_task(int(mk.TaskType.NOP), b"", signals=[gate])
+    other = b.new_event()
+    b.add_task(int(mk.TaskType.NOP), b"", signals=[other])
+    e1 = b.gemm(x, w1, h, extra_waits=[(gate, 1, False, False)])
+    b.gemm(h, w2, y, a_ready=e1, extra_waits=[(gate, 1, False, False), (other, 1, False, False)])
+    queues = mk.assign_static_queues(b.tasks, b.num_workers, b.num_comm_workers)
+    joins = [i for i, t in enumerate(b.tasks) if t.get("attach_to") is not None]
+    assert joins, "the second GEMM's tiles have three conditions each: joins expected"
+    where = {t: (w, k) for w, q in enumerate(queues) for k, t in enumerate(q)}
+    for j in joins:
+        (wj, kj), (wt, kt) = where[j], where[b.tasks[j]["attach_to"]]
+        assert wj == wt and kj < kt and all(b.tasks[queues[wj][k]].get("attach_to") == b.tasks[j]["attach_to"] for k in range(kj, kt))
+    assert sorted(t for q in queues for t in q) == list(range(len(b.tasks)))
+    mk.simulate_static_queues([(b.tasks, queues)])
+
+
+def test_a_join_behind_the_leader_half_would_deadlock_and_the_simulator_sees_it(planning):
+    """The failure this check exists for: a condition of the second half of a two-CTA tile queued BEHIND the leader half."""
+    b = mk.ProgramBuilder(torch.device("cpu"), num_workers=4, cta_pair=True)
+    x, w1, y = _bf(256, 128), _bf(256, 128), _bf(256, 256)
+    b.gemm(x, w1, y)
+    queues = mk.assign_static_queues(b.tasks, b.num_workers, b.num_comm_workers)
+    mk.simulate_static_queues([(b.tasks, queues)])                      # the real order is fine
+    # hand-made bad order: a join the partner half waits for, placed behind the leader half on the leader's worker
+    tasks = [dict(t) for t in b.tasks]
+    ev = b.new_event()
+    join = dict(type=int(mk.TaskType.NOP), flags=0, node_id=0, wait_event=[-1, -1], wait_count=[0, 0], signal_event=[ev, -1],
+                signal_peer=-1, signal_peer_event=-1, raw=b"", worker=None, pair_half=None)
+    tasks.append(join)
+    partner = next(i for i, t in enumerate(tasks) if t.get("pair_half") == 1)
+    tasks[partner]["wait_event"], tasks[partner]["wait_count"] = [ev, -1], [1, 0]
+    bad = [list(q) for q in queues]
+    leader_q = next(w for w, q in enumerate(bad) if partner - 1 in q)
+    bad[leader_q].insert(bad[leader_q].index(partner - 1) + 1, len(tasks) - 1)
+    with pytest.raises(RuntimeError, match="deadlocks"):
+        mk.simulate_static_queues([(tasks, bad)])
+
+
+def test_join_is_a_balanced_tree(planning):
+    b = mk.ProgramBuilder(torch.device("cpu"), num_workers=8)
+    evs = [b.new_event() for _ in range(64)]
+    n0 = len(b.tasks)
+    out = b.join([(e, 1, False, False) for e in evs])
+    assert len(out) == 2 and len(b.tasks) - n0 == 62
+    # depth: follow the events back to the leaves
+    made = {t["signal_event"][0]: t for t in b.tasks[n0:]}
+
+    def depth(ev):
+        t = made.get(ev)
+        return 0 if t is None else 1 + max(depth(e) for e in t["wait_event"] if e >= 0)
+
+    assert max(depth(w[0]) for w in out) == 5                            # log2(64) - 1 levels under the two survivors
+
+
+class _FakeHeap:
+    """Enough of a symmetric heap for planning: one address space per rank, the same offsets on every rank."""
+
+    def __init__(self, rank, world, nbytes=1 << 28):
+        self.rank, self.world, self.nbytes = rank, world, nbytes
+        self._buf = torch.empty(nbytes, dtype=torch.uint8)
+        self._base = self._buf.data_ptr()
+        self._cursor = 0
+        self.mode = "ipc"
+
+    def alloc(self, shape, dtype, zero=False):
+        shape = tuple(shape) if isinstance(shape, (tuple, list, torch.Size)) else (shape,)
+        n = torch.empty((), dtype=dtype).element_size()
+        for s in shape:
+            n *= s
+        start = (self._cursor + 255) // 256 * 256
+        self._cursor = start + n
+        assert self._cursor <= self.nbytes
+        return self._buf[start:start + n].view(dtype).view(shape)
+
+    def owns(self, t):
+        return self._base <= t.data_ptr() and t.data_ptr() + t.numel() * t.element_size() <= self._base + self.nbytes
+
+    def offset_of(self, t):
+        assert self.owns(t)
+        return t.data_ptr() - self._base
+
+    def peer_base(self, r):
+        return self._base
+
+    def multicast_base(self):
+        return 0
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("pair", [False, True])
+def test_tensor_parallel_mlp_schedules_of_all_ranks_run_together(planning, world, pair):
+    """all-gather -> GEMM -> GEMM -> reduce-scatter, one program per rank, all ranks simulated together: every
+    cross-rank condition (arrival of gathered rows, of partial tiles, the closing waits) has to resolve."""
+    from maco_b200.parallel import fused
+    T, H, F = 128 * world * 2, 256, 512 * world
+    rows, f_local = T // world, F // world
+    programs = []
+    for rank in range(world):
+        heap = _FakeHeap(rank, world)
+        b = mk.ProgramBuilder(torch.device("cpu"), num_workers=24, num_comm_workers=4, heap=heap, cta_pair=pair)
+        x_full = heap.alloc((T, H), torch.bfloat16)
+        x_shard = x_full[rank * rows:(rank + 1) * rows]
+        staging = heap.alloc((world, rows, H), torch.bfloat16)
+        w1, h, w2, y = _bf(2 * f_local, H), _bf(T, f_local), _bf(H, f_local), _bf(rows, H)
+        fence = fused.epoch_fence_event(b)
+        ag = fused.allgather_push(b, x_shard, x_full, fence=fence)
+        order = fused.gathered_order(rank, world, rows // mk.BM, False)
+        e1 = b.gemm(x_full, w1, h, epilogue="swiglu", a_ready=ag, m_blocks=order)
+        _, e_out = fused.gemm_reduce_scatter(b, h, w2, staging, y, a_ready=e1)
+        fused.epoch_fence_signal(b, [(e_out.all_event[0], e_out.all_event[1], False, False)])
+        programs.append((b.tasks, mk.assign_static_queues(b.tasks, b.num_workers, b.num_comm_workers)))
+    # every rank emits the same events in the same order, so an event index means the same thing everywhere
+    assert len({len(t) for t, _ in programs}) == 1
+    mk.simulate_static_queues(programs)
