@@ -206,6 +206,21 @@ def settle(torch, seconds: float = 1.0) -> None:
     time.sleep(seconds)
 
 
+def place_near_gpu(local_rank: int) -> str:
+    """Both arms: run this rank on the CPUs next to its GPU before any pinned memory is allocated, so the per-step
+    input copy does not cross the socket interconnect (maco_b200/utils/numa.py, loaded by path: host placement only,
+    no kernel or engine code). Returns a one-line description for the JSON line."""
+    import importlib.util
+    try:
+        spec = importlib.util.spec_from_file_location("_maco_numa", os.path.join(REPO, "maco_b200", "utils", "numa.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        r = mod.bind_host_to_gpu(local_rank)
+        return f"{r['reason']} ({r['cpus']} cpus)"
+    except Exception as e:
+        return f"unchanged ({type(e).__name__})"
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -213,6 +228,7 @@ def run_ours(args):
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local_rank)
+    placement = place_near_gpu(local_rank)
     sys.path.insert(0, REPO)
     import maco_b200 as maco
     from maco_b200 import _native
@@ -269,7 +285,7 @@ def run_ours(args):
                        "l2": "per-GPU working set (activations + weights) exceeds the 126 MB L2; no flush",
                        "scheduler": args.mode, "gemm_tiles": "two-CTA 256x256" if layer.program.cta_pair else "one-CTA 128x256",
                        "heap": (heap.mode + ("+multicast" if heap.multicast_base() else "")) if heap is not None else "none",
-                       "comm_workers": layer.program.num_comm_workers},
+                       "comm_workers": layer.program.num_comm_workers, "host_placement": placement},
             "tflops_per_gpu": round(flops / world / (us * 1e-6) / 1e12, 1),
             "clocks": clocks,
             "e2e": {"value": round(us_e2e, 2), "unit": "us", "h2d_bytes_per_step": x_host.numel() * 2,
@@ -317,6 +333,7 @@ def run_reference(args):
     import torch.distributed as dist
     rank, local_rank, world = dist_env()
     torch.cuda.set_device(local_rank)
+    placement = place_near_gpu(local_rank)
     sys.path.insert(0, ref_dir)
     with contextlib.redirect_stdout(sys.stderr):          # the reference prints banners on stdout
         import maco
@@ -426,7 +443,8 @@ def run_reference(args):
             "config": {"model": "TP SwiGLU MLP forward (all-gather->GEMM, GEMM->reduce-scatter)", "global_batch": args.tokens,
                        "seq_len": args.tokens, "hidden": args.hidden, "ffn": args.ffn, "parallelism": f"tp{world}",
                        "l2": "per-GPU working set (activations + weights) exceeds the 126 MB L2; no flush",
-                       "path": "reference TaskGraph + StreamRuntime (torch.mm) + maco.comm.patterns (NCCL)"},
+                       "path": "reference TaskGraph + StreamRuntime (torch.mm) + maco.comm.patterns (NCCL)",
+                       "host_placement": placement},
             "tflops_per_gpu": round(flops / world / (us * 1e-6) / 1e12, 1),
             "clocks": clocks,
             "e2e": {"value": round(us_e2e, 2), "unit": "us", "h2d_bytes_per_step": x_host.numel() * 2,

@@ -2,7 +2,7 @@
 """Stand-alone collectives: this package's in-kernel forms against NCCL, and the overlap-efficiency figure.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-        benchmarks/bench_collectives.py [--out gpurun_out/collectives_N.jsonl]
+        benchmarks/bench_collectives.py [--out collectives_N.jsonl]
 
 * all-reduce sweep (fp32, 4 KB .. 64 MB): NCCL, peer pushes through staging slots, and (on a multicast-bound
   heap) multimem.ld_reduce / multimem.st through the NVSwitch;

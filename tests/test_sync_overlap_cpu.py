@@ -166,3 +166,29 @@ def test_context_objects():
         assert pc(torch.randn(3, 4)).shape == (3, 2)
         pc.register_tensor(torch.randn(2), "t")
         assert pc.worker_config["num_workers"] == 8
+
+
+def test_host_placement_respects_the_cpus_the_process_may_use(monkeypatch):
+    """bind_host_to_gpu only ever narrows the affinity to GPU-local CPUs it is allowed to use, and reports why it
+    did nothing otherwise (fake NVML answers; sched_setaffinity is intercepted)."""
+    import os
+    from maco_b200.utils import numa
+    if not hasattr(os, "sched_setaffinity"):
+        pytest.skip("no sched_setaffinity")
+    allowed = {0, 1, 2, 3}
+    calls = []
+    monkeypatch.setattr(os, "sched_getaffinity", lambda pid: set(allowed))
+    monkeypatch.setattr(os, "sched_setaffinity", lambda pid, cpus: calls.append(set(cpus)))
+    monkeypatch.setattr(numa, "local_cpus", lambda i: {2, 3, 8, 9})
+    r = numa.bind_host_to_gpu(0)
+    assert r["bound"] and calls == [{2, 3}] and r["cpus"] == 2
+    calls.clear()
+    monkeypatch.setattr(numa, "local_cpus", lambda i: {8, 9})            # nothing local is available: unchanged
+    assert not numa.bind_host_to_gpu(0)["bound"] and calls == []
+    monkeypatch.setattr(numa, "local_cpus", lambda i: set())             # NVML knows nothing: unchanged
+    assert not numa.bind_host_to_gpu(0)["bound"] and calls == []
+    monkeypatch.setattr(numa, "local_cpus", lambda i: {0, 1, 2, 3, 4})   # already local only: unchanged
+    assert not numa.bind_host_to_gpu(0)["bound"] and calls == []
+    monkeypatch.setenv("MACO_NUMA_BIND", "0")
+    monkeypatch.setattr(numa, "local_cpus", lambda i: {2, 3})
+    assert not numa.bind_host_to_gpu(0)["bound"] and calls == []
