@@ -172,7 +172,7 @@ extern "C" {
 // them off) receives per CTA [0] producer cycles waiting for a free stage, [1] MMA warp waiting for a free
 // accumulator, [2] MMA warp waiting for operands, [3] MMA warp total, [4] producer total. Word [7] of the buffer
 // is read as experiment switches (results are then meaningless): 1 = epilogue does the barrier handshake only,
-// 2 = the MMA warp does not wait for operands, 4 = no operand loads (use with 2).
+// 8 = the first CTA pair also logs a %globaltimer time line of its producer and MMA loops behind word 4096.
 void maco_gemm_set_debug(long long* buf) { g_gemm_dbg = buf; }
 
 // Returns 0 on success; -2 means "operands are not TMA-addressable, use maco_gemm_simt".

@@ -165,7 +165,7 @@ MACO_DEVICE bool gemm_mma_tile(uint8_t* smem, const GemmCtrl& c, uint32_t tmem_b
   uint32_t accum = 0;
   for (int kb = 0; kb < k_blocks; ++kb) {
     if (prof) t0 = clock64();
-    if (!(prof && (prof[3] & 2)) && !mbar_wait(&c.full[s], ph, budget_ns, c.abort_word)) { it += kb; return false; }
+    if (!mbar_wait(&c.full[s], ph, budget_ns, c.abort_word)) { it += kb; return false; }
     if (prof) prof[2] += clock64() - t0;
     const uint32_t b_lo = a_lo + kAB16;
 #pragma unroll
@@ -614,7 +614,7 @@ MACO_DEVICE bool pair_mma_tile(uint8_t* smem, const GemmCtrl& c, uint32_t tmem_b
   uint32_t accum = 0;
   for (int kb = 0; kb < k_blocks; ++kb) {
     if (prof) t0 = clock64();
-    if (!(prof && (prof[3] & 2)) && !mbar_wait(&c.full[s], ph, budget_ns, c.abort_word)) { it += kb; return false; }
+    if (!mbar_wait(&c.full[s], ph, budget_ns, c.abort_word)) { it += kb; return false; }
     if (prof) prof[2] += clock64() - t0;
     if (prof && prof[4] && prof[5] < 512) reinterpret_cast<uint64_t*>(prof[4])[2 * prof[5]] = globaltimer_ns();
     const uint32_t b_lo = a_lo + kAB16;
@@ -705,7 +705,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < num_tiles && !(variant & 4); tile += num_pairs) {
+      for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
         int mp, nb;
         gemm_tile_coords(tile, m_pairs, n_tiles, mp, nb);
         ok = pair_produce_tile<BN, kPairStages, A_MN, B_MN>(smem, c, rank, &tmA, &tmB, (mp * 2 + (int)rank) * kBM, nb * BN, 0,
@@ -772,12 +772,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles && !(variant & 4); tile += gridDim.x) {
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         int mb, nb;
         gemm_tile_coords(tile, m_tiles, n_tiles, mb, nb);
         ok = gemm_produce_tile<BN, STAGES, A_MN, B_MN>(smem, c, &tmA, &tmB, mb * kBM, nb * BN, 0, k_blocks, it, budget_ns, pp, kStepElems);
       }
-      if (!ok || (variant & 2)) gemm_drain_loads<STAGES>(c, it);      // experiment switch 2: see the two-CTA kernel
+      if (!ok) gemm_drain_loads<STAGES>(c, it);
       if (dbg != nullptr) { dbg[blockIdx.x * 8 + 0] = prof[0]; dbg[blockIdx.x * 8 + 4] = clock64() - t_begin; }
     }
     __syncwarp();
