@@ -142,7 +142,9 @@ class DPMLPStackBackward:
             if e_next is not None:
                 e_dz = e_next
         b.add_task(int(TaskType.NOP), b"", waits=b.join(done_events))
-        self.program = b.build()
+        # (a CPU device plans only: the task list stays in ``self.builder`` for host-side schedule checks)
+        self.builder = b
+        self.program = b.build() if self.device.type == "cuda" else None
 
     def backward(self, stream=None) -> torch.Tensor:
         """One persistent launch: all dgrad / wgrad GEMMs plus the averaged gradient all-reduce."""

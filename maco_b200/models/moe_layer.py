@@ -104,8 +104,9 @@ class MoEEPLayer:
         # Dropped-pair count of the last step, delivered without a blocking read: every forward() copies the counter
         # into pinned host memory behind the launch, and the NEXT forward() (or dropped()) looks at it. A step that
         # dropped pairs therefore never goes unnoticed, and nothing waits for the GPU on the way.
-        self._drop_host = torch.zeros(1, dtype=torch.int32).pin_memory()
-        self._drop_event = torch.cuda.Event()
+        on_gpu = dev.type == "cuda"
+        self._drop_host = torch.zeros(1, dtype=torch.int32).pin_memory() if on_gpu else torch.zeros(1, dtype=torch.int32)
+        self._drop_event = torch.cuda.Event() if on_gpu else None
         self._drop_pending = False
         self.total_dropped = 0
         self.on_drop = on_drop
@@ -198,7 +199,9 @@ class MoEEPLayer:
                        waits=[(e_ret, n_ret, True, False)], signals=[e_out])
             n_out += 1
         fused.epoch_fence_signal(b, [(e_out, n_out, False, False)])
-        self.program = b.build()
+        # (a CPU device plans only: the task list stays in ``self.builder`` for host-side schedule checks)
+        self.builder = b
+        self.program = b.build() if self.device.type == "cuda" else None
 
     def forward(self, x: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
         """One step. ``on_drop`` ("warn", "raise", "ignore") says what happens when an EARLIER step turns out to have

@@ -137,7 +137,9 @@ class Qwen3DecodeLayer:
                                      w_blocked=self.wb_down)
         if self.world > 1:
             fused.epoch_fence_signal(b, [(e_out.all_event[0], e_out.all_event[1], False, False)])
-        self.program = b.build()
+        # (a CPU device plans only: the task list stays in ``self.builder`` for host-side schedule checks)
+        self.builder = b
+        self.program = b.build() if self.device.type == "cuda" else None
 
     def forward(self, x: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
         """One decode step for ``x`` [batch, hidden] (copied into ``self.x``; None = already there)."""

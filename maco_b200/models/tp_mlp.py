@@ -83,7 +83,9 @@ class TPSwiGLUMLP:
                 _, eo = fused.gemm_reduce_scatter(b, self.h, self.w_down, staging, self.y_shard, a_ready=e1)
                 fused.epoch_fence_signal(b, [(eo.all_event[0], eo.all_event[1], False, False),
                                              (e1.all_event[0], e1.all_event[1], False, False)])
-            self.programs.append(b.build())
+            # (a CPU device plans only: the task lists stay in ``self.builders`` for host-side schedule checks)
+            self.builders = getattr(self, "builders", []) + [b]
+            self.programs.append(b.build() if dev.type == "cuda" else None)
             self.x_shards.append(x_shard)
         self.program, self.x_shard = self.programs[0], self.x_shards[0]
 

@@ -147,3 +147,38 @@ def test_tensor_parallel_mlp_schedules_of_all_ranks_run_together(planning, world
     # every rank emits the same events in the same order, so an event index means the same thing everywhere
     assert len({len(t) for t, _ in programs}) == 1
     mk.simulate_static_queues(programs)
+
+
+def _programs(make, world):
+    progs = []
+    for rank in range(world):
+        heap = _FakeHeap(rank, world, nbytes=1 << 29) if world > 1 else None
+        m = make(rank, world, heap)
+        builders = getattr(m, "builders", None) or [m.builder]
+        b = builders[0]
+        progs.append((b.tasks, mk.assign_static_queues(b.tasks, b.num_workers, b.num_comm_workers)))
+    return progs
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_model_programs_have_deadlock_free_static_schedules(planning, world):
+    """The four layer programs of the package, planned on the CPU for every rank of a 1-8 rank job and run together by
+    the schedule simulator: tensor-parallel MLP, data-parallel backward with tile-wise gradient all-reduce, the Qwen3
+    decode layer with fused all-reduces, the expert-parallel MoE layer (counted tiles all treated as live)."""
+    from maco_b200.models.dp_mlp_stack import DPMLPStackBackward
+    from maco_b200.models.moe_layer import MoEEPLayer
+    from maco_b200.models.qwen3_layer import Qwen3DecodeLayer
+    from maco_b200.models.tp_mlp import TPSwiGLUMLP
+    cpu = torch.device("cpu")
+    mk.simulate_static_queues(_programs(
+        lambda r, w, h: TPSwiGLUMLP(256 * w, 256, 512 * w, rank=r, world=w, heap=h, device=cpu, num_workers=24, comm_workers=4), world))
+    mk.simulate_static_queues(_programs(
+        lambda r, w, h: DPMLPStackBackward(layers=3, hidden=max(512, 128 * w), tokens=512, rank=r, world=w, heap=h, device=cpu,
+                                           comm_workers=4), world))
+    mk.simulate_static_queues(_programs(
+        lambda r, w, h: Qwen3DecodeLayer(hidden=1024, q_heads=8 * max(2, w), kv_heads=max(2, w), ffn=2048, batch=8, kv_len=300,
+                                         rank=r, world=w, heap=h, device=cpu), world))
+    if world > 1:                       # (one rank uses a device-side private heap)
+        mk.simulate_static_queues(_programs(
+            lambda r, w, h: MoEEPLayer(hidden=256, experts=8, top_k=2, inter=128, tokens=256, rank=r, world=w, heap=h, device=cpu,
+                                       capacity_factor=4.0), world))
