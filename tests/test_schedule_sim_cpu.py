@@ -182,3 +182,40 @@ def test_model_programs_have_deadlock_free_static_schedules(planning, world):
         mk.simulate_static_queues(_programs(
             lambda r, w, h: MoEEPLayer(hidden=256, experts=8, top_k=2, inter=128, tokens=256, rank=r, world=w, heap=h, device=cpu,
                                        capacity_factor=4.0), world))
+
+
+def test_split_k_finishing_form_follows_the_destination(planning):
+    """A local result is finished by the last-arriving tile (no SPLITK_FIN tasks); a result that goes into every rank's
+    heap keeps the finishing tasks (spread over all workers)."""
+    b = mk.ProgramBuilder(torch.device("cpu"), num_workers=32)
+    x, w, out = _bf(64, 1024), _bf(512, 1024), _bf(64, 512)
+    ev = b.gemm_splitk(x, w, out, split_k=4)
+    kinds = [t["type"] for t in b.tasks]
+    assert mk.T_SPLITK_FIN not in kinds and kinds.count(int(mk.TaskType.LINEAR)) == 2 * 4
+    assert ev.all_event[1] == 8                                     # every tile signals; the last arrival has finished the columns
+    b2 = mk.ProgramBuilder(torch.device("cpu"), num_workers=32, heap=_FakeHeap(0, 2))
+    arrived = b2.new_event()
+    ev2 = b2.gemm_splitk(x, w, None, split_k=4, heap_out_off=4096, ld_out=512, signal_peer_event=arrived)
+    kinds2 = [t["type"] for t in b2.tasks]
+    assert kinds2.count(mk.T_SPLITK_FIN) == ev2.all_event[1] > 0
+    assert all(t["signal_peer"] == -2 for t in b2.tasks if t["type"] == mk.T_SPLITK_FIN)
+    # blocked weights: shape is checked
+    from maco_b200.ops.gemm import block_weight
+    b.gemm_splitk(x, w, out, split_k=4, w_blocked=block_weight(w))
+    with pytest.raises(ValueError, match="w_blocked"):
+        b.gemm_splitk(x, w, out, split_k=4, w_blocked=w)
+
+
+def test_several_slot_residual_epilogue_packs_and_validates(planning):
+    import struct
+    b = mk.ProgramBuilder(torch.device("cpu"), num_workers=8)
+    i = b.add_epilogue(0x1000, 512, torch.bfloat16, 256, 512, mode="residual", aux_ptr=0x2000, ld_aux=512, aux_dtype=torch.bfloat16,
+                       aux_slots=(4, 1, 256))
+    pack = struct.unpack_from("<i", b.epis[i], len(b.epis[i]) - 4)[0]
+    assert pack & 15 == 4 and (pack >> 4) & 15 == 1 and pack >> 8 == 256
+    with pytest.raises(ValueError):
+        b.add_epilogue(0x1000, 512, torch.bfloat16, 256, 512, mode="residual", aux_ptr=0x2000, ld_aux=512,
+                       aux_dtype=torch.bfloat16, aux_slots=(1, 0, 256))
+    j = b.add_epilogue(0, 256, torch.bfloat16, 512, 256, mode="scatter_rows", aux_ptr=0x3000, bias_type=8)
+    mode, _, bias_type = struct.unpack_from("<iii", b.epis[j], 40)
+    assert mode == mk.EPI["scatter_rows"] and bias_type == 8
