@@ -560,11 +560,17 @@ __device__ void general_role(const MacoProgram& p, uint32_t w, uint32_t q_base, 
           MacoEltArgs fa = *reinterpret_cast<const MacoEltArgs*>(e.aux);
           const int c0 = fa.i0 == 1 ? g.n0 / 2 : g.n0;    // SwiGLU folds 256 workspace columns into 128 outputs
           fa.in0 = reinterpret_cast<const float*>(fa.in0) + g.n0;
+          if (fa.i0 == 3) {
+            fa.ld_out = g.n0 / 128;                        // first head of this column block; in1 is the parameter block
+            fa.cols = 256;
+            splitk_finalize(p, fa, tid);
+          } else {
           if (fa.in1 != nullptr) fa.in1 = reinterpret_cast<const uint16_t*>(fa.in1) + c0;
           fa.in2 = reinterpret_cast<const void*>(reinterpret_cast<unsigned long long>(fa.in2) + (unsigned long long)c0 * 2ull);
           if (fa.out != nullptr) fa.out = reinterpret_cast<uint16_t*>(fa.out) + c0;
           fa.cols = fa.i0 == 1 ? 128 : 256;
           splitk_finalize(p, fa, tid);
+          }
         }
       }
     } else {

@@ -140,6 +140,24 @@ struct MacoEltArgs {              /* row-wise / element-wise task over rows [row
   int32_t i0, i1;
 };
 
+/* Parameter block of the "QK-norm + RoPE + cache scatter" finishing pass of a split-K QKV projection (SPLITK_FIN
+   operator 3): column block h of the fp32 sums is head h; heads [0, hq) are queries (per-head RMSNorm with q_norm,
+   RoPE, row r -> q_out[r, h, :]), heads [hq, hq + hkv) keys (k_norm, RoPE, -> k_cache[r, h - hq, pos, :]), the last hkv
+   heads values (copied -> v_cache[r, j, pos, :]). head_dim 128, 16-bit outputs; cos_sin is [rows, 128] with the
+   cosines of a row in its first 64 entries and the sines in the last 64. Strides in elements. */
+struct MacoQkRopeParams {
+  void* q_out;
+  void* k_cache;
+  void* v_cache;
+  const void* q_norm;
+  const void* k_norm;
+  const void* cos_sin;
+  long long kv_batch_stride, kv_head_stride;
+  int32_t hq, hkv, pos, dtype;
+  float eps;
+  int32_t _pad;
+};
+
 struct MacoCommArgs {             /* 2-D block (rows x row_bytes) of a buffer in the symmetric heap */
   uint64_t src_off;               /* byte offset of the source inside a rank's heap */
   uint64_t dst_off;               /* byte offset of the destination inside a rank's heap */

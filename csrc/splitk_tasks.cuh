@@ -16,6 +16,7 @@
 //        (all four already offset to the task's first column)
 //   row0, rows; cols = output columns of this task; dtype = output type; ld_out = output row stride (elements)
 //   i0   0: out = sum   1: SwiGLU over 256-column blocks [gate 128 | up 128]   2: out = sum + aux
+//        3: QK-norm + RoPE + scatter into q / the K and V caches (splitk_finalize_qkrope; in1 = MacoQkRopeParams)
 //   i1   -1: store to `out`   -2: store to every rank's heap at in2
 #pragma once
 #include "elementwise.cuh"
@@ -80,10 +81,77 @@ MACO_DEVICE void splitk_finalize_t(const Program& p, const MacoEltArgs& a, int t
   }
 }
 
+// Operator 3: the sums of a QKV projection become rotated queries, and keys / values in their cache rows, without
+// an intermediate QKV buffer or a separate QK-norm + RoPE pass. One warp per (row, head); a lane owns elements
+// {2l, 2l+1} of both halves of the head (the pairs RoPE rotates), as in elt_qknorm_rope.
+//   in0 = fp32 sums at the first head of this block, ld_in = row stride; in1 = MacoQkRopeParams;
+//   rows = batch rows; cols = columns of the block (a multiple of 128); ld_out = index of the block's first head.
+__device__ __noinline__ void splitk_finalize_qkrope(const MacoEltArgs& ar, int tid) {
+  const MacoEltArgs a = ar;
+  const MacoQkRopeParams q = *reinterpret_cast<const MacoQkRopeParams*>(a.in1);
+  const int warp = tid >> 5, lane = tid & 31;
+  const int heads = a.cols / 128;
+  const bool bf = q.dtype == MACO_DT_BF16;
+  auto up = [bf](uint32_t w) { return bf ? unpack_bf16x2(w) : __half22float2(*reinterpret_cast<const __half2*>(&w)); };
+  auto pk = [bf](float x, float y) {
+    if (bf) return pack_bf16x2(x, y);
+    const __half2 h = __floats2half2_rn(x, y);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  };
+  float* ws = const_cast<float*>(reinterpret_cast<const float*>(a.in0));
+  const float2 zero = make_float2(0.f, 0.f);
+  const int units = a.rows * heads;
+  constexpr int U = 4;             // (row, head) units per warp and pass: every load of a pass is issued before the first use
+  for (int u0 = warp * U; u0 < units; u0 += 4 * U) {
+    float2 x1[U], x2[U];
+    uint32_t cr[U], sr[U];
+    float2* src[U];
+    int head[U];
+    long long row[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int u = u0 + k < units ? u0 + k : units - 1;        // clamped: loaded anyway, dropped below
+      const int r = u / heads, hl = u - r * heads;
+      head[k] = a.ld_out + hl;
+      row[k] = a.row0 + r;
+      src[k] = reinterpret_cast<float2*>(ws + row[k] * a.ld_in + hl * 128);
+      x1[k] = __ldcg(src[k] + lane); x2[k] = __ldcg(src[k] + 32 + lane);
+      const uint32_t* cs = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(q.cos_sin) + row[k] * 128);
+      cr[k] = cs[lane]; sr[k] = cs[32 + lane];
+    }
+    const uint32_t* wq = reinterpret_cast<const uint32_t*>(q.q_norm);
+    const uint32_t* wk = reinterpret_cast<const uint32_t*>(q.k_norm);
+    const float2 wq1 = up(wq[lane]), wq2 = up(wq[32 + lane]), wk1 = up(wk[lane]), wk2 = up(wk[32 + lane]);
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      if (u0 + k >= units) break;                               // uniform over the warp
+      src[k][lane] = zero; src[k][32 + lane] = zero;
+      // the projection's result in the layer's 16-bit type first (what a separate pass would have read)
+      float2 a1 = up(pk(x1[k].x, x1[k].y)), a2 = up(pk(x2[k].x, x2[k].y));
+      if (head[k] >= q.hq + q.hkv) {                             // value head: into the cache row of the new token
+        uint32_t* o = reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(q.v_cache) + row[k] * q.kv_batch_stride +
+                                                  (long long)(head[k] - q.hq - q.hkv) * q.kv_head_stride + (long long)q.pos * 128);
+        o[lane] = pk(a1.x, a1.y); o[32 + lane] = pk(a2.x, a2.y);
+        continue;
+      }
+      const bool is_q = head[k] < q.hq;
+      const float2 w1 = is_q ? wq1 : wk1, w2 = is_q ? wq2 : wk2, c = up(cr[k]), sn = up(sr[k]);
+      const float rstd = rsqrtf(warp_sum(a1.x * a1.x + a1.y * a1.y + a2.x * a2.x + a2.y * a2.y) / 128.f + q.eps);
+      a1.x *= rstd * w1.x; a1.y *= rstd * w1.y; a2.x *= rstd * w2.x; a2.y *= rstd * w2.y;
+      uint32_t* o = is_q ? reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(q.q_out) + (row[k] * q.hq + head[k]) * 128)
+                         : reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(q.k_cache) + row[k] * q.kv_batch_stride +
+                                                       (long long)(head[k] - q.hq) * q.kv_head_stride + (long long)q.pos * 128);
+      o[lane] = pk(a1.x * c.x - a2.x * sn.x, a1.y * c.y - a2.y * sn.y);
+      o[32 + lane] = pk(a2.x * c.x + a1.x * sn.x, a2.y * c.y + a1.y * sn.y);
+    }
+  }
+}
+
 template <typename Program>
 __device__ __noinline__ void splitk_finalize(const Program& p, const MacoEltArgs& ar, int tid) {
   const MacoEltArgs a = ar;
-  if (a.i0 == 1) splitk_finalize_t<true>(p, a, tid);
+  if (a.i0 == 3) splitk_finalize_qkrope(a, tid);
+  else if (a.i0 == 1) splitk_finalize_t<true>(p, a, tid);
   else splitk_finalize_t<false>(p, a, tid);
 }
 

@@ -1,7 +1,7 @@
 """Qwen3-style decoder layer, decode step (one new token per sequence), tensor parallel.
 
     h1 = rmsnorm(x)                       q,k,v = h1 Wqkv^T           (heads split over ranks)
-    q,k = rope(rmsnorm_per_head(q,k))     K,V cache[pos] = k,v
+    q,k = rope(rmsnorm_per_head(q,k))     K,V cache[pos] = k,v      (in the finishing pass of the QKV projection)
     a   = attention(q, Kcache, Vcache)    o = a Wo^T   -> all-reduce, + x        = y1
     h2  = rmsnorm(y1)                     g = silu(h2 Wg^T) * (h2 Wu^T)
     d   = g Wd^T -> all-reduce, + y1      = out
@@ -42,7 +42,10 @@ class Qwen3DecodeLayer:
                  batch: int = 64, kv_len: int = 4096, *, rank: int = 0, world: int = 1, heap=None,
                  device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16, theta: float = 1e6,
                  eps: float = 1e-6, seed: int = 0, mode: str = "static", trace: bool = False,
-                 splits: Optional[int] = None, weight_std: float = 0.02, blocked_weights: bool = False):
+                 splits: Optional[int] = None, weight_std: float = 0.02, blocked_weights: bool = False,
+                 fused_rope: Optional[bool] = None):
+        import os
+        self.fused_rope = (os.environ.get("MACO_QWEN3_FUSED_ROPE", "1") != "0") if fused_rope is None else bool(fused_rope)
         if head_dim != 128:
             raise ValueError("head_dim must be 128")
         if q_heads % world or kv_heads % world or ffn % (world * 64):
@@ -56,6 +59,7 @@ class Qwen3DecodeLayer:
         if self.G > 8:
             raise ValueError("at most 8 query heads per KV head")
         self.f_local = ffn // world
+        self.fused_rope = self.fused_rope and (self.hq + 2 * self.hkv) % 2 == 0 and batch <= BM   # whole 256-column tiles of heads
         dev = self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         B, H, D, hq, hkv = batch, hidden, head_dim, self.hq, self.hkv
         g = torch.Generator(device="cpu").manual_seed(seed * 1000 + rank)
@@ -101,6 +105,20 @@ class Qwen3DecodeLayer:
         e_h1 = b.elementwise(int(TaskType.RMSNORM), self.x, self.h1, in1=self.w_in, rows=B, cols=H, f0=self.eps,
                              extra_waits=fence)
         # the four projections are weight-streaming GEMMs with 64 rows: split-K tiles over every SM
+        if self.fused_rope:
+            # QK-norm, RoPE and the K / V cache update happen in the finishing pass of the projection itself: no QKV
+            # buffer, no separate tasks, one dependency hop less before attention
+            e_qkv = b.gemm_splitk(self.h1, self.w_qkv, None, epilogue="qk_rope", a_ready=e_h1, w_blocked=self.wb_qkv,
+                                  rope=dict(q_out=self.q_rot, k_cache=self.k_cache, v_cache=self.v_cache, q_norm=self.q_norm,
+                                            k_norm=self.k_norm, cos_sin=self.cos_sin, hq=hq, hkv=hkv, pos=self.pos, eps=self.eps))
+            ready = [(e_qkv.all_event[0], e_qkv.all_event[1], False, False)]
+        else:
+            ready = self._rope_tasks(b, e_h1)
+        self._rest_of_layer(b, ready, mode)
+
+    def _rope_tasks(self, b, e_h1):
+        B, H, D, hq, hkv, G, S = self.batch, self.hidden, self.D, self.hq, self.hkv, self.G, self.S
+        qw = (hq + 2 * hkv) * D
         e_qkv = b.gemm_splitk(self.h1, self.w_qkv, self.qkv, a_ready=e_h1, w_blocked=self.wb_qkv)
         qkv_done = (e_qkv.all_event[0], e_qkv.all_event[1], False, False)
         # QK-norm + RoPE: q into its own buffer, k straight into the cache row of the new token, v copied
@@ -121,7 +139,10 @@ class Qwen3DecodeLayer:
                                 rows=B, cols=D, ld_in=qw, ld_out=hkv * S * D, extra_waits=[qkv_done], rows_per_task=B,
                                 all_event=e_rope)
             n_rope += e_k.all_event[1] + e_v.all_event[1]
-        ready = [(e_rope, n_rope, False, False)]
+        return [(e_rope, n_rope, False, False)]
+
+    def _rest_of_layer(self, b, ready, mode):
+        B, H, D, hq, hkv, G, S = self.batch, self.hidden, self.D, self.hq, self.hkv, self.G, self.S
         # split-KV attention on the tensor cores: one task per (sequence, kv head, split), then the merges
         merged, n_merged = b.attention_decode(self.q_rot.view(B, hq, D), self.k_cache, self.v_cache, self.attn.view(B, hq, D),
                                               kv_len=S, splits=self.splits, waits=ready, balance=(mode == "static"))

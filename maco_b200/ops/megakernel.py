@@ -573,7 +573,7 @@ class ProgramBuilder:
                     a_ready: Optional[RowEvents] = None, extra_waits: Sequence[Tuple[int, int, bool, bool]] = (),
                     heap_out_off: Optional[int] = None, ld_out: Optional[int] = None,
                     signal_peer_event: int = -1, rows_per_task: int = 0, fused_finish: Optional[bool] = None,
-                    w_blocked: Optional[torch.Tensor] = None) -> RowEvents:
+                    w_blocked: Optional[torch.Tensor] = None, rope: Optional[dict] = None) -> RowEvents:
         """``out = op(a @ w.T)`` for at most 128 rows, bound by streaming ``w`` out of HBM.
 
         The K dimension is cut into ``split_k`` slices (0: enough slices for every worker to hold a tile),
@@ -582,6 +582,11 @@ class ProgramBuilder:
         interleaved gate/up layout, "residual" with ``aux``) and writes the 16-bit result: into ``out``, or,
         with ``heap_out_off``, at that byte offset of EVERY rank's symmetric heap (the exchange step of a
         one-shot all-reduce), bumping ``signal_peer_event`` on every rank.
+        ``epilogue="qk_rope"`` (a fused QKV projection, head_dim 128; needs ``rope`` = dict(q_out [M, hq, 128],
+        k_cache, v_cache [M, hkv, S, 128], q_norm, k_norm [128], cos_sin [M, 128], hq, hkv, pos, eps) and ``out=None``):
+        the finishing pass applies the per-head RMSNorm and RoPE to the query and key heads and writes queries to
+        ``q_out`` and keys / values straight into row ``pos`` of their caches (MacoQkRopeParams in csrc/maco_types.h);
+        no QKV buffer and no separate QK-norm + RoPE tasks. Fused finishing only.
         ``w_blocked``: the same weight laid out tile by tile (``ops.block_weight(w)``, [N/256, K/64, 256, 64]); the
         tiles then load contiguous 32 KB blocks (``w`` itself is not read).
         ``fused_finish`` (default: on for a local ``out``, off with ``heap_out_off``; env ``MACO_SPLITK_FUSED=0``
@@ -597,7 +602,23 @@ class ProgramBuilder:
         Nn = w.shape[0]
         if M > BM or w.shape[1] != K or Nn % 256 or K % BK:
             raise ValueError("gemm_splitk: at most 128 rows, N a multiple of 256, K a multiple of 64")
-        mode = {None: 0, "none": 0, "swiglu": 1, "residual": 2}[epilogue]
+        mode = {None: 0, "none": 0, "swiglu": 1, "residual": 2, "qk_rope": 3}[epilogue]
+        rope_dev = None
+        if mode == 3:
+            if rope is None or out is not None or heap_out_off is not None or fused_finish is False:
+                raise ValueError("gemm_splitk: epilogue 'qk_rope' takes rope=..., out=None, a local result and fused finishing")
+            hq, hkv = int(rope["hq"]), int(rope["hkv"])
+            q_out, kc, vc = rope["q_out"], rope["k_cache"], rope["v_cache"]
+            if Nn != (hq + 2 * hkv) * 128 or kc.shape[-1] != 128 or kc.dim() != 4 or kc.shape[1] != hkv or not kc.is_contiguous() \
+                    or not vc.is_contiguous() or vc.shape != kc.shape or tuple(q_out.shape) != (M, hq, 128) or not q_out.is_contiguous() \
+                    or rope["cos_sin"].shape != (M, 128) or not (0 <= int(rope["pos"]) < kc.shape[2]):
+                raise ValueError("gemm_splitk: rope tensors do not match (hq + 2 hkv) heads of 128 and caches [M, hkv, S, 128]")
+            fused_finish = True
+            blob = struct.pack("<QQQQQQqqiiiifi", q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), rope["q_norm"].data_ptr(),
+                               rope["k_norm"].data_ptr(), rope["cos_sin"].data_ptr(), kc.stride(0), kc.stride(1), hq, hkv,
+                               int(rope["pos"]), N.DTYPE_CODE[q_out.dtype], float(rope["eps"]), 0)
+            rope_dev = torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(a.device)
+            self.keepalive += [rope_dev, q_out, kc, vc, rope["q_norm"], rope["k_norm"], rope["cos_sin"]]
         n_tiles, k_blocks = Nn // 256, K // BK
         if split_k <= 0:
             split_k = pick_split_k(n_tiles, k_blocks, self.num_workers)
@@ -632,7 +653,8 @@ class ProgramBuilder:
             # (MACO_EPI_SPLITK_FUSED in csrc/maco_types.h): no finishing tasks, no hop between the two halves
             counters = torch.zeros(n_tiles, device=a.device, dtype=torch.int32)
             self.launch_state.append(counters)
-            fin = _pack_elt(ws.data_ptr(), aux.data_ptr() if aux is not None else 0, heap_out_off or 0,
+            fin = _pack_elt(ws.data_ptr(), rope_dev.data_ptr() if rope_dev is not None else (aux.data_ptr() if aux is not None else 0),
+                            heap_out_off or 0,
                             out.data_ptr() if out is not None else 0, 0, M, out_cols, dt, Nn, ld_o, i0=mode,
                             i1=-2 if heap_out_off is not None else -1)
             fin_dev = torch.frombuffer(bytearray(fin), dtype=torch.uint8).to(a.device)
