@@ -219,3 +219,20 @@ def test_several_slot_residual_epilogue_packs_and_validates(planning):
     j = b.add_epilogue(0, 256, torch.bfloat16, 512, 256, mode="scatter_rows", aux_ptr=0x3000, bias_type=8)
     mode, _, bias_type = struct.unpack_from("<iii", b.epis[j], 40)
     assert mode == mk.EPI["scatter_rows"] and bias_type == 8
+
+
+def test_qk_rope_finishing_checks_its_tensors(planning):
+    """The QKV projection that finishes with QK-norm + RoPE + cache scatter: shapes are validated when the program is planned."""
+    b = mk.ProgramBuilder(torch.device("cpu"), num_workers=32)
+    B, hq, hkv, S = 8, 6, 2, 33
+    x, w = _bf(B, 512), _bf((hq + 2 * hkv) * 128, 512)
+    rope = dict(q_out=_bf(B, hq, 128), k_cache=_bf(B, hkv, S, 128), v_cache=_bf(B, hkv, S, 128), q_norm=_bf(128), k_norm=_bf(128),
+                cos_sin=_bf(B, 128), hq=hq, hkv=hkv, pos=S - 1, eps=1e-6)
+    ev = b.gemm_splitk(x, w, None, epilogue="qk_rope", rope=rope, split_k=2)
+    assert mk.T_SPLITK_FIN not in [t["type"] for t in b.tasks] and ev.all_event[1] == 2 * (hq + 2 * hkv) // 2
+    with pytest.raises(ValueError, match="qk_rope"):
+        b.gemm_splitk(x, w, _bf(B, (hq + 2 * hkv) * 128), epilogue="qk_rope", rope=rope)           # no output buffer in this form
+    with pytest.raises(ValueError, match="rope tensors"):
+        b.gemm_splitk(x, w, None, epilogue="qk_rope", rope=dict(rope, pos=S))                      # outside the cache
+    with pytest.raises(ValueError, match="rope tensors"):
+        b.gemm_splitk(x, w, None, epilogue="qk_rope", rope=dict(rope, hq=hq + 1))                  # heads do not match the weight
