@@ -10,7 +10,6 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 ENV = {"NCCL_NVLS_ENABLE": "0"}
 # the symmetric heap with and without the NVSwitch multicast binding (multimem tasks on / off); a box whose
 # GPUs cannot join a multicast object runs "nvls" as plain peer memory too
-heaps = pytest.mark.parametrize("heap_mode", ["nvls", "ipc"])
 
 
 def _env(heap_mode):
@@ -18,6 +17,12 @@ def _env(heap_mode):
 _NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
 worlds = pytest.mark.parametrize("world", [pytest.param(w, marks=pytest.mark.skipif(_NGPU < w, reason=f"needs {w} GPUs"))
                                            for w in (2, 4, 8)])
+# (world, heap form) pairs: the multicast-bound heap at every size, the IPC form (the fallback where a GPU cannot join
+# a multicast object) at two ranks; MACO_TEST_ALL_HEAPS=1 adds the IPC form at four and eight
+import os as _os
+_PAIRS = [(2, "nvls"), (2, "ipc"), (4, "nvls"), (8, "nvls")] + ([(4, "ipc"), (8, "ipc")] if _os.environ.get("MACO_TEST_ALL_HEAPS") == "1" else [])
+world_heaps = pytest.mark.parametrize("world,heap_mode", [
+    pytest.param(w, h, id=f"{w}-{h}", marks=pytest.mark.skipif(_NGPU < w, reason=f"needs {w} GPUs")) for w, h in _PAIRS])
 
 
 def _setup(rank, world, heap_mb=256):
@@ -190,8 +195,7 @@ def _collectives(rank, world):
     maco.cleanup()
 
 
-@heaps
-@worlds
+@world_heaps
 def test_peer_collectives(world, heap_mode):
     run_ranks(_collectives, world, env=_env(heap_mode), timeout=150)
 
@@ -222,8 +226,7 @@ def _tp_mlp(rank, world):
     maco.cleanup()
 
 
-@heaps
-@worlds
+@world_heaps
 def test_fused_tp_mlp_matches_reference(world, heap_mode):
     run_ranks(_tp_mlp, world, env=_env(heap_mode), timeout=150)
 
@@ -428,8 +431,7 @@ def _graph_collectives(rank, world):
     maco.cleanup()
 
 
-@heaps
-@worlds
+@world_heaps
 def test_multirank_taskgraph_runs_in_the_persistent_kernel(world, heap_mode):
     run_ranks(_graph_collectives, world, env=_env(heap_mode), timeout=150)
 
