@@ -8,11 +8,11 @@ from tests._dist import run_ranks
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 ENV = {"NCCL_NVLS_ENABLE": "0"}
-# the symmetric heap with and without the NVSwitch multicast binding (multimem tasks on / off); a box whose
-# GPUs cannot join a multicast object runs "nvls" as plain peer memory too
 
 
 def _env(heap_mode):
+    """MACO_HEAP: "nvls" = the symmetric heap bound to an NVSwitch multicast object (multimem tasks on; a box whose GPUs
+    cannot join one runs it as plain peer memory), "ipc" = the CUDA-IPC form without the binding."""
     return dict(ENV, MACO_HEAP=heap_mode)
 _NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
 worlds = pytest.mark.parametrize("world", [pytest.param(w, marks=pytest.mark.skipif(_NGPU < w, reason=f"needs {w} GPUs"))
