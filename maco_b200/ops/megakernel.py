@@ -962,6 +962,12 @@ class Program:
         self.d_ctrl = torch.zeros(8, dtype=torch.int32, device=dev)        # [0] abort word, [1] task counter
         W = self.num_workers
         queues = assign_static_queues(b.tasks, self.num_workers, self.num_comm_workers)
+        from ..config import config as _dbg_cfg
+        if _dbg_cfg.debug and b.heap is None and self.mode == MODE_STATIC:
+            # debug layer: run the queues on the host first; an order that can deadlock is reported here, with the
+            # stuck tasks, instead of as a device-side wait that runs out (single-rank programs: nothing to wait
+            # for on a peer)
+            simulate_static_queues([(b.tasks, queues)])
         stride = max(1, max(len(q) for q in queues))
         sq = np.full((W, stride), QUEUE_TERMINATE, dtype=np.uint32)
         for w, q in enumerate(queues):
