@@ -174,8 +174,9 @@ __device__ __noinline__ void attn_decode_task_t(const MacoEltArgs& ar, int tid, 
 // MN-major A operand (four 64 x 64 panels). Only the small operands are built by threads: Q once per
 // task, P once per chunk, both written in the 128-byte-swizzled K-major layout the descriptors expect.
 //
-// Memory latency, not bandwidth, bounds one SM here (a split is read once, nothing is reused), so the
-// K / V chunks go through their own ring of six 32 KB stages over the worker's operand memory
+// Three roles share a task: the worker's TMA warp streams K / V (attn_produce), its MMA warp issues every
+// product (attn_mma), the four general warps do the softmax (attn_consume). A split is read once and nothing is
+// reused, so the K / V chunks go through their own ring of six 32 KB stages over the worker's operand memory
 // (192 KB in flight per SM) with barriers of their own, and the per-chunk dependency chain is kept
 // short:
 //   * scores run one chunk ahead (S double buffered in TMEM columns 0-15 / 16-31);
@@ -292,9 +293,10 @@ MACO_DEVICE bool attn_bar_or(bool pred) {
   return r != 0;
 }
 
-// Consumer side: all 128 general threads. `ait`: this task's first use of the attention ring.
-// `chunk_seq` counts the chunks this worker has processed (buffer index and parity of the MMA
-// barriers); every thread keeps its own copy.
+// Softmax side: all 128 general threads; they wait for scores, stage P and post "P staged", and never issue a
+// tensor-core product themselves (attn_mma does, on the MMA warp). `ait`: this task's first use of the attention
+// ring (kept for symmetry with the other two roles). `chunk_seq` counts the chunks this worker has processed
+// (buffer index and parity of the MMA barriers); every thread keeps its own copy.
 template <int DTT>
 __device__ __noinline__ bool attn_consume_t(const MacoEltArgs& ar, int tid, uint8_t* scratch, const AttnPipe& pp, uint32_t ait,
                                             uint32_t& chunk_seq) {
