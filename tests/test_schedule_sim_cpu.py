@@ -236,3 +236,32 @@ def test_qk_rope_finishing_checks_its_tensors(planning):
         b.gemm_splitk(x, w, None, epilogue="qk_rope", rope=dict(rope, pos=S))                      # outside the cache
     with pytest.raises(ValueError, match="rope tensors"):
         b.gemm_splitk(x, w, None, epilogue="qk_rope", rope=dict(rope, hq=hq + 1))                  # heads do not match the weight
+
+
+def test_makespan_estimate_orders_and_accounts(planning):
+    """The timed run of the schedules: a chain of dependent tasks costs the sum of its durations plus one hop per edge,
+    independent tasks on different workers overlap, and more communication workers finish an all-gather earlier."""
+    b = mk.ProgramBuilder(torch.device("cpu"), num_workers=4)
+    e1, e2 = b.new_event(), b.new_event()
+    b.add_task(int(mk.TaskType.NOP), b"", signals=[e1])
+    b.add_task(int(mk.TaskType.NOP), b"", waits=[(e1, 1, False, False)], signals=[e2])
+    b.add_task(int(mk.TaskType.NOP), b"", waits=[(e2, 1, False, False)])
+    b.add_task(int(mk.TaskType.NOP), b"")                                   # independent, on another worker
+    q = mk.assign_static_queues(b.tasks, b.num_workers, 0)
+    r = mk.estimate_makespan([(b.tasks, q)], cost=lambda t: 10.0, hop_us=2.0)
+    assert r["span_us"][0] == pytest.approx(3 * 10.0 + 2 * 2.0)
+    assert 0 < r["busy_fraction"][0] <= 1
+
+    from maco_b200.models.tp_mlp import TPSwiGLUMLP
+    ends = []
+    for cw in (2, 8):
+        progs = []
+        for rank in range(4):
+            m = TPSwiGLUMLP(2048, 512, 2048, rank=rank, world=4, heap=_FakeHeap(rank, 4), device=torch.device("cpu"),
+                            num_workers=32, comm_workers=cw)
+            bb = m.builders[0]
+            progs.append((bb.tasks, mk.assign_static_queues(bb.tasks, bb.num_workers, bb.num_comm_workers)))
+        res = mk.estimate_makespan(progs)
+        assert len(set(round(s, 3) for s in res["span_us"])) == 1            # symmetric ranks end together
+        ends.append(res["last_end_by_type_us"][0][int(mk.TaskType.ALLGATHER)])
+    assert ends[1] < ends[0]
