@@ -503,6 +503,11 @@ class ProgramBuilder:
         idx = self._tmap_cache.get(key)
         if idx is not None:
             return idx
+        if self.device.type != "cuda":
+            # planning mode: tensor maps are encoded by the CUDA driver; the task lists do not need their contents
+            self.tmaps.append(b"\0" * 128)
+            self._tmap_cache[key] = len(self.tmaps) - 1
+            return len(self.tmaps) - 1
         buf = ctypes.create_string_buffer(128)
         rc = _lib().maco_encode_operand_tmap(buf, t.data_ptr(), rows, cols, ld, int(mn_major), box_rows)
         N.check(rc, "maco_encode_operand_tmap")

@@ -312,6 +312,43 @@ class SymmetricHeap:
         self._closed = True
 
 
+class PlanningHeap:
+    """Host-memory stand-in for one rank of a ``world``-rank symmetric heap, for planning without GPUs: model
+    builders on a CPU device take it as their ``heap``, allocate their buffers from it (the same offsets on every
+    rank, as the real heap guarantees) and produce the task lists that ``ops.megakernel.simulate_static_queues`` and
+    ``estimate_makespan`` run. Nothing is ever copied between ranks; the memory is untouched virtual address space."""
+
+    def __init__(self, rank: int, world: int, nbytes: int = 1 << 30):
+        self.rank, self.world = int(rank), int(world)
+        self.device = torch.device("cpu")
+        self.mode = "planning"
+        self.nbytes = (int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN
+        self._whole = torch.empty(self.nbytes, dtype=torch.uint8)
+        self._base = self._whole.data_ptr()
+        self._ranges = RangeAllocator(self.nbytes)
+
+    def alloc(self, shape, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        return SymmetricHeap.alloc(self, shape, dtype, False)        # never touch the pages: planning only
+
+    def free(self, t: torch.Tensor) -> None:
+        self._ranges.free(self.offset_of(t))
+
+    free_bytes = SymmetricHeap.free_bytes
+    offset_of = SymmetricHeap.offset_of
+
+    def owns(self, t: torch.Tensor) -> bool:
+        if not isinstance(t, torch.Tensor) or t.numel() == 0:
+            return False
+        p = t.data_ptr()
+        return self._base <= p and p + t.numel() * t.element_size() <= self._base + self.nbytes
+
+    def peer_base(self, r: int) -> int:
+        return self._base
+
+    def multicast_base(self) -> int:
+        return 0
+
+
 class LocalHeap:
     """A one-rank stand-in with the interface of :class:`SymmetricHeap`: programs whose tasks address
     buffers as "heap base + offset" (the MoE and fused-collective tasks) run unchanged on a single GPU."""

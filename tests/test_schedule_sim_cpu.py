@@ -9,17 +9,9 @@ from maco_b200.ops import megakernel as mk
 
 
 @pytest.fixture
-def planning(monkeypatch):
-    """Builder without tensor maps: planning needs the tasks and their order only."""
-    counter = {"n": 0}
-
-    def fake_tmap(self, *a, **k):
-        counter["n"] += 1
-        self.tmaps.append(b"\0" * 128)
-        return len(self.tmaps) - 1
-
-    monkeypatch.setattr(mk.ProgramBuilder, "_tmap", fake_tmap)
-    return counter
+def planning():
+    """A builder on a CPU device plans only: tasks and their order, no tensor maps, no build()."""
+    return None
 
 
 def _bf(*shape):
@@ -87,38 +79,9 @@ def test_join_is_a_balanced_tree(planning):
     assert max(depth(w[0]) for w in out) == 5                            # log2(64) - 1 levels under the two survivors
 
 
-class _FakeHeap:
-    """Enough of a symmetric heap for planning: one address space per rank, the same offsets on every rank."""
-
-    def __init__(self, rank, world, nbytes=1 << 28):
-        self.rank, self.world, self.nbytes = rank, world, nbytes
-        self._buf = torch.empty(nbytes, dtype=torch.uint8)
-        self._base = self._buf.data_ptr()
-        self._cursor = 0
-        self.mode = "ipc"
-
-    def alloc(self, shape, dtype, zero=False):
-        shape = tuple(shape) if isinstance(shape, (tuple, list, torch.Size)) else (shape,)
-        n = torch.empty((), dtype=dtype).element_size()
-        for s in shape:
-            n *= s
-        start = (self._cursor + 255) // 256 * 256
-        self._cursor = start + n
-        assert self._cursor <= self.nbytes
-        return self._buf[start:start + n].view(dtype).view(shape)
-
-    def owns(self, t):
-        return self._base <= t.data_ptr() and t.data_ptr() + t.numel() * t.element_size() <= self._base + self.nbytes
-
-    def offset_of(self, t):
-        assert self.owns(t)
-        return t.data_ptr() - self._base
-
-    def peer_base(self, r):
-        return self._base
-
-    def multicast_base(self):
-        return 0
+def _FakeHeap(rank, world, nbytes=1 << 28):
+    from maco_b200.parallel.symm_heap import PlanningHeap
+    return PlanningHeap(rank, world, nbytes)
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
