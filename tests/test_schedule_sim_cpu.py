@@ -141,10 +141,9 @@ def test_model_programs_have_deadlock_free_static_schedules(planning, world):
     mk.simulate_static_queues(_programs(
         lambda r, w, h: Qwen3DecodeLayer(hidden=1024, q_heads=8 * max(2, w), kv_heads=max(2, w), ffn=2048, batch=8, kv_len=300,
                                          rank=r, world=w, heap=h, device=cpu), world))
-    if world > 1:                       # (one rank uses a device-side private heap)
-        mk.simulate_static_queues(_programs(
-            lambda r, w, h: MoEEPLayer(hidden=256, experts=8, top_k=2, inter=128, tokens=256, rank=r, world=w, heap=h, device=cpu,
-                                       capacity_factor=4.0), world))
+    mk.simulate_static_queues(_programs(
+        lambda r, w, h: MoEEPLayer(hidden=256, experts=8, top_k=2, inter=128, tokens=256, rank=r, world=w,
+                                   heap=h if h is not None else _FakeHeap(0, 1), device=cpu, capacity_factor=4.0), world))
 
 
 def test_split_k_finishing_form_follows_the_destination(planning):
